@@ -1,0 +1,149 @@
+// Shared host-side declarations of libb200mlir: context, error recording,
+// launch accounting and the internal launch functions of every kernel file.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "b200mlir_capi.h"
+
+namespace b200 {
+
+// ---- error recording (thread-local, like cudaGetLastError) ------------------
+int set_error(int code, const char *fmt, ...);
+void clear_error();
+
+#define B200_CUDA(expr)                                                          \
+  do {                                                                           \
+    cudaError_t _e = (expr);                                                     \
+    if (_e != cudaSuccess)                                                       \
+      return b200::set_error(B200MLIR_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,  \
+                             cudaGetErrorString(_e), __FILE__, __LINE__);        \
+  } while (0)
+
+#define B200_TRY(expr)          \
+  do {                          \
+    int _rc = (expr);           \
+    if (_rc != 0) return _rc;   \
+  } while (0)
+
+// ---- process-wide context ------------------------------------------------------
+struct Options {
+  double rms_eps = 1e-5;           // test_rms_norm.py:17
+  double iterations = 10;          // hexagon_options.py:51
+  double enable_weight_resident = 1;
+  double gemm_variant = -1;        // -1: dispatcher chooses
+  double kloop_block_k = 64;
+  double w8a16_variant = -1;
+};
+
+struct Context {
+  bool ready = false;
+  int device = -1;
+  int sm_count = 0;
+  int cc_major = 0, cc_minor = 0;
+  size_t l2_bytes = 0;
+  size_t persisting_l2_max = 0;
+  std::string gpu_name;
+  cudaStream_t stream = nullptr;
+  int *d_status = nullptr;  // device status word: 0 clean, else first failure
+  Options opt;
+};
+
+Context &ctx();
+int ensure_ready();  // lazy init on device 0 if b200mlir_init was not called
+extern std::atomic<int64_t> g_launches;
+inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+int check_launch(const char *what);
+
+// Persistent per-process workspace (grown on demand, never inside a capture).
+int workspace(size_t bytes, void **out);
+// Second, independent workspace for callers that hold the first.
+int workspace2(size_t bytes, void **out);
+
+// ---- pointer classification / host staging -------------------------------------
+bool is_device_ptr(const void *p);
+
+// ---- kernels (each returns 0 or an error code; all enqueue on ctx().stream) -------
+// row_kernels.cu
+int launch_softmax_f16(const __half *x, __half *y, int64_t rows, int64_t cols, int64_t ldx,
+                       int64_t ldy);
+int launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols, int64_t ldx,
+                       int64_t ldy);
+int launch_rmsnorm_f16(const __half *x, const __half *w, __half *y, int64_t rows, int64_t cols,
+                       int64_t ldx, int64_t ldy, float eps);
+int launch_rmsnorm_f32(const float *x, const float *w, float *y, int64_t rows, int64_t cols,
+                       int64_t ldx, int64_t ldy, float eps);
+int launch_silu_f16(const __half *x, __half *y, int64_t n);
+int launch_silu_f32(const float *x, float *y, int64_t n);
+int launch_swiglu_f16(const __half *g, const __half *u, __half *y, int64_t n);
+int launch_add_f16(const __half *a, const __half *b, __half *y, int64_t n);
+
+// layout.cu
+int launch_pack_weight_f16(const uint16_t *src, uint16_t *dst, int64_t k, int64_t n, int64_t ld);
+int launch_pack_act_f16(const uint16_t *src, uint16_t *dst, int64_t rows, int64_t cols,
+                        int64_t ld);
+int launch_unpack_acc_f16(const uint16_t *tiles, uint16_t *dst, int64_t rows, int64_t cols,
+                          int64_t ld);
+
+// GEMM epilogue selector shared by every GEMM variant.
+enum Epilogue : int {
+  EPI_F16 = 0,        // C16 = f16(acc)
+  EPI_F32_RES = 1,    // C32 = f32(f16(acc)) [+ R32]
+  EPI_KLOOP_F16 = 2,  // C16 = f16(sum_seg f32(f16(acc_seg)))
+  EPI_F16_RES16 = 3,  // C16 = f16(f32(f16(acc)) + f32(R16))
+  EPI_SWIGLU = 4      // B holds [Wg | Wu] interleaved per tile; C16 = swiglu
+};
+
+struct GemmArgs {
+  const void *a = nullptr;  // [M,K] row-major fp16 (int8 for the i8 path)
+  const void *b = nullptr;  // [K,N] row-major
+  void *c = nullptr;        // [M,N]
+  const void *res = nullptr;
+  const void *b2 = nullptr;  // second B operand (EPI_SWIGLU: Wu), same shape/stride as b
+  int64_t m = 0, n = 0, k = 0;
+  int64_t lda = 0, ldb = 0, ldc = 0, ldres = 0;
+  int epilogue = EPI_F16;
+  int block_k = 0;  // EPI_KLOOP_F16 only
+};
+
+// gemm_simt.cu — any-shape fallback ("hmx-tail"/"hvx" plans of the reference)
+int launch_gemm_simt(const GemmArgs &g);
+int launch_gemm_i8_simt(const int8_t *a, const int8_t *b, int32_t *c, int64_t m, int64_t n,
+                        int64_t k, int64_t lda, int64_t ldb, int64_t ldc);
+
+// gemm_tcgen05.cu — tensor-core variants
+int tc_variant_count();
+struct TcVariantInfo {
+  const char *name;
+  int bm, bn, bk, stages, cta_group;
+  int smem_bytes, tmem_cols;
+};
+const TcVariantInfo &tc_variant_info(int v);
+// "ok" or a refusal reason for variant v on (m,n,k) with the given epilogue.
+const char *tc_variant_verdict(int v, const GemmArgs &g);
+int launch_gemm_tc(int v, const GemmArgs &g);
+
+// w8a16.cu
+struct W8A16Weight {
+  const void *src = nullptr;     // caller's row-major int8 [K,N] (identity key)
+  const void *scales = nullptr;  // fp16 [N]
+  void *image = nullptr;         // pre-swizzled device image
+  void *scales_dev = nullptr;
+  int64_t k = 0, n = 0;
+  size_t image_bytes = 0;
+  bool l2_persist = false;
+};
+int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
+int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
+                 int64_t ldc);
+
+// dispatch.cpp
+int gemm_dispatch(const GemmArgs &g);  // picks a variant (option / cache / heuristic) and launches
+int choose_gemm_variant(const GemmArgs &g, std::string *why);  // -1 => simt fallback
+
+}  // namespace b200

@@ -1,0 +1,535 @@
+// Seam 1: the kernel entry points, in the calling convention of the reference's
+// generated wrapper (backend/hexagon_launcher_base.py:58-60,72-74;
+// backend/triton_hexagon_launcher.py:241-252).  Validates descriptors, stages
+// host tensors through device memory, and hands device pointers to the
+// dispatcher.  Nothing here computes on the CPU.
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.h"
+
+namespace b200 {
+namespace {
+
+// Host tensors are copied to stream-ordered device temporaries and back.
+class Stager {
+ public:
+  ~Stager() { release(); }
+  // Returns a device pointer for `p` (p itself when it already is one).
+  int in(const void *p, size_t bytes, const void **dev) {
+    if (!p || bytes == 0 || is_device_ptr(p)) {
+      *dev = p;
+      return 0;
+    }
+    void *d = nullptr;
+    B200_CUDA(cudaMallocAsync(&d, bytes, ctx().stream));
+    items_.push_back({d, nullptr, 0});
+    B200_CUDA(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, ctx().stream));
+    *dev = d;
+    return 0;
+  }
+  int out(void *p, size_t bytes, void **dev, bool preload = false) {
+    if (!p || bytes == 0 || is_device_ptr(p)) {
+      *dev = p;
+      return 0;
+    }
+    void *d = nullptr;
+    B200_CUDA(cudaMallocAsync(&d, bytes, ctx().stream));
+    items_.push_back({d, p, bytes});
+    if (preload) B200_CUDA(cudaMemcpyAsync(d, p, bytes, cudaMemcpyHostToDevice, ctx().stream));
+    *dev = d;
+    host_out_ = true;
+    return 0;
+  }
+  // Copy results back and wait when any tensor lived on the host.
+  int finish() {
+    for (auto &it : items_)
+      if (it.host) B200_CUDA(cudaMemcpyAsync(it.host, it.dev, it.bytes, cudaMemcpyDeviceToHost, ctx().stream));
+    int rc = 0;
+    if (!items_.empty()) {
+      cudaError_t e = cudaStreamSynchronize(ctx().stream);
+      if (e != cudaSuccess) rc = set_error(B200MLIR_ERR_CUDA, "stream sync failed: %s", cudaGetErrorString(e));
+    }
+    release();
+    return rc;
+  }
+
+ private:
+  struct Item {
+    void *dev;
+    void *host;
+    size_t bytes;
+  };
+  void release() {
+    for (auto &it : items_) cudaFreeAsync(it.dev, ctx().stream);
+    items_.clear();
+  }
+  std::vector<Item> items_;
+  bool host_out_ = false;
+};
+
+struct View2 {
+  void *p;
+  int64_t rows, cols, ld;
+  size_t span(size_t esz) const { return rows > 0 && cols > 0 ? ((size_t)(rows - 1) * ld + cols) * esz : 0; }
+};
+struct View1 {
+  void *p;
+  int64_t n;
+};
+
+int view2(const char *what, int64_t rank, const B200MemRef2D *d, size_t esz, View2 *v) {
+  if (rank != 2 || !d)
+    return set_error(B200MLIR_ERR_BAD_ARG, "%s: expected a rank-2 memref descriptor (got rank %lld)", what, (long long)rank);
+  if (d->sizes[0] < 0 || d->sizes[1] < 0)
+    return set_error(B200MLIR_ERR_BAD_ARG, "%s: negative extent", what);
+  if (d->sizes[1] > 1 && d->strides[1] != 1)
+    return set_error(B200MLIR_ERR_BAD_ARG, "%s: innermost stride must be 1 (dense rows)", what);
+  if (d->sizes[0] > 1 && d->strides[0] < d->sizes[1])
+    return set_error(B200MLIR_ERR_BAD_ARG, "%s: row stride %lld below row length %lld", what,
+                     (long long)d->strides[0], (long long)d->sizes[1]);
+  if (!d->aligned && d->sizes[0] * d->sizes[1] != 0)
+    return set_error(B200MLIR_ERR_BAD_ARG, "%s: null data pointer", what);
+  v->p = (char *)d->aligned + d->offset * (int64_t)esz;
+  v->rows = d->sizes[0];
+  v->cols = d->sizes[1];
+  v->ld = d->sizes[0] > 1 ? d->strides[0] : d->sizes[1];
+  if (v->ld < v->cols) v->ld = v->cols;
+  return 0;
+}
+
+int view1(const char *what, int64_t rank, const B200MemRef1D *d, size_t esz, View1 *v) {
+  if (rank != 1 || !d)
+    return set_error(B200MLIR_ERR_BAD_ARG, "%s: expected a rank-1 memref descriptor (got rank %lld)", what, (long long)rank);
+  if (d->sizes[0] < 0) return set_error(B200MLIR_ERR_BAD_ARG, "%s: negative extent", what);
+  if (d->sizes[0] > 1 && d->strides[0] != 1)
+    return set_error(B200MLIR_ERR_BAD_ARG, "%s: stride must be 1", what);
+  if (!d->aligned && d->sizes[0] != 0) return set_error(B200MLIR_ERR_BAD_ARG, "%s: null data pointer", what);
+  v->p = (char *)d->aligned + d->offset * (int64_t)esz;
+  v->n = d->sizes[0];
+  return 0;
+}
+
+inline bool not_first_program(int px, int py, int pz) { return (px | py | pz) != 0; }
+
+int check_grid(int nx, int ny, int nz, int px, int py, int pz) {
+  if (nx < 1 || ny < 1 || nz < 1 || px < 0 || py < 0 || pz < 0 || px >= nx || py >= ny || pz >= nz)
+    return set_error(B200MLIR_ERR_BAD_ARG, "program id (%d,%d,%d) outside grid (%d,%d,%d)", px, py, pz, nx, ny, nz);
+  return 0;
+}
+
+int matmul_impl(int epilogue, int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc,
+                B200MemRef2D *c, int64_t rr, B200MemRef2D *res) {
+  B200_TRY(ensure_ready());
+  View2 A, B, C, R{nullptr, 0, 0, 0};
+  const size_t c_esz = epilogue == EPI_F32_RES ? 4 : 2;
+  B200_TRY(view2("A", ra, a, 2, &A));
+  B200_TRY(view2("B", rb, b, 2, &B));
+  B200_TRY(view2("C", rc, c, c_esz, &C));
+  const bool has_res = epilogue == EPI_F32_RES && rr != 0 && res && res->aligned;
+  if (has_res) B200_TRY(view2("residual", rr, res, 4, &R));
+  if (A.cols != B.rows || C.rows != A.rows || C.cols != B.cols)
+    return set_error(B200MLIR_ERR_BAD_ARG, "matmul: shapes [%lld,%lld]x[%lld,%lld]->[%lld,%lld] do not agree",
+                     (long long)A.rows, (long long)A.cols, (long long)B.rows, (long long)B.cols,
+                     (long long)C.rows, (long long)C.cols);
+  if (has_res && (R.rows != C.rows || R.cols != C.cols))
+    return set_error(B200MLIR_ERR_BAD_ARG, "matmul: residual shape differs from C");
+  if (C.rows == 0 || C.cols == 0) return 0;
+  Stager st;
+  GemmArgs g;
+  B200_TRY(st.in(A.p, A.span(2), &g.a));
+  B200_TRY(st.in(B.p, B.span(2), &g.b));
+  // C rows may be a strided view into a wider matrix: keep the bytes between rows
+  B200_TRY(st.out(C.p, C.span(c_esz), &g.c, C.ld != C.cols));
+  if (has_res) B200_TRY(st.in(R.p, R.span(4), &g.res));
+  g.m = A.rows; g.n = B.cols; g.k = A.cols;
+  g.lda = A.ld; g.ldb = B.ld; g.ldc = C.ld; g.ldres = R.ld;
+  g.epilogue = epilogue;
+  g.block_k = (int)ctx().opt.kloop_block_k;
+  B200_TRY(gemm_dispatch(g));
+  return st.finish();
+}
+
+// ---- w8a16 resident weights --------------------------------------------------------------
+std::mutex g_w_mu;
+std::unordered_map<const void *, W8A16Weight> g_weights;
+
+int register_weight_locked(const void *wq, const void *scales, int64_t k, int64_t n, int l2_persist,
+                           W8A16Weight **out) {
+  auto it = g_weights.find(wq);
+  if (it != g_weights.end()) {
+    if (it->second.k != k || it->second.n != n)
+      return set_error(B200MLIR_ERR_BAD_ARG, "w8a16: weight at %p re-registered with a different shape", wq);
+    if (out) *out = &it->second;
+    return 0;
+  }
+  Context &c = ctx();
+  W8A16Weight w;
+  w.src = wq; w.scales = scales; w.k = k; w.n = n; w.l2_persist = l2_persist != 0;
+  const int8_t *wq_dev = (const int8_t *)wq;
+  void *tmp = nullptr;
+  if (!is_device_ptr(wq)) {
+    B200_CUDA(cudaMalloc(&tmp, (size_t)k * n));
+    B200_CUDA(cudaMemcpyAsync(tmp, wq, (size_t)k * n, cudaMemcpyHostToDevice, c.stream));
+    wq_dev = (const int8_t *)tmp;
+  }
+  int rc = w8a16_build_image(wq_dev, k, n, &w.image, &w.image_bytes);
+  if (rc == 0) {
+    cudaError_t e = cudaMalloc(&w.scales_dev, (size_t)n * 2);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(w.scales_dev, scales, (size_t)n * 2, cudaMemcpyDefault, c.stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c.stream);
+    if (e != cudaSuccess) rc = set_error(B200MLIR_ERR_CUDA, "w8a16: scales copy failed: %s", cudaGetErrorString(e));
+  }
+  if (tmp) cudaFree(tmp);
+  if (rc) {
+    if (w.image) cudaFree(w.image);
+    if (w.scales_dev) cudaFree(w.scales_dev);
+    return rc;
+  }
+  if (w.l2_persist && c.persisting_l2_max > 0) {
+    // Decode GEMMs re-read the same image every call: pin as much of it as the
+    // device allows in L2.  The setting lives in this process's context only.
+    size_t want = w.image_bytes < c.persisting_l2_max ? w.image_bytes : c.persisting_l2_max;
+    cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, want);
+    cudaStreamAttrValue attr = {};
+    attr.accessPolicyWindow.base_ptr = w.image;
+    attr.accessPolicyWindow.num_bytes = want;
+    attr.accessPolicyWindow.hitRatio = 1.0f;
+    attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+    attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+    if (cudaStreamSetAttribute(c.stream, cudaStreamAttributeAccessPolicyWindow, &attr) != cudaSuccess)
+      cudaGetLastError();  // a hint; not having it is not an error
+  }
+  auto ins = g_weights.emplace(wq, w);
+  if (out) *out = &ins.first->second;
+  return 0;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+#define ENTER_KERNEL()                                                                     \
+  clear_error();                                                                           \
+  if (check_grid(num_programs_x, num_programs_y, num_programs_z, pid_x, pid_y, pid_z)) return; \
+  if (not_first_program(pid_x, pid_y, pid_z)) return
+
+extern "C" {
+
+void matmul(int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc, B200MemRef2D *c,
+            B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  matmul_impl(EPI_F16, ra, a, rb, b, rc, c, 0, nullptr);
+}
+
+void klooped_matmul(int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc,
+                    B200MemRef2D *c, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  matmul_impl(EPI_KLOOP_F16, ra, a, rb, b, rc, c, 0, nullptr);
+}
+
+void matmul_f32out(int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc,
+                   B200MemRef2D *c32, int64_t rr, B200MemRef2D *res32, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  matmul_impl(EPI_F32_RES, ra, a, rb, b, rc, c32, rr, res32);
+}
+
+void matmul_i8(int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc, B200MemRef2D *c,
+               B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  if (ensure_ready()) return;
+  View2 A, B, C;
+  if (view2("A", ra, a, 1, &A) || view2("B", rb, b, 1, &B) || view2("C", rc, c, 4, &C)) return;
+  if (A.cols != B.rows || C.rows != A.rows || C.cols != B.cols) {
+    set_error(B200MLIR_ERR_BAD_ARG, "matmul_i8: shapes do not agree");
+    return;
+  }
+  if (C.rows == 0 || C.cols == 0) return;
+  Stager st;
+  const void *da, *db;
+  void *dc;
+  if (st.in(A.p, A.span(1), &da) || st.in(B.p, B.span(1), &db) || st.out(C.p, C.span(4), &dc, C.ld != C.cols)) return;
+  if (launch_gemm_i8_simt((const int8_t *)da, (const int8_t *)db, (int32_t *)dc, A.rows, B.cols, A.cols, A.ld,
+                          B.ld, C.ld))
+    return;
+  st.finish();
+}
+
+static void softmax_impl(bool f16, int64_t rx, B200MemRef2D *x, int64_t ry, B200MemRef2D *y) {
+  if (ensure_ready()) return;
+  const size_t esz = f16 ? 2 : 4;
+  View2 X, Y;
+  if (view2("x", rx, x, esz, &X) || view2("output", ry, y, esz, &Y)) return;
+  if (X.rows != Y.rows || X.cols != Y.cols) {
+    set_error(B200MLIR_ERR_BAD_ARG, "softmax: input and output shapes differ");
+    return;
+  }
+  if (X.rows == 0 || X.cols == 0) return;
+  Stager st;
+  const void *dx;
+  void *dy;
+  if (st.in(X.p, X.span(esz), &dx) || st.out(Y.p, Y.span(esz), &dy, Y.ld != Y.cols)) return;
+  int rc = f16 ? launch_softmax_f16((const __half *)dx, (__half *)dy, X.rows, X.cols, X.ld, Y.ld)
+               : launch_softmax_f32((const float *)dx, (float *)dy, X.rows, X.cols, X.ld, Y.ld);
+  if (rc) return;
+  st.finish();
+}
+
+void softmax_kernel_float16(int64_t rx, B200MemRef2D *x, int64_t ry, B200MemRef2D *y, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  softmax_impl(true, rx, x, ry, y);
+}
+void softmax_kernel_float32(int64_t rx, B200MemRef2D *x, int64_t ry, B200MemRef2D *y, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  softmax_impl(false, rx, x, ry, y);
+}
+
+static void rmsnorm_impl(bool f16, int64_t rx, B200MemRef2D *x, int64_t ry, B200MemRef2D *y, int64_t rw,
+                         B200MemRef1D *w) {
+  if (ensure_ready()) return;
+  const size_t esz = f16 ? 2 : 4;
+  View2 X, Y;
+  View1 W;
+  if (view2("x", rx, x, esz, &X) || view2("y", ry, y, esz, &Y) || view1("weights", rw, w, esz, &W)) return;
+  if (X.rows != Y.rows || X.cols != Y.cols || W.n != X.cols) {
+    set_error(B200MLIR_ERR_BAD_ARG, "rms_norm: shapes do not agree");
+    return;
+  }
+  if (X.rows == 0 || X.cols == 0) return;
+  Stager st;
+  const void *dx, *dw;
+  void *dy;
+  if (st.in(X.p, X.span(esz), &dx) || st.in(W.p, (size_t)W.n * esz, &dw) ||
+      st.out(Y.p, Y.span(esz), &dy, Y.ld != Y.cols))
+    return;
+  const float eps = (float)ctx().opt.rms_eps;
+  int rc = f16 ? launch_rmsnorm_f16((const __half *)dx, (const __half *)dw, (__half *)dy, X.rows, X.cols, X.ld,
+                                    Y.ld, eps)
+               : launch_rmsnorm_f32((const float *)dx, (const float *)dw, (float *)dy, X.rows, X.cols, X.ld,
+                                    Y.ld, eps);
+  if (rc) return;
+  st.finish();
+}
+
+void rms_norm_fwd_kernel_float16(int64_t rx, B200MemRef2D *x, int64_t ry, B200MemRef2D *y, int64_t rw,
+                                 B200MemRef1D *w, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  rmsnorm_impl(true, rx, x, ry, y, rw, w);
+}
+void rms_norm_fwd_kernel_float32(int64_t rx, B200MemRef2D *x, int64_t ry, B200MemRef2D *y, int64_t rw,
+                                 B200MemRef1D *w, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  rmsnorm_impl(false, rx, x, ry, y, rw, w);
+}
+
+// op: 0 silu f16, 1 silu f32, 2 swiglu f16, 3 add f16
+static void ew_impl(int op, int64_t r0, B200MemRef1D *a, int64_t r1, B200MemRef1D *b, int64_t r2,
+                    B200MemRef1D *o) {
+  if (ensure_ready()) return;
+  const size_t esz = op == 1 ? 4 : 2;
+  View1 A, B{nullptr, 0}, O;
+  if (view1("input 0", r0, a, esz, &A) || view1("output", r2, o, esz, &O)) return;
+  if (op >= 2 && view1("input 1", r1, b, esz, &B)) return;
+  if (A.n != O.n || (op >= 2 && B.n != A.n)) {
+    set_error(B200MLIR_ERR_BAD_ARG, "elementwise: lengths differ");
+    return;
+  }
+  if (A.n == 0) return;
+  Stager st;
+  const void *da, *db = nullptr;
+  void *dout;
+  if (st.in(A.p, (size_t)A.n * esz, &da) || (op >= 2 && st.in(B.p, (size_t)B.n * esz, &db)) ||
+      st.out(O.p, (size_t)O.n * esz, &dout))
+    return;
+  int rc = 0;
+  switch (op) {
+    case 0: rc = launch_silu_f16((const __half *)da, (__half *)dout, A.n); break;
+    case 1: rc = launch_silu_f32((const float *)da, (float *)dout, A.n); break;
+    case 2: rc = launch_swiglu_f16((const __half *)da, (const __half *)db, (__half *)dout, A.n); break;
+    default: rc = launch_add_f16((const __half *)da, (const __half *)db, (__half *)dout, A.n); break;
+  }
+  if (rc) return;
+  st.finish();
+}
+
+void silu_kernel_float16(int64_t rx, B200MemRef1D *x, int64_t ry, B200MemRef1D *y, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  ew_impl(0, rx, x, 0, nullptr, ry, y);
+}
+void silu_kernel_float32(int64_t rx, B200MemRef1D *x, int64_t ry, B200MemRef1D *y, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  ew_impl(1, rx, x, 0, nullptr, ry, y);
+}
+void swiglu_kernel_float16(int64_t rg, B200MemRef1D *g, int64_t ru, B200MemRef1D *u, int64_t ro,
+                           B200MemRef1D *o, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  ew_impl(2, rg, g, ru, u, ro, o);
+}
+void add_kernel_float16(int64_t rx, B200MemRef1D *x, int64_t ry, B200MemRef1D *y, int64_t ro,
+                        B200MemRef1D *o, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  ew_impl(3, rx, x, ry, y, ro, o);
+}
+
+int b200mlir_w8a16_register_weight(const void *wq, const void *scales, int64_t k, int64_t n, int l2_persist) {
+  clear_error();
+  B200_TRY(ensure_ready());
+  if (!wq || !scales || k <= 0 || n <= 0)
+    return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 register: null pointer or empty shape");
+  std::lock_guard<std::mutex> lk(g_w_mu);
+  return register_weight_locked(wq, scales, k, n, l2_persist, nullptr);
+}
+
+int b200mlir_w8a16_unregister_weight(const void *wq) {
+  clear_error();
+  std::lock_guard<std::mutex> lk(g_w_mu);
+  auto it = g_weights.find(wq);
+  if (it == g_weights.end()) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 unregister: unknown weight");
+  cudaStreamSynchronize(ctx().stream);
+  cudaFree(it->second.image);
+  cudaFree(it->second.scales_dev);
+  g_weights.erase(it);
+  return 0;
+}
+
+void w8a16_matmul(int64_t ra, B200MemRef2D *a, int64_t rw, B200MemRef2D *wq, int64_t rs, B200MemRef1D *s,
+                  int64_t rc, B200MemRef2D *c, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  if (ensure_ready()) return;
+  View2 A, W, C;
+  View1 S;
+  if (view2("A", ra, a, 2, &A) || view2("Wq", rw, wq, 1, &W) || view1("scales", rs, s, 2, &S) ||
+      view2("C", rc, c, 2, &C))
+    return;
+  if (A.cols != W.rows || C.rows != A.rows || C.cols != W.cols || S.n != W.cols) {
+    set_error(B200MLIR_ERR_BAD_ARG, "w8a16_matmul: shapes do not agree");
+    return;
+  }
+  if (W.ld != W.cols) {
+    set_error(B200MLIR_ERR_BAD_ARG, "w8a16_matmul: the weight must be dense row-major");
+    return;
+  }
+  if (C.rows == 0 || C.cols == 0) return;
+  const bool resident = ctx().opt.enable_weight_resident != 0;
+  W8A16Weight local, *w = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_w_mu);
+    if (resident) {
+      if (register_weight_locked(W.p, S.p, W.rows, W.cols, 0, &w)) return;
+      local = *w;
+    }
+  }
+  Stager st;
+  void *tmp_w = nullptr;
+  if (!resident) {
+    // residency off: the image is rebuilt for this call and dropped afterwards
+    const void *dw, *ds;
+    if (st.in(W.p, (size_t)W.rows * W.cols, &dw) || st.in(S.p, (size_t)S.n * 2, &ds)) return;
+    local.k = W.rows; local.n = W.cols; local.scales_dev = const_cast<void *>(ds);
+    if (w8a16_build_image((const int8_t *)dw, W.rows, W.cols, &local.image, &local.image_bytes)) return;
+    tmp_w = local.image;
+  }
+  const void *da;
+  void *dc;
+  int rcode = st.in(A.p, A.span(2), &da);
+  if (!rcode) rcode = st.out(C.p, C.span(2), &dc, C.ld != C.cols);
+  if (!rcode) rcode = launch_w8a16((const __half *)da, local, (__half *)dc, A.rows, A.ld, C.ld);
+  if (!rcode) rcode = st.finish();
+  if (tmp_w) {
+    cudaStreamSynchronize(ctx().stream);
+    cudaFree(tmp_w);
+  }
+}
+
+void mlp_block_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
+                       B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
+                       int64_t ro, B200MemRef2D *out, float eps, int add_residual, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  if (ensure_ready()) return;
+  View2 X, WG, WU, WD, O;
+  View1 G;
+  if (view2("x", rx, x, 2, &X) || view1("gain", rg, gain, 2, &G) || view2("Wg", rwg, wg, 2, &WG) ||
+      view2("Wu", rwu, wu, 2, &WU) || view2("Wd", rwd, wd, 2, &WD) || view2("out", ro, out, 2, &O))
+    return;
+  const int64_t T = X.rows, D = X.cols, F = WG.cols;
+  if (G.n != D || WG.rows != D || WU.rows != D || WU.cols != F || WD.rows != F || WD.cols != D ||
+      O.rows != T || O.cols != D || WU.ld != WG.ld) {
+    set_error(B200MLIR_ERR_BAD_ARG, "mlp_block: shapes do not agree");
+    return;
+  }
+  if (T == 0 || D == 0) return;
+  Stager st;
+  const void *dx, *dg, *dwg, *dwu, *dwd;
+  void *dout;
+  if (st.in(X.p, X.span(2), &dx) || st.in(G.p, (size_t)D * 2, &dg) || st.in(WG.p, WG.span(2), &dwg) ||
+      st.in(WU.p, WU.span(2), &dwu) || st.in(WD.p, WD.span(2), &dwd) ||
+      st.out(O.p, O.span(2), &dout, O.ld != O.cols))
+    return;
+  void *h = nullptr, *act = nullptr;
+  if (workspace((size_t)T * D * 2, &h) || workspace2((size_t)T * F * 2, &act)) return;
+  // 1. h = rmsnorm(x) * gain
+  if (launch_rmsnorm_f16((const __half *)dx, (const __half *)dg, (__half *)h, T, D, X.ld, D, eps)) return;
+  // 2. act = silu(h·Wg) * (h·Wu), fused in the GEMM epilogue
+  GemmArgs g1;
+  g1.a = h; g1.b = dwg; g1.b2 = dwu; g1.c = act;
+  g1.m = T; g1.n = F; g1.k = D; g1.lda = D; g1.ldb = WG.ld; g1.ldc = F;
+  g1.epilogue = EPI_SWIGLU;
+  if (gemm_dispatch(g1)) return;
+  // 3. out = act·Wd (+ x through the f32 residual read-out)
+  GemmArgs g2;
+  g2.a = act; g2.b = dwd; g2.c = dout;
+  g2.m = T; g2.n = D; g2.k = F; g2.lda = F; g2.ldb = WD.ld; g2.ldc = O.ld;
+  if (add_residual) {
+    g2.epilogue = EPI_F16_RES16;
+    g2.res = dx;
+    g2.ldres = X.ld;
+  }
+  if (gemm_dispatch(g2)) return;
+  st.finish();
+}
+
+int b200mlir_pack_weight_f16(const void *src, void *dst, int64_t k, int64_t n, int64_t ld) {
+  clear_error();
+  B200_TRY(ensure_ready());
+  if (!src || !dst || k <= 0 || n <= 0 || ld < n) return set_error(B200MLIR_ERR_BAD_ARG, "pack_weight: bad argument");
+  Stager st;
+  const void *ds;
+  void *dd;
+  const size_t out_bytes = (size_t)((k + 31) / 32) * ((n + 31) / 32) * 2048;
+  B200_TRY(st.in(src, ((size_t)(k - 1) * ld + n) * 2, &ds));
+  B200_TRY(st.out(dst, out_bytes, &dd));
+  B200_TRY(launch_pack_weight_f16((const uint16_t *)ds, (uint16_t *)dd, k, n, ld));
+  return st.finish();
+}
+
+int b200mlir_pack_act_f16(const void *src, void *dst, int64_t rows, int64_t cols, int64_t ld) {
+  clear_error();
+  B200_TRY(ensure_ready());
+  if (!src || !dst || rows <= 0 || cols <= 0 || ld < cols) return set_error(B200MLIR_ERR_BAD_ARG, "pack_act: bad argument");
+  Stager st;
+  const void *ds;
+  void *dd;
+  const size_t out_bytes = (size_t)((rows + 31) / 32) * ((cols + 31) / 32) * 2048;
+  B200_TRY(st.in(src, ((size_t)(rows - 1) * ld + cols) * 2, &ds));
+  B200_TRY(st.out(dst, out_bytes, &dd));
+  B200_TRY(launch_pack_act_f16((const uint16_t *)ds, (uint16_t *)dd, rows, cols, ld));
+  return st.finish();
+}
+
+int b200mlir_unpack_acc_f16(const void *tiles, void *dst, int64_t rows, int64_t cols, int64_t ld) {
+  clear_error();
+  B200_TRY(ensure_ready());
+  if (!tiles || !dst || rows <= 0 || cols <= 0 || ld < cols) return set_error(B200MLIR_ERR_BAD_ARG, "unpack_acc: bad argument");
+  Stager st;
+  const void *ds;
+  void *dd;
+  const size_t in_bytes = (size_t)((rows + 31) / 32) * ((cols + 31) / 32) * 2048;
+  B200_TRY(st.in(tiles, in_bytes, &ds));
+  B200_TRY(st.out(dst, ((size_t)(rows - 1) * ld + cols) * 2, &dd, ld != cols));
+  B200_TRY(launch_unpack_acc_f16((const uint16_t *)ds, (uint16_t *)dd, rows, cols, ld));
+  return st.finish();
+}
+
+}  // extern "C"

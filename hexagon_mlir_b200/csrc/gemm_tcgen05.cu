@@ -1,0 +1,456 @@
+// fp16 GEMM on the 5th-generation tensor cores (tcgen05 + TMEM), fed by TMA.
+//
+// What this replaces in the reference, piece by piece:
+//   * hmx_pack_act / hmx_pack_weight (hmx/src/HMXLayout.c:70-545): TMA's 128-byte
+//     swizzle rearranges row-major global tiles on their way into shared memory;
+//     there is no pack kernel and no packed copy of A or B in HBM.
+//   * the 2-slot DMA ring of hmx-partition
+//     (lib/Dialect/Hmx/Transforms/HmxPartitionPass.cpp:10-84): a STAGES-deep
+//     mbarrier ring filled by one producer thread.
+//   * hmx_acc_clear / hmx_mma_f16 (hmx/src/HMXAPI.c:36-55): tcgen05.mma with the
+//     accumulate flag off on a tile's first K step, fp32 accumulators in TMEM.
+//   * hmx_acc_store + hmx_unpack_acc (HMXAPI.c:39-44, HMXLayout.c:776-999) on a
+//     second thread in batches (HmxVectorExecutor.h:1-27): four epilogue warps
+//     drain one TMEM accumulator stage (tcgen05.ld, convert, fused epilogue,
+//     store) while the MMA thread fills the other.
+//
+// One persistent CTA per SM, 192 threads: warp 0 = TMA producer (one lane),
+// warp 1 = TMEM owner + MMA issuer (one lane), warps 2-5 = epilogue.
+// A is [M,K] row-major (K-major operand); B is [K,N] row-major, consumed as it
+// lies through an MN-major shared-memory descriptor.
+#include <cstring>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.h"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;
+constexpr int BK = 64;                   // 64 fp16 = one 128-byte swizzle row
+constexpr int A_STAGE_BYTES = BM * 128;  // 16 KiB
+constexpr int B_SLAB_BYTES = BK * 128;   // 64 k-rows x 64 n (128 B) = 8 KiB
+constexpr int GROUP_M = 8;
+constexpr int NUM_THREADS = 192;
+
+struct TcParams {
+  void *c;
+  const void *res;
+  int64_t ldc, ldres;
+  int m, n, k;
+  int m_blocks, n_blocks, num_tiles, k_blocks;
+  int *status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int &m_blk,
+                                            int &n_blk) {
+  const int per_group = GROUP_M * n_blocks;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int gsz = min(m_blocks - first_m, GROUP_M);
+  const int in_group = tile - group * per_group;
+  m_blk = first_m + in_group % gsz;
+  n_blk = in_group / gsz;
+}
+
+__device__ __forceinline__ __half silu_h(__half x) {
+  __half e = __float2half_rn(__expf(-__half2float(x)));
+  __half d = __float2half_rn(1.0f + __half2float(e));
+  return __float2half_rn(__fdividef(__half2float(x), __half2float(d)));
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+template <int BN_MMA, int STAGES, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmB2, const TcParams p) {
+  constexpr int BN_OUT = (EPI == EPI_SWIGLU) ? BN_MMA / 2 : BN_MMA;
+  constexpr int N_SLABS = BN_MMA / 64;
+  constexpr int B_STAGE_BYTES = N_SLABS * B_SLAB_BYTES;
+  constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  constexpr int TMEM_COLS = 2 * BN_MMA <= 32 ? 32 : 2 * BN_MMA;  // power of two by construction
+  constexpr uint32_t IDESC = make_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, /*A K-major*/ 0,
+                                        /*B MN-major*/ 1, BM, BN_MMA);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  // control block after the stages
+  const uint32_t ctrl = smem_base + STAGES * STAGE_BYTES;
+  const uint32_t bar_full = ctrl;                     // STAGES x 8
+  const uint32_t bar_empty = ctrl + 8 * STAGES;       // STAGES x 8
+  const uint32_t bar_tfull = ctrl + 16 * STAGES;      // 2 x 8
+  const uint32_t bar_tempty = ctrl + 16 * STAGES + 16;  // 2 x 8
+  const uint32_t tmem_slot = ctrl + 16 * STAGES + 32;
+  uint8_t *ctrl_gen = smem_raw + (ctrl - smem_u32(smem_raw));
+  volatile uint32_t *tmem_slot_gen = reinterpret_cast<volatile uint32_t *>(ctrl_gen + 16 * STAGES + 32);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_gen + 16 * STAGES + 36);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 4);  // one arrive per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tmB2);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, TMEM_COLS);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
+        const int m0 = m_blk * BM, n0 = n_blk * BN_OUT;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 1, tile)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(full, STAGE_BYTES);
+          tma_load_2d(sa, &tmA, full, kb * BK, m0);
+#pragma unroll
+          for (int s = 0; s < N_SLABS; ++s) {
+            if (EPI == EPI_SWIGLU && s >= N_SLABS / 2)
+              tma_load_2d(sb + s * B_SLAB_BYTES, &tmB2, full, n0 + (s - N_SLABS / 2) * 64, kb * BK);
+            else
+              tma_load_2d(sb + s * B_SLAB_BYTES, &tmB, full, n0 + s * 64, kb * BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 2, tile)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_MMA);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 3, tile)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            // A: K-major, 8-row groups 1024 B apart; one K=16 step is 32 bytes inside the swizzle row
+            const uint64_t adesc = smem_desc_sw128(sa + k * 32, 16, 1024);
+            // B: MN-major, 64-column slabs B_SLAB_BYTES apart, 8-k groups 1024 B apart;
+            // one K=16 step is 16 rows of 128 bytes
+            const uint64_t bdesc = smem_desc_sw128(sb + k * 2048, B_SLAB_BYTES, 1024);
+            mma_f16_ss(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
+          }
+          mma_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        mma_commit(bar_tfull + 8 * acc);  // accumulator complete
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
+      const int m0 = m_blk * BM, n0 = n_blk * BN_OUT;
+      bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 4, tile);
+      ok = __all_sync(0xffffffffu, ok);  // the loads below need the warp converged
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.m;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA);
+#pragma unroll 1
+      for (int c = 0; c < BN_OUT / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        uint32_t r2[32];
+        if (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + BN_OUT + c * 32, r2);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.n) continue;
+        if (EPI == EPI_F16 || EPI == EPI_F16_RES16 || EPI == EPI_SWIGLU) {
+          __half *cp = reinterpret_cast<__half *>(p.c) + (int64_t)row * p.ldc + col0;
+          const __half *rp = reinterpret_cast<const __half *>(p.res) + (int64_t)row * p.ldres + col0;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col0 + v * 8 >= p.n) break;  // N is a multiple of 8
+            uint4 o;
+            uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+            if (EPI == EPI_F16) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                ow[j] = pack_h2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+            } else if (EPI == EPI_F16_RES16) {
+              // f16(f32(f16(acc)) + f32(res)): the engine reads out fp16, the residual is added wide
+              const uint4 rv = *reinterpret_cast<const uint4 *>(rp + v * 8);
+              const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 t = __half22float2(__floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]),
+                                                            __uint_as_float(r[v * 8 + 2 * j + 1])));
+                float2 rr = __half22float2(rh[j]);
+                ow[j] = pack_h2(t.x + rr.x, t.y + rr.y);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                __half g0 = __float2half_rn(__uint_as_float(r[v * 8 + 2 * j]));
+                __half g1 = __float2half_rn(__uint_as_float(r[v * 8 + 2 * j + 1]));
+                __half u0 = __float2half_rn(__uint_as_float(r2[v * 8 + 2 * j]));
+                __half u1 = __float2half_rn(__uint_as_float(r2[v * 8 + 2 * j + 1]));
+                ow[j] = pack_h2(__half2float(silu_h(g0)) * __half2float(u0),
+                                __half2float(silu_h(g1)) * __half2float(u1));
+              }
+            }
+            *reinterpret_cast<uint4 *>(cp + v * 8) = o;
+          }
+        } else if (EPI == EPI_F32_RES) {
+          float *cp = reinterpret_cast<float *>(p.c) + (int64_t)row * p.ldc + col0;
+          const float *rp = reinterpret_cast<const float *>(p.res) + (int64_t)row * p.ldres + col0;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            if (col0 + v * 4 >= p.n) break;  // N is a multiple of 8
+            float4 o;
+            float *of = reinterpret_cast<float *>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              of[j] = __half2float(__float2half_rn(__uint_as_float(r[v * 4 + j])));
+            if (p.res) {
+              const float4 rv = *reinterpret_cast<const float4 *>(rp + v * 4);
+              o.x += rv.x; o.y += rv.y; o.z += rv.z; o.w += rv.w;
+            }
+            *reinterpret_cast<float4 *>(cp + v * 4) = o;
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    if (*abort_flag) {
+      // A wait ran out: give copies and MMAs still in flight a bounded time to
+      // land before the TMEM columns and shared memory are handed back.
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [outer, inner] with row pitch ld elements; box {box_inner, box_outer}.
+int make_map_2d(CUtensorMap *map, const void *base, CUtensorMapDataType dt, int elem_bytes,
+                int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return set_error(B200MLIR_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(B200MLIR_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+struct Variant {
+  TcVariantInfo info;
+};
+
+constexpr int ctrl_bytes(int stages) { return 16 * stages + 64; }
+constexpr int smem_for(int bn_mma, int stages) {
+  return stages * (A_STAGE_BYTES + (bn_mma / 64) * B_SLAB_BYTES) + ctrl_bytes(stages) + 1024;
+}
+
+const TcVariantInfo kVariants[] = {
+    {"tc128x256x64_s4", 128, 256, 64, 4, 1, smem_for(256, 4), 512},
+    {"tc128x128x64_s6", 128, 128, 64, 6, 1, smem_for(128, 6), 256},
+    {"tc128x64x64_s8", 128, 64, 64, 8, 1, smem_for(64, 8), 128},
+};
+constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
+
+template <int BN_MMA, int STAGES, int EPI>
+int launch_one(const GemmArgs &g, const TcVariantInfo &vi) {
+  constexpr int BN_OUT = (EPI == EPI_SWIGLU) ? BN_MMA / 2 : BN_MMA;
+  Context &c = ctx();
+  CUtensorMap tmA, tmB, tmB2;
+  B200_TRY(make_map_2d(&tmA, g.a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.k, g.m, g.lda, BK, BM));
+  B200_TRY(make_map_2d(&tmB, g.b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.n, g.k, g.ldb, 64, BK));
+  if (EPI == EPI_SWIGLU)
+    B200_TRY(make_map_2d(&tmB2, g.b2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.n, g.k, g.ldb, 64, BK));
+  else
+    tmB2 = tmB;
+  TcParams p;
+  p.c = g.c;
+  p.res = g.res;
+  p.ldc = g.ldc;
+  p.ldres = g.ldres;
+  p.m = (int)g.m;
+  p.n = (int)g.n;
+  p.k = (int)g.k;
+  p.m_blocks = (int)((g.m + BM - 1) / BM);
+  p.n_blocks = (int)((g.n + BN_OUT - 1) / BN_OUT);
+  p.num_tiles = p.m_blocks * p.n_blocks;
+  p.k_blocks = (int)((g.k + BK - 1) / BK);
+  p.status = c.d_status;
+  auto kern = gemm_tc_kernel<BN_MMA, STAGES, EPI>;
+  static bool attr_set = false;  // one per template instantiation
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, vi.smem_bytes));
+    attr_set = true;
+  }
+  int grid = p.num_tiles < c.sm_count ? p.num_tiles : c.sm_count;
+  kern<<<grid, NUM_THREADS, vi.smem_bytes, c.stream>>>(tmA, tmB, tmB2, p);
+  return check_launch(vi.name);
+}
+
+template <int BN_MMA, int STAGES>
+int launch_epi(const GemmArgs &g, const TcVariantInfo &vi) {
+  switch (g.epilogue) {
+    case EPI_F16: return launch_one<BN_MMA, STAGES, EPI_F16>(g, vi);
+    case EPI_F32_RES: return launch_one<BN_MMA, STAGES, EPI_F32_RES>(g, vi);
+    case EPI_F16_RES16: return launch_one<BN_MMA, STAGES, EPI_F16_RES16>(g, vi);
+    case EPI_SWIGLU:
+      if constexpr (BN_MMA >= 128) return launch_one<BN_MMA, STAGES, EPI_SWIGLU>(g, vi);
+      return set_error(B200MLIR_ERR_UNSUPPORTED, "swiglu epilogue needs a variant with BN >= 128");
+    default:
+      return set_error(B200MLIR_ERR_UNSUPPORTED, "tensor-core gemm: epilogue %d not built",
+                       g.epilogue);
+  }
+}
+
+bool al16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+
+}  // namespace
+
+int tc_variant_count() { return kNumVariants; }
+const TcVariantInfo &tc_variant_info(int v) { return kVariants[v]; }
+
+// Legality of one variant for one problem.  The vocabulary follows the
+// reference's refusal reasons (hmx_search.py:196-205): "min-rows" and
+// "tile-alignment" mean the same thing; the VTCM budget becomes the
+// shared-memory / TMEM budget of the variant.
+const char *tc_variant_verdict(int v, const GemmArgs &g) {
+  if (v < 0 || v >= kNumVariants) return "no-such-variant";
+  const TcVariantInfo &vi = kVariants[v];
+  if (g.m <= 4) return "min-rows";  // HmxTarget.h:100,201 — decode rows go to the vector path
+  if (g.k < 8 || g.n < 8) return "tile-alignment";
+  if (g.k % 8 || g.n % 8 || g.lda % 8 || g.ldb % 8) return "tile-alignment";
+  if (!al16(g.a) || !al16(g.b) || !al16(g.c)) return "tile-alignment";
+  if (g.epilogue == EPI_F32_RES) {
+    if (g.ldc % 4 || (g.res && (g.ldres % 4 || !al16(g.res)))) return "tile-alignment";
+  } else {
+    if (g.ldc % 8) return "tile-alignment";
+    if (g.epilogue == EPI_F16_RES16 && (g.ldres % 8 || !al16(g.res))) return "tile-alignment";
+  }
+  if (g.epilogue == EPI_SWIGLU && (!g.b2 || !al16(g.b2))) return "tile-alignment";
+  if (g.epilogue == EPI_SWIGLU && vi.bn < 128) return "epilogue-unsupported";
+  if (g.epilogue == EPI_KLOOP_F16) return "epilogue-unsupported";
+  if (g.m > 0x7fffffff || g.n > 0x7fffffff || g.k > 0x7fffffff) return "extent-range";
+  if (((g.m + BM - 1) / BM) * ((g.n + 31) / 32) > 0x3fffffff) return "extent-range";
+  if (vi.smem_bytes > 227 * 1024) return "smem-budget";
+  if (vi.tmem_cols > 512) return "tmem-budget";
+  return "ok";
+}
+
+int launch_gemm_tc(int v, const GemmArgs &g) {
+  B200_TRY(ensure_ready());
+  const char *verdict = tc_variant_verdict(v, g);
+  if (strcmp(verdict, "ok") != 0)
+    return set_error(B200MLIR_ERR_UNSUPPORTED, "gemm variant %d refused: %s", v, verdict);
+  const TcVariantInfo &vi = kVariants[v];
+  switch (v) {
+    case 0: return launch_epi<256, 4>(g, vi);
+    case 1: return launch_epi<128, 6>(g, vi);
+    case 2: return launch_epi<64, 8>(g, vi);
+  }
+  return set_error(B200MLIR_ERR_BAD_ARG, "no such gemm variant %d", v);
+}
+
+}  // namespace b200

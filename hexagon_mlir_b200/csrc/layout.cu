@@ -1,0 +1,105 @@
+// Tile-image layout kernels: the reference's 32x32 fp16 tile ("crouton") images.
+//
+// Element (r, c) of a tile lives at byte 128*(r>>1) + 4*c + 2*(r&1)
+// (qcom_hexagon_backend/bin/runtime/hmx/src/HMXLayout.c:9-14).  On B200 the
+// GEMM kernels do not consume these images — TMA's 128-byte swizzle does the
+// row-major -> tile rearrangement on the way into shared memory — so these
+// kernels exist for interchange with hosts that hold or expect the reference's
+// pre-packed weight / accumulator images.  Pure permutations: every thread
+// moves one 4-byte word (a row pair of one column), reads and writes coalesced
+// on the tile side.
+#include "common.h"
+
+namespace b200 {
+namespace {
+
+// Word w (0..511) of a tile holds rows (2j, 2j+1) of column c, j = w/32, c = w%32.
+__global__ void __launch_bounds__(256)
+pack_rowmajor_to_tiles(const uint16_t *__restrict__ src, uint32_t *__restrict__ dst, int64_t rows,
+                       int64_t cols, int64_t ld, int64_t tiles_r, int64_t tiles_c,
+                       bool weight_order) {
+  // weight_order: tile grid is [Nt (col tiles), Kt (row tiles)]; else [Mt, Kt] = [row, col].
+  const int64_t total = tiles_r * tiles_c * 512;
+  for (int64_t w = (int64_t)blockIdx.x * 256 + threadIdx.x; w < total;
+       w += (int64_t)gridDim.x * 256) {
+    int64_t tile = w >> 9;
+    int word = (int)(w & 511);
+    int j = word >> 5, c = word & 31;
+    int64_t tr, tc;
+    if (weight_order) {
+      tc = tile / tiles_r;
+      tr = tile % tiles_r;
+    } else {
+      tr = tile / tiles_c;
+      tc = tile % tiles_c;
+    }
+    int64_t r0 = tr * 32 + 2 * j, col = tc * 32 + c;
+    uint32_t lo = 0, hi = 0;
+    if (col < cols) {
+      if (r0 < rows) lo = src[r0 * ld + col];
+      if (r0 + 1 < rows) hi = src[(r0 + 1) * ld + col];
+    }
+    dst[w] = lo | (hi << 16);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+unpack_tiles_to_rowmajor(const uint32_t *__restrict__ tiles, uint16_t *__restrict__ dst,
+                         int64_t rows, int64_t cols, int64_t ld, int64_t tiles_r,
+                         int64_t tiles_c) {
+  const int64_t total = tiles_r * tiles_c * 512;
+  for (int64_t w = (int64_t)blockIdx.x * 256 + threadIdx.x; w < total;
+       w += (int64_t)gridDim.x * 256) {
+    int64_t tile = w >> 9;
+    int word = (int)(w & 511);
+    int j = word >> 5, c = word & 31;
+    int64_t tr = tile / tiles_c, tc = tile % tiles_c;
+    int64_t r0 = tr * 32 + 2 * j, col = tc * 32 + c;
+    uint32_t v = tiles[w];
+    if (col < cols) {
+      if (r0 < rows) dst[r0 * ld + col] = (uint16_t)(v & 0xffffu);
+      if (r0 + 1 < rows) dst[(r0 + 1) * ld + col] = (uint16_t)(v >> 16);
+    }
+  }
+}
+
+unsigned grid_for(int64_t words) {
+  int64_t blocks = (words + 255) / 256;
+  int64_t cap = (int64_t)ctx().sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (unsigned)blocks;
+}
+
+}  // namespace
+
+int launch_pack_weight_f16(const uint16_t *src, uint16_t *dst, int64_t k, int64_t n, int64_t ld) {
+  B200_TRY(ensure_ready());
+  if (k <= 0 || n <= 0) return 0;
+  int64_t kt = (k + 31) / 32, nt = (n + 31) / 32;
+  pack_rowmajor_to_tiles<<<grid_for(kt * nt * 512), 256, 0, ctx().stream>>>(
+      src, reinterpret_cast<uint32_t *>(dst), k, n, ld, kt, nt, true);
+  return check_launch("pack_weight_f16");
+}
+
+int launch_pack_act_f16(const uint16_t *src, uint16_t *dst, int64_t rows, int64_t cols,
+                        int64_t ld) {
+  B200_TRY(ensure_ready());
+  if (rows <= 0 || cols <= 0) return 0;
+  int64_t mt = (rows + 31) / 32, kt = (cols + 31) / 32;
+  pack_rowmajor_to_tiles<<<grid_for(mt * kt * 512), 256, 0, ctx().stream>>>(
+      src, reinterpret_cast<uint32_t *>(dst), rows, cols, ld, mt, kt, false);
+  return check_launch("pack_act_f16");
+}
+
+int launch_unpack_acc_f16(const uint16_t *tiles, uint16_t *dst, int64_t rows, int64_t cols,
+                          int64_t ld) {
+  B200_TRY(ensure_ready());
+  if (rows <= 0 || cols <= 0) return 0;
+  int64_t mt = (rows + 31) / 32, nt = (cols + 31) / 32;
+  unpack_tiles_to_rowmajor<<<grid_for(mt * nt * 512), 256, 0, ctx().stream>>>(
+      reinterpret_cast<const uint32_t *>(tiles), dst, rows, cols, ld, mt, nt);
+  return check_launch("unpack_acc_f16");
+}
+
+}  // namespace b200

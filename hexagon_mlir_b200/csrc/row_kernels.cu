@@ -1,0 +1,418 @@
+// Vector row kernels: softmax, RMSNorm, SiLU, SwiGLU, add.
+//
+// The reference lowers these to loops over one 128-byte HVX vector with a
+// rotate-butterfly reduction
+// (qcom_hexagon_backend/lib/Conversion/LinalgToLLVM/VectorRowReducePass.cpp:9-34,
+//  include/hexagon/Dialect/Hvx/IR/HvxOps.td:28-64).  Here a row is held in
+// registers by a group of threads: one pass over HBM, 128-bit loads and
+// stores, shuffle-butterfly reductions, fp32 internals.  The fp16 kernels keep
+// the reference's rounding points (f16 subtract, f16-rounded exponentials,
+// f32 sum) so results differ from it only through exp/rsqrt approximations.
+#include "common.h"
+
+namespace b200 {
+namespace {
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// Reduce over the TPR threads that share a row.  TPR == 32: one warp, shuffles
+// only.  TPR > 32: the whole block shares one row; partials cross warps
+// through shared memory.
+template <int TPR, bool IS_MAX>
+__device__ __forceinline__ float group_reduce(float v, float *scratch) {
+  v = IS_MAX ? warp_max(v) : warp_sum(v);
+  if (TPR > 32) {
+    constexpr int NW = TPR / 32;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    __syncthreads();  // scratch may still be read from the previous reduction
+    if (l == 0) scratch[w] = v;
+    __syncthreads();
+    float t = l < NW ? scratch[l] : (IS_MAX ? -INFINITY : 0.0f);
+    v = IS_MAX ? warp_max(t) : warp_sum(t);
+  }
+  return v;
+}
+
+union H8 {
+  uint4 u;
+  __half2 h2[4];
+  __half h[8];
+};
+
+// ---- softmax, fp16, row in registers ------------------------------------------------
+template <int TPR, int VPL>
+__global__ void __launch_bounds__(TPR > 32 ? TPR : 256)
+softmax_f16_kernel(const __half *__restrict__ x, __half *__restrict__ y, int64_t rows, int cols,
+                   int64_t ldx, int64_t ldy) {
+  __shared__ float scratch[32];
+  constexpr int ROWS_PER_BLOCK = TPR > 32 ? 1 : 256 / 32;
+  const int lane = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
+  const int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + (TPR > 32 ? 0 : (threadIdx.x >> 5));
+  const bool live = row < rows;  // dead warps still take part in no block-level sync (TPR==32)
+  if (TPR == 32 && !live) return;
+  const int nvec = cols >> 3;
+  const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * ldx);
+  uint4 *yr = reinterpret_cast<uint4 *>(y + row * ldy);
+
+  H8 v[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    int idx = i * TPR + lane;
+    if (idx < nvec) v[i].u = __ldg(xr + idx);
+  }
+  // 1. running max in f16 (softmax.md:167-177)
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+    if (i * TPR + lane < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m = fmaxf(m, __half2float(v[i].h[j]));
+    }
+  m = group_reduce<TPR, true>(m, scratch);
+  const __half mh = __float2half_rn(m);  // exact: m is an f16 value
+  // 2. e = f16(exp(f32(x - m))) with the subtract in f16; 3. s = sum f32(e)
+  float s = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+    if (i * TPR + lane < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        __half z = __hsub(v[i].h[j], mh);
+        __half e = __float2half_rn(__expf(__half2float(z)));
+        v[i].h[j] = e;
+        s += __half2float(e);
+      }
+    }
+  s = group_reduce<TPR, false>(s, scratch);
+  // 4. y = f16(f32(e) / s)
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    int idx = i * TPR + lane;
+    if (idx < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[i].h[j] = __float2half_rn(__fdividef(__half2float(v[i].h[j]), s));
+      yr[idx] = v[i].u;
+    }
+  }
+}
+
+// Any shape / alignment: one block per row, three passes over the row (it sits
+// in L1/L2 after the first).
+template <typename T>
+__device__ __forceinline__ float ld_f(const T *p);
+template <>
+__device__ __forceinline__ float ld_f<__half>(const __half *p) { return __half2float(*p); }
+template <>
+__device__ __forceinline__ float ld_f<float>(const float *p) { return *p; }
+
+__global__ void __launch_bounds__(256)
+softmax_f16_generic(const __half *__restrict__ x, __half *__restrict__ y, int64_t rows,
+                    int64_t cols, int64_t ldx, int64_t ldy) {
+  __shared__ float scratch[32];
+  const int64_t row = blockIdx.x;
+  const __half *xr = x + row * ldx;
+  __half *yr = y + row * ldy;
+  float m = -INFINITY;
+  for (int64_t j = threadIdx.x; j < cols; j += 256) m = fmaxf(m, __half2float(xr[j]));
+  m = group_reduce<256, true>(m, scratch);
+  const __half mh = __float2half_rn(m);
+  float s = 0.0f;
+  for (int64_t j = threadIdx.x; j < cols; j += 256) {
+    __half e = __float2half_rn(__expf(__half2float(__hsub(xr[j], mh))));
+    s += __half2float(e);
+  }
+  s = group_reduce<256, false>(s, scratch);
+  for (int64_t j = threadIdx.x; j < cols; j += 256) {
+    __half e = __float2half_rn(__expf(__half2float(__hsub(xr[j], mh))));
+    yr[j] = __float2half_rn(__fdividef(__half2float(e), s));
+  }
+}
+
+__global__ void __launch_bounds__(256)
+softmax_f32_generic(const float *__restrict__ x, float *__restrict__ y, int64_t rows, int64_t cols,
+                    int64_t ldx, int64_t ldy) {
+  __shared__ float scratch[32];
+  const int64_t row = blockIdx.x;
+  const float *xr = x + row * ldx;
+  float *yr = y + row * ldy;
+  float m = -INFINITY;
+  for (int64_t j = threadIdx.x; j < cols; j += 256) m = fmaxf(m, xr[j]);
+  m = group_reduce<256, true>(m, scratch);
+  float s = 0.0f;
+  for (int64_t j = threadIdx.x; j < cols; j += 256) s += expf(xr[j] - m);
+  s = group_reduce<256, false>(s, scratch);
+  for (int64_t j = threadIdx.x; j < cols; j += 256) yr[j] = expf(xr[j] - m) / s;
+}
+
+// ---- RMSNorm -------------------------------------------------------------------------
+template <int TPR, int VPL>
+__global__ void __launch_bounds__(TPR > 32 ? TPR : 256)
+rmsnorm_f16_kernel(const __half *__restrict__ x, const __half *__restrict__ w,
+                   __half *__restrict__ y, int64_t rows, int cols, int64_t ldx, int64_t ldy,
+                   float eps) {
+  __shared__ float scratch[32];
+  constexpr int ROWS_PER_BLOCK = TPR > 32 ? 1 : 256 / 32;
+  const int lane = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
+  const int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + (TPR > 32 ? 0 : (threadIdx.x >> 5));
+  if (TPR == 32 && row >= rows) return;
+  const int nvec = cols >> 3;
+  const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * ldx);
+  const uint4 *wr = reinterpret_cast<const uint4 *>(w);
+  uint4 *yr = reinterpret_cast<uint4 *>(y + row * ldy);
+  H8 v[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    int idx = i * TPR + lane;
+    if (idx < nvec) v[i].u = __ldg(xr + idx);
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+    if (i * TPR + lane < nvec) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __half22float2(v[i].h2[j]);
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+      }
+    }
+  ss = group_reduce<TPR, false>(ss, scratch);
+  const float inv = rsqrtf(ss / (float)cols + eps);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    int idx = i * TPR + lane;
+    if (idx < nvec) {
+      H8 g;
+      g.u = __ldg(wr + idx);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __half22float2(v[i].h2[j]);
+        float2 gg = __half22float2(g.h2[j]);
+        v[i].h2[j] = __floats2half2_rn(f.x * inv * gg.x, f.y * inv * gg.y);
+      }
+      yr[idx] = v[i].u;
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void st_f(T *p, float v);
+template <>
+__device__ __forceinline__ void st_f<__half>(__half *p, float v) { *p = __float2half_rn(v); }
+template <>
+__device__ __forceinline__ void st_f<float>(float *p, float v) { *p = v; }
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rmsnorm_generic(const T *__restrict__ x, const T *__restrict__ w, T *__restrict__ y, int64_t rows,
+                int64_t cols, int64_t ldx, int64_t ldy, float eps) {
+  __shared__ float scratch[32];
+  const int64_t row = blockIdx.x;
+  const T *xr = x + row * ldx;
+  T *yr = y + row * ldy;
+  float ss = 0.0f;
+  for (int64_t j = threadIdx.x; j < cols; j += 256) {
+    float f = ld_f(xr + j);
+    ss = fmaf(f, f, ss);
+  }
+  ss = group_reduce<256, false>(ss, scratch);
+  const float inv = rsqrtf(ss / (float)cols + eps);
+  for (int64_t j = threadIdx.x; j < cols; j += 256)
+    st_f(yr + j, ld_f(xr + j) * inv * ld_f(w + j));
+}
+
+// ---- elementwise -------------------------------------------------------------------------
+// silu(x) = x / (1 + f16(exp(f32(-x)))), add and divide in f16 (test_silu.py:48)
+__device__ __forceinline__ __half silu_h(__half x) {
+  __half e = __float2half_rn(__expf(-__half2float(x)));
+  __half d = __float2half_rn(1.0f + __half2float(e));
+  return __float2half_rn(__fdividef(__half2float(x), __half2float(d)));
+}
+
+enum { EW_SILU = 0, EW_SWIGLU = 1, EW_ADD = 2 };
+
+template <int OP>
+__device__ __forceinline__ __half ew_apply(__half a, __half b) {
+  if (OP == EW_SILU) return silu_h(a);
+  if (OP == EW_SWIGLU) return __float2half_rn(__half2float(silu_h(a)) * __half2float(b));
+  return __float2half_rn(__half2float(a) + __half2float(b));
+}
+
+// Each thread owns UNROLL 16-byte vectors, all loads issued before any math so
+// that every SM keeps tens of KB in flight.
+template <int OP, int UNROLL>
+__global__ void __launch_bounds__(256)
+ew_f16_kernel(const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ y,
+              int64_t n) {
+  const int64_t nvec = n >> 3;
+  const int64_t base = ((int64_t)blockIdx.x * 256 * UNROLL) + threadIdx.x;
+  const uint4 *av = reinterpret_cast<const uint4 *>(a);
+  const uint4 *bv = reinterpret_cast<const uint4 *>(b);
+  uint4 *yv = reinterpret_cast<uint4 *>(y);
+  H8 va[UNROLL], vb[UNROLL];
+#pragma unroll
+  for (int i = 0; i < UNROLL; ++i) {
+    int64_t idx = base + (int64_t)i * 256;
+    if (idx < nvec) {
+      va[i].u = __ldg(av + idx);
+      if (OP != EW_SILU) vb[i].u = __ldg(bv + idx);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < UNROLL; ++i) {
+    int64_t idx = base + (int64_t)i * 256;
+    if (idx < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) va[i].h[j] = ew_apply<OP>(va[i].h[j], vb[i].h[j]);
+      yv[idx] = va[i].u;
+    }
+  }
+  // ragged tail (n % 8 elements), one thread
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    for (int64_t j = nvec << 3; j < n; ++j)
+      y[j] = ew_apply<OP>(a[j], OP != EW_SILU ? b[j] : a[j]);
+}
+
+template <int OP>
+__global__ void __launch_bounds__(256)
+ew_f16_scalar(const __half *__restrict__ a, const __half *__restrict__ b, __half *__restrict__ y,
+              int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256)
+    y[i] = ew_apply<OP>(a[i], OP != EW_SILU ? b[i] : a[i]);
+}
+
+__global__ void __launch_bounds__(256)
+silu_f32_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t n) {
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (int64_t)gridDim.x * 256) {
+    float v = x[i];
+    y[i] = v / (1.0f + expf(-v));
+  }
+}
+
+bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
+
+template <int OP>
+int launch_ew(const __half *a, const __half *b, __half *y, int64_t n, const char *what) {
+  B200_TRY(ensure_ready());
+  if (n <= 0) return 0;
+  cudaStream_t s = ctx().stream;
+  if (aligned16(a) && aligned16(y) && (OP == EW_SILU || aligned16(b))) {
+    constexpr int UNROLL = 4;
+    int64_t nvec = n >> 3;
+    int64_t blocks = (nvec + 256 * UNROLL - 1) / (256 * UNROLL);
+    if (blocks < 1) blocks = 1;
+    ew_f16_kernel<OP, UNROLL><<<(unsigned)blocks, 256, 0, s>>>(a, b, y, n);
+  } else {
+    int64_t blocks = (n + 255) / 256;
+    int64_t cap = (int64_t)ctx().sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    ew_f16_scalar<OP><<<(unsigned)blocks, 256, 0, s>>>(a, b, y, n);
+  }
+  return check_launch(what);
+}
+
+}  // namespace
+
+#define ROW_DISPATCH(KERNEL, ...)                                                        \
+  do {                                                                                   \
+    if (cols <= 256) {                                                                   \
+      KERNEL<32, 1><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(__VA_ARGS__);             \
+    } else if (cols <= 512) {                                                            \
+      KERNEL<32, 2><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(__VA_ARGS__);             \
+    } else if (cols <= 1024) {                                                           \
+      KERNEL<32, 4><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(__VA_ARGS__);             \
+    } else if (cols <= 2048) {                                                           \
+      KERNEL<32, 8><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(__VA_ARGS__);             \
+    } else if (cols <= 4096) {                                                           \
+      KERNEL<128, 4><<<(unsigned)rows, 128, 0, s>>>(__VA_ARGS__);                        \
+    } else if (cols <= 8192) {                                                           \
+      KERNEL<256, 4><<<(unsigned)rows, 256, 0, s>>>(__VA_ARGS__);                        \
+    } else if (cols <= 16384) {                                                          \
+      KERNEL<512, 4><<<(unsigned)rows, 512, 0, s>>>(__VA_ARGS__);                        \
+    } else {                                                                             \
+      KERNEL<1024, 4><<<(unsigned)rows, 1024, 0, s>>>(__VA_ARGS__);                      \
+    }                                                                                    \
+  } while (0)
+
+static bool row_fast_path(const void *x, const void *y, int64_t cols, int64_t ldx, int64_t ldy) {
+  return cols % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && aligned16(x) && aligned16(y) &&
+         cols <= 32768;
+}
+
+int launch_softmax_f16(const __half *x, __half *y, int64_t rows, int64_t cols, int64_t ldx,
+                       int64_t ldy) {
+  B200_TRY(ensure_ready());
+  if (rows <= 0 || cols <= 0) return 0;
+  if (rows > 0x7fffffff) return set_error(B200MLIR_ERR_BAD_ARG, "softmax: too many rows");
+  cudaStream_t s = ctx().stream;
+  if (row_fast_path(x, y, cols, ldx, ldy)) {
+    ROW_DISPATCH(softmax_f16_kernel, x, y, rows, (int)cols, ldx, ldy);
+  } else {
+    softmax_f16_generic<<<(unsigned)rows, 256, 0, s>>>(x, y, rows, cols, ldx, ldy);
+  }
+  return check_launch("softmax_f16");
+}
+
+int launch_softmax_f32(const float *x, float *y, int64_t rows, int64_t cols, int64_t ldx,
+                       int64_t ldy) {
+  B200_TRY(ensure_ready());
+  if (rows <= 0 || cols <= 0) return 0;
+  if (rows > 0x7fffffff) return set_error(B200MLIR_ERR_BAD_ARG, "softmax: too many rows");
+  softmax_f32_generic<<<(unsigned)rows, 256, 0, ctx().stream>>>(x, y, rows, cols, ldx, ldy);
+  return check_launch("softmax_f32");
+}
+
+int launch_rmsnorm_f16(const __half *x, const __half *w, __half *y, int64_t rows, int64_t cols,
+                       int64_t ldx, int64_t ldy, float eps) {
+  B200_TRY(ensure_ready());
+  if (rows <= 0 || cols <= 0) return 0;
+  if (rows > 0x7fffffff) return set_error(B200MLIR_ERR_BAD_ARG, "rms_norm: too many rows");
+  cudaStream_t s = ctx().stream;
+  if (row_fast_path(x, y, cols, ldx, ldy) && aligned16(w)) {
+    ROW_DISPATCH(rmsnorm_f16_kernel, x, w, y, rows, (int)cols, ldx, ldy, eps);
+  } else {
+    rmsnorm_generic<__half><<<(unsigned)rows, 256, 0, s>>>(x, w, y, rows, cols, ldx, ldy, eps);
+  }
+  return check_launch("rmsnorm_f16");
+}
+
+int launch_rmsnorm_f32(const float *x, const float *w, float *y, int64_t rows, int64_t cols,
+                       int64_t ldx, int64_t ldy, float eps) {
+  B200_TRY(ensure_ready());
+  if (rows <= 0 || cols <= 0) return 0;
+  if (rows > 0x7fffffff) return set_error(B200MLIR_ERR_BAD_ARG, "rms_norm: too many rows");
+  rmsnorm_generic<float><<<(unsigned)rows, 256, 0, ctx().stream>>>(x, w, y, rows, cols, ldx, ldy,
+                                                                   eps);
+  return check_launch("rmsnorm_f32");
+}
+
+int launch_silu_f16(const __half *x, __half *y, int64_t n) {
+  return launch_ew<EW_SILU>(x, x, y, n, "silu_f16");
+}
+int launch_swiglu_f16(const __half *g, const __half *u, __half *y, int64_t n) {
+  return launch_ew<EW_SWIGLU>(g, u, y, n, "swiglu_f16");
+}
+int launch_add_f16(const __half *a, const __half *b, __half *y, int64_t n) {
+  return launch_ew<EW_ADD>(a, b, y, n, "add_f16");
+}
+int launch_silu_f32(const float *x, float *y, int64_t n) {
+  B200_TRY(ensure_ready());
+  if (n <= 0) return 0;
+  int64_t blocks = (n + 255) / 256;
+  int64_t cap = (int64_t)ctx().sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  silu_f32_kernel<<<(unsigned)blocks, 256, 0, ctx().stream>>>(x, y, n);
+  return check_launch("silu_f32");
+}
+
+}  // namespace b200

@@ -1,0 +1,535 @@
+// Context, error recording, options and the hexagon_runtime_* seam
+// (qcom_hexagon_backend/bin/runtime/include/HexagonCAPI.h:26-68,
+//  bin/runtime/include/RuntimeDMA.h:39-51) answered on a CUDA device.
+#include <cstdarg>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "common.h"
+
+namespace b200 {
+
+static thread_local int t_err_code = 0;
+static thread_local char t_err_msg[512] = {0};
+std::atomic<int64_t> g_launches{0};
+
+int set_error(int code, const char *fmt, ...) {
+  t_err_code = code;
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(t_err_msg, sizeof(t_err_msg), fmt, ap);
+  va_end(ap);
+  return code;
+}
+void clear_error() {
+  t_err_code = 0;
+  t_err_msg[0] = 0;
+}
+
+Context &ctx() {
+  static Context c;
+  return c;
+}
+
+static std::mutex g_mu;
+
+static int init_locked(int device) {
+  Context &c = ctx();
+  if (c.ready && c.device == device) return 0;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count == 0)
+    return set_error(B200MLIR_ERR_NO_DEVICE, "no CUDA device: %s",
+                     e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+  if (device < 0 || device >= count)
+    return set_error(B200MLIR_ERR_BAD_ARG, "device %d out of range (have %d)", device, count);
+  B200_CUDA(cudaSetDevice(device));
+  cudaDeviceProp p;
+  B200_CUDA(cudaGetDeviceProperties(&p, device));
+  if (p.major != 10)
+    return set_error(B200MLIR_ERR_NO_DEVICE,
+                     "device %d is sm_%d%d; this library is built for sm_100a only", device,
+                     p.major, p.minor);
+  c.device = device;
+  c.sm_count = p.multiProcessorCount;
+  c.cc_major = p.major;
+  c.cc_minor = p.minor;
+  c.l2_bytes = (size_t)p.l2CacheSize;
+  c.persisting_l2_max = (size_t)p.persistingL2CacheMaxSize;
+  c.gpu_name = p.name;
+  if (!c.d_status) {
+    B200_CUDA(cudaMalloc(&c.d_status, 256));
+    B200_CUDA(cudaMemset(c.d_status, 0, 256));
+  }
+  c.ready = true;
+  return 0;
+}
+
+int ensure_ready() {
+  Context &c = ctx();
+  if (c.ready) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur != c.device) cudaSetDevice(c.device);
+    return 0;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = 0;
+  return init_locked(dev);
+}
+
+int check_launch(const char *what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return set_error(B200MLIR_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+  count_launch();
+  return 0;
+}
+
+// Two grow-only workspaces.  Growing frees and reallocates, so it must not
+// happen inside a stream capture: callers warm up once outside any capture.
+struct Arena {
+  void *p = nullptr;
+  size_t cap = 0;
+};
+static Arena g_ws[2];
+
+static int ws_get(int which, size_t bytes, void **out) {
+  Arena &a = g_ws[which];
+  if (bytes > a.cap) {
+    size_t want = ((bytes + (1u << 20) - 1) >> 20) << 20;
+    if (a.p) {
+      B200_CUDA(cudaStreamSynchronize(ctx().stream));
+      B200_CUDA(cudaFree(a.p));
+      a.p = nullptr;
+      a.cap = 0;
+    }
+    B200_CUDA(cudaMalloc(&a.p, want));
+    a.cap = want;
+  }
+  *out = a.p;
+  return 0;
+}
+int workspace(size_t bytes, void **out) { return ws_get(0, bytes, out); }
+int workspace2(size_t bytes, void **out) { return ws_get(1, bytes, out); }
+
+bool is_device_ptr(const void *p) {
+  if (!p) return false;
+  cudaPointerAttributes at;
+  cudaError_t e = cudaPointerGetAttributes(&at, p);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged;
+}
+
+// ---- residency bookkeeping -----------------------------------------------------------
+struct Resident {
+  void *ptr = nullptr;
+  uint32_t bytes = 0;
+  uint32_t align = 0;
+  bool freed = false;
+};
+struct ResidentState {
+  bool entered = false;
+  uint64_t lo = 0, hi = 0;
+  std::map<std::pair<uint64_t, uint32_t>, Resident> workspaces;  // (key, instance)
+  std::unordered_map<uint64_t, Resident> weights;                // source address
+  std::unordered_map<void *, Resident *> by_ptr;
+};
+static ResidentState g_res;
+
+static bool supported_alignment(uint32_t a) {
+  return a != 0 && (a & (a - 1)) == 0 && a <= 2048;
+}
+
+static void *resident_alloc(uint32_t bytes, uint32_t align) {
+  void *p = nullptr;
+  // cudaMalloc returns >= 256-byte aligned memory; over-allocate for more.
+  size_t extra = align > 256 ? align : 0;
+  if (cudaMalloc(&p, (size_t)bytes + extra) != cudaSuccess) {
+    set_error(B200MLIR_ERR_CUDA, "resident allocation of %u bytes failed: %s", bytes,
+              cudaGetErrorString(cudaGetLastError()));
+    return nullptr;
+  }
+  uintptr_t u = (uintptr_t)p;
+  if (extra) u = (u + align - 1) & ~(uintptr_t)(align - 1);
+  return (void *)u;
+}
+
+// ---- copy tokens ---------------------------------------------------------------------
+struct CopyRing {
+  static constexpr int kSlots = 128;  // the reference ring holds 128 descriptors
+  cudaEvent_t ev[kSlots] = {};
+  uint32_t token_of[kSlots] = {};
+  bool used[kSlots] = {};
+  uint32_t next = 0;
+  cudaStream_t stream = nullptr;
+};
+static CopyRing g_ring;
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200mlir_init(int device) {
+  clear_error();
+  std::lock_guard<std::mutex> lk(g_mu);
+  return init_locked(device);
+}
+
+int b200mlir_set_stream(void *s) {
+  clear_error();
+  B200_TRY(ensure_ready());
+  ctx().stream = (cudaStream_t)s;
+  return 0;
+}
+
+int b200mlir_synchronize(void) {
+  clear_error();
+  B200_TRY(ensure_ready());
+  B200_CUDA(cudaStreamSynchronize(ctx().stream));
+  return 0;
+}
+
+int b200mlir_last_error(char *buf, int cap) {
+  if (buf && cap > 0) {
+    strncpy(buf, t_err_msg, (size_t)cap - 1);
+    buf[cap - 1] = 0;
+  }
+  return t_err_code;
+}
+
+const char *b200mlir_version(void) { return "b200mlir 0.1 (sm_100a)"; }
+
+int64_t b200mlir_launch_count(void) { return g_launches.load(); }
+void b200mlir_reset_launch_count(void) { g_launches.store(0); }
+
+int b200mlir_device_status(void) {
+  clear_error();
+  if (ensure_ready()) return -1;
+  int h[2] = {0, 0};
+  if (cudaStreamSynchronize(ctx().stream) != cudaSuccess ||
+      cudaMemcpy(h, ctx().d_status, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    set_error(B200MLIR_ERR_CUDA, "reading the device status word failed: %s",
+              cudaGetErrorString(cudaGetLastError()));
+    return -1;
+  }
+  if (h[0] != 0) {
+    set_error(B200MLIR_ERR_DEVICE_WAIT, "a bounded device wait expired (site %d, detail %d)",
+              h[0], h[1]);
+    cudaMemset(ctx().d_status, 0, 256);
+  }
+  return h[0];
+}
+
+static double *option_slot(const char *name) {
+  Options &o = ctx().opt;
+  if (!name) return nullptr;
+  if (!strcmp(name, "rmsNormEpsilon")) return &o.rms_eps;
+  if (!strcmp(name, "iterations")) return &o.iterations;
+  if (!strcmp(name, "enableWeightResident")) return &o.enable_weight_resident;
+  if (!strcmp(name, "gemmVariant")) return &o.gemm_variant;
+  if (!strcmp(name, "kloopBlockK")) return &o.kloop_block_k;
+  if (!strcmp(name, "w8a16Variant")) return &o.w8a16_variant;
+  return nullptr;
+}
+
+int b200mlir_set_option(const char *name, double value) {
+  clear_error();
+  double *s = option_slot(name);
+  if (!s) return set_error(B200MLIR_ERR_BAD_ARG, "unknown option '%s'", name ? name : "(null)");
+  *s = value;
+  return 0;
+}
+
+int b200mlir_get_option(const char *name, double *value) {
+  clear_error();
+  double *s = option_slot(name);
+  if (!s || !value)
+    return set_error(B200MLIR_ERR_BAD_ARG, "unknown option '%s'", name ? name : "(null)");
+  *value = *s;
+  return 0;
+}
+
+// ---- seam 2: alloc / copy ----------------------------------------------------------------
+void *hexagon_runtime_alloc_1d(size_t bytes, uint64_t alignment, bool isVtcm) {
+  clear_error();
+  if (ensure_ready()) return nullptr;
+  if (bytes == 0 || (alignment & (alignment - 1)) != 0) {
+    set_error(B200MLIR_ERR_BAD_ARG, "alloc_1d: bytes=%zu alignment=%llu unsupported", bytes,
+              (unsigned long long)alignment);
+    return nullptr;
+  }
+  (void)isVtcm;
+  if (alignment > 256) {
+    set_error(B200MLIR_ERR_BAD_ARG,
+              "alloc_1d: alignment %llu above the 256-byte device allocation granule; use the "
+              "resident entry points for 2 KiB-aligned tiles",
+              (unsigned long long)alignment);
+    return nullptr;
+  }
+  void *p = nullptr;
+  if (cudaMalloc(&p, bytes) != cudaSuccess) {
+    set_error(B200MLIR_ERR_CUDA, "alloc_1d(%zu) failed: %s", bytes,
+              cudaGetErrorString(cudaGetLastError()));
+    return nullptr;
+  }
+  return p;
+}
+
+void hexagon_runtime_free_1d(void *ptr) {
+  clear_error();
+  if (ptr && cudaFree(ptr) != cudaSuccess)
+    set_error(B200MLIR_ERR_CUDA, "free_1d failed: %s", cudaGetErrorString(cudaGetLastError()));
+}
+
+void *hexagon_runtime_alloc_2d(size_t numBlocks, size_t blockSize, uint64_t alignment,
+                               bool isVtcm) {
+  // The reference returns a table of block pointers; on one flat HBM address
+  // space the blocks are one contiguous allocation, block i at i*blockSize.
+  if (numBlocks == 0 || blockSize == 0) {
+    set_error(B200MLIR_ERR_BAD_ARG, "alloc_2d: zero-sized request");
+    return nullptr;
+  }
+  return hexagon_runtime_alloc_1d(numBlocks * blockSize, alignment, isVtcm);
+}
+
+void hexagon_runtime_free_2d(void *ptr) { hexagon_runtime_free_1d(ptr); }
+
+void hexagon_runtime_copy(void *dst, void *src, size_t nbytes, bool, bool) {
+  clear_error();
+  if (ensure_ready()) return;
+  if (!dst || !src) {
+    set_error(B200MLIR_ERR_BAD_ARG, "copy: null pointer");
+    return;
+  }
+  if (nbytes == 0) return;
+  cudaError_t e = cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDefault, ctx().stream);
+  if (e == cudaSuccess && !(is_device_ptr(dst) && is_device_ptr(src)))
+    e = cudaStreamSynchronize(ctx().stream);  // host side must observe completion
+  if (e != cudaSuccess) set_error(B200MLIR_ERR_CUDA, "copy failed: %s", cudaGetErrorString(e));
+}
+
+// ---- seam 2: residency ---------------------------------------------------------------------
+int32_t hexagon_runtime_resident_scope_enter_v2(uint64_t lo, uint64_t hi) {
+  clear_error();
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_res.entered) {
+    g_res.entered = true;
+    g_res.lo = lo;
+    g_res.hi = hi;
+    return 0;
+  }
+  if (g_res.lo == lo && g_res.hi == hi) return 0;
+  set_error(B200MLIR_ERR_SCOPE, "resident scope already entered with a different id");
+  return -1;
+}
+
+void *hexagon_runtime_workspace_resident_v2(uint64_t key, uint32_t bytes, uint32_t alignment,
+                                            uint32_t instance) {
+  clear_error();
+  if (ensure_ready()) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_res.entered) {
+    set_error(B200MLIR_ERR_SCOPE, "workspace_resident before resident_scope_enter");
+    return nullptr;
+  }
+  if (bytes == 0 || !supported_alignment(alignment)) {
+    set_error(B200MLIR_ERR_BAD_ARG, "workspace_resident: bytes=%u alignment=%u unsupported", bytes,
+              alignment);
+    return nullptr;
+  }
+  auto k = std::make_pair(key, instance);
+  auto it = g_res.workspaces.find(k);
+  if (it != g_res.workspaces.end()) {
+    if (it->second.bytes != bytes || it->second.align != alignment) {
+      set_error(B200MLIR_ERR_BAD_ARG,
+                "workspace_resident: key reused with a different (bytes, alignment) descriptor");
+      return nullptr;
+    }
+    it->second.freed = false;
+    return it->second.ptr;
+  }
+  void *p = resident_alloc(bytes, alignment);
+  if (!p) return nullptr;
+  Resident &r = g_res.workspaces[k];
+  r.ptr = p;
+  r.bytes = bytes;
+  r.align = alignment;
+  g_res.by_ptr[p] = &r;
+  return p;
+}
+
+static void *weight_resident(uint64_t src, uint32_t bytes, uint32_t alignment) {
+  clear_error();
+  if (ensure_ready()) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_res.entered) {
+    set_error(B200MLIR_ERR_SCOPE, "weight_resident before resident_scope_enter");
+    return nullptr;
+  }
+  if (src == 0 || bytes == 0 || !supported_alignment(alignment)) {
+    set_error(B200MLIR_ERR_BAD_ARG, "weight_resident: src/bytes/alignment unsupported");
+    return nullptr;
+  }
+  auto it = g_res.weights.find(src);
+  if (it != g_res.weights.end()) {
+    if (it->second.bytes != bytes || it->second.align != alignment) {
+      set_error(B200MLIR_ERR_BAD_ARG,
+                "weight_resident: source reused with a different (bytes, alignment) descriptor");
+      return nullptr;
+    }
+    it->second.freed = false;
+    return it->second.ptr;  // same address forever; the source is not read again
+  }
+  void *p = resident_alloc(bytes, alignment);
+  if (!p) return nullptr;
+  cudaError_t e = cudaMemcpyAsync(p, (const void *)(uintptr_t)src, bytes, cudaMemcpyDefault,
+                                  ctx().stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx().stream);
+  if (e != cudaSuccess) {
+    set_error(B200MLIR_ERR_CUDA, "weight_resident: copy of the image failed: %s",
+              cudaGetErrorString(e));
+    return nullptr;
+  }
+  Resident &r = g_res.weights[src];
+  r.ptr = p;
+  r.bytes = bytes;
+  r.align = alignment;
+  g_res.by_ptr[p] = &r;
+  return p;
+}
+
+void *hexagon_runtime_weight_resident_v2(uint64_t src, uint32_t bytes, uint32_t alignment) {
+  return weight_resident(src, bytes, alignment);
+}
+// The reference keeps a DDR mirror for weights too large for VTCM; with one
+// HBM pool both entry points name the same resident store.
+void *hexagon_runtime_weight_resident_ddr_v2(uint64_t src, uint32_t bytes, uint32_t alignment) {
+  return weight_resident(src, bytes, alignment);
+}
+
+int32_t hexagon_runtime_resident_free_v2(void *ptr, uint32_t bytes) {
+  clear_error();
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_res.by_ptr.find(ptr);
+  if (it == g_res.by_ptr.end() || it->second->bytes != bytes) {
+    set_error(B200MLIR_ERR_BAD_ARG, "resident_free: pointer/bytes match no registered resident");
+    return -1;
+  }
+  it->second->freed = true;  // recorded; the pinned block is not released
+  return 0;
+}
+
+void hexagon_runtime_hmx_ensure(void) {}
+void hexagon_runtime_hmx_unlock(void) {}
+
+// ---- seam 2: asynchronous copies -----------------------------------------------------------
+static uint32_t dma_issue(void *src, void *dst, uint32_t width, uint32_t height,
+                          uint32_t srcStride, uint32_t dstStride, int *status) {
+  clear_error();
+  const uint32_t kNone = 0xFFFFFFFFu;
+  auto refuse = [&](const char *why) {
+    if (status) *status = -1;
+    set_error(B200MLIR_ERR_BAD_ARG, "dma start refused: %s", why);
+    return kNone;
+  };
+  if (ensure_ready()) {
+    if (status) *status = -1;
+    return kNone;
+  }
+  if (!src || !dst) return refuse("null address");
+  if (width == 0 || height == 0) return refuse("empty transfer");
+  if (height > 1 && (srcStride < width || dstStride < width)) return refuse("stride below width");
+  std::lock_guard<std::mutex> lk(g_mu);
+  CopyRing &r = g_ring;
+  if (!r.stream && cudaStreamCreateWithFlags(&r.stream, cudaStreamNonBlocking) != cudaSuccess)
+    return refuse("copy stream creation failed");
+  int slot = -1;
+  for (int i = 0; i < CopyRing::kSlots; ++i)
+    if (!r.used[i]) {
+      slot = i;
+      break;
+    }
+  if (slot < 0) return refuse("descriptor ring full");
+  if (!r.ev[slot] &&
+      cudaEventCreateWithFlags(&r.ev[slot], cudaEventDisableTiming) != cudaSuccess)
+    return refuse("event creation failed");
+  cudaError_t e =
+      height == 1
+          ? cudaMemcpyAsync(dst, src, width, cudaMemcpyDefault, r.stream)
+          : cudaMemcpy2DAsync(dst, dstStride, src, srcStride, width, height, cudaMemcpyDefault,
+                              r.stream);
+  if (e == cudaSuccess) e = cudaEventRecord(r.ev[slot], r.stream);
+  if (e != cudaSuccess) return refuse(cudaGetErrorString(e));
+  uint32_t token = r.next++;
+  if (token == kNone) token = r.next++;
+  r.used[slot] = true;
+  r.token_of[slot] = token;
+  if (status) *status = 0;
+  return token;
+}
+
+uint32_t hexagon_runtime_dma_start(void *src, int, void *dst, int, uint32_t length, bool, bool,
+                                   int *status) {
+  return dma_issue(src, dst, length, 1, length, length, status);
+}
+
+uint32_t hexagon_runtime_dma2d_start(void *src, int, void *dst, int, uint32_t width,
+                                     uint32_t height, uint32_t srcStride, uint32_t dstStride, bool,
+                                     bool, bool, uint32_t, int *status) {
+  return dma_issue(src, dst, width, height, srcStride, dstStride, status);
+}
+
+void hexagon_runtime_dma_wait(uint32_t token) {
+  clear_error();
+  if (token == 0xFFFFFFFFu) return;
+  cudaEvent_t ev = nullptr;
+  int slot = -1;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (int i = 0; i < CopyRing::kSlots; ++i)
+      if (g_ring.used[i] && g_ring.token_of[i] == token) {
+        slot = i;
+        ev = g_ring.ev[i];
+        break;
+      }
+  }
+  if (slot < 0) return;  // unknown or already retired: nothing to wait for
+  cudaError_t e = cudaEventSynchronize(ev);
+  if (e != cudaSuccess) set_error(B200MLIR_ERR_CUDA, "dma_wait: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_ring.used[slot] = false;
+}
+
+int b200mlir_benchmark(b200mlir_thunk fn, void *user, int iterations, double *mean_us) {
+  clear_error();
+  B200_TRY(ensure_ready());
+  if (!fn || iterations < 1 || !mean_us)
+    return set_error(B200MLIR_ERR_BAD_ARG, "benchmark: null thunk / iterations < 1");
+  cudaStream_t s = ctx().stream;
+  cudaEvent_t e0, e1;
+  B200_CUDA(cudaEventCreate(&e0));
+  B200_CUDA(cudaEventCreate(&e1));
+  fn(user);  // discarded warm call (hexagon_launcher_base.py:114-153)
+  B200_CUDA(cudaStreamSynchronize(s));
+  B200_CUDA(cudaEventRecord(e0, s));
+  for (int i = 0; i < iterations; ++i) fn(user);
+  B200_CUDA(cudaEventRecord(e1, s));
+  B200_CUDA(cudaEventSynchronize(e1));
+  float ms = 0;
+  B200_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *mean_us = (double)ms * 1000.0 / iterations;
+  return t_err_code;
+}
+
+}  // extern "C"

@@ -1,0 +1,300 @@
+// w8a16 GEMM: fp16 activations x int8 weights with per-output-channel fp16
+// scales, fp32 accumulate, fp16 output.
+//
+// The reference has no such operator (its matrix engine admits f16/f32 only,
+// include/hexagon/Dialect/Hmx/IR/HmxDType.h:59,69); what it does have, and
+// what this file keeps, is the weight-residency contract: a weight is packed
+// once into the layout the engine consumes and the same resident image is used
+// by every later launch (lib/Dialect/Hmx/Transforms/WeightResidentPass.cpp:9-93,
+// backend/hmx_weight_prepack.py:124-212).
+//
+// Resident image: [strip = n/32][kstep = k/16][lane 0..31][16 bytes].  The 16
+// bytes of a lane are exactly the B fragments of four m16n8k16 MMAs (four n8
+// tiles of the strip) for one k16 step, stored as q+128 so that two bytes
+// become two fp16 values with one byte-permute and one subtract — the dequant
+// happens in registers and the row-major weight is never read again.  A warp
+// streams one strip: 512 contiguous bytes per k-step.
+//
+// Decode shapes are HBM-bound, so the work list (n-block, k-step) is cut into
+// equal contiguous ranges over 2 CTAs per SM (no tail wave); partial sums go to
+// an fp32 scratch with red.add and a small second kernel scales, rounds and
+// re-zeroes it.
+#include <mma.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.h"
+
+namespace b200 {
+namespace {
+
+constexpr int WARPS = 8;              // strips per CTA (n-block = 256 columns)
+constexpr int KC_STEPS = 64;          // k16 steps of A held in shared memory at once (1024 k)
+constexpr int A_PITCH = KC_STEPS * 16 + 8;  // halves; +8 keeps ldmatrix conflict-free
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(saddr));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Two biased bytes -> two fp16 values: 0x64xx is 1024 + xx, minus 1152 gives xx - 128.
+__device__ __forceinline__ uint32_t dq2(uint32_t word, uint32_t selector) {
+  uint32_t h;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(h) : "r"(word), "r"(0x64646464u), "r"(selector));
+  const uint32_t bias = 0x64806480u;  // half2(1152, 1152)
+  uint32_t out;
+  asm("sub.f16x2 %0, %1, %2;" : "=r"(out) : "r"(h), "r"(bias));
+  return out;
+}
+
+// MT = number of 16-row tiles of A (M <= 16*MT).
+template <int MT>
+__global__ void __launch_bounds__(WARPS * 32, MT >= 4 ? 1 : 2)
+w8a16_stream_kernel(const __half *__restrict__ A, int64_t lda, const uint4 *__restrict__ image,
+                    float *__restrict__ ws, int M, int N, int K, int ksteps, int n_blocks,
+                    int n_strips) {
+  extern __shared__ __half a_smem[];  // [MT*16][A_PITCH]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t total = (int64_t)n_blocks * ksteps;
+  const int64_t u_begin = total * blockIdx.x / gridDim.x;
+  const int64_t u_end = total * (blockIdx.x + 1) / gridDim.x;
+
+  int64_t u = u_begin;
+  while (u < u_end) {
+    const int nb = (int)(u / ksteps);
+    const int ks0 = (int)(u - (int64_t)nb * ksteps);
+    const int64_t want_end = (int64_t)ks0 + (u_end - u);
+    int ks1 = want_end < (int64_t)ksteps ? (int)want_end : ksteps;
+    if (ks1 - ks0 > KC_STEPS) ks1 = ks0 + KC_STEPS;
+    const int nsteps = ks1 - ks0;
+    const int strip = nb * WARPS + warp;
+
+    // stage A[:, ks0*16 : ks1*16] (zero rows beyond M, zero columns beyond K)
+    __syncthreads();
+    const int vec_per_row = nsteps * 2;  // 16-byte vectors
+    for (int i = threadIdx.x; i < MT * 16 * vec_per_row; i += WARPS * 32) {
+      const int r = i / vec_per_row, v = i - r * vec_per_row;
+      const int k = ks0 * 16 + v * 8;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (r < M && k < K) val = *reinterpret_cast<const uint4 *>(A + (int64_t)r * lda + k);
+      *reinterpret_cast<uint4 *>(a_smem + r * A_PITCH + v * 8) = val;
+    }
+    __syncthreads();
+
+    if (strip < n_strips) {
+      float acc[MT][4][4];
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[m][j][e] = 0.0f;
+
+      const uint4 *wp = image + ((int64_t)strip * ksteps + ks0) * 32 + lane;
+      // ldmatrix source row/col of this lane inside a 16x16 A tile
+      const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int lcol = (lane >> 4) * 8;
+      const uint32_t a_base =
+          (uint32_t)__cvta_generic_to_shared(a_smem) + (uint32_t)(lrow * A_PITCH + lcol) * 2u;
+
+      constexpr int PF = 8;  // weight vectors in flight per lane
+      uint4 wbuf[PF];
+#pragma unroll
+      for (int i = 0; i < PF; ++i)
+        if (i < nsteps) wbuf[i] = __ldg(wp + (int64_t)i * 32);
+
+      for (int s0 = 0; s0 < nsteps; s0 += PF) {
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+          const int s = s0 + i;
+          if (s >= nsteps) break;
+          const uint4 w = wbuf[i];
+          if (s + PF < nsteps) wbuf[i] = __ldg(wp + (int64_t)(s + PF) * 32);
+          const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+          uint32_t b[4][2];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            b[j][0] = dq2(words[j], 0x5140u);  // k = 2t, 2t+1
+            b[j][1] = dq2(words[j], 0x5342u);  // k = 2t+8, 2t+9
+          }
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            uint32_t a[4];
+            ldmatrix_x4(a, a_base + (uint32_t)((m * 16 * A_PITCH + s * 16) * 2));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mma_16816(acc[m][j], a, b[j][0], b[j][1]);
+          }
+        }
+      }
+
+      // flush partial sums: c0,c1 -> (row g, cols 2t,2t+1); c2,c3 -> (row g+8, ...)
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int col = strip * 32 + j * 8 + 2 * t;
+          const int r0 = m * 16 + g, r1 = r0 + 8;
+          if (col < N) {
+            if (r0 < M) {
+              atomicAdd(ws + (int64_t)r0 * N + col, acc[m][j][0]);
+              if (col + 1 < N) atomicAdd(ws + (int64_t)r0 * N + col + 1, acc[m][j][1]);
+            }
+            if (r1 < M) {
+              atomicAdd(ws + (int64_t)r1 * N + col, acc[m][j][2]);
+              if (col + 1 < N) atomicAdd(ws + (int64_t)r1 * N + col + 1, acc[m][j][3]);
+            }
+          }
+        }
+    }
+    u += nsteps;
+  }
+}
+
+// C = f16(ws * scale[n]); ws is left zeroed for the next call.
+__global__ void __launch_bounds__(256)
+w8a16_finalize_kernel(float *__restrict__ ws, const __half *__restrict__ scales,
+                      __half *__restrict__ C, int M, int N, int64_t ldc) {
+  const int64_t total = (int64_t)M * N;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * 256) {
+    const int r = (int)(i / N), c = (int)(i - (int64_t)r * N);
+    const float v = ws[i];
+    ws[i] = 0.0f;
+    C[(int64_t)r * ldc + c] = __float2half_rn(v * __half2float(scales[c]));
+  }
+}
+
+// row-major int8 [K,N] -> resident image (one 16-byte chunk per thread)
+__global__ void __launch_bounds__(256)
+w8a16_swizzle_kernel(const int8_t *__restrict__ wq, uint4 *__restrict__ image, int K, int N,
+                     int ksteps, int n_strips) {
+  const int64_t total = (int64_t)n_strips * ksteps * 32;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * 256) {
+    const int lane = (int)(i & 31);
+    const int64_t sk = i >> 5;
+    const int ks = (int)(sk % ksteps);
+    const int strip = (int)(sk / ksteps);
+    const int g = lane >> 2, t = lane & 3;
+    uint32_t words[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = strip * 32 + j * 8 + g;
+      const int kk[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
+      uint32_t w = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int k = ks * 16 + kk[e];
+        int q = (n < N && k < K) ? (int)wq[(int64_t)k * N + n] : 0;
+        w |= (uint32_t)((q + 128) & 0xff) << (8 * e);
+      }
+      words[j] = w;
+    }
+    image[i] = make_uint4(words[0], words[1], words[2], words[3]);
+  }
+}
+
+float *g_ws = nullptr;  // fp32 scratch, kept zero between calls
+size_t g_ws_elems = 0;
+
+int ensure_ws(size_t elems) {
+  if (elems <= g_ws_elems) return 0;
+  if (g_ws) {
+    B200_CUDA(cudaStreamSynchronize(ctx().stream));
+    B200_CUDA(cudaFree(g_ws));
+    g_ws = nullptr;
+    g_ws_elems = 0;
+  }
+  B200_CUDA(cudaMalloc(&g_ws, elems * sizeof(float)));
+  B200_CUDA(cudaMemsetAsync(g_ws, 0, elems * sizeof(float), ctx().stream));
+  g_ws_elems = elems;
+  return 0;
+}
+
+template <int MT>
+int launch_stream(const __half *a, int64_t lda, const W8A16Weight &w, float *ws, int m) {
+  Context &c = ctx();
+  const int ksteps = (int)((w.k + 15) / 16);
+  const int n_strips = (int)((w.n + 31) / 32);
+  const int n_blocks = (n_strips + WARPS - 1) / WARPS;
+  const size_t smem = (size_t)MT * 16 * A_PITCH * sizeof(__half);
+  auto kern = w8a16_stream_kernel<MT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set = true;
+  }
+  int64_t total = (int64_t)n_blocks * ksteps;
+  int grid = c.sm_count * 2;
+  if (grid > total) grid = (int)total;
+  kern<<<grid, WARPS * 32, smem, c.stream>>>(a, lda, (const uint4 *)w.image, ws, m, (int)w.n,
+                                             (int)w.k, ksteps, n_blocks, n_strips);
+  return check_launch("w8a16_stream");
+}
+
+}  // namespace
+
+int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes) {
+  B200_TRY(ensure_ready());
+  const int ksteps = (int)((k + 15) / 16);
+  const int n_strips = (int)((n + 31) / 32);
+  const size_t sz = (size_t)n_strips * ksteps * 512;
+  void *img = nullptr;
+  B200_CUDA(cudaMalloc(&img, sz));
+  int64_t total = (int64_t)n_strips * ksteps * 32;
+  int64_t blocks = (total + 255) / 256;
+  int64_t cap = (int64_t)ctx().sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  w8a16_swizzle_kernel<<<(unsigned)blocks, 256, 0, ctx().stream>>>(wq_dev, (uint4 *)img, (int)k,
+                                                                   (int)n, ksteps, n_strips);
+  int rc = check_launch("w8a16_swizzle");
+  if (rc) {
+    cudaFree(img);
+    return rc;
+  }
+  *image = img;
+  *bytes = sz;
+  return 0;
+}
+
+int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
+                 int64_t ldc) {
+  B200_TRY(ensure_ready());
+  if (m <= 0 || w.n <= 0) return 0;
+  if (((uintptr_t)a & 15u) || lda % 8)
+    return set_error(B200MLIR_ERR_BAD_ARG,
+                     "w8a16: activations must be 16-byte aligned with a row stride multiple of 8");
+  if (w.k % 8) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16: K must be a multiple of 8");
+  Context &cx = ctx();
+  // Rows are processed in passes of at most 64 (four m16 tiles of accumulators per warp).
+  for (int64_t m0 = 0; m0 < m; m0 += 64) {
+    const int mp = (int)((m - m0) < 64 ? (m - m0) : 64);
+    B200_TRY(ensure_ws((size_t)64 * (size_t)w.n));
+    const __half *ap = a + m0 * lda;
+    int rc;
+    if (mp <= 16) rc = launch_stream<1>(ap, lda, w, g_ws, mp);
+    else if (mp <= 32) rc = launch_stream<2>(ap, lda, w, g_ws, mp);
+    else rc = launch_stream<4>(ap, lda, w, g_ws, mp);
+    B200_TRY(rc);
+    int64_t total = (int64_t)mp * w.n;
+    int64_t blocks = (total + 255) / 256;
+    int64_t cap = (int64_t)cx.sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    w8a16_finalize_kernel<<<(unsigned)blocks, 256, 0, cx.stream>>>(
+        g_ws, (const __half *)w.scales_dev, c + m0 * ldc, mp, (int)w.n, ldc);
+    B200_TRY(check_launch("w8a16_finalize"));
+  }
+  return 0;
+}
+
+}  // namespace b200

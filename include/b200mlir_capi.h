@@ -1,0 +1,293 @@
+/* b200mlir_capi.h — the C ABI of libb200mlir.so.
+ *
+ * A B200 (sm_100a) implementation of the operator hot path that the
+ * hexagon-mlir backend lowers linalg/Triton kernels into.  Two seams of the
+ * reference are answered here, with the same names, argument order and
+ * argument meaning, so that a host that binds the reference's symbols can bind
+ * these instead:
+ *
+ *   seam 1  the compiled-kernel entry points the generated wrapper calls
+ *           (one (rank, descriptor*) pair per tensor, scalars by value, then
+ *            num_programs x/y/z and program_id x/y/z);
+ *   seam 2  the runtime the kernels call (hexagon_runtime_*).
+ *
+ * Plain C: pointers, sizes and integers only.  Every tensor pointer may be a
+ * CUDA device pointer or an ordinary host pointer; host tensors are staged
+ * through device memory inside the call (copy in, compute, copy out, wait).
+ * Device tensors are processed asynchronously on the stream set with
+ * b200mlir_set_stream (default: the legacy default stream).
+ *
+ * Errors: the reference's entry points return void and abort on failure.
+ * These never abort; a failed call leaves its outputs untouched, and
+ * b200mlir_last_error() returns the code and message of the most recent
+ * failure on the calling thread.  There is no CPU fallback: without a usable
+ * CUDA device every compute entry fails with B200MLIR_ERR_NO_DEVICE.
+ *
+ * Citations are file:line inside the reference project (hexagon-mlir).
+ */
+#ifndef B200MLIR_CAPI_H
+#define B200MLIR_CAPI_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_API __attribute__((visibility("default")))
+
+/* ---- descriptors ---------------------------------------------------------
+ * MLIR memref descriptor, every index field int64
+ * (test/utils/dsp/include/common.h:15-27). */
+typedef struct {
+  void *allocated;
+  void *aligned;
+  int64_t offset;
+  int64_t sizes[1];
+  int64_t strides[1];
+} B200MemRef1D;
+
+typedef struct {
+  void *allocated;
+  void *aligned;
+  int64_t offset;
+  int64_t sizes[2];
+  int64_t strides[2];
+} B200MemRef2D;
+
+enum {
+  B200MLIR_OK = 0,
+  B200MLIR_ERR_NO_DEVICE = 1,   /* no CUDA device / driver, or not sm_100 */
+  B200MLIR_ERR_BAD_ARG = 2,     /* rank, shape, stride or pointer contract broken */
+  B200MLIR_ERR_CUDA = 3,        /* a CUDA call failed; message carries the text */
+  B200MLIR_ERR_SCOPE = 4,       /* resident request outside / against the scope */
+  B200MLIR_ERR_DEVICE_WAIT = 5, /* a bounded device-side wait ran out */
+  B200MLIR_ERR_UNSUPPORTED = 6, /* no kernel variant is legal for this request */
+  B200MLIR_ERR_VERIFY = 7       /* autotune candidate produced a wrong result */
+};
+
+/* ---- library management (no counterpart in the reference: its runtime is a
+ * process-wide singleton created on first use,
+ * qcom_hexagon_backend/bin/runtime/include/HexagonAPI.h:47-115) ------------- */
+B200_API int b200mlir_init(int device);
+B200_API int b200mlir_set_stream(void *cuda_stream);
+B200_API int b200mlir_synchronize(void);
+B200_API int b200mlir_last_error(char *buf, int cap);
+B200_API const char *b200mlir_version(void);
+/* Kernels of this library launched by this process since the last reset. */
+B200_API int64_t b200mlir_launch_count(void);
+B200_API void b200mlir_reset_launch_count(void);
+/* Status word the device kernels write when a bounded wait expires; 0 = clean.
+ * Reading it synchronises the stream. */
+B200_API int b200mlir_device_status(void);
+
+/* Options, the subset of the reference's option dataclass that reaches this
+ * path (qcom_hexagon_backend/backend/hexagon_options.py:16-278).  Names are
+ * the reference's: "enableWeightResident", "iterations", plus
+ * "rmsNormEpsilon" (a tl.constexpr in the reference kernel,
+ * test/python/triton/test_rms_norm.py:17,39), "gemmVariant" (-1 = dispatcher's
+ * choice) and "kloopBlockK".  Returns 0, or B200MLIR_ERR_BAD_ARG for an
+ * unknown name. */
+B200_API int b200mlir_set_option(const char *name, double value);
+B200_API int b200mlir_get_option(const char *name, double *value);
+
+/* ---- seam 1: kernel entry points ------------------------------------------
+ * Signature rule: backend/hexagon_launcher_base.py:58-60,72-74 and
+ * backend/triton_hexagon_launcher.py:241-252 — tensors as (rank, descriptor*),
+ * tl.constexpr parameters not passed (backend/driver.py:207-212), six trailing
+ * ints.  One call computes the WHOLE problem: the instance with program id
+ * (0,0,0) enqueues it and every other instance of a grid>1 launch returns at
+ * once, which keeps the reference's "each program owns a row slice" contract
+ * observable from outside (same bytes written once).
+ */
+#define B200_GRID_ARGS int num_programs_x, int num_programs_y, int num_programs_z, \
+                       int pid_x, int pid_y, int pid_z
+
+/* C[M,N] = A[M,K]·B[K,N]; fp16 in, fp32 accumulate, fp16 out; C overwritten.
+ * Kernel: test/python/triton/test_matmul.py:32-72.  Engine leaves replaced:
+ * qcom_hexagon_backend/bin/runtime/hmx/src/HMXAPI.c:22-55 (bias_init, acc_clear,
+ * mma, acc_store) and the pack/unpack leaves of hmx/src/HMXLayout.c. */
+B200_API void matmul(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B200MemRef2D *b,
+                     int64_t rank_c, B200MemRef2D *c, B200_GRID_ARGS);
+/* Same contraction with the K-segmented accumulation of a K-looped tl.dot:
+ * each BLOCK_K segment is read out as fp16, widened and added in fp32
+ * (test/python/triton/test_matmul_kloop.py:27-34,87-98).  BLOCK_K = option
+ * "kloopBlockK" (default 64). */
+B200_API void klooped_matmul(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B200MemRef2D *b,
+                             int64_t rank_c, B200MemRef2D *c, B200_GRID_ARGS);
+/* fp32 read-out with optional fp32 residual: C32 = f32(f16(A·B)) [+ R]
+ * (hmx_unpack_acc_f32_bulk, hmx/src/HMXLayout.c:868-999; `res` may be NULL /
+ * rank 0). */
+B200_API void matmul_f32out(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B200MemRef2D *b,
+                            int64_t rank_c, B200MemRef2D *c32, int64_t rank_r,
+                            B200MemRef2D *res32, B200_GRID_ARGS);
+/* int8 x int8 -> int32, exact (the reference routes integer matmuls to exact
+ * vector loops: include/hexagon/Dialect/Hmx/Transforms/HmxTarget.h:198-200). */
+B200_API void matmul_i8(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B200MemRef2D *b,
+                        int64_t rank_c, B200MemRef2D *c, B200_GRID_ARGS);
+
+/* Row softmax (test/python/triton/test_softmax.py:39-70; lowered form
+ * docs/tutorials/triton/softmax.md:150-226). */
+B200_API void softmax_kernel_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_y,
+                                     B200MemRef2D *y, B200_GRID_ARGS);
+B200_API void softmax_kernel_float32(int64_t rank_x, B200MemRef2D *x, int64_t rank_y,
+                                     B200MemRef2D *y, B200_GRID_ARGS);
+/* RMSNorm y = x * rsqrt(mean(x^2) + eps) * w
+ * (test/python/triton/test_rms_norm.py:32-60); eps = option "rmsNormEpsilon". */
+B200_API void rms_norm_fwd_kernel_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_y,
+                                          B200MemRef2D *y, int64_t rank_w, B200MemRef1D *w,
+                                          B200_GRID_ARGS);
+B200_API void rms_norm_fwd_kernel_float32(int64_t rank_x, B200MemRef2D *x, int64_t rank_y,
+                                          B200MemRef2D *y, int64_t rank_w, B200MemRef1D *w,
+                                          B200_GRID_ARGS);
+/* SiLU x / (1 + exp(-x)) (test/python/triton/test_silu.py:38-49). */
+B200_API void silu_kernel_float16(int64_t rank_x, B200MemRef1D *x, int64_t rank_y,
+                                  B200MemRef1D *y, B200_GRID_ARGS);
+B200_API void silu_kernel_float32(int64_t rank_x, B200MemRef1D *x, int64_t rank_y,
+                                  B200MemRef1D *y, B200_GRID_ARGS);
+/* Vector add (test/python/triton/test_vec_add.py), the residual-add generic. */
+B200_API void add_kernel_float16(int64_t rank_x, B200MemRef1D *x, int64_t rank_y,
+                                 B200MemRef1D *y, int64_t rank_o, B200MemRef1D *out,
+                                 B200_GRID_ARGS);
+
+/* Ops the reference has no kernel for; they follow the same convention and
+ * are defined as the composition its lowering would produce. */
+/* out = silu(gate) * up, the fused two-input elementwise generic
+ * (qcom_hexagon_backend/lib/Conversion/LinalgToLLVM/FusionPass.cpp). */
+B200_API void swiglu_kernel_float16(int64_t rank_g, B200MemRef1D *gate, int64_t rank_u,
+                                    B200MemRef1D *up, int64_t rank_o, B200MemRef1D *out,
+                                    B200_GRID_ARGS);
+/* C[M,N] = A[M,K] · dequant(Wq[K,N], s[N]); Wq int8 row-major, s fp16 per
+ * output channel, fp32 accumulate, fp16 out.  No reference function (HMX admits
+ * f16/f32 only: include/hexagon/Dialect/Hmx/IR/HmxDType.h:59,69). */
+B200_API void w8a16_matmul(int64_t rank_a, B200MemRef2D *a, int64_t rank_w, B200MemRef2D *wq,
+                           int64_t rank_s, B200MemRef1D *scales, int64_t rank_c,
+                           B200MemRef2D *c, B200_GRID_ARGS);
+/* Llama-style MLP block over this rank's shard of the hidden dimension:
+ *   h = rmsnorm(x, gain, eps); a = swiglu(h·Wg, h·Wu); out = a·Wd (+ x if add_residual)
+ * Wg, Wu: [D, F_local]; Wd: [F_local, D].  With tensor parallelism each rank
+ * passes its column block of Wg/Wu and row block of Wd, add_residual = 0, sums
+ * `out` over ranks and adds x afterwards (add_kernel_float16). */
+B200_API void mlp_block_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_gain,
+                                B200MemRef1D *gain, int64_t rank_wg, B200MemRef2D *wg,
+                                int64_t rank_wu, B200MemRef2D *wu, int64_t rank_wd,
+                                B200MemRef2D *wd, int64_t rank_o, B200MemRef2D *out,
+                                float eps, int add_residual, B200_GRID_ARGS);
+
+/* ---- seam 2: runtime ---------------------------------------------------------
+ * qcom_hexagon_backend/bin/runtime/include/HexagonCAPI.h:26-68.  `isVtcm`
+ * selected the 8 MiB on-chip scratch on Hexagon; here every allocation is HBM
+ * and the flag only asks for 2 KiB alignment.  alloc never returns NULL for a
+ * valid request on a working device; on failure it returns NULL and records
+ * the error instead of aborting the process. */
+B200_API void *hexagon_runtime_alloc_1d(size_t bytes, uint64_t alignment, bool isVtcm);
+B200_API void hexagon_runtime_free_1d(void *ptr);
+B200_API void *hexagon_runtime_alloc_2d(size_t numBlocks, size_t blockSize, uint64_t alignment,
+                                        bool isVtcm);
+B200_API void hexagon_runtime_free_2d(void *ptr);
+B200_API void hexagon_runtime_copy(void *dst, void *src, size_t nbytes, bool isDstVtcm,
+                                   bool isSrcVtcm);
+/* Residency (HexagonCAPI.h:39-57; impl bin/runtime/src/HexagonCAPI.cpp:132-206).
+ * One immutable scope per process; requests before scope entry fail; a weight
+ * is identified by its source address and exact (bytes, alignment) descriptor
+ * and the same device address is returned on every later request.  The
+ * resident copy of a weight is a device buffer that stays allocated until the
+ * process exits. */
+B200_API int32_t hexagon_runtime_resident_scope_enter_v2(uint64_t scopeLow64, uint64_t scopeHigh64);
+B200_API void *hexagon_runtime_workspace_resident_v2(uint64_t key, uint32_t bytes,
+                                                     uint32_t alignment, uint32_t instance);
+B200_API void *hexagon_runtime_weight_resident_v2(uint64_t src, uint32_t bytes, uint32_t alignment);
+B200_API void *hexagon_runtime_weight_resident_ddr_v2(uint64_t src, uint32_t bytes,
+                                                      uint32_t alignment);
+B200_API int32_t hexagon_runtime_resident_free_v2(void *ptr, uint32_t bytes);
+/* Engine lock (HexagonCAPI.h:59-68).  SMs are not a single locked engine;
+ * kept so that compiled callers link, and they do nothing. */
+B200_API void hexagon_runtime_hmx_ensure(void);
+B200_API void hexagon_runtime_hmx_unlock(void);
+/* Asynchronous copies (bin/runtime/include/RuntimeDMA.h:39-51).  A refused
+ * start returns 0xFFFFFFFF and sets *status = -1; waiting on that token
+ * returns at once.  Strides, width in bytes. */
+B200_API uint32_t hexagon_runtime_dma_start(void *src, int srcAS, void *dst, int dstAS,
+                                            uint32_t length, bool bypassCacheSrc,
+                                            bool bypassCacheDst, int *status);
+B200_API uint32_t hexagon_runtime_dma2d_start(void *src, int srcAS, void *dst, int dstAS,
+                                              uint32_t width, uint32_t height,
+                                              uint32_t srcStride, uint32_t dstStride,
+                                              bool bypassCacheSrc, bool bypassCacheDst,
+                                              bool isOrdered, uint32_t cacheAllocationPolicy,
+                                              int *status);
+B200_API void hexagon_runtime_dma_wait(uint32_t token);
+
+/* ---- weight residency for the GEMMs (replaces the host packer
+ * qcom_hexagon_backend/backend/hmx_weight_prepack.py:124-212 and
+ * WeightResidentPass, lib/Dialect/Hmx/Transforms/WeightResidentPass.cpp:9-93).
+ * Registers a [K,N] int8 weight + fp16 scales by source address: the first
+ * call builds the pre-swizzled device image once; later w8a16_matmul calls
+ * with the same Wq pointer use it without touching the row-major source.
+ * Returns 0 or an error code.  `l2_persist` != 0 also asks for an L2
+ * persistence window over the image for decode-shaped calls. */
+B200_API int b200mlir_w8a16_register_weight(const void *wq, const void *scales, int64_t k,
+                                            int64_t n, int l2_persist);
+B200_API int b200mlir_w8a16_unregister_weight(const void *wq);
+/* Row-major fp16 [K,N] -> the reference's weight tile image [Nt,Kt,16,32,2]
+ * and back-compatible activation/accumulator images (device or host pointers).
+ * (hmx_pack_weight_f16_bulk / hmx_pack_act_f16_bulk / hmx_unpack_acc_f16_bulk,
+ * hmx/include/HMXAPI.h:81-106,231-262) */
+B200_API int b200mlir_pack_weight_f16(const void *src, void *dst, int64_t k, int64_t n,
+                                      int64_t src_stride);
+B200_API int b200mlir_pack_act_f16(const void *src, void *dst, int64_t rows, int64_t cols,
+                                   int64_t src_stride);
+B200_API int b200mlir_unpack_acc_f16(const void *tiles, void *dst, int64_t rows, int64_t cols,
+                                     int64_t dst_stride);
+
+/* ---- dispatch and tile search (replaces
+ * qcom_hexagon_backend/backend/hmx_search.py and the legality predicate
+ * include/hexagon/Dialect/Hmx/Transforms/HmxTarget.h:195-222,341-383) --------- */
+/* Number of hand-written GEMM variants and a JSON description of variant i. */
+B200_API int b200mlir_gemm_variant_count(void);
+B200_API int b200mlir_gemm_variant_info(int variant, char *json, int cap);
+/* Verdict of one variant on one shape: "ok" or a rejection reason
+ * ("min-rows", "tile-alignment", "smem-budget", "tmem-budget", ...).  Returns
+ * 1 when legal, 0 when refused, <0 on a bad variant index. */
+B200_API int b200mlir_gemm_variant_verdict(int variant, int64_t m, int64_t n, int64_t k,
+                                           char *reason, int cap);
+/* JSON record of what the dispatcher would run for this shape and why
+ * (plan / reason vocabulary of
+ * include/hexagon/Dialect/Hmx/Transforms/HmxManifest.h:81-100). */
+B200_API int b200mlir_gemm_explain(int64_t m, int64_t n, int64_t k, char *json, int cap);
+/* Search the variant list for one shape on the current device: enumerate,
+ * refuse illegal ones, order by modelled lower bound, measure each with one
+ * discarded launch + timed launches (3 repetitions, q50/q20/q80), verify the
+ * first repetition against `expected` checks, crown only past max(3*CV, 15%),
+ * void the round if the canary drifted.  Result cached by (M,N,K,dtype,gpu,
+ * build).  Writes a JSON report; returns the champion variant or <0. */
+B200_API int b200mlir_gemm_autotune(int64_t m, int64_t n, int64_t k, char *json, int cap);
+/* The verdict stage alone, on measurements supplied by the caller instead of
+ * the device — the reference tests its search loop the same way, with a fake
+ * launcher (qcom_hexagon_backend/test/test_hmx_search_loop_contract.py:134-158).
+ * times_us[3*v + {0,1,2}] = {q50, q20, q80} of variant v (a non-finite or
+ * non-positive q50 means the candidate failed); canary = {q50, q20, q80} or
+ * NULL; canary_reference_q50 <= 0 or NaN = no reference yet.  Returns the
+ * champion variant or -1. */
+B200_API int b200mlir_gemm_search_scripted(int64_t m, int64_t n, int64_t k, const double *times_us,
+                                           int n_variants, int control_variant,
+                                           const double *canary, double canary_reference_q50,
+                                           char *json, int cap);
+B200_API int b200mlir_autotune_cache_load(const char *path);
+B200_API int b200mlir_autotune_cache_save(const char *path);
+B200_API void b200mlir_autotune_cache_clear(void);
+
+/* Benchmark protocol of the generated wrapper
+ * (backend/hexagon_launcher_base.py:114-159;
+ * test/utils/dsp/include/hexagon_benchmark.h:57-72): the caller's thunk is run
+ * once and discarded, then `iterations` times between two CUDA events on the
+ * library's stream.  *mean_us receives the mean per call. */
+typedef void (*b200mlir_thunk)(void *user);
+B200_API int b200mlir_benchmark(b200mlir_thunk fn, void *user, int iterations, double *mean_us);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MLIR_CAPI_H */

@@ -153,7 +153,13 @@ Judgement judge_round(std::vector<Measured> rows, int control_variant, const dou
   const Measured *control = nullptr;
   for (auto *r : measured)
     if (r->variant == control_variant) control = r;
-  const Measured *incumbent = control ? control : (measured.empty() ? nullptr : measured[0]);
+  // A control arm that was nominated but scored inf leaves no arm to judge a
+  // win against: no champion.  With no control nominated the walk starts at
+  // the first enumerated candidate (hmx_search.py:1467-1487).
+  bool control_nominated = false;
+  for (auto &r : rows) control_nominated |= r.variant == control_variant;
+  const Measured *incumbent =
+      control ? control : (control_nominated || measured.empty() ? nullptr : measured[0]);
   std::ostringstream cmp;
   bool first = true;
   int step = 0;

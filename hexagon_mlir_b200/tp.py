@@ -1,0 +1,98 @@
+"""Multi-GPU partitioning of the two configs that shard: the large GEMM (column blocks of
+B and C per rank, no collective) and the Llama-style MLP block (column-split gate/up,
+row-split down, one all-reduce of the block output).
+
+The reference partitions a decode GEMM the same way inside one device: every program
+takes one [K, BN] column block of a single resident weight
+(qcom_hexagon_backend/test/Dialect/Hmx/Transforms/weight-resident-nsplit.mlir:9-27);
+across GPUs the cut is the same, one process per GPU, torch.distributed for the plumbing.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import launcher as _l
+
+
+def shard_bounds(extent: int, rank: int, world: int, granule: int = 8):
+    """[lo, hi) of this rank's block of `extent`, cut on multiples of `granule` (the
+    16-byte alignment the tensor-core path needs for fp16 row strides)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} outside world {world}")
+    units = -(-extent // granule)
+    lo = min(extent, (rank * units // world) * granule)
+    hi = min(extent, ((rank + 1) * units // world) * granule)
+    return lo, hi
+
+
+def shard_columns(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    lo, hi = shard_bounds(t.shape[1], rank, world)
+    return t[:, lo:hi].contiguous()
+
+
+def shard_rows(t: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    lo, hi = shard_bounds(t.shape[0], rank, world)
+    return t[lo:hi].contiguous()
+
+
+def _device_mlp(x, gain, wg, wu, wd, out, eps, add_residual):
+    _l.mlp_block[(1,)](x, gain, wg, wu, wd, out, eps=eps, add_residual=add_residual)
+
+
+def _device_add(a, b, out):
+    _l.add_kernel[(1,)](a.reshape(-1), b.reshape(-1), out.reshape(-1))
+
+
+class TensorParallelMLP:
+    """out = x + down(swiglu(gate(h), up(h))), h = rmsnorm(x)·gain, hidden dimension sharded.
+
+    Each rank holds Wg[:, lo:hi], Wu[:, lo:hi], Wd[lo:hi, :] and computes a partial
+    [T, D] output; the partials are summed with one all-reduce and the residual is added
+    afterwards on every rank.  The token dimension is cut into `chunks` pieces so that the
+    all-reduce of piece i runs while piece i+1 is computed.  `compute` / `add` default to
+    the library's kernels; the CPU tests of the partitioning logic inject stand-ins.
+    """
+
+    def __init__(self, gain, wg, wu, wd, eps=1e-6, group=None, chunks=4, compute=None, add=None):
+        self.gain, self.wg, self.wu, self.wd = gain, wg, wu, wd
+        self.eps = float(eps)
+        self.group = group
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.chunks = max(1, int(chunks))
+        self.compute = compute or _device_mlp
+        self.add = add or _device_add
+        self._partial = None
+
+    def __call__(self, x, out):
+        if self.world == 1:
+            self.compute(x, self.gain, self.wg, self.wu, self.wd, out, self.eps, True)
+            return out
+        if self._partial is None or self._partial.shape != x.shape or self._partial.device != x.device:
+            self._partial = torch.empty_like(x)
+        t = x.shape[0]
+        step = -(-t // self.chunks)
+        works = []
+        for r0 in range(0, t, step):
+            r1 = min(t, r0 + step)
+            part = self._partial[r0:r1]
+            self.compute(x[r0:r1], self.gain, self.wg, self.wu, self.wd, part, self.eps, False)
+            works.append(dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        for w in works:
+            w.wait()
+        self.add(self._partial, x, out)
+        return out
+
+
+class ColumnShardedGemm:
+    """C[:, lo:hi] = A · B[:, lo:hi] on each rank; A replicated; no collective."""
+
+    def __init__(self, rank: int, world: int):
+        self.rank, self.world = rank, world
+
+    def bounds(self, n: int):
+        return shard_bounds(n, self.rank, self.world)
+
+    def __call__(self, a, b_shard, c_shard):
+        _l.matmul[(1,)](a, b_shard, c_shard)
+        return c_shard

@@ -32,3 +32,20 @@ def oracle():
 def philox(seed):
     import numpy as np
     return np.random.Generator(np.random.Philox(seed))
+
+
+def max_abs_rel(got, ref):
+    """max|got - ref| / max|ref| — the 'max-abs-rel' error the tolerances are stated in."""
+    import numpy as np
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    denom = max(float(np.abs(ref).max()), 1e-30)
+    return float(np.abs(got - ref).max()) / denom
+
+
+@pytest.fixture(scope="session")
+def cuda():
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return torch

@@ -1,0 +1,130 @@
+"""Generates the committed golden fixtures from the reference itself.
+
+Run in a container that has the reference checkout (default /root/reference):
+
+    python tests/golden/make_golden.py
+
+It (1) runs the reference's own layout leaves (HMXLayout.c, compiled by
+oracle/Makefile target "ref") on seeded inputs and stores inputs + outputs, and
+(2) imports the reference's stdlib-only backend/hmx_search.py and stores what
+its search-loop functions return on scripted measurements.  The tests read the
+fixtures only; nothing at test time touches the reference.
+"""
+import importlib.util
+import json
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+REF = os.environ.get("HEXMLIR_REFERENCE_ROOT", "/root/reference")
+
+import oracle  # noqa: E402
+
+
+def layout_fixture():
+    oracle.build(with_ref=True)
+    assert oracle.ref_lib() is not None, "reference layout leaves did not build"
+    rng = np.random.Generator(np.random.Philox(1234))
+    out = {}
+    for name, (k, n) in {"w64x96": (64, 96), "w70x45": (70, 45), "w32x32": (32, 32),
+                         "w1x33": (1, 33)}.items():
+        w = rng.uniform(-4, 4, (k, n)).astype(np.float16)
+        out[f"{name}_src"] = w.view(np.uint16)
+        out[f"{name}_weight_image"] = oracle.ref_pack_weight_f16(w)
+        out[f"{name}_act_image"] = oracle.ref_pack_act_f16(w)
+        tiles = oracle.ref_pack_act_f16(w)
+        out[f"{name}_unpacked"] = oracle.ref_unpack_acc_f16(tiles, k, n)
+        res = rng.normal(0, 1, (k, n)).astype(np.float32)
+        out[f"{name}_res"] = res
+        out[f"{name}_unpacked_f32_res"] = oracle.ref_unpack_acc_f32(tiles, k, n, res)
+    f = rng.normal(0, 100, (64, 64)).astype(np.float32)
+    f[0, :8] = [-0.0, 0.0, 65504.0, 65520.0, 1e-8, -1e-8, 6.1e-5, 2049.0]
+    out["f32_src"] = f
+    with np.errstate(over="ignore"):
+        out["f32_weight_image"] = oracle.ref_pack_weight_f32(f)
+    np.savez_compressed(os.path.join(HERE, "layout_golden.npz"), **out)
+
+
+def search_fixture():
+    path = os.path.join(REF, "qcom_hexagon_backend", "backend", "hmx_search.py")
+    spec = importlib.util.spec_from_file_location("ref_hmx_search", path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["ref_hmx_search"] = mod
+    spec.loader.exec_module(mod)
+    g = {}
+    g["constants"] = dict(TILE_EDGE=mod.TILE_EDGE, MIN_ROWS=mod.MIN_ROWS,
+                          CHAMPION_CV_FACTOR=mod.CHAMPION_CV_FACTOR,
+                          CHAMPION_MARGIN_FLOOR=mod.CHAMPION_MARGIN_FLOOR)
+    g["champion_gate"] = [[cv, mod.champion_gate(cv)] for cv in
+                          [0.0, 0.01, 0.049, 0.05, 0.051, 0.1, 0.5, float("nan")]]
+    g["quantile"] = [[s, q, mod._quantile(s, q)] for s in
+                     ([1.0], [3.0, 1.0, 2.0], [10.0, 20.0, 40.0], [5.0, 7.0]) for q in (0.5, 0.2, 0.8)]
+    g["calibration_iters"] = [[us, mod.calibration_iters(us)] for us in
+                              [0.5, 1.0, 100.0, 2000.0, 1e6, 1e7]]
+    g["tile_verdict"] = [[bm, bn, bk, mod.tile_verdict(bm, bn, bk)] for bm, bn, bk in
+                         [(32, 32, 32), (4, 32, 32), (1, 32, 32), (64, 48, 32), (1024, 1024, 1024),
+                          (2048, 1024, 1024), (1024, 1024, 2048), (512, 512, 512)]]
+    g["span_count"] = [[m, n, k, list(t), mod.span_count(m, n, k, t)] for m, n, k, t in
+                       [(1024, 1024, 1024, (128, 256, 64)), (1000, 1000, 1000, (128, 128, 64)),
+                        (16384, 16384, 8192, (128, 256, 64))]]
+    # canary verdicts
+    def rec(q50, q20, q80):
+        return {"q50_pcyc": q50, "q20_pcyc": q20, "q80_pcyc": q80}
+    cases = {
+        "missing": (None, None),
+        "unmeasured": (rec(float("inf"), float("inf"), float("inf")), 100.0),
+        "reference_established": (rec(100.0, 99.0, 101.0), None),
+        "ok": (rec(105.0, 104.0, 106.0), 100.0),
+        "drift": (rec(130.0, 129.0, 131.0), 100.0),
+        "noisy_ok": (rec(130.0, 120.0, 140.0), 100.0),
+    }
+    g["canary"] = {}
+    for name, (metrics, ref) in cases.items():
+        v = mod.canary_verdict(metrics, ref)
+        g["canary"][name] = {"metrics": metrics, "reference": ref, "status": v["status"],
+                             "healthy": v["healthy"]}
+    # champion rounds on scripted measurements; labels a/b/c stand for three
+    # candidates visited in this order, "a" the control arm
+    def rows(ts):
+        return [dict(cfg=lbl, tiles=[i, 0, 0], q50_pcyc=t[0], q20_pcyc=t[1], q80_pcyc=t[2])
+                for i, (lbl, t) in enumerate(zip("abc", ts))]
+    rounds = {
+        "control_keeps": [(100, 99, 101), (95, 94, 96), (90, 89, 91)],
+        "clear_takeover": [(100, 99, 101), (80, 79, 81), (120, 119, 121)],
+        "chain": [(100, 99, 101), (80, 79, 81), (60, 59, 61)],
+        "noisy_blocks": [(100, 80, 120), (70, 69, 71), (200, 199, 201)],
+        "exactly_on_gate": [(100, 100, 100), (85, 85, 85), (300, 300, 300)],
+        "failed_candidate": [(100, 99, 101), (float("inf"),) * 3, (50, 49, 51)],
+        "control_failed": [(float("inf"),) * 3, (80, 79, 81), (60, 59, 61)],
+    }
+    g["rounds"] = {}
+    healthy = rec(100.0, 99.0, 101.0)
+    for name, ts in rounds.items():
+        r = mod.judge_champion_round(rows(ts), control="a", canary=healthy, canary_reference=100.0,
+                                     iters=10)
+        g["rounds"][name] = {
+            "timings": [[None if x == float("inf") else x for x in t] for t in ts],
+            "champion": r["champion"], "round_verdict": r["round_verdict"],
+            "champion_significant": r["champion_significant"], "unmeasured": r["unmeasured"],
+            "outcomes": [c["outcome"] for c in r["comparisons"]],
+        }
+    r = mod.judge_champion_round(rows(rounds["clear_takeover"]), control="a",
+                                 canary=rec(150.0, 149.0, 151.0), canary_reference=100.0, iters=10)
+    g["rounds"]["void_round"] = {
+        "timings": [list(t) for t in rounds["clear_takeover"]], "champion": r["champion"],
+        "round_verdict": r["round_verdict"], "champion_significant": r["champion_significant"],
+        "unmeasured": r["unmeasured"], "outcomes": [c["outcome"] for c in r["comparisons"]],
+        "canary": [150.0, 149.0, 151.0],
+    }
+    with open(os.path.join(HERE, "search_golden.json"), "w") as f:
+        json.dump(g, f, indent=1, sort_keys=True)
+
+
+if __name__ == "__main__":
+    layout_fixture()
+    search_fixture()
+    print("wrote", sorted(os.listdir(HERE)))

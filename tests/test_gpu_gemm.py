@@ -1,0 +1,162 @@
+"""fp16 GEMM through the C ABI against the oracle.  North-star tolerance: max-abs-rel 1e-2;
+the tensor-core path accumulates in fp32 like the oracle, so the observed error is an fp16 ulp."""
+import numpy as np
+import pytest
+
+from conftest import max_abs_rel, philox
+
+pytestmark = pytest.mark.gpu
+
+TOL_GEMM = 1e-2
+SIMT = 99
+
+
+def run_matmul(hm, a, b, variant=-1, kernel=None, **opts):
+    c = np.full((a.shape[0], b.shape[1]), np.float16(7), np.float16)
+    hm.set_option("gemmVariant", variant)
+    try:
+        (kernel or hm.matmul)[(1,)](a, b, c, **opts)
+    finally:
+        hm.set_option("gemmVariant", -1)
+    assert hm.device_status() == 0
+    return c
+
+
+def n_variants(hm):
+    return len(hm.gemm_variants())
+
+
+@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, -1])
+def test_c1_config(hm, oracle, variant):
+    """M=N=K=1024, U[-1,1], seed 0."""
+    rng = philox(0)
+    a = rng.uniform(-1, 1, (1024, 1024)).astype(np.float16)
+    b = rng.uniform(-1, 1, (1024, 1024)).astype(np.float16)
+    want = oracle.gemm_f16(a, b)
+    got = run_matmul(hm, a, b, variant)
+    assert max_abs_rel(got, want) <= TOL_GEMM
+    rel = np.linalg.norm(got.astype(np.float32) - want.astype(np.float32)) / np.linalg.norm(want.astype(np.float32))
+    assert rel < 2e-3  # test_matmul_kloop.py:66-68
+    assert (got.view(np.uint16) != want.view(np.uint16)).mean() < 0.05  # fp32 sum order only
+
+
+def test_reference_test_shape(hm, oracle):
+    """1024x512x64, torch.rand inputs, atol 2e-1 (test_matmul.py:17-22,86-88)."""
+    rng = philox(40)
+    a = rng.uniform(0, 1, (1024, 64)).astype(np.float16)
+    b = rng.uniform(0, 1, (64, 512)).astype(np.float16)
+    got = run_matmul(hm, a, b, N_ROWS=1024, N_COLUMNS=512, N_INNER=64, enableMultiThreading=True,
+                     enableVTCMTiling=True, enableConvertToHexagonmem=True, enableHexagonmemCopyToDMA=True)
+    ref = a.astype(np.float32) @ b.astype(np.float32)
+    assert np.abs(got.astype(np.float32) - ref).max() <= 2e-1
+    assert max_abs_rel(got, oracle.gemm_f16(a, b)) <= TOL_GEMM
+
+
+@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("mnk", [(128, 256, 64), (128, 64, 128), (5, 8, 8), (129, 264, 72),
+                                 (300, 520, 200), (256, 256, 4096), (1000, 1000, 1000),
+                                 (64, 2048, 512), (2048, 64, 320)])
+def test_tensor_core_variants_edge_shapes(hm, oracle, variant, mnk):
+    m, n, k = mnk
+    rng = philox(41)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float16)
+    assert hm.gemm_variant_verdict(variant, m, n, k) == "ok"
+    assert max_abs_rel(run_matmul(hm, a, b, variant), oracle.gemm_f16(a, b)) <= TOL_GEMM
+
+
+@pytest.mark.parametrize("mnk", [(1, 64, 64), (4, 32, 32), (33, 45, 70), (31, 33, 1), (64, 63, 64),
+                                 (127, 129, 130), (2, 11008, 512)])
+def test_shapes_the_engine_refuses_take_the_vector_path(hm, oracle, mnk):
+    m, n, k = mnk
+    rng = philox(42)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float16)
+    assert hm.gemm_explain(m, n, k)["plan"] == "cuda-core"
+    assert max_abs_rel(run_matmul(hm, a, b), oracle.gemm_f16(a, b)) <= TOL_GEMM
+
+
+def test_strided_views_and_device_tensors(hm, oracle, cuda):
+    rng = philox(43)
+    big_a = cuda.from_numpy(rng.uniform(-1, 1, (256, 640)).astype(np.float16)).cuda()
+    big_b = cuda.from_numpy(rng.uniform(-1, 1, (512, 1024)).astype(np.float16)).cuda()
+    big_c = cuda.full((256, 2048), 3.0, dtype=cuda.float16, device="cuda")
+    a, b, c = big_a[:, :512], big_b[:, 256:768], big_c[:, 512:1024]
+    hm.matmul[(1,)](a, b, c)
+    want = oracle.gemm_f16(np.ascontiguousarray(a.cpu().numpy()), np.ascontiguousarray(b.cpu().numpy()))
+    assert max_abs_rel(c.cpu().numpy(), want) <= TOL_GEMM
+    assert float((big_c[:, :512] - 3).abs().max()) == 0 and float((big_c[:, 1024:] - 3).abs().max()) == 0
+
+
+@pytest.mark.parametrize("block_k", [32, 64, 128])
+def test_klooped_matmul(hm, oracle, block_k):
+    """256x256x512 K-looped (test_matmul_kloop.py:66-68): fp16 read-out per segment."""
+    rng = philox(44)
+    a = rng.uniform(-1, 1, (256, 512)).astype(np.float16)
+    b = rng.uniform(-1, 1, (512, 256)).astype(np.float16)
+    got = run_matmul(hm, a, b, kernel=hm.klooped_matmul, BLOCK_K=block_k)
+    want = oracle.gemm_f16(a, b, block_k=block_k)
+    assert max_abs_rel(got, want) <= TOL_GEMM
+    assert (got.view(np.uint16) != want.view(np.uint16)).mean() < 0.05
+
+
+@pytest.mark.parametrize("variant", [SIMT, 0])
+def test_f32_readout_with_residual(hm, oracle, variant):
+    rng = philox(45)
+    a = rng.uniform(-1, 1, (256, 192)).astype(np.float16)
+    b = rng.uniform(-1, 1, (192, 384)).astype(np.float16)
+    r = rng.normal(0, 1, (256, 384)).astype(np.float32)
+    hm.set_option("gemmVariant", variant)
+    try:
+        c = np.zeros((256, 384), np.float32)
+        hm.matmul_f32out(a, b, c)
+        assert max_abs_rel(c, oracle.gemm_f16_f32out(a, b)) <= TOL_GEMM
+        # the read-out is an fp16 image widened: every value is exactly an fp16 number
+        assert np.array_equal(c, c.astype(np.float16).astype(np.float32))
+        hm.matmul_f32out(a, b, c, r)
+        assert max_abs_rel(c, oracle.gemm_f16_f32out(a, b, r)) <= TOL_GEMM
+    finally:
+        hm.set_option("gemmVariant", -1)
+
+
+@pytest.mark.parametrize("mnk", [(33, 45, 70), (256, 512, 1024), (1, 8, 4096)])
+def test_int8_accumulation_bit_exact(hm, oracle, mnk):
+    m, n, k = mnk
+    rng = philox(46)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    c = np.zeros((m, n), np.int32)
+    hm.matmul_i8[(1,)](a, b, c)
+    assert np.array_equal(c, oracle.gemm_i8_i32(a, b))
+
+
+def test_empty_and_bad_shapes(hm):
+    a = np.zeros((0, 64), np.float16)
+    hm.matmul[(1,)](a, np.zeros((64, 32), np.float16), np.zeros((0, 32), np.float16))
+    with pytest.raises(hm.B200Error):
+        hm.matmul[(1,)](np.zeros((8, 16), np.float16), np.zeros((8, 16), np.float16), np.zeros((8, 16), np.float16))
+
+
+def test_linearity_at_scale(hm, cuda):
+    """Size-independent property at a large shape: (2A)·B == 2(A·B) exactly in fp16."""
+    g = cuda.Generator(device="cuda").manual_seed(4)
+    a = (cuda.rand((2048, 4096), generator=g, device="cuda") * 2 - 1).half()
+    b = (cuda.rand((4096, 4096), generator=g, device="cuda") * 2 - 1).half()
+    c1 = cuda.empty((2048, 4096), dtype=cuda.float16, device="cuda")
+    c2 = cuda.empty_like(c1)
+    hm.matmul[(1,)](a, b, c1)
+    hm.matmul[(1,)](a * 2, b, c2)
+    assert hm.device_status() == 0
+    assert bool((c1 * 2 == c2).all())
+
+
+def test_autotune_on_device(hm):
+    hm.autotune_cache_clear()
+    rep = hm.gemm_autotune(1024, 1024, 1024)
+    assert rep["round_verdict"] == "valid", rep
+    assert rep["measured_configs"] == len(hm.gemm_variants()), rep
+    assert rep["champion_variant"] >= 0 and rep["unmeasured"] == []
+    assert hm.gemm_explain(1024, 1024, 1024)["reason"] == "autotune cache"
+    again = hm.gemm_autotune(1024, 1024, 1024)
+    assert again.get("cache_hit") is True
+    hm.autotune_cache_clear()

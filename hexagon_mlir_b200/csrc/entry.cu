@@ -84,9 +84,10 @@ int view2(const char *what, int64_t rank, const B200MemRef2D *d, size_t esz, Vie
     return set_error(B200MLIR_ERR_BAD_ARG, "%s: expected a rank-2 memref descriptor (got rank %lld)", what, (long long)rank);
   if (d->sizes[0] < 0 || d->sizes[1] < 0)
     return set_error(B200MLIR_ERR_BAD_ARG, "%s: negative extent", what);
-  if (d->sizes[1] > 1 && d->strides[1] != 1)
+  const bool empty = d->sizes[0] == 0 || d->sizes[1] == 0;
+  if (!empty && d->sizes[1] > 1 && d->strides[1] != 1)
     return set_error(B200MLIR_ERR_BAD_ARG, "%s: innermost stride must be 1 (dense rows)", what);
-  if (d->sizes[0] > 1 && d->strides[0] < d->sizes[1])
+  if (!empty && d->sizes[0] > 1 && d->strides[0] < d->sizes[1])
     return set_error(B200MLIR_ERR_BAD_ARG, "%s: row stride %lld below row length %lld", what,
                      (long long)d->strides[0], (long long)d->sizes[1]);
   if (!d->aligned && d->sizes[0] * d->sizes[1] != 0)

@@ -147,7 +147,11 @@ def test_linearity_at_scale(hm, cuda):
     hm.matmul[(1,)](a, b, c1)
     hm.matmul[(1,)](a * 2, b, c2)
     assert hm.device_status() == 0
-    assert bool((c1 * 2 == c2).all())
+    # scaling by two commutes with every rounding except where fp16(A·B) is subnormal
+    normal = c1.abs() >= 2.0 ** -14
+    assert bool(((c1 * 2 == c2) | ~normal).all())
+    assert float(((c1.float() * 2 - c2.float()).abs() * (~normal)).max()) <= 2.0 ** -23
+    assert float(normal.float().mean()) > 0.99
 
 
 def test_autotune_on_device(hm):

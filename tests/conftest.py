@@ -15,9 +15,11 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def hm():
     """The product package; building it first if the shared library is missing."""
-    from hexagon_mlir_b200 import build
-    if not os.path.exists(build.LIB):
-        build.build_library()
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("b200mlir_build", os.path.join(ROOT, "hexagon_mlir_b200", "build.py"))
+    build = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(build)
+    build.build_library()  # no-op when the library is newer than its sources
     import hexagon_mlir_b200
     return hexagon_mlir_b200
 

@@ -96,6 +96,8 @@ _SIGNATURES = {
     "hexagon_runtime_dma_wait": (None, [ctypes.c_uint32]),
     "b200mlir_w8a16_register_weight": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_int]),
     "b200mlir_w8a16_unregister_weight": (c_int, [c_void_p]),
+    "b200mlir_w8a16_matmul_static_scratch": (c_int, [c_void_p, c_i64, c_void_p, c_void_p, c_void_p, c_i64,
+                                                     c_i64, c_i64, c_i64, c_void_p]),
     "b200mlir_pack_weight_f16": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64]),
     "b200mlir_pack_act_f16": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64]),
     "b200mlir_unpack_acc_f16": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64]),

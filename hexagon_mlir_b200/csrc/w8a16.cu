@@ -298,3 +298,106 @@ int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, in
 }
 
 }  // namespace b200
+
+// ---- w8a16 for callers that cannot allocate ----------------------------------------------
+// Some hosts hand this library a fixed set of device buffers and forbid any
+// further allocation on their thread: a serving loop that has already carved
+// up the whole device, a plugin running inside another runtime's memory
+// budget, code between stream-capture begin and end.  For them the fp32
+// partial-sum scratch of the decode GEMM lives in the library image itself.
+namespace b200 {
+namespace {
+
+constexpr int kStaticMaxRows = 64;
+constexpr int kStaticMaxCols = 16384;
+// 4 MiB per GPU that loads the library, held until the process exits.
+static __device__ __align__(256) float g_static_scratch[kStaticMaxRows * kStaticMaxCols];
+
+struct StaticDevice {
+  bool ready = false;
+  float *scratch = nullptr;  // device address of g_static_scratch on this device
+  int sm_count = 0;
+};
+constexpr int kMaxDevices = 64;
+StaticDevice g_static_dev[kMaxDevices];
+std::mutex g_static_mu;
+
+// Once per device, with that device current.  In host code the array's name is
+// only a handle; the address a kernel can use comes from cudaGetSymbolAddress.
+int static_device_setup(int dev, StaticDevice **out) {
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  StaticDevice &d = g_static_dev[dev];
+  if (!d.ready) {
+    float *p = nullptr;
+    B200_CUDA(cudaGetSymbolAddress((void **)&p, g_static_scratch));
+    int sms = 0;
+    B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(1 * 16 * A_PITCH * sizeof(__half))));
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(2 * 16 * A_PITCH * sizeof(__half))));
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   (int)(4 * 16 * A_PITCH * sizeof(__half))));
+    d.scratch = p;
+    d.sm_count = sms;
+    d.ready = true;
+  }
+  *out = &d;
+  return 0;
+}
+
+template <int MT>
+void launch_stream_static(cudaStream_t s, int sm_count, const __half *a, int64_t lda, const uint4 *image,
+                          float *ws, int m, int n, int k) {
+  const int ksteps = (k + 15) / 16;
+  const int n_strips = (n + 31) / 32;
+  const int n_blocks = (n_strips + WARPS - 1) / WARPS;
+  const size_t smem = (size_t)MT * 16 * A_PITCH * sizeof(__half);
+  int64_t total = (int64_t)n_blocks * ksteps;
+  int grid = sm_count * 2;
+  if (grid > total) grid = (int)total;
+  w8a16_stream_kernel<MT><<<grid, WARPS * 32, smem, s>>>(a, lda, image, ws, m, n, k, ksteps, n_blocks, n_strips);
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int b200mlir_w8a16_matmul_static_scratch(const void *a, int64_t lda, const void *image,
+                                                    const void *scales, void *c, int64_t ldc, int64_t m,
+                                                    int64_t n, int64_t k, void *cuda_stream) {
+  using namespace b200;
+  clear_error();
+  if (!a || !image || !scales || !c)
+    return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 static-scratch: null pointer");
+  if (m < 1 || n < 1 || k < 1)
+    return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 static-scratch: empty shape");
+  if (m > kStaticMaxRows || n > kStaticMaxCols)
+    return set_error(B200MLIR_ERR_UNSUPPORTED,
+                     "w8a16 static-scratch: M=%lld, N=%lld exceed the built-in scratch (M <= %d, N <= %d); "
+                     "use w8a16_matmul, which allocates its scratch",
+                     (long long)m, (long long)n, kStaticMaxRows, kStaticMaxCols);
+  if (((uintptr_t)a & 15u) || ((uintptr_t)image & 15u) || lda % 8 || k % 8 || lda < k || ldc < n)
+    return set_error(B200MLIR_ERR_BAD_ARG,
+                     "w8a16 static-scratch: A and the image must be 16-byte aligned, K and lda multiples of 8");
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return set_error(B200MLIR_ERR_BAD_ARG, "device index %d out of range", dev);
+  StaticDevice *d = nullptr;
+  B200_TRY(static_device_setup(dev, &d));
+  cudaStream_t s = (cudaStream_t)cuda_stream;
+  float *ws = d->scratch;
+  // the array keeps whatever the previous call left: the partial sums must start at zero
+  B200_CUDA(cudaMemsetAsync(ws, 0, (size_t)m * (size_t)n * sizeof(float), s));
+  const __half *ap = (const __half *)a;
+  const uint4 *img = (const uint4 *)image;
+  if (m <= 16) launch_stream_static<1>(s, d->sm_count, ap, lda, img, ws, (int)m, (int)n, (int)k);
+  else if (m <= 32) launch_stream_static<2>(s, d->sm_count, ap, lda, img, ws, (int)m, (int)n, (int)k);
+  else launch_stream_static<4>(s, d->sm_count, ap, lda, img, ws, (int)m, (int)n, (int)k);
+  B200_TRY(check_launch("w8a16_stream(static scratch)"));
+  int64_t total = m * n;
+  int64_t blocks = (total + 255) / 256;
+  int64_t cap = (int64_t)d->sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  w8a16_finalize_kernel<<<(unsigned)blocks, 256, 0, s>>>(ws, (const __half *)scales, (__half *)c, (int)m, (int)n, ldc);
+  return check_launch("w8a16_finalize(static scratch)");
+}

@@ -231,6 +231,38 @@ B200_API void hexagon_runtime_dma_wait(uint32_t token);
 B200_API int b200mlir_w8a16_register_weight(const void *wq, const void *scales, int64_t k,
                                             int64_t n, int l2_persist);
 B200_API int b200mlir_w8a16_unregister_weight(const void *wq);
+/* w8a16 GEMM that never allocates.  It has no counterpart in the reference.
+ *
+ * Who needs it: a host that may not call cudaMalloc where it calls this
+ * library — an inference server that reserved all device memory up front and
+ * treats any later allocation as a fault, a plugin living inside another
+ * runtime's memory pool, or code on a latency-critical thread where the
+ * implicit synchronisation of cudaMalloc/cudaFree is not acceptable.
+ * w8a16_matmul keeps its fp32 partial-sum scratch in a buffer it allocates and
+ * grows; here that scratch is a fixed 4 MiB array inside the library image
+ * (every GPU that loads the library holds it until the process exits).
+ *
+ * Limits: 1 <= M <= 64 and 1 <= N <= 16384 (M*N floats of scratch); larger
+ * shapes are rejected with B200MLIR_ERR_UNSUPPORTED.  K and lda multiples of
+ * 8; `a` and `image` 16-byte aligned.  All pointers are DEVICE pointers owned
+ * by the caller; `cuda_stream` is the stream to enqueue on (NULL = default).
+ *
+ * `image` is the pre-swizzled weight, (ceil(N/32) * ceil(K/16) * 512) bytes
+ * laid out [strip = n/32][kstep = k/16][lane 0..31][16 bytes]: with g = lane/4,
+ * t = lane%4, byte 4*j + e (j, e in 0..3) holds q[k][n] + 128 for
+ * n = 32*strip + 8*j + g and k = 16*kstep + {2t, 2t+1, 2t+8, 2t+9}[e]; positions
+ * outside [K, N] hold 128.  `scales` is fp16 [N]; C = f16(sum * scales[n]).
+ *
+ * The first call on each device looks up the array's device address and sets
+ * kernel attributes; make that first call before any stream capture begins.
+ * Every call uses the same array: it is cleared at the start of each call, and
+ * two calls that overlap on the GPU (different streams, or two threads) race
+ * on it and corrupt each other's sums — serialise them.
+ * Returns 0 or an error code (message through b200mlir_last_error). */
+B200_API int b200mlir_w8a16_matmul_static_scratch(const void *a, int64_t lda, const void *image,
+                                                  const void *scales, void *c, int64_t ldc,
+                                                  int64_t m, int64_t n, int64_t k,
+                                                  void *cuda_stream);
 /* Row-major fp16 [K,N] -> the reference's weight tile image [Nt,Kt,16,32,2]
  * and back-compatible activation/accumulator images (device or host pointers).
  * (hmx_pack_weight_f16_bulk / hmx_pack_act_f16_bulk / hmx_unpack_acc_f16_bulk,

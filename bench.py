@@ -209,16 +209,22 @@ def graph_timed(torch, fn, reps, inner):
     return e0.elapsed_time(e1) / (reps * inner)
 
 
-def extras_single_gpu(torch, hm, peaks):
-    """The other configs of the metric, one GPU.  Each entry: algorithmic work / device time."""
+def extras_single_gpu(torch, hm, peaks, only=None):
+    """The other configs of the metric, one GPU.  Each entry: algorithmic work / device time.
+    `only` restricts the run to the cases whose name starts with it (profiling captures)."""
     out = {}
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
+
+    def want(name):
+        return only is None or name.startswith(only)
 
     def rand_h(shape, lo=-1.0, hi=1.0):
         return (torch.rand(shape, generator=g, device=dev) * (hi - lo) + lo).half()
 
     for n in (1024, 4096):
+        if not want(f"gemm_f16_{n}"):
+            continue
         # rotate over enough operand sets to exceed L2 between launches
         sets = max(2, int(np.ceil(3 * 126e6 / (3 * n * n * 2))))
         sets = min(sets, 24)
@@ -236,6 +242,8 @@ def extras_single_gpu(torch, hm, peaks):
         out[f"gemm_f16_{n}^3"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                                   "variant": hm.gemm_explain(n, n, n)["name"]}
         del A, B, C
+    if only is not None and not any(want(x) for x in ("softmax", "rmsnorm", "swiglu", "w8a16")):
+        return out
     # C2 softmax [4096,1024]: 16 MiB in + out per launch; 12 buffer pairs (201 MB) rotate past L2
     sets = 12
     X = [(torch.randn((4096, 1024), generator=g, device=dev) * 3).half() for _ in range(sets)]
@@ -352,6 +360,10 @@ def run_product_arm(args):
     if multi:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     peaks, peak_kind = load_peaks()
+    if args.case:
+        # one small case of `extra` alone (what the ncu captures under profiles/ run)
+        print(json.dumps({"case": args.case, "result": extras_single_gpu(torch, hm, peaks, only=args.case)}))
+        return 0
 
     # inputs resident in HBM: A replicated, this rank's column block of B and C
     n_lo, n_hi = rank * N // world, (rank + 1) * N // world
@@ -445,6 +457,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--case", default="", help="run one case of `extra` only: gemm_f16_1024, gemm_f16_4096, "
+                                               "softmax (the row kernels and w8a16 together)")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup

@@ -141,6 +141,10 @@ struct W8A16Weight {
 int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
 int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
                  int64_t ldc);
+// w8a16_decode.cu
+int w8a16_build_block_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
+int launch_w8a16_decode(const __half *a, const void *block_image, const __half *scales_dev, int64_t k,
+                        int64_t n, __half *c, int64_t m, int64_t lda, int64_t ldc);
 
 // dispatch.cpp
 int gemm_dispatch(const GemmArgs &g);  // picks a variant (option / cache / heuristic) and launches

@@ -69,38 +69,44 @@ softmax_f16_kernel(const __half *__restrict__ x, __half *__restrict__ y, int64_t
     int idx = i * TPR + lane;
     if (idx < nvec) v[i].u = __ldg(xr + idx);
   }
-  // 1. running max in f16 (softmax.md:167-177)
-  float m = -INFINITY;
+  // 1. running max in f16 (softmax.md:167-177), two lanes per instruction
+  __half2 m2 = __float2half2_rn(-INFINITY);
 #pragma unroll
   for (int i = 0; i < VPL; ++i)
     if (i * TPR + lane < nvec) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) m = fmaxf(m, __half2float(v[i].h[j]));
+      for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, v[i].h2[j]);
     }
+  float m = fmaxf(__low2float(m2), __high2float(m2));
   m = group_reduce<TPR, true>(m, scratch);
-  const __half mh = __float2half_rn(m);  // exact: m is an f16 value
+  m2 = __float2half2_rn(m);  // exact: m is an f16 value
   // 2. e = f16(exp(f32(x - m))) with the subtract in f16; 3. s = sum f32(e)
   float s = 0.0f;
 #pragma unroll
   for (int i = 0; i < VPL; ++i)
     if (i * TPR + lane < nvec) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        __half z = __hsub(v[i].h[j], mh);
-        __half e = __float2half_rn(__expf(__half2float(z)));
-        v[i].h[j] = e;
-        s += __half2float(e);
+      for (int j = 0; j < 4; ++j) {
+        const float2 z = __half22float2(__hsub2(v[i].h2[j], m2));
+        const __half2 e = __floats2half2_rn(__expf(z.x), __expf(z.y));
+        v[i].h2[j] = e;
+        const float2 ef = __half22float2(e);
+        s += ef.x + ef.y;
       }
     }
   s = group_reduce<TPR, false>(s, scratch);
-  // 4. y = f16(f32(e) / s)
+  // 4. y = f16(f32(e) / s), as a multiply by the row's reciprocal
+  //    (qcom_hexagon_backend/lib/Transforms/DivToMulOptimizationPass.cpp:9-18)
+  const float inv = __frcp_rn(s);
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     int idx = i * TPR + lane;
     if (idx < nvec) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        v[i].h[j] = __float2half_rn(__fdividef(__half2float(v[i].h[j]), s));
+      for (int j = 0; j < 4; ++j) {
+        const float2 ef = __half22float2(v[i].h2[j]);
+        v[i].h2[j] = __floats2half2_rn(ef.x * inv, ef.y * inv);
+      }
       yr[idx] = v[i].u;
     }
   }

@@ -57,7 +57,10 @@ __device__ __forceinline__ uint32_t dq2(uint32_t word, uint32_t selector) {
 }
 
 // MT = number of 16-row tiles of A (M <= 16*MT).
-template <int MT>
+// BLOCKED selects the image layout: false = strip-major [strip][kstep][lane],
+// true = the resident blocked image [n/256][k/64][strip 0..7][kstep 0..3][lane]
+// (w8a16_decode.cu), where `ksteps` counts the padded k16 steps (4 per chunk).
+template <int MT, bool BLOCKED>
 __global__ void __launch_bounds__(WARPS * 32, MT >= 4 ? 1 : 2)
 w8a16_stream_kernel(const __half *__restrict__ A, int64_t lda, const uint4 *__restrict__ image,
                     float *__restrict__ ws, int M, int N, int K, int ksteps, int n_blocks,
@@ -100,7 +103,13 @@ w8a16_stream_kernel(const __half *__restrict__ A, int64_t lda, const uint4 *__re
 #pragma unroll
           for (int e = 0; e < 4; ++e) acc[m][j][e] = 0.0f;
 
-      const uint4 *wp = image + ((int64_t)strip * ksteps + ks0) * 32 + lane;
+      // address of this lane's 16 bytes for local step s (global k-step ks0 + s)
+      auto wptr = [&](int s) -> const uint4 * {
+        const int ks = ks0 + s;
+        if (BLOCKED)
+          return image + ((((int64_t)(strip >> 3) * (ksteps >> 2) + (ks >> 2)) * 8 + (strip & 7)) * 4 + (ks & 3)) * 32 + lane;
+        return image + ((int64_t)strip * ksteps + ks) * 32 + lane;
+      };
       // ldmatrix source row/col of this lane inside a 16x16 A tile
       const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
       const int lcol = (lane >> 4) * 8;
@@ -111,7 +120,7 @@ w8a16_stream_kernel(const __half *__restrict__ A, int64_t lda, const uint4 *__re
       uint4 wbuf[PF];
 #pragma unroll
       for (int i = 0; i < PF; ++i)
-        if (i < nsteps) wbuf[i] = __ldg(wp + (int64_t)i * 32);
+        if (i < nsteps) wbuf[i] = __ldg(wptr(i));
 
       for (int s0 = 0; s0 < nsteps; s0 += PF) {
 #pragma unroll
@@ -119,7 +128,7 @@ w8a16_stream_kernel(const __half *__restrict__ A, int64_t lda, const uint4 *__re
           const int s = s0 + i;
           if (s >= nsteps) break;
           const uint4 w = wbuf[i];
-          if (s + PF < nsteps) wbuf[i] = __ldg(wp + (int64_t)(s + PF) * 32);
+          if (s + PF < nsteps) wbuf[i] = __ldg(wptr(s + PF));
           const uint32_t words[4] = {w.x, w.y, w.z, w.w};
           uint32_t b[4][2];
 #pragma unroll
@@ -174,97 +183,10 @@ w8a16_finalize_kernel(float *__restrict__ ws, const __half *__restrict__ scales,
   }
 }
 
-// row-major int8 [K,N] -> resident image (one 16-byte chunk per thread)
-__global__ void __launch_bounds__(256)
-w8a16_swizzle_kernel(const int8_t *__restrict__ wq, uint4 *__restrict__ image, int K, int N,
-                     int ksteps, int n_strips) {
-  const int64_t total = (int64_t)n_strips * ksteps * 32;
-  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * 256) {
-    const int lane = (int)(i & 31);
-    const int64_t sk = i >> 5;
-    const int ks = (int)(sk % ksteps);
-    const int strip = (int)(sk / ksteps);
-    const int g = lane >> 2, t = lane & 3;
-    uint32_t words[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = strip * 32 + j * 8 + g;
-      const int kk[4] = {2 * t, 2 * t + 1, 2 * t + 8, 2 * t + 9};
-      uint32_t w = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int k = ks * 16 + kk[e];
-        int q = (n < N && k < K) ? (int)wq[(int64_t)k * N + n] : 0;
-        w |= (uint32_t)((q + 128) & 0xff) << (8 * e);
-      }
-      words[j] = w;
-    }
-    image[i] = make_uint4(words[0], words[1], words[2], words[3]);
-  }
-}
-
-float *g_ws = nullptr;  // fp32 scratch, kept zero between calls
-size_t g_ws_elems = 0;
-
-int ensure_ws(size_t elems) {
-  if (elems <= g_ws_elems) return 0;
-  if (g_ws) {
-    B200_CUDA(cudaStreamSynchronize(ctx().stream));
-    B200_CUDA(cudaFree(g_ws));
-    g_ws = nullptr;
-    g_ws_elems = 0;
-  }
-  B200_CUDA(cudaMalloc(&g_ws, elems * sizeof(float)));
-  B200_CUDA(cudaMemsetAsync(g_ws, 0, elems * sizeof(float), ctx().stream));
-  g_ws_elems = elems;
-  return 0;
-}
-
-template <int MT>
-int launch_stream(const __half *a, int64_t lda, const W8A16Weight &w, float *ws, int m) {
-  Context &c = ctx();
-  const int ksteps = (int)((w.k + 15) / 16);
-  const int n_strips = (int)((w.n + 31) / 32);
-  const int n_blocks = (n_strips + WARPS - 1) / WARPS;
-  const size_t smem = (size_t)MT * 16 * A_PITCH * sizeof(__half);
-  auto kern = w8a16_stream_kernel<MT>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_set = true;
-  }
-  int64_t total = (int64_t)n_blocks * ksteps;
-  int grid = c.sm_count * 2;
-  if (grid > total) grid = (int)total;
-  kern<<<grid, WARPS * 32, smem, c.stream>>>(a, lda, (const uint4 *)w.image, ws, m, (int)w.n,
-                                             (int)w.k, ksteps, n_blocks, n_strips);
-  return check_launch("w8a16_stream");
-}
-
 }  // namespace
 
 int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes) {
-  B200_TRY(ensure_ready());
-  const int ksteps = (int)((k + 15) / 16);
-  const int n_strips = (int)((n + 31) / 32);
-  const size_t sz = (size_t)n_strips * ksteps * 512;
-  void *img = nullptr;
-  B200_CUDA(cudaMalloc(&img, sz));
-  int64_t total = (int64_t)n_strips * ksteps * 32;
-  int64_t blocks = (total + 255) / 256;
-  int64_t cap = (int64_t)ctx().sm_count * 32;
-  if (blocks > cap) blocks = cap;
-  w8a16_swizzle_kernel<<<(unsigned)blocks, 256, 0, ctx().stream>>>(wq_dev, (uint4 *)img, (int)k,
-                                                                   (int)n, ksteps, n_strips);
-  int rc = check_launch("w8a16_swizzle");
-  if (rc) {
-    cudaFree(img);
-    return rc;
-  }
-  *image = img;
-  *bytes = sz;
-  return 0;
+  return w8a16_build_block_image(wq_dev, k, n, image, bytes);
 }
 
 int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
@@ -275,24 +197,11 @@ int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, in
     return set_error(B200MLIR_ERR_BAD_ARG,
                      "w8a16: activations must be 16-byte aligned with a row stride multiple of 8");
   if (w.k % 8) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16: K must be a multiple of 8");
-  Context &cx = ctx();
-  // Rows are processed in passes of at most 64 (four m16 tiles of accumulators per warp).
+  // Rows go through the tensor-core kernel in passes of at most 64.
   for (int64_t m0 = 0; m0 < m; m0 += 64) {
-    const int mp = (int)((m - m0) < 64 ? (m - m0) : 64);
-    B200_TRY(ensure_ws((size_t)64 * (size_t)w.n));
-    const __half *ap = a + m0 * lda;
-    int rc;
-    if (mp <= 16) rc = launch_stream<1>(ap, lda, w, g_ws, mp);
-    else if (mp <= 32) rc = launch_stream<2>(ap, lda, w, g_ws, mp);
-    else rc = launch_stream<4>(ap, lda, w, g_ws, mp);
-    B200_TRY(rc);
-    int64_t total = (int64_t)mp * w.n;
-    int64_t blocks = (total + 255) / 256;
-    int64_t cap = (int64_t)cx.sm_count * 8;
-    if (blocks > cap) blocks = cap;
-    w8a16_finalize_kernel<<<(unsigned)blocks, 256, 0, cx.stream>>>(
-        g_ws, (const __half *)w.scales_dev, c + m0 * ldc, mp, (int)w.n, ldc);
-    B200_TRY(check_launch("w8a16_finalize"));
+    const int64_t mp = (m - m0) < 64 ? (m - m0) : 64;
+    B200_TRY(launch_w8a16_decode(a + m0 * lda, w.image, (const __half *)w.scales_dev, w.k, w.n,
+                                 c + m0 * ldc, mp, lda, ldc));
   }
   return 0;
 }
@@ -332,11 +241,11 @@ int static_device_setup(int dev, StaticDevice **out) {
     B200_CUDA(cudaGetSymbolAddress((void **)&p, g_static_scratch));
     int sms = 0;
     B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(1 * 16 * A_PITCH * sizeof(__half))));
-    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(2 * 16 * A_PITCH * sizeof(__half))));
-    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(4 * 16 * A_PITCH * sizeof(__half))));
     d.scratch = p;
     d.sm_count = sms;
@@ -356,7 +265,7 @@ void launch_stream_static(cudaStream_t s, int sm_count, const __half *a, int64_t
   int64_t total = (int64_t)n_blocks * ksteps;
   int grid = sm_count * 2;
   if (grid > total) grid = (int)total;
-  w8a16_stream_kernel<MT><<<grid, WARPS * 32, smem, s>>>(a, lda, image, ws, m, n, k, ksteps, n_blocks, n_strips);
+  w8a16_stream_kernel<MT, false><<<grid, WARPS * 32, smem, s>>>(a, lda, image, ws, m, n, k, ksteps, n_blocks, n_strips);
 }
 
 }  // namespace

@@ -1,0 +1,85 @@
+"""Tensor-parallel MLP block and column-sharded GEMM on real GPUs (NCCL, one process per
+GPU).  Skipped when fewer than two devices are visible."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _problem():
+    rng = np.random.Generator(np.random.Philox(3))
+    t, d, f = 512, 1024, 2752
+    x = rng.normal(0, 1, (t, d)).astype(np.float16)
+    gain = np.ones(d, np.float16)
+    wg = rng.normal(0, 0.02, (d, f)).astype(np.float16)
+    wu = rng.normal(0, 0.02, (d, f)).astype(np.float16)
+    wd = rng.normal(0, 0.02, (f, d)).astype(np.float16)
+    return x, gain, wg, wu, wd
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    import hexagon_mlir_b200 as hm
+    from hexagon_mlir_b200 import tp
+    hm.init(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    x, gain, wg, wu, wd = _problem()
+    T = lambda a: torch.from_numpy(a).cuda()
+    block = tp.TensorParallelMLP(T(gain), tp.shard_columns(T(wg), rank, world), tp.shard_columns(T(wu), rank, world),
+                                 tp.shard_rows(T(wd), rank, world), eps=1e-6, group=dist.group.WORLD, chunks=4)
+    xt = T(x)
+    out = torch.zeros_like(xt)
+    for _ in range(2):
+        block(xt, out)
+    torch.cuda.synchronize()
+    status = hm.device_status()
+    lo, hi = tp.shard_bounds(wg.shape[1], rank, world)
+    cshard = torch.zeros((x.shape[0], hi - lo), dtype=torch.float16, device="cuda")
+    tp.ColumnShardedGemm(rank, world)(xt, tp.shard_columns(T(wg), rank, world), cshard)
+    torch.cuda.synchronize()
+    q.put((rank, status, out.cpu().numpy(), lo, hi, cshard.cpu().numpy()))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2])
+def test_tensor_parallel_mlp_on_gpus(oracle, cuda, world):
+    if cuda.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    x, gain, wg, wu, wd = _problem()
+    want = oracle.mlp(x, gain, wg, wu, wd, 1e-6).astype(np.float32)
+    full = np.zeros((x.shape[0], wg.shape[1]), np.float16)
+    for rank, status, out, lo, hi, cshard in results:
+        assert status == 0
+        err = np.abs(out.astype(np.float32) - want).max() / np.abs(want).max()
+        assert err <= 1e-2, (rank, err)
+        full[:, lo:hi] = cshard
+    assert np.array_equal(results[0][2], results[1][2])
+    ref = oracle.gemm_f16(x, wg).astype(np.float32)
+    assert np.abs(full.astype(np.float32) - ref).max() / np.abs(ref).max() <= 1e-2

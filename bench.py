@@ -336,10 +336,20 @@ def mlp_extra(torch, hm, dist, rank, world):
 
     def step():
         block(x, out)
+    mode = "eager"
+    if world > 1:
+        try:
+            block.captured(x, out)
+
+            def step():
+                block.captured(x, out)
+            mode = "cuda-graph"
+        except Exception as exc:  # capture of the collective is an optimisation, not a requirement
+            mode = f"eager ({type(exc).__name__})"
     ms = timed(torch, step, 20, 5, dist if world > 1 else None)
     flops = 6.0 * t * d * f
     return {"ms": ms, "tokens_per_s": t / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
-            "parallelism": f"tp{world}", "allreduce_bytes": t * d * 2 if world > 1 else 0}
+            "parallelism": f"tp{world}", "allreduce_bytes": t * d * 2 if world > 1 else 0, "launch": mode}
 
 
 def run_product_arm(args):

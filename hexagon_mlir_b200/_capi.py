@@ -11,7 +11,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200mlir.so")
+# B200MLIR_LIB names another build of the same library (e.g. an instrumented one)
+LIB_PATH = os.environ.get("B200MLIR_LIB") or os.path.join(_HERE, "libb200mlir.so")
 
 c_i64 = ctypes.c_int64
 c_int = ctypes.c_int

@@ -122,11 +122,15 @@ struct TcVariantInfo {
   const char *name;
   int bm, bn, bk, stages, cta_group;
   int smem_bytes, tmem_cols;
+  double model_eff;  // fraction of the tensor pipe this tiling sustained when measured
 };
 const TcVariantInfo &tc_variant_info(int v);
 // "ok" or a refusal reason for variant v on (m,n,k) with the given epilogue.
 const char *tc_variant_verdict(int v, const GemmArgs &g);
 int launch_gemm_tc(int v, const GemmArgs &g);
+// gemm_tcgen05_2cta.cu
+int launch_gemm_tc_pair(const GemmArgs &g);
+int pair_variant_smem_bytes();
 
 // w8a16.cu
 struct W8A16Weight {

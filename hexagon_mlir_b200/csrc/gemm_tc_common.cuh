@@ -1,0 +1,147 @@
+// Pieces shared by the 1-CTA and the 2-CTA tensor-core GEMM kernels: the kernel
+// parameter block, the tile walk, the fused epilogues and the tensor-map helper.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <mutex>
+
+#include "common.h"
+
+namespace b200 {
+namespace {
+
+constexpr int GROUP_M = 8;
+
+struct TcParams {
+  void *c;
+  const void *res;
+  int64_t ldc, ldres;
+  int m, n, k;
+  int m_blocks, n_blocks, num_tiles, k_blocks;
+  int *status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int &m_blk,
+                                            int &n_blk) {
+  const int per_group = GROUP_M * n_blocks;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int gsz = min(m_blocks - first_m, GROUP_M);
+  const int in_group = tile - group * per_group;
+  m_blk = first_m + in_group % gsz;
+  n_blk = in_group / gsz;
+}
+
+__device__ __forceinline__ __half silu_h(__half x) {
+  __half e = __float2half_rn(__expf(-__half2float(x)));
+  __half d = __float2half_rn(1.0f + __half2float(e));
+  return __float2half_rn(__fdividef(__half2float(x), __half2float(d)));
+}
+
+__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t *>(&h);
+}
+
+
+// One 32-column chunk of one accumulator row: r (and r2 for the SwiGLU pair) hold the
+// fp32 accumulators of columns [col0, col0+32) of `row`.
+template <int EPI>
+__device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], const uint32_t (&r2)[32], int row,
+                                                     int col0, const TcParams &p) {
+  if (EPI == EPI_F16 || EPI == EPI_F16_RES16 || EPI == EPI_SWIGLU) {
+    __half *cp = reinterpret_cast<__half *>(p.c) + (int64_t)row * p.ldc + col0;
+    const __half *rp = reinterpret_cast<const __half *>(p.res) + (int64_t)row * p.ldres + col0;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      if (col0 + v * 8 >= p.n) break;  // N is a multiple of 8
+      uint4 o;
+      uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+      if (EPI == EPI_F16) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          ow[j] = pack_h2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+      } else if (EPI == EPI_F16_RES16) {
+        // f16(f32(f16(acc)) + f32(res)): the engine reads out fp16, the residual is added wide
+        const uint4 rv = *reinterpret_cast<const uint4 *>(rp + v * 8);
+        const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 t = __half22float2(__floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]),
+                                                      __uint_as_float(r[v * 8 + 2 * j + 1])));
+          float2 rr = __half22float2(rh[j]);
+          ow[j] = pack_h2(t.x + rr.x, t.y + rr.y);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __half g0 = __float2half_rn(__uint_as_float(r[v * 8 + 2 * j]));
+          __half g1 = __float2half_rn(__uint_as_float(r[v * 8 + 2 * j + 1]));
+          __half u0 = __float2half_rn(__uint_as_float(r2[v * 8 + 2 * j]));
+          __half u1 = __float2half_rn(__uint_as_float(r2[v * 8 + 2 * j + 1]));
+          ow[j] = pack_h2(__half2float(silu_h(g0)) * __half2float(u0),
+                          __half2float(silu_h(g1)) * __half2float(u1));
+        }
+      }
+      *reinterpret_cast<uint4 *>(cp + v * 8) = o;
+    }
+  } else if (EPI == EPI_F32_RES) {
+    float *cp = reinterpret_cast<float *>(p.c) + (int64_t)row * p.ldc + col0;
+    const float *rp = reinterpret_cast<const float *>(p.res) + (int64_t)row * p.ldres + col0;
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      if (col0 + v * 4 >= p.n) break;  // N is a multiple of 8
+      float4 o;
+      float *of = reinterpret_cast<float *>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        of[j] = __half2float(__float2half_rn(__uint_as_float(r[v * 4 + j])));
+      if (p.res) {
+        const float4 rv = *reinterpret_cast<const float4 *>(rp + v * 4);
+        o.x += rv.x; o.y += rv.y; o.z += rv.z; o.w += rv.w;
+      }
+      *reinterpret_cast<float4 *>(cp + v * 4) = o;
+    }
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [outer, inner] with row pitch ld elements; box {box_inner, box_outer}.
+int make_map_2d(CUtensorMap *map, const void *base, CUtensorMapDataType dt, int elem_bytes,
+                int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return set_error(B200MLIR_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(B200MLIR_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+
+}  // namespace
+}  // namespace b200

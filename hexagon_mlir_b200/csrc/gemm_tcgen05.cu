@@ -23,6 +23,7 @@
 #include <unordered_map>
 
 #include "common.h"
+#include "gemm_tc_common.cuh"
 #include "ptx_sm100.cuh"
 
 namespace b200 {
@@ -34,39 +35,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;                   // 64 fp16 = one 128-byte swizzle row
 constexpr int A_STAGE_BYTES = BM * 128;  // 16 KiB
 constexpr int B_SLAB_BYTES = BK * 128;   // 64 k-rows x 64 n (128 B) = 8 KiB
-constexpr int GROUP_M = 8;
 constexpr int NUM_THREADS = 192;
-
-struct TcParams {
-  void *c;
-  const void *res;
-  int64_t ldc, ldres;
-  int m, n, k;
-  int m_blocks, n_blocks, num_tiles, k_blocks;
-  int *status;
-};
-
-__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int &m_blk,
-                                            int &n_blk) {
-  const int per_group = GROUP_M * n_blocks;
-  const int group = tile / per_group;
-  const int first_m = group * GROUP_M;
-  const int gsz = min(m_blocks - first_m, GROUP_M);
-  const int in_group = tile - group * per_group;
-  m_blk = first_m + in_group % gsz;
-  n_blk = in_group / gsz;
-}
-
-__device__ __forceinline__ __half silu_h(__half x) {
-  __half e = __float2half_rn(__expf(-__half2float(x)));
-  __half d = __float2half_rn(1.0f + __half2float(e));
-  return __float2half_rn(__fdividef(__half2float(x), __half2float(d)));
-}
-
-__device__ __forceinline__ uint32_t pack_h2(float a, float b) {
-  __half2 h = __floats2half2_rn(a, b);
-  return *reinterpret_cast<uint32_t *>(&h);
-}
 
 template <int BN_MMA, int STAGES, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -221,60 +190,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
         if (!row_ok || col0 >= p.n) continue;
-        if (EPI == EPI_F16 || EPI == EPI_F16_RES16 || EPI == EPI_SWIGLU) {
-          __half *cp = reinterpret_cast<__half *>(p.c) + (int64_t)row * p.ldc + col0;
-          const __half *rp = reinterpret_cast<const __half *>(p.res) + (int64_t)row * p.ldres + col0;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (col0 + v * 8 >= p.n) break;  // N is a multiple of 8
-            uint4 o;
-            uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
-            if (EPI == EPI_F16) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                ow[j] = pack_h2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
-            } else if (EPI == EPI_F16_RES16) {
-              // f16(f32(f16(acc)) + f32(res)): the engine reads out fp16, the residual is added wide
-              const uint4 rv = *reinterpret_cast<const uint4 *>(rp + v * 8);
-              const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 t = __half22float2(__floats2half2_rn(__uint_as_float(r[v * 8 + 2 * j]),
-                                                            __uint_as_float(r[v * 8 + 2 * j + 1])));
-                float2 rr = __half22float2(rh[j]);
-                ow[j] = pack_h2(t.x + rr.x, t.y + rr.y);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                __half g0 = __float2half_rn(__uint_as_float(r[v * 8 + 2 * j]));
-                __half g1 = __float2half_rn(__uint_as_float(r[v * 8 + 2 * j + 1]));
-                __half u0 = __float2half_rn(__uint_as_float(r2[v * 8 + 2 * j]));
-                __half u1 = __float2half_rn(__uint_as_float(r2[v * 8 + 2 * j + 1]));
-                ow[j] = pack_h2(__half2float(silu_h(g0)) * __half2float(u0),
-                                __half2float(silu_h(g1)) * __half2float(u1));
-              }
-            }
-            *reinterpret_cast<uint4 *>(cp + v * 8) = o;
-          }
-        } else if (EPI == EPI_F32_RES) {
-          float *cp = reinterpret_cast<float *>(p.c) + (int64_t)row * p.ldc + col0;
-          const float *rp = reinterpret_cast<const float *>(p.res) + (int64_t)row * p.ldres + col0;
-#pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            if (col0 + v * 4 >= p.n) break;  // N is a multiple of 8
-            float4 o;
-            float *of = reinterpret_cast<float *>(&o);
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              of[j] = __half2float(__float2half_rn(__uint_as_float(r[v * 4 + j])));
-            if (p.res) {
-              const float4 rv = *reinterpret_cast<const float4 *>(rp + v * 4);
-              o.x += rv.x; o.y += rv.y; o.z += rv.z; o.w += rv.w;
-            }
-            *reinterpret_cast<float4 *>(cp + v * 4) = o;
-          }
-        }
+        epilogue_store_chunk<EPI>(r, r2, row, col0, p);
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -303,42 +219,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
 // ---- host side ------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
-            cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  });
-  return fn;
-}
-
-// 2-D row-major tensor [outer, inner] with row pitch ld elements; box {box_inner, box_outer}.
-int make_map_2d(CUtensorMap *map, const void *base, CUtensorMapDataType dt, int elem_bytes,
-                int64_t inner, int64_t outer, int64_t ld, int box_inner, int box_outer) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return set_error(B200MLIR_ERR_NO_DEVICE, "cuTensorMapEncodeTiled is not available");
-  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS)
-    return set_error(B200MLIR_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return 0;
-}
-
 struct Variant {
   TcVariantInfo info;
 };
@@ -349,9 +229,11 @@ constexpr int smem_for(int bn_mma, int stages) {
 }
 
 const TcVariantInfo kVariants[] = {
-    {"tc128x256x64_s4", 128, 256, 64, 4, 1, smem_for(256, 4), 512},
-    {"tc128x128x64_s6", 128, 128, 64, 6, 1, smem_for(128, 6), 256},
-    {"tc128x64x64_s8", 128, 64, 64, 8, 1, smem_for(64, 8), 128},
+    {"tc128x256x64_s4", 128, 256, 64, 4, 1, smem_for(256, 4), 512, 0.75},
+    {"tc128x128x64_s6", 128, 128, 64, 6, 1, smem_for(128, 6), 256, 0.50},
+    {"tc128x64x64_s8", 128, 64, 64, 8, 1, smem_for(64, 8), 128, 0.30},
+    // a pair of CTAs per 256 x 256 tile (gemm_tcgen05_2cta.cu)
+    {"tc256x256x64_2cta_s6", 256, 256, 64, 6, 2, 6 * 32768 + 16 * 6 + 64 + 1024, 512, 0.85},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -449,6 +331,7 @@ int launch_gemm_tc(int v, const GemmArgs &g) {
     case 0: return launch_epi<256, 4>(g, vi);
     case 1: return launch_epi<128, 6>(g, vi);
     case 2: return launch_epi<64, 8>(g, vi);
+    case 3: return launch_gemm_tc_pair(g);
   }
   return set_error(B200MLIR_ERR_BAD_ARG, "no such gemm variant %d", v);
 }

@@ -1,0 +1,367 @@
+// fp16 GEMM, 2-CTA form: a pair of CTAs on two SMs (a cluster of 2) works on one
+// 256 x 256 output tile with tcgen05.mma.cta_group::2.
+//
+// Why: with one CTA per 128 x 256 tile every K=64 step pulls 48 KiB through the
+// L2 -> SM path and reads 12 KiB of shared memory per MMA; pairing two SMs halves
+// the B traffic of each — CTA r loads its own 128 rows of A and only its half
+// (128 columns) of B, and the tensor cores of both SMs read both halves.  No
+// TMA multicast is used anywhere: every CTA issues plain tiled loads (with the
+// cta_group::2 form, whose only effect is that the completion may be signalled
+// on the leader CTA's mbarrier).
+//
+// Roles per CTA (192 threads): warp 0 lane 0 = TMA producer for this CTA's
+// operands; warp 1 = TMEM owner, and in the leader CTA (cluster rank 0) lane 0
+// issues the MMAs for the pair; warps 2-5 = epilogue of this CTA's 128 rows.
+// Barriers: full[s] lives in the leader and counts both producers; empty[s] and
+// tmem_full[a] are signalled in both CTAs by a multicast tcgen05.commit;
+// tmem_empty[a] lives in the leader and counts the epilogue warps of both CTAs.
+#include <cstdlib>
+#include <cstring>
+
+#include "common.h"
+#include "gemm_tc_common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace b200 {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM2 = 128;                    // rows per CTA (256 per pair)
+constexpr int BK2 = 64;
+constexpr int A2_BYTES = BM2 * 128;         // 16 KiB
+constexpr int SLAB_BYTES = BK2 * 128;       // 64 k-rows x 64 n = 8 KiB
+constexpr int B2_BYTES = 2 * SLAB_BYTES;    // this CTA's 128 columns of B: 16 KiB
+constexpr int STAGE2_BYTES = A2_BYTES + B2_BYTES;
+constexpr int THREADS2 = 192;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `addr` (a shared::cta address here) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void remote_expect_tx(uint32_t cluster_bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void remote_arrive(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+// Tiled load into THIS CTA's shared memory; completion bytes go to `cluster_bar`,
+// which may be the leader CTA's barrier.  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t cluster_bar, int c0,
+                                                 int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far are done.
+__device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"(mask)
+      : "memory");
+}
+
+#ifdef G2_TRACE
+__device__ long long g2_trace_buf[2 * 6 * 64];
+#define TR2(role, i) do { if (pair == 1 && (i) < 64) trace_s[(role) * 64 + (i)] = clock64(); } while (0)
+#else
+#define TR2(role, i) do { } while (0)
+#endif
+
+// EPI_SWIGLU: the pair's MMA N = 256 is [gate 128 | up 128]; CTA 0 loads the Wg tile,
+// CTA 1 the Wu tile, and each CTA's accumulator rows hold both halves.
+template <int STAGES, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS2, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmB2, const TcParams p) {
+  constexpr int BN_MMA = 256;
+  constexpr int BN_OUT = (EPI == EPI_SWIGLU) ? 128 : 256;
+  constexpr int TMEM_COLS = 512;  // two accumulator stages of 256 columns
+  constexpr uint32_t IDESC = make_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, /*A K-major*/ 0,
+                                        /*B MN-major*/ 1, 256, BN_MMA);
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t ctrl = smem_base + STAGES * STAGE2_BYTES;
+  const uint32_t bar_full = ctrl;                       // STAGES (used in the leader)
+  const uint32_t bar_empty = ctrl + 8 * STAGES;         // STAGES (both CTAs)
+  const uint32_t bar_tfull = ctrl + 16 * STAGES;        // 2 (both CTAs)
+  const uint32_t bar_tempty = ctrl + 16 * STAGES + 16;  // 2 (used in the leader)
+  const uint32_t tmem_slot = ctrl + 16 * STAGES + 32;
+  uint8_t *ctrl_gen = smem_raw + (ctrl - smem_u32(smem_raw));
+  volatile uint32_t *tmem_slot_gen = reinterpret_cast<volatile uint32_t *>(ctrl_gen + 16 * STAGES + 32);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_gen + 16 * STAGES + 36);
+
+#ifdef G2_TRACE
+  __shared__ long long trace_s[6 * 64];
+#endif
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 2);   // one arrive.expect_tx per CTA of the pair
+      mbar_init(bar_empty + 8 * s, 1);  // the multicast commit
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar_tfull + 8 * s, 1);
+      mbar_init(bar_tempty + 8 * s, 8);  // four epilogue warps in each CTA
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (EPI == EPI_SWIGLU) tma_prefetch_desc(&tmB2);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc_pair(tmem_slot, TMEM_COLS);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();  // the peer's barriers exist before anything is signalled on them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_gen;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: this CTA's 128 rows of A and 128 columns of B ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+        int m_blk, n_blk;
+        tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
+        const int m0 = m_blk * 256 + (int)rank * BM2;
+        const int n0 = n_blk * BN_OUT;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (tile == pair) TR2(0, kb);
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 31, tile)) {
+            ok = false;
+            break;
+          }
+          if (tile == pair) TR2(1, kb);
+          const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);  // the leader's barrier
+          const uint32_t sa = smem_base + stage * STAGE2_BYTES;
+          const uint32_t sb = sa + A2_BYTES;
+          remote_expect_tx(full, STAGE2_BYTES);
+          tma_load_2d_pair(sa, &tmA, full, kb * BK2, m0);
+          if (EPI == EPI_SWIGLU) {
+            const CUtensorMap *mb = leader ? &tmB : &tmB2;  // gate half / up half
+            tma_load_2d_pair(sb, mb, full, n0, kb * BK2);
+            tma_load_2d_pair(sb + SLAB_BYTES, mb, full, n0 + 64, kb * BK2);
+          } else {
+            const int nb = n0 + (int)rank * 128;
+            tma_load_2d_pair(sb, &tmB, full, nb, kb * BK2);
+            tma_load_2d_pair(sb + SLAB_BYTES, &tmB, full, nb + 64, kb * BK2);
+          }
+          if (tile == pair) TR2(2, kb);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 32, tile)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_MMA);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (tile == pair) TR2(3, kb);
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 33, tile)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          if (tile == pair) TR2(4, kb);
+          const uint32_t sa = smem_base + stage * STAGE2_BYTES;
+          const uint32_t sb = sa + A2_BYTES;
+          const uint64_t adesc = smem_desc_sw128(sa, 16, 1024);
+          const uint64_t bdesc = smem_desc_sw128(sb, SLAB_BYTES, 1024);
+#pragma unroll
+          for (int k = 0; k < BK2 / 16; ++k)
+            mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), IDESC,
+                         (kb | k) != 0 ? 1u : 0u);
+          mma_commit_pair(bar_empty + 8 * stage);  // both producers may refill the stage
+          if (tile == pair) TR2(5, kb);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        mma_commit_pair(bar_tfull + 8 * acc);  // accumulators complete in both CTAs
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5): this CTA's 128 rows ----------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
+      int m_blk, n_blk;
+      tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
+      const int m0 = m_blk * 256 + (int)rank * BM2, n0 = n_blk * BN_OUT;
+      bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 34, tile);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.m;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA);
+#pragma unroll 1
+      for (int c = 0; c < BN_OUT / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        uint32_t r2[32];
+        if (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + BN_OUT + c * 32, r2);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (!row_ok || col0 >= p.n) continue;
+        epilogue_store_chunk<EPI>(r, r2, row, col0, p);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) remote_arrive(map_to_cta(bar_tempty + 8 * acc, 0));  // the leader's barrier
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before_sync();
+  __syncthreads();
+  // Neither CTA may leave (or free TMEM) while the other can still signal its
+  // barriers or have MMAs of the pair in flight.
+  if (warp == 1 && *abort_flag)
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+  cluster_sync();
+#ifdef G2_TRACE
+  if (pair == 1) for (int i = threadIdx.x; i < 6 * 64; i += blockDim.x) g2_trace_buf[rank * 6 * 64 + i] = trace_s[i];
+#endif
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+constexpr int kStages2 = 6;
+constexpr int kSmem2 = kStages2 * STAGE2_BYTES + 16 * kStages2 + 64 + 1024;
+
+template <int EPI>
+int launch_pair(const GemmArgs &g) {
+  constexpr int BN_OUT = (EPI == EPI_SWIGLU) ? 128 : 256;
+  Context &c = ctx();
+  CUtensorMap tmA, tmB, tmB2;
+  B200_TRY(make_map_2d(&tmA, g.a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.k, g.m, g.lda, BK2, BM2));
+  B200_TRY(make_map_2d(&tmB, g.b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.n, g.k, g.ldb, 64, BK2));
+  if (EPI == EPI_SWIGLU)
+    B200_TRY(make_map_2d(&tmB2, g.b2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.n, g.k, g.ldb, 64, BK2));
+  else
+    tmB2 = tmB;
+  TcParams p;
+  p.c = g.c;
+  p.res = g.res;
+  p.ldc = g.ldc;
+  p.ldres = g.ldres;
+  p.m = (int)g.m;
+  p.n = (int)g.n;
+  p.k = (int)g.k;
+  p.m_blocks = (int)((g.m + 255) / 256);
+  p.n_blocks = (int)((g.n + BN_OUT - 1) / BN_OUT);
+  p.num_tiles = p.m_blocks * p.n_blocks;
+  p.k_blocks = (int)((g.k + BK2 - 1) / BK2);
+  p.status = c.d_status;
+  auto kern = gemm_tc2_kernel<kStages2, EPI>;
+  static int max_pairs = 0;  // one per template instantiation
+  if (max_pairs == 0) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2));
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(2 * (c.sm_count / 2));
+    q.blockDim = dim3(THREADS2);
+    q.dynamicSmemBytes = kSmem2;
+    int clusters = 0;
+    // SMs pair up inside a GPC only: ask how many pairs can be resident at once
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &q) != cudaSuccess || clusters < 1) {
+      cudaGetLastError();
+      clusters = c.sm_count / 2 - 4;
+    }
+    max_pairs = clusters < c.sm_count / 2 ? clusters : c.sm_count / 2;
+    if (getenv("B200MLIR_DEBUG")) fprintf(stderr, "[b200mlir] 2-CTA gemm: %d resident pairs (occupancy query %d)\n", max_pairs, clusters);
+  }
+  int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  kern<<<2 * pairs, THREADS2, kSmem2, c.stream>>>(tmA, tmB, tmB2, p);
+  return check_launch("tc256x256x64_2cta");
+}
+
+}  // namespace
+
+int pair_variant_smem_bytes() { return kSmem2; }
+
+#ifdef G2_TRACE
+extern "C" __attribute__((visibility("default"))) int b200mlir_debug_get_trace2(long long *host) {
+  return (int)cudaMemcpyFromSymbol(host, g2_trace_buf, sizeof(long long) * 2 * 6 * 64);
+}
+#endif
+
+int launch_gemm_tc_pair(const GemmArgs &g) {
+  switch (g.epilogue) {
+    case EPI_F16: return launch_pair<EPI_F16>(g);
+    case EPI_F32_RES: return launch_pair<EPI_F32_RES>(g);
+    case EPI_F16_RES16: return launch_pair<EPI_F16_RES16>(g);
+    case EPI_SWIGLU: return launch_pair<EPI_SWIGLU>(g);
+    default: return set_error(B200MLIR_ERR_UNSUPPORTED, "2-CTA gemm: epilogue %d not built", g.epilogue);
+  }
+}
+
+}  // namespace b200

@@ -54,15 +54,17 @@ std::string cache_key(int64_t m, int64_t n, int64_t k, int epi) {
   return os.str();
 }
 
-// Modelled lower bound in SM clocks.  Per 64-deep K block a 128 x BN tile costs
-// the larger of the tensor time (128 x BN x 16 MMA = BN/2 clocks, four per
-// block) and the shared-memory read time ((128+BN) x 64 x 2 bytes at 128 B/clk);
-// tiles run in waves over the SMs.  Orders candidates; never crowns one.
+// Modelled time in SM clocks.  A tile of bm x bn needs bm*bn*64*2 / (8192 * cta_group)
+// tensor clocks per 64-deep K block at full rate, and each tiling sustains only a
+// measured fraction of that rate (narrow tiles are bound by shared-memory and L2
+// traffic per flop); tiles run in waves over the SMs (SM pairs for cta_group 2).
+// Orders candidates; never crowns one.
 double model_clocks(const TcVariantInfo &vi, int64_t m, int64_t n, int64_t k, int sms) {
   const double tiles = std::ceil((double)m / vi.bm) * std::ceil((double)n / vi.bn);
-  const double waves = std::ceil(tiles / (double)std::max(1, sms));
+  const double slots = std::max(1, sms / vi.cta_group);
+  const double waves = std::ceil(tiles / slots);
   const double kblocks = std::ceil((double)k / vi.bk);
-  const double per_block = std::max(2.0 * vi.bn, (double)(vi.bm + vi.bn));
+  const double per_block = (double)vi.bm * vi.bn * vi.bk * 2.0 / (8192.0 * vi.cta_group) / vi.model_eff;
   return waves * (kblocks * per_block + 1500.0);
 }
 

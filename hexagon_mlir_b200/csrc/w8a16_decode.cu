@@ -396,7 +396,7 @@ int launch_tc(const CUtensorMap &tmA, const TcDecodeParams &p) {
   lay.tile_bytes = ((((ch_max + 7) / 8) * 8 * 128) + 1023) / 1024 * 1024;
   lay.slot_bytes = (NM * 128 + ch_max * 64 + 1023) / 1024 * 1024;
 #ifdef W8_TRACE
-  const int ctrl_bytes = 16 * MAX_SLOTS + 16 * 2 * G + 64 + 8 * 64 * 8 + 64;
+  const int ctrl_bytes = 16 * MAX_SLOTS + 16 * 2 * G + 64 + 8192;
 #else
   const int ctrl_bytes = 16 * MAX_SLOTS + 16 * 2 * G + 64;
 #endif
@@ -409,7 +409,11 @@ int launch_tc(const CUtensorMap &tmA, const TcDecodeParams &p) {
   auto kern = w8a16_tc_kernel<NM, G>;
   static bool attr_set = false;
   if (!attr_set) {
+#ifdef W8_TRACE
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 8192));
+#else
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+#endif
     attr_set = true;
   }
   kern<<<grid, (3 * G + 1) * 32, smem, cx.stream>>>(tmA, p, lay);

@@ -63,6 +63,33 @@ class TensorParallelMLP:
         self.compute = compute or _device_mlp
         self.add = add or _device_add
         self._partial = None
+        self._graph = None
+        self._graph_key = None
+
+    def captured(self, x, out):
+        """Run the block through a CUDA graph captured on first use for this (x, out) pair.
+
+        The tensor-parallel step is a dozen short launches plus one NCCL call per chunk; issued
+        from Python it is bound by the host.  Capturing the whole step (kernels and all-reduces)
+        and replaying it removes that cost.  The graph reads and writes the very tensors given
+        here: refill `x` in place between replays."""
+        key = (x.data_ptr(), out.data_ptr(), tuple(x.shape))
+        if self._graph is None or self._graph_key != key:
+            self(x, out)  # warm-up outside capture: workspaces, NCCL channels, kernel attributes
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                self(x, out)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    self(x, out)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self._graph, self._graph_key = graph, key
+        self._graph.replay()
+        return out
 
     def __call__(self, x, out):
         if self.world == 1:

@@ -26,7 +26,7 @@ def n_variants(hm):
     return len(hm.gemm_variants())
 
 
-@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, -1])
+@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, 3, -1])
 def test_c1_config(hm, oracle, variant):
     """M=N=K=1024, U[-1,1], seed 0."""
     rng = philox(0)
@@ -52,7 +52,7 @@ def test_reference_test_shape(hm, oracle):
     assert max_abs_rel(got, oracle.gemm_f16(a, b)) <= TOL_GEMM
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3])
 @pytest.mark.parametrize("mnk", [(128, 256, 64), (128, 64, 128), (5, 8, 8), (129, 264, 72),
                                  (300, 520, 200), (256, 256, 4096), (1000, 1000, 1000),
                                  (64, 2048, 512), (2048, 64, 320)])
@@ -100,7 +100,7 @@ def test_klooped_matmul(hm, oracle, block_k):
     assert (got.view(np.uint16) != want.view(np.uint16)).mean() < 0.05
 
 
-@pytest.mark.parametrize("variant", [SIMT, 0])
+@pytest.mark.parametrize("variant", [SIMT, 0, 3])
 def test_f32_readout_with_residual(hm, oracle, variant):
     rng = philox(45)
     a = rng.uniform(-1, 1, (256, 192)).astype(np.float16)

@@ -129,7 +129,7 @@ const TcVariantInfo &tc_variant_info(int v);
 const char *tc_variant_verdict(int v, const GemmArgs &g);
 int launch_gemm_tc(int v, const GemmArgs &g);
 // gemm_tcgen05_2cta.cu
-int launch_gemm_tc_pair(const GemmArgs &g);
+int launch_gemm_tc_pair(const GemmArgs &g, bool deep_k);
 int pair_variant_smem_bytes();
 
 // w8a16.cu

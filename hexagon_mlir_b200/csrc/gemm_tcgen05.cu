@@ -234,6 +234,7 @@ const TcVariantInfo kVariants[] = {
     {"tc128x64x64_s8", 128, 64, 64, 8, 1, smem_for(64, 8), 128, 0.30},
     // a pair of CTAs per 256 x 256 tile (gemm_tcgen05_2cta.cu)
     {"tc256x256x64_2cta_s6", 256, 256, 64, 6, 2, 6 * 32768 + 16 * 6 + 64 + 1024, 512, 0.85},
+    {"tc256x256x128_2cta_s3", 256, 256, 128, 3, 2, 6 * 32768 + 16 * 6 + 64 + 1024, 512, 0.10},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -331,7 +332,8 @@ int launch_gemm_tc(int v, const GemmArgs &g) {
     case 0: return launch_epi<256, 4>(g, vi);
     case 1: return launch_epi<128, 6>(g, vi);
     case 2: return launch_epi<64, 8>(g, vi);
-    case 3: return launch_gemm_tc_pair(g);
+    case 3: return launch_gemm_tc_pair(g, false);
+    case 4: return launch_gemm_tc_pair(g, true);
   }
   return set_error(B200MLIR_ERR_BAD_ARG, "no such gemm variant %d", v);
 }

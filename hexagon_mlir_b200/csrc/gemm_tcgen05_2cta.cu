@@ -103,7 +103,8 @@ __device__ long long g2_trace_buf[2 * 6 * 64];
 
 // EPI_SWIGLU: the pair's MMA N = 256 is [gate 128 | up 128]; CTA 0 loads the Wg tile,
 // CTA 1 the Wu tile, and each CTA's accumulator rows hold both halves.
-template <int STAGES, int EPI>
+// NSUB: 64-deep K sub-tiles per stage (one barrier round trip and one commit per stage).
+template <int STAGES, int NSUB, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS2, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmB2, const TcParams p) {
@@ -114,7 +115,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                                         /*B MN-major*/ 1, 256, BN_MMA);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t ctrl = smem_base + STAGES * STAGE2_BYTES;
+  constexpr int STAGE_BYTES = NSUB * STAGE2_BYTES;
+  constexpr int BKS = NSUB * BK2;  // K per stage
+  const uint32_t ctrl = smem_base + STAGES * STAGE_BYTES;
   const uint32_t bar_full = ctrl;                       // STAGES (used in the leader)
   const uint32_t bar_empty = ctrl + 8 * STAGES;         // STAGES (both CTAs)
   const uint32_t bar_tfull = ctrl + 16 * STAGES;        // 2 (both CTAs)
@@ -176,18 +179,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           if (tile == pair) TR2(1, kb);
           const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);  // the leader's barrier
-          const uint32_t sa = smem_base + stage * STAGE2_BYTES;
-          const uint32_t sb = sa + A2_BYTES;
-          remote_expect_tx(full, STAGE2_BYTES);
-          tma_load_2d_pair(sa, &tmA, full, kb * BK2, m0);
-          if (EPI == EPI_SWIGLU) {
-            const CUtensorMap *mb = leader ? &tmB : &tmB2;  // gate half / up half
-            tma_load_2d_pair(sb, mb, full, n0, kb * BK2);
-            tma_load_2d_pair(sb + SLAB_BYTES, mb, full, n0 + 64, kb * BK2);
-          } else {
-            const int nb = n0 + (int)rank * 128;
-            tma_load_2d_pair(sb, &tmB, full, nb, kb * BK2);
-            tma_load_2d_pair(sb + SLAB_BYTES, &tmB, full, nb + 64, kb * BK2);
+          remote_expect_tx(full, STAGE_BYTES);
+#pragma unroll
+          for (int sub = 0; sub < NSUB; ++sub) {
+            const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * STAGE2_BYTES;
+            const uint32_t sb = sa + A2_BYTES;
+            const int k0 = kb * BKS + sub * BK2;
+            tma_load_2d_pair(sa, &tmA, full, k0, m0);
+            if (EPI == EPI_SWIGLU) {
+              const CUtensorMap *mb = leader ? &tmB : &tmB2;  // gate half / up half
+              tma_load_2d_pair(sb, mb, full, n0, k0);
+              tma_load_2d_pair(sb + SLAB_BYTES, mb, full, n0 + 64, k0);
+            } else {
+              const int nb = n0 + (int)rank * 128;
+              tma_load_2d_pair(sb, &tmB, full, nb, k0);
+              tma_load_2d_pair(sb + SLAB_BYTES, &tmB, full, nb + 64, k0);
+            }
           }
           if (tile == pair) TR2(2, kb);
           if (++stage == STAGES) {
@@ -217,14 +224,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           tc_fence_after_sync();
           if (tile == pair) TR2(4, kb);
-          const uint32_t sa = smem_base + stage * STAGE2_BYTES;
-          const uint32_t sb = sa + A2_BYTES;
-          const uint64_t adesc = smem_desc_sw128(sa, 16, 1024);
-          const uint64_t bdesc = smem_desc_sw128(sb, SLAB_BYTES, 1024);
 #pragma unroll
-          for (int k = 0; k < BK2 / 16; ++k)
-            mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), IDESC,
-                         (kb | k) != 0 ? 1u : 0u);
+          for (int sub = 0; sub < NSUB; ++sub) {
+            const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * STAGE2_BYTES;
+            const uint32_t sb = sa + A2_BYTES;
+            const uint64_t adesc = smem_desc_sw128(sa, 16, 1024);
+            const uint64_t bdesc = smem_desc_sw128(sb, SLAB_BYTES, 1024);
+#pragma unroll
+            for (int k = 0; k < BK2 / 16; ++k)
+              mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), IDESC,
+                           (kb | sub | k) != 0 ? 1u : 0u);
+          }
           mma_commit_pair(bar_empty + 8 * stage);  // both producers may refill the stage
           if (tile == pair) TR2(5, kb);
           if (++stage == STAGES) {
@@ -295,11 +305,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
-constexpr int kStages2 = 6;
-constexpr int kSmem2 = kStages2 * STAGE2_BYTES + 16 * kStages2 + 64 + 1024;
+constexpr int kSmem2 = 6 * STAGE2_BYTES + 16 * 6 + 64 + 1024;  // the same ring bytes for (6 x 64) and (3 x 128)
 
-template <int EPI>
-int launch_pair(const GemmArgs &g) {
+template <int STAGES, int NSUB, int EPI>
+int launch_pair(const GemmArgs &g, const char *name) {
   constexpr int BN_OUT = (EPI == EPI_SWIGLU) ? 128 : 256;
   Context &c = ctx();
   CUtensorMap tmA, tmB, tmB2;
@@ -320,9 +329,9 @@ int launch_pair(const GemmArgs &g) {
   p.m_blocks = (int)((g.m + 255) / 256);
   p.n_blocks = (int)((g.n + BN_OUT - 1) / BN_OUT);
   p.num_tiles = p.m_blocks * p.n_blocks;
-  p.k_blocks = (int)((g.k + BK2 - 1) / BK2);
+  p.k_blocks = (int)((g.k + NSUB * BK2 - 1) / (NSUB * BK2));
   p.status = c.d_status;
-  auto kern = gemm_tc2_kernel<kStages2, EPI>;
+  auto kern = gemm_tc2_kernel<STAGES, NSUB, EPI>;
   static int max_pairs = 0;  // one per template instantiation
   if (max_pairs == 0) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2));
@@ -341,7 +350,7 @@ int launch_pair(const GemmArgs &g) {
   }
   int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
   kern<<<2 * pairs, THREADS2, kSmem2, c.stream>>>(tmA, tmB, tmB2, p);
-  return check_launch("tc256x256x64_2cta");
+  return check_launch(name);
 }
 
 }  // namespace
@@ -354,14 +363,20 @@ extern "C" __attribute__((visibility("default"))) int b200mlir_debug_get_trace2(
 }
 #endif
 
-int launch_gemm_tc_pair(const GemmArgs &g) {
+template <int STAGES, int NSUB>
+int launch_pair_epi(const GemmArgs &g, const char *name) {
   switch (g.epilogue) {
-    case EPI_F16: return launch_pair<EPI_F16>(g);
-    case EPI_F32_RES: return launch_pair<EPI_F32_RES>(g);
-    case EPI_F16_RES16: return launch_pair<EPI_F16_RES16>(g);
-    case EPI_SWIGLU: return launch_pair<EPI_SWIGLU>(g);
+    case EPI_F16: return launch_pair<STAGES, NSUB, EPI_F16>(g, name);
+    case EPI_F32_RES: return launch_pair<STAGES, NSUB, EPI_F32_RES>(g, name);
+    case EPI_F16_RES16: return launch_pair<STAGES, NSUB, EPI_F16_RES16>(g, name);
+    case EPI_SWIGLU: return launch_pair<STAGES, NSUB, EPI_SWIGLU>(g, name);
     default: return set_error(B200MLIR_ERR_UNSUPPORTED, "2-CTA gemm: epilogue %d not built", g.epilogue);
   }
+}
+
+// deep_k: 128-deep stages (three of them) instead of six 64-deep ones
+int launch_gemm_tc_pair(const GemmArgs &g, bool deep_k) {
+  return deep_k ? launch_pair_epi<3, 2>(g, "tc256x256x128_2cta") : launch_pair_epi<6, 1>(g, "tc256x256x64_2cta");
 }
 
 }  // namespace b200

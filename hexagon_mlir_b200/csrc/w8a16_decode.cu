@@ -1,22 +1,32 @@
-// w8a16 GEMM on tcgen05 with the dequantisation done on the way through shared
-// memory: C[M,N] = A[M,K] · (q[K,N] · s[N]).
+// w8a16 GEMM on tcgen05 with the dequantisation done in registers on the way
+// from HBM to shared memory: C[M,N] = A[M,K] · (q[K,N] · s[N]).
 //
 // The op is weight streaming (45 MB of int8 for the 4096 x 11008 config), so the
 // kernel is arranged around the weight image, not around A:
 //   * every CTA (one per SM, persistent) owns a contiguous range of output
-//     channels for the WHOLE of K — no split-K, no partial sums, no atomics, no
-//     scratch, and the result is bit-reproducible;
-//   * operands are swapped: the weights are the MMA's "A" operand (up to 128
-//     channels per instruction, K-major), the activations its "B" operand
-//     (N_mma = M rows padded to NM), so an M=1..16 decode step costs a
-//     128 x 16 x 16 MMA (8 clocks) per K=16 step;
-//   * one producer thread keeps a deep ring of stages full: one bulk copy of the
-//     CTA's channels x 64 k of int8 plus one TMA tile of activations per stage;
-//   * eight converter warps turn each stage's bytes (stored as q+128) into fp16
-//     with a byte-permute and one subtract and write them in the 128-byte
-//     swizzled K-major layout the MMA reads (three 16 KiB buffers);
-//   * one thread issues the MMAs into a TMEM accumulator [channel][row]; at the
-//     end of K the converter warps read it out, scale by s[n], round and store.
+//     channels for the WHOLE of K — no split-K, no partial sums in memory, no
+//     atomics, no scratch, and the result is bit-reproducible;
+//   * the weights are brought in by the converter threads themselves with
+//     16-byte cp.async copies into a private shared-memory ring, seven K=128
+//     steps ahead (≈66 KB in flight per SM).  Measured on B200: bulk/TMA copies
+//     that miss L2 sustain only ~11 B/clk per SM (the copy engine's queue of
+//     outstanding requests is short), about half of an SM's share of HBM
+//     bandwidth; register prefetch does not work either, because a warp has only
+//     a handful of scoreboard slots and a wait on an old load also waits for the
+//     newer loads that share its slot; cp.async groups have neither limit;
+//   * a converter thread owns one (channel, 16-k group) position for the whole
+//     K loop: 16 bytes (stored as q+128) become 16 fp16 values with byte-permutes
+//     and one subtract each, written in the 128-byte swizzled K-major layout the
+//     MMA reads;
+//   * operands are swapped: the weights are the MMA's "A" operand (channels on
+//     the 128 rows), the activations its "B" operand (N_mma = M rows padded to
+//     NM), so a decode step costs a 128 x 16 x 16 MMA per K=16 step.  A 128-row
+//     MMA occupies the tensor pipe for ~48 clocks however narrow it is and
+//     issuing one costs its thread about as much, so K steps alternate between
+//     two issuing threads with one TMEM accumulator each;
+//   * activations come through a small TMA ring (they are L2 hits); at the end
+//     of K the first four converter warps read TMEM, add the two partial sums,
+//     scale by s[n], round and store.
 //
 // Resident image, built once per weight (the analogue of the reference's
 // pre-packed weight: backend/hmx_weight_prepack.py:124-212,
@@ -32,19 +42,15 @@ namespace {
 
 using namespace ptx;
 
-constexpr int CH_MAX = 128;                 // channels per pass = MMA M
+constexpr int CH_PASS = 80;          // channels per pass: 4 positions each on 320 converter threads
+constexpr int CONV_W = 10;           // converter warps
+constexpr int ISSUERS = 2;
+constexpr int D_AHEAD = 8;           // depth of the int8 ring (K=128 steps)
+constexpr int STG_BYTES = 2 * CH_PASS * 64;  // one ring slot: two [80][64 B] int8 sub-chunks, 10 KiB
+constexpr int NB = 4;                // fp16 tile / activation buffers
+constexpr int TILE_BYTES = 2 * CH_PASS * 128;  // two [80][64] fp16 sub-tiles (K = 128): 20 KiB
+constexpr int THREADS = (CONV_W + 1 + ISSUERS) * 32;
 
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
-  return v;
-}
 __device__ __forceinline__ void sts128(uint32_t saddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(saddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -58,6 +64,19 @@ __device__ __forceinline__ uint32_t dq2(uint32_t word, uint32_t selector) {
 __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t saddr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+  return v;
+}
 __device__ __forceinline__ void tmem_ld_32x32_x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -68,6 +87,16 @@ __device__ __forceinline__ void tmem_ld_32x32_x16(uint32_t taddr, uint32_t (&r)[
       : "memory");
 }
 
+// Region stamps for timeline debugging (the analogue of the reference's light-weight
+// profiling regions, lib/Transforms/HexagonLWPInstrumentation.cpp): compiled in only
+// with -DB200MLIR_W8_TRACE; CTA 3 records clock64() per role and step.
+#ifdef B200MLIR_W8_TRACE
+__device__ long long g_trace_buf[8 * 64];
+#define TR(role, u) do { if (blockIdx.x == 3 && (u) < 64) trace_s[(role) * 64 + (u)] = clock64(); } while (0)
+#else
+#define TR(role, u) do { } while (0)
+#endif
+
 struct TcDecodeParams {
   const uint8_t *image;  // [k_chunks][n][64]
   const __half *scales;
@@ -77,78 +106,49 @@ struct TcDecodeParams {
   int *status;
 };
 
-#ifdef W8_TRACE
-__device__ long long g_trace_buf[8 * 64];
-#define TR(role, u) do { if (blockIdx.x == 3 && (u) < 64) trace_s[(role) * 64 + (u)] = clock64(); } while (0)
-#else
-#define TR(role, u) do { } while (0)
-#endif
-
-struct TcLayout {
-  int n_slots;     // ring depth (<= MAX_SLOTS)
-  int slot_bytes;  // activation tile + this launch's widest int8 slab, multiple of 1024
-  int tile_bytes;  // fp16 weight tile: channels rounded up to 8 rows of 128 bytes, multiple of 1024
-};
-constexpr int MAX_SLOTS = 32;
-
-// NM: activation rows padded to the MMA's N (16..256, multiple of 16).
-// G: independent convert->MMA pipelines.  The costs that shape this (measured on
-// B200): a 128-row MMA occupies the tensor pipe for at least ~48 clocks however
-// narrow it is, issuing one costs its thread about as much, a commit-to-wake
-// round trip is ~200 clocks and a converter group needs a few hundred clocks per
-// K=64 step — while HBM delivers a step's bytes every ~200 clocks.  So K steps
-// are dealt round-robin to G pipelines, each with two converter warps, two fp16
-// tiles, one issuing thread and one TMEM accumulator; one producer thread feeds
-// all of them through a deep ring of int8 slots (that ring, not the fp16 tiles,
-// is what keeps ~100 KB per SM in flight).  The read-out adds the G partial sums.
-template <int NM, int G>
-__global__ void __launch_bounds__((2 * G + 1 + G) * 32, 1)
-w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p, const TcLayout lay) {
-  constexpr int A_BYTES = NM * 128;
-  constexpr int NB = 2 * G;           // fp16 tiles
-  constexpr int CONV_W = 2 * G;       // converter warps
-  constexpr int TMEM_COLS = NM * G < 32 ? 32 : NM * G;
-  static_assert(TMEM_COLS <= 512 && (TMEM_COLS & (TMEM_COLS - 1)) == 0, "TMEM columns");
+// NM: activation rows padded to the MMA's N (16 or 64).
+template <int NM>
+__global__ void __launch_bounds__(THREADS, 1)
+w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p) {
+  constexpr int A_BYTES = 2 * NM * 128;  // two [NM][64] activation sub-tiles per K=128 step
+  constexpr int TMEM_COLS = NM * ISSUERS < 32 ? 32 : NM * ISSUERS;
   constexpr uint32_t IDESC = make_idesc(/*D f32*/ 1, /*A f16*/ 0, /*B f16*/ 0, /*A K-major*/ 0,
                                         /*B K-major*/ 0, 128, NM);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  // fp16 tiles first: a 128-row MMA reads past a shorter tile into the next tile / the ring
-  const uint32_t ring = base + NB * lay.tile_bytes;
-  const uint32_t ctrl = ring + lay.n_slots * lay.slot_bytes;
-  const uint32_t bar_full = ctrl;                          // MAX_SLOTS
-  const uint32_t bar_empty = ctrl + 8 * MAX_SLOTS;         // MAX_SLOTS
-  const uint32_t bar_conv = ctrl + 16 * MAX_SLOTS;         // NB
-  const uint32_t bar_cempty = bar_conv + 8 * NB;           // NB
-  const uint32_t bar_afull = bar_cempty + 8 * NB;          // 1
-  const uint32_t bar_aempty = bar_afull + 8;               // 1
+  // fp16 tiles first: a 128-row MMA reads 48 rows past an 80-row tile, into the next tile / the activation ring
+  const uint32_t act0 = base + NB * TILE_BYTES;
+  const uint32_t stg0 = act0 + NB * A_BYTES;               // int8 ring (also absorbs the last tile's over-read)
+  const uint32_t ctrl = stg0 + D_AHEAD * STG_BYTES;
+  const uint32_t bar_conv = ctrl;                          // NB: fp16 tile written (CONV_W arrivals)
+  const uint32_t bar_act = ctrl + 8 * NB;                  // NB: activation sub-tiles landed (TMA)
+  const uint32_t bar_free = ctrl + 16 * NB;                // NB: MMAs of the buffer done (commit)
+  const uint32_t bar_afull = ctrl + 24 * NB;               // accumulators complete (ISSUERS commits)
+  const uint32_t bar_aempty = bar_afull + 8;               // accumulators read out (CONV_W arrivals)
   const uint32_t tmem_slot = bar_aempty + 8;
   uint8_t *ctrl_gen = smem_raw + (ctrl - smem_u32(smem_raw));
-  const int misc = 16 * MAX_SLOTS + 16 * NB + 16;
+  const int misc = 24 * NB + 16;
   volatile uint32_t *tmem_slot_gen = reinterpret_cast<volatile uint32_t *>(ctrl_gen + misc);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_gen + misc + 4);
 
-#ifdef W8_TRACE
+#ifdef B200MLIR_W8_TRACE
   __shared__ long long trace_s[8 * 64];
 #endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // this CTA's channels, walked in passes of at most CH_MAX
+  // this CTA's channels, walked in passes of at most CH_PASS
   const int c_begin = (int)((int64_t)p.n * blockIdx.x / gridDim.x);
   const int c_end = (int)((int64_t)p.n * (blockIdx.x + 1) / gridDim.x);
-  const int passes = (c_end - c_begin + CH_MAX - 1) / CH_MAX;
+  const int passes = (c_end - c_begin + CH_PASS - 1) / CH_PASS;
   const int kch = p.k_chunks;
-  const int ns = lay.n_slots;
+  const int steps = (kch + 1) >> 1;  // K=128 steps per pass
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < ns; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
-    }
     for (int b = 0; b < NB; ++b) {
-      mbar_init(bar_conv + 8 * b, 2);  // the two converter warps of the pipeline
-      mbar_init(bar_cempty + 8 * b, 1);
+      mbar_init(bar_conv + 8 * b, CONV_W);
+      mbar_init(bar_act + 8 * b, 1);
+      mbar_init(bar_free + 8 * b, 1);
     }
-    mbar_init(bar_afull, G);
+    mbar_init(bar_afull, ISSUERS);
     mbar_init(bar_aempty, CONV_W);
     *abort_flag = 0;
     fence_barrier_init();
@@ -163,123 +163,124 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p,
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
 
+  // Every CTA needs the same activation tile for a given k chunk; each CTA starts
+  // at its own step so that they do not all ask one L2 slice for the same lines at
+  // once (owning all of K, the order of the sum is free).
+  const int rot = (int)((blockIdx.x * 19u) % (unsigned)steps);
+
   if (warp == CONV_W) {
-    // ---------------- producer: one bulk copy + one activation tile per K=64 step ----------------
+    // ---------------- producer: the activation sub-tiles of each K=128 step ----------------
     if (lane == 0) {
-      // Every CTA needs the same activation tile for a given k chunk; each CTA
-      // starts at its own chunk so that they do not all ask one L2 slice for the
-      // same lines at once (owning all of K, the order of the sum is free).
-      const int rot = (int)((blockIdx.x * 37u) % (unsigned)kch);
-      int slot = 0;
-      uint32_t phase = 0;
+      int t = 0;
       for (int pass = 0; pass < passes; ++pass) {
-        const int ch0 = c_begin + pass * CH_MAX;
-        const int ch = min(CH_MAX, c_end - ch0);
-        const uint8_t *src = p.image + (int64_t)ch0 * 64;
-        int kc = rot;
-        for (int j = 0; j < kch; ++j) {
-          TR(0, j);
-          if (!mbar_wait(bar_empty + 8 * slot, phase ^ 1u, abort_flag, p.status, 21, j)) goto done;
-          TR(1, j);
-          const uint32_t full = bar_full + 8 * slot;
-          const uint32_t dst = ring + slot * lay.slot_bytes;
-          mbar_expect_tx(full, (uint32_t)(ch * 64 + A_BYTES));
-          tma_load_2d(dst, &tmA, full, kc * 64, 0);
-          bulk_load(dst + A_BYTES, src + (int64_t)kc * p.n * 64, (uint32_t)(ch * 64), full);
-          if (++kc == kch) kc = 0;
-          if (++slot == ns) {
-            slot = 0;
-            phase ^= 1u;
-          }
+        int st = rot;
+        for (int j = 0; j < steps; ++j, ++t) {
+          const int b = t % NB;
+          TR(6, t);
+          if (!mbar_wait(bar_free + 8 * b, (uint32_t)(((t / NB) & 1) ^ 1), abort_flag, p.status, 21, t)) goto done;
+          const uint32_t full = bar_act + 8 * b;
+          const uint32_t dst = act0 + b * A_BYTES;
+          mbar_expect_tx(full, A_BYTES);
+          tma_load_2d(dst, &tmA, full, st * 128, 0);                  // k chunk 2*st (zero fill past K)
+          tma_load_2d(dst + NM * 128, &tmA, full, st * 128 + 64, 0);  // k chunk 2*st + 1
+          if (++st == steps) st = 0;
         }
       }
     }
   } else if (warp > CONV_W) {
-    // ---------------- MMA issuer of pipeline g: steps u = g, g+G, ... ----------------
+    // ---------------- MMA issuer g: steps t = g, g+2, ... ----------------
     if (lane == 0) {
       const int g = warp - (CONV_W + 1);
       const uint32_t d_tmem = tmem_base + (uint32_t)(g * NM);
-      const int units = passes * kch;
-      int slot = g % ns;
-      uint32_t sphase = (uint32_t)((g / ns) & 1);
-      int t = 0;  // this pipeline's step count
-      int u = g;
+      int t = 0;
       for (int pass = 0; pass < passes; ++pass) {
-        const int u_end = (pass + 1) * kch;
-        if (pass > 0 && !mbar_wait(bar_aempty, (pass & 1) ^ 1u, abort_flag, p.status, 22, pass)) goto done;
+        if (pass > 0 && !mbar_wait(bar_aempty, (uint32_t)((pass & 1) ^ 1), abort_flag, p.status, 22, pass)) goto done;
         uint32_t accumulate = 0;
-        for (; u < u_end && u < units; u += G, ++t) {
-          const int b = g + G * (t & 1);
-          TR(5, u);
-          if (!mbar_wait(bar_conv + 8 * b, (uint32_t)((t >> 1) & 1), abort_flag, p.status, 23, u)) goto done;
+        for (int j = 0; j < steps; ++j, ++t) {
+          if ((t % ISSUERS) != g) continue;
+          const int b = t % NB;
+          const uint32_t ph = (uint32_t)((t / NB) & 1);
+          TR(3, t);
+          if (!mbar_wait(bar_conv + 8 * b, ph, abort_flag, p.status, 23, t)) goto done;
+          if (!mbar_wait(bar_act + 8 * b, ph, abort_flag, p.status, 24, t)) goto done;
           tc_fence_after_sync();
-          TR(6, u);
-          const uint64_t adesc = smem_desc_sw128(base + b * lay.tile_bytes, 16, 1024);   // fp16 weights [<=128][64]
-          const uint64_t bdesc = smem_desc_sw128(ring + slot * lay.slot_bytes, 16, 1024);  // activations [NM][64]
+          TR(4, t);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            mma_f16_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, accumulate);
-            accumulate = 1;
+          for (int sub = 0; sub < 2; ++sub) {
+            const uint64_t adesc = smem_desc_sw128(base + b * TILE_BYTES + sub * (CH_PASS * 128), 16, 1024);
+            const uint64_t bdesc = smem_desc_sw128(act0 + b * A_BYTES + sub * (NM * 128), 16, 1024);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              mma_f16_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, accumulate);
+              accumulate = 1;
+            }
           }
-          mma_commit(bar_empty + 8 * slot);   // the slot (activation tile) may be refilled
-          mma_commit(bar_cempty + 8 * b);     // the fp16 tile may be rewritten
-          TR(7, u);
-          slot += G;
-          while (slot >= ns) {
-            slot -= ns;
-            sphase ^= 1u;
-          }
+          mma_commit(bar_free + 8 * b);  // the fp16 tile and the activation buffer may be rewritten
+          TR(5, t);
         }
         mma_commit(bar_afull);
       }
-      (void)sphase;
     }
   } else {
-    // ---------------- converters: pipeline g = warps 2g, 2g+1; read-out by warps 0..3 ----------------
-    const int g = warp >> 1;
-    const int tid = (warp & 1) * 32 + lane;  // 0..63 inside the pipeline
-    const int q = warp & 3;                  // TMEM lane quadrant this warp may read
-    const int units = passes * kch;
-    int slot = g % ns;
-    uint32_t sphase = (uint32_t)((g / ns) & 1);
+    // ---------------- converters (warps 0..9); read-out by warps 0..3 ----------------
+    const int tid = threadIdx.x;       // position: channel = tid / 4, 16-k group = tid % 4
+    const int row = tid >> 2, jj = tid & 3;
+    const int q = warp & 3;            // TMEM lane quadrant this warp may read
+    // where this position lands in a sub-tile: two 16-byte chunks of the channel's 128-byte row
+    const uint32_t off0 = (uint32_t)(row * 128 + (((2 * jj) ^ (row & 7)) << 4));
+    const uint32_t off1 = (uint32_t)(row * 128 + (((2 * jj + 1) ^ (row & 7)) << 4));
+    const int64_t chunk_stride = (int64_t)p.n * 4;  // uint4 per k chunk
     int t = 0;
-    int u = g;
     for (int pass = 0; pass < passes; ++pass) {
-      const int ch0 = c_begin + pass * CH_MAX;
-      const int ch = min(CH_MAX, c_end - ch0);
-      const int u_end = (pass + 1) * kch;
-      for (; u < u_end && u < units; u += G, ++t) {
-        const int b = g + G * (t & 1);
-        if (tid == 0) TR(2, u);
-        bool ok = mbar_wait(bar_full + 8 * slot, sphase, abort_flag, p.status, 26, u) &&
-                  mbar_wait(bar_cempty + 8 * b, (uint32_t)(((t >> 1) & 1) ^ 1), abort_flag, p.status, 27, u);
+      const int ch0 = c_begin + pass * CH_PASS;
+      const int ch = min(CH_PASS, c_end - ch0);
+      const bool mine = row < ch;
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.image) + ((int64_t)(ch0 + row) * 4 + jj);
+      // zero weight is the byte 128: used for k chunks past the end of the image
+      const uint4 zero = make_uint4(0x80808080u, 0x80808080u, 0x80808080u, 0x80808080u);
+      const uint32_t my_stg = stg0 + (uint32_t)tid * 16;  // this thread's 16 bytes inside a sub-chunk
+      // copies of step j (rotated) into ring slot j % D_AHEAD; always one commit per call
+      auto issue = [&](int j) {
+        if (j < steps && mine) {
+          int st = j + rot;
+          if (st >= steps) st -= steps;
+          const int kc = 2 * st;
+          const uint32_t dst = my_stg + (uint32_t)((j % D_AHEAD) * STG_BYTES);
+          if (kc < kch) cp_async16(dst, src + (int64_t)kc * chunk_stride);
+          if (kc + 1 < kch) cp_async16(dst + CH_PASS * 64, src + (int64_t)(kc + 1) * chunk_stride);
+        }
+        cp_async_commit();
+      };
+      for (int d = 0; d < D_AHEAD - 1; ++d) issue(d);
+      for (int j = 0; j < steps; ++j, ++t) {
+        const int b = t % NB;
+        cp_async_wait<D_AHEAD - 2>();  // this thread's copies of step j have landed
+        bool ok = mbar_wait(bar_free + 8 * b, (uint32_t)(((t / NB) & 1) ^ 1), abort_flag, p.status, 27, t);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) goto done;
-        if (tid == 0) TR(3, u);
-        const uint32_t src = ring + slot * lay.slot_bytes + A_BYTES;
-        const uint32_t dst = base + b * lay.tile_bytes;
-        // task = (channel, 16-k group): 16 bytes in, two 16-byte chunks of the channel's row out
-        for (int task = tid; task < ch * 4; task += 64) {
-          const int row = task >> 2, jj = task & 3;
-          const uint4 w = lds128(src + (uint32_t)task * 16);
-          const uint32_t rbase = dst + (uint32_t)row * 128;
-          const uint32_t c0 = (uint32_t)(((2 * jj) ^ (row & 7)) << 4), c1 = (uint32_t)(((2 * jj + 1) ^ (row & 7)) << 4);
-          sts128(rbase + c0, dq2(w.x, 0x5140u), dq2(w.x, 0x5342u), dq2(w.y, 0x5140u), dq2(w.y, 0x5342u));
-          sts128(rbase + c1, dq2(w.z, 0x5140u), dq2(w.z, 0x5342u), dq2(w.w, 0x5140u), dq2(w.w, 0x5342u));
+        if (mine) {
+          int st = j + rot;
+          if (st >= steps) st -= steps;
+          const int kc = 2 * st;
+          const uint32_t slot = my_stg + (uint32_t)((j % D_AHEAD) * STG_BYTES);
+          const uint32_t tile = base + b * TILE_BYTES;
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            const uint4 v = (kc + sub < kch) ? lds128(slot + sub * (CH_PASS * 64)) : zero;
+            const uint32_t tb = tile + sub * (CH_PASS * 128);
+            sts128(tb + off0, dq2(v.x, 0x5140u), dq2(v.x, 0x5342u), dq2(v.y, 0x5140u), dq2(v.y, 0x5342u));
+            sts128(tb + off1, dq2(v.z, 0x5140u), dq2(v.z, 0x5342u), dq2(v.w, 0x5140u), dq2(v.w, 0x5342u));
+          }
         }
-        fence_async_smem();  // generic-proxy writes must be visible to the tensor core's reads
+        issue(j + D_AHEAD - 1);  // refills the slot this thread read one step ago
+        fence_async_smem();      // generic-proxy writes must be visible to the tensor core's reads
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_conv + 8 * b);
-        if (tid == 0) TR(4, u);
-        slot += G;
-        while (slot >= ns) {
-          slot -= ns;
-          sphase ^= 1u;
-        }
       }
+      cp_async_wait<0>();
       // end of K for this pass: read the accumulators out, add them, scale, round, store
       {
-        bool ok = mbar_wait(bar_afull, pass & 1, abort_flag, p.status, 25, pass);
+        bool ok = mbar_wait(bar_afull, (uint32_t)(pass & 1), abort_flag, p.status, 25, pass);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) goto done;
         tc_fence_after_sync();
@@ -288,7 +289,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p,
           const bool live = chl < ch;
           const float sc = live ? __half2float(p.scales[ch0 + chl]) : 0.0f;
           const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
-          const int used = min(G, kch);  // accumulators that received an MMA
+          const int used = min(ISSUERS, steps);  // accumulators that received an MMA
 #pragma unroll 1
           for (int m0 = 0; m0 < NM; m0 += 16) {
             if (m0 >= p.m) break;  // uniform across the warp
@@ -320,7 +321,7 @@ done:
   // ---------------- teardown ----------------
   tc_fence_before_sync();
   __syncthreads();
-#ifdef W8_TRACE
+#ifdef B200MLIR_W8_TRACE
   if (blockIdx.x == 3) for (int i = threadIdx.x; i < 8 * 64; i += blockDim.x) g_trace_buf[i] = trace_s[i];
 #endif
   if (warp == CONV_W + 1) {
@@ -384,45 +385,26 @@ int make_a_map(CUtensorMap *map, const void *a, int64_t m, int64_t k, int64_t ld
   return 0;
 }
 
-template <int NM, int G>
+template <int NM>
 int launch_tc(const CUtensorMap &tmA, const TcDecodeParams &p) {
   Context &cx = ctx();
-  int grid = cx.sm_count;
-  if (grid > p.n) grid = p.n;
-  // widest channel range any CTA gets in one pass
-  int ch_max = (p.n + grid - 1) / grid;
-  if (ch_max > CH_MAX) ch_max = CH_MAX;
-  TcLayout lay;
-  lay.tile_bytes = ((((ch_max + 7) / 8) * 8 * 128) + 1023) / 1024 * 1024;
-  lay.slot_bytes = (NM * 128 + ch_max * 64 + 1023) / 1024 * 1024;
-#ifdef W8_TRACE
-  const int ctrl_bytes = 16 * MAX_SLOTS + 16 * 2 * G + 64 + 8192;
-#else
-  const int ctrl_bytes = 16 * MAX_SLOTS + 16 * 2 * G + 64;
-#endif
-  const int budget = 227 * 1024 - 1024 - ctrl_bytes - 2 * G * lay.tile_bytes;
-  lay.n_slots = budget / lay.slot_bytes;
-  if (lay.n_slots > MAX_SLOTS) lay.n_slots = MAX_SLOTS;
-  if (lay.n_slots < G + 1)
-    return set_error(B200MLIR_ERR_UNSUPPORTED, "w8a16: shared memory too small for %d rows", NM);
-  const int smem = 2 * G * lay.tile_bytes + lay.n_slots * lay.slot_bytes + ctrl_bytes + 1024;
-  auto kern = w8a16_tc_kernel<NM, G>;
+  constexpr int smem = NB * TILE_BYTES + NB * 2 * NM * 128 + D_AHEAD * STG_BYTES + 24 * NB + 64 + 1024;
+  static_assert(smem <= 227 * 1024, "w8a16 tensor-core kernel exceeds shared memory");
+  auto kern = w8a16_tc_kernel<NM>;
   static bool attr_set = false;
   if (!attr_set) {
-#ifdef W8_TRACE
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 8192));
-#else
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-#endif
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
-  kern<<<grid, (3 * G + 1) * 32, smem, cx.stream>>>(tmA, p, lay);
+  int grid = cx.sm_count;
+  if (grid > p.n) grid = p.n;
+  kern<<<grid, THREADS, smem, cx.stream>>>(tmA, p);
   return check_launch("w8a16_tc");
 }
 
 }  // namespace
 
-#ifdef W8_TRACE
+#ifdef B200MLIR_W8_TRACE
 extern "C" __attribute__((visibility("default"))) int b200mlir_debug_get_trace(long long *host) {
   return (int)cudaMemcpyFromSymbol(host, g_trace_buf, sizeof(long long) * 8 * 64);
 }
@@ -449,15 +431,15 @@ int w8a16_build_block_image(const int8_t *wq_dev, int64_t k, int64_t n, void **i
   return 0;
 }
 
-// Up to 256 rows per call (the caller loops over row passes).
+// Up to 64 rows per call (the caller loops over row passes).
 int launch_w8a16_decode(const __half *a, const void *block_image, const __half *scales_dev, int64_t k,
                         int64_t n, __half *c, int64_t m, int64_t lda, int64_t ldc) {
   B200_TRY(ensure_ready());
-  if (m < 1 || m > 256) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 tensor-core pass takes 1..256 rows");
+  if (m < 1 || m > 64) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 tensor-core pass takes 1..64 rows");
   if (n > 0x7fffffff || k > 0x7fffffff) return set_error(B200MLIR_ERR_UNSUPPORTED, "w8a16: extent too large");
   TcDecodeParams p;
   p.k_chunks = (int)((k + 63) / 64);
-  const int nm = m <= 16 ? 16 : (m <= 64 ? 64 : 256);
+  const int nm = m <= 16 ? 16 : 64;
   CUtensorMap tmA;
   B200_TRY(make_a_map(&tmA, a, m, k, lda, nm));
   p.image = (const uint8_t *)block_image;
@@ -467,9 +449,7 @@ int launch_w8a16_decode(const __half *a, const void *block_image, const __half *
   p.m = (int)m;
   p.n = (int)n;
   p.status = ctx().d_status;
-  if (nm == 16) return launch_tc<16, 4>(tmA, p);
-  if (nm == 64) return launch_tc<64, 4>(tmA, p);
-  return launch_tc<256, 2>(tmA, p);
+  return nm == 16 ? launch_tc<16>(tmA, p) : launch_tc<64>(tmA, p);
 }
 
 }  // namespace b200

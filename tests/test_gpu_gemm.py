@@ -26,7 +26,7 @@ def n_variants(hm):
     return len(hm.gemm_variants())
 
 
-@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, 3, -1])
+@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, 3, 4, -1])
 def test_c1_config(hm, oracle, variant):
     """M=N=K=1024, U[-1,1], seed 0."""
     rng = philox(0)
@@ -52,7 +52,7 @@ def test_reference_test_shape(hm, oracle):
     assert max_abs_rel(got, oracle.gemm_f16(a, b)) <= TOL_GEMM
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
 @pytest.mark.parametrize("mnk", [(128, 256, 64), (128, 64, 128), (5, 8, 8), (129, 264, 72),
                                  (300, 520, 200), (256, 256, 4096), (1000, 1000, 1000),
                                  (64, 2048, 512), (2048, 64, 320)])

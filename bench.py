@@ -43,55 +43,51 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons through NVML (read-only) from a thread while the
+    timed region runs; a 2 ms period resolves regions of a few tens of milliseconds."""
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+               "sw_power_cap": 0x4}
 
     def __init__(self, index: int):
         self.index = index
-        self.rows = []
-        self.proc = None
+        self.sm, self.reason_bits, self.max_mhz = [], 0, None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        except Exception:
+            self._h = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append(line.strip())
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
     def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            parts = [p.strip() for p in r.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, v in zip(names, parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+        reasons = sorted(n for n, bit in self.REASONS.items() if self.reason_bits & bit)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+                "sm_min_mhz": min(self.sm) if self.sm else None, "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(self.sm)}
 
 
 # ---- the reference arm / CPU baseline: the oracle on host cores -----------------------------
@@ -102,19 +98,21 @@ def cpu_gemm_sample(target_s: float = 12.0):
     threads = oracle.hw_threads()
     rng = np.random.Generator(np.random.Philox(4))
     b = rng.uniform(-1, 1, (K, N)).astype(np.float16)
-    rows = 8
-    a = rng.uniform(-1, 1, (rows, K)).astype(np.float16)
-    t0 = time.perf_counter()
-    oracle.gemm_f16(a, b, threads=threads)
-    pilot = time.perf_counter() - t0  # includes widening B to fp32 once per call
-    t0 = time.perf_counter()
-    oracle.gemm_f16(a, b, threads=threads)
-    pilot = min(pilot, time.perf_counter() - t0)
-    per_row = max(pilot / rows, 1e-6)
-    rows = int(max(threads, min(512, target_s / per_row)))
-    rows -= rows % max(1, min(threads, rows))
-    a = rng.uniform(-1, 1, (rows, K)).astype(np.float16)
-    return a, b, rows, threads
+
+    def once(rows):
+        a = rng.uniform(-1, 1, (rows, K)).astype(np.float16)
+        t0 = time.perf_counter()
+        oracle.gemm_f16(a, b, threads=threads)
+        return time.perf_counter() - t0
+    once(threads)  # page in
+    # every call widens B to fp32 once (fixed cost); the slope between two slab sizes is the per-row cost
+    t_small, t_large = once(threads), once(3 * threads)
+    per_row = max((t_large - t_small) / (2 * threads), 1e-6)
+    fixed = max(t_small - per_row * threads, 0.0)
+    rows = int(max(threads, min(4096, (target_s - fixed) / per_row)))
+    rows -= rows % threads
+    a = rng.uniform(-1, 1, (max(rows, threads), K)).astype(np.float16)
+    return a, b, a.shape[0], threads
 
 
 def cpu_time_once(a, b, threads):
@@ -222,9 +220,9 @@ def extras_single_gpu(torch, hm, peaks, only=None):
     def rand_h(shape, lo=-1.0, hi=1.0):
         return (torch.rand(shape, generator=g, device=dev) * (hi - lo) + lo).half()
 
-    for n in (1024, 4096):
-        if not want(f"gemm_f16_{n}"):
-            continue
+    for n in (1024, 4096, 8192):
+        if not want(f"gemm_f16_{n}") or (n == 8192 and only is None):
+            continue  # 8192^3 runs only when asked for by name (the 2-CTA kernel's capture)
         # rotate over enough operand sets to exceed L2 between launches
         sets = max(2, int(np.ceil(3 * 126e6 / (3 * n * n * 2))))
         sets = min(sets, 24)
@@ -242,80 +240,82 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         out[f"gemm_f16_{n}^3"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                                   "variant": hm.gemm_explain(n, n, n)["name"]}
         del A, B, C
-    if only is not None and not any(want(x) for x in ("softmax", "rmsnorm", "swiglu", "w8a16")):
-        return out
-    # C2 softmax [4096,1024]: 16 MiB in + out per launch; 12 buffer pairs (201 MB) rotate past L2
-    sets = 12
-    X = [(torch.randn((4096, 1024), generator=g, device=dev) * 3).half() for _ in range(sets)]
-    Y = [torch.empty_like(X[0]) for _ in range(sets)]
-    state = {"i": 0}
-
-    def sm():
-        i = state["i"] % sets
-        state["i"] += 1
-        hm.softmax_kernel[(1,)](X[i], Y[i])
-    ms = graph_timed(torch, sm, reps=10, inner=sets * 2)
-    gbs = 2 * 4096 * 1024 * 2 / (ms * 1e-3) / 1e9
-    out["softmax_f16_4096x1024"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
-    del X, Y
-    # RMSNorm / SwiGLU at the MLP's shapes
-    x = torch.randn((2048, 4096), generator=g, device=dev).half()
-    xs = [x.clone() for _ in range(8)]
-    ys = [torch.empty_like(x) for _ in range(8)]
-    w = torch.ones(4096, dtype=torch.float16, device=dev)
-    state = {"i": 0}
-
-    def rn():
-        i = state["i"] % 8
-        state["i"] += 1
-        hm.rms_norm_fwd_kernel[(1,)](xs[i], ys[i], w, EPSILON=1e-6)
-    ms = graph_timed(torch, rn, reps=10, inner=16)
-    gbs = (2 * 2048 * 4096 * 2 + 4096 * 2) / (ms * 1e-3) / 1e9
-    out["rmsnorm_f16_2048x4096"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
-    del xs, ys
-    nel = 2048 * 11008
-    gs = [torch.randn(nel, generator=g, device=dev).half() for _ in range(3)]
-    us = [torch.randn(nel, generator=g, device=dev).half() for _ in range(3)]
-    os_ = [torch.empty(nel, dtype=torch.float16, device=dev) for _ in range(3)]
-    state = {"i": 0}
-
-    def sw():
-        i = state["i"] % 3
-        state["i"] += 1
-        hm.swiglu_kernel[(1,)](gs[i], us[i], os_[i])
-    ms = graph_timed(torch, sw, reps=10, inner=6)
-    gbs = 3 * nel * 2 / (ms * 1e-3) / 1e9
-    out["swiglu_f16_2048x11008"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
-    del gs, us, os_
-    # C3 w8a16: four distinct resident weights (180 MB) rotate past L2 = cold-L2 number;
-    # one weight re-used = L2-resident number
-    k, n = 4096, 11008
-    Wq = [torch.randint(-127, 128, (k, n), generator=g, device=dev, dtype=torch.int8) for _ in range(4)]
-    S = (torch.rand(n, generator=g, device=dev) * 0.019 + 0.001).half()
-    for mrows in (1, 16, 256):
-        a = torch.randn((mrows, k), generator=g, device=dev).half()
-        c = torch.empty((mrows, n), dtype=torch.float16, device=dev)
+    if want("softmax"):
+        # C2 softmax [4096,1024]: 16 MiB in + out per launch; 12 buffer pairs (201 MB) rotate past L2
+        sets = 12
+        X = [(torch.randn((4096, 1024), generator=g, device=dev) * 3).half() for _ in range(sets)]
+        Y = [torch.empty_like(X[0]) for _ in range(sets)]
         state = {"i": 0}
 
-        def wf():
-            i = state["i"] % 4
+        def sm():
+            i = state["i"] % sets
             state["i"] += 1
-            hm.w8a16_matmul[(1,)](a, Wq[i], S, c)
+            hm.softmax_kernel[(1,)](X[i], Y[i])
+        ms = graph_timed(torch, sm, reps=10, inner=sets * 2)
+        gbs = 2 * 4096 * 1024 * 2 / (ms * 1e-3) / 1e9
+        out["softmax_f16_4096x1024"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+        del X, Y
+    if want("rmsnorm"):
+        # RMSNorm / SwiGLU at the MLP's shapes
+        x = torch.randn((2048, 4096), generator=g, device=dev).half()
+        xs = [x.clone() for _ in range(8)]
+        ys = [torch.empty_like(x) for _ in range(8)]
+        w = torch.ones(4096, dtype=torch.float16, device=dev)
+        state = {"i": 0}
 
-        def wf_same():
-            hm.w8a16_matmul[(1,)](a, Wq[0], S, c)
-        for _ in range(4):
-            wf()
-        ms = graph_timed(torch, wf, reps=10, inner=8)
-        ms_hot = graph_timed(torch, wf_same, reps=10, inner=8)
-        bytes_ = k * n + 2 * n + 2 * mrows * k + 2 * mrows * n
-        gbs = bytes_ / (ms * 1e-3) / 1e9
-        out[f"w8a16_m{mrows}_4096x11008"] = {
-            "us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-            "us_weight_in_l2": ms_hot * 1e3, "tflops": 2.0 * mrows * k * n / (ms * 1e-3) / 1e12}
-    for wq_ in Wq:
-        hm.unregister_w8a16_weight(wq_)
-    del Wq
+        def rn():
+            i = state["i"] % 8
+            state["i"] += 1
+            hm.rms_norm_fwd_kernel[(1,)](xs[i], ys[i], w, EPSILON=1e-6)
+        ms = graph_timed(torch, rn, reps=10, inner=16)
+        gbs = (2 * 2048 * 4096 * 2 + 4096 * 2) / (ms * 1e-3) / 1e9
+        out["rmsnorm_f16_2048x4096"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+        del xs, ys
+    if want("swiglu"):
+        nel = 2048 * 11008
+        gs = [torch.randn(nel, generator=g, device=dev).half() for _ in range(3)]
+        us = [torch.randn(nel, generator=g, device=dev).half() for _ in range(3)]
+        os_ = [torch.empty(nel, dtype=torch.float16, device=dev) for _ in range(3)]
+        state = {"i": 0}
+
+        def sw():
+            i = state["i"] % 3
+            state["i"] += 1
+            hm.swiglu_kernel[(1,)](gs[i], us[i], os_[i])
+        ms = graph_timed(torch, sw, reps=10, inner=6)
+        gbs = 3 * nel * 2 / (ms * 1e-3) / 1e9
+        out["swiglu_f16_2048x11008"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+        del gs, us, os_
+    if want("w8a16"):
+        # C3 w8a16: four distinct resident weights (180 MB) rotate past L2 = cold-L2 number;
+        # one weight re-used = L2-resident number
+        k, n = 4096, 11008
+        Wq = [torch.randint(-127, 128, (k, n), generator=g, device=dev, dtype=torch.int8) for _ in range(4)]
+        S = (torch.rand(n, generator=g, device=dev) * 0.019 + 0.001).half()
+        for mrows in (1, 16, 256):
+            a = torch.randn((mrows, k), generator=g, device=dev).half()
+            c = torch.empty((mrows, n), dtype=torch.float16, device=dev)
+            state = {"i": 0}
+
+            def wf():
+                i = state["i"] % 4
+                state["i"] += 1
+                hm.w8a16_matmul[(1,)](a, Wq[i], S, c)
+
+            def wf_same():
+                hm.w8a16_matmul[(1,)](a, Wq[0], S, c)
+            for _ in range(4):
+                wf()
+            ms = graph_timed(torch, wf, reps=10, inner=8)
+            ms_hot = graph_timed(torch, wf_same, reps=10, inner=8)
+            bytes_ = k * n + 2 * n + 2 * mrows * k + 2 * mrows * n
+            gbs = bytes_ / (ms * 1e-3) / 1e9
+            out[f"w8a16_m{mrows}_4096x11008"] = {
+                "us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                "us_weight_in_l2": ms_hot * 1e3, "tflops": 2.0 * mrows * k * n / (ms * 1e-3) / 1e12}
+        for wq_ in Wq:
+            hm.unregister_w8a16_weight(wq_)
+        del Wq
     return out
 
 
@@ -359,6 +359,11 @@ def run_product_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # Libraries (NCCL's version banner, for one) print to stdout; the contract is ONE JSON line
+    # there, so everything else goes to stderr and the line is written to the saved descriptor.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world != args.gpus and world > 1:
         args.gpus = world
     if not torch.cuda.is_available():
@@ -372,7 +377,8 @@ def run_product_arm(args):
     peaks, peak_kind = load_peaks()
     if args.case:
         # one small case of `extra` alone (what the ncu captures under profiles/ run)
-        print(json.dumps({"case": args.case, "result": extras_single_gpu(torch, hm, peaks, only=args.case)}))
+        line = json.dumps({"case": args.case, "result": extras_single_gpu(torch, hm, peaks, only=args.case)})
+        os.write(json_fd, (line + "\n").encode())
         return 0
 
     # inputs resident in HBM: A replicated, this rank's column block of B and C
@@ -454,7 +460,8 @@ def run_product_arm(args):
                     "d2h_bytes_per_step": M * n_loc * 2 * world, "steps": e2e_steps, "matches_device_run": e2e_ok},
             "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
         }
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
     if multi:
         dist.destroy_process_group()
     return 0
@@ -467,8 +474,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--case", default="", help="run one case of `extra` only: gemm_f16_1024, gemm_f16_4096, "
-                                               "softmax (the row kernels and w8a16 together)")
+    ap.add_argument("--case", default="", help="run one case of `extra` only (profiling captures): gemm_f16_1024, "
+                                               "gemm_f16_4096, gemm_f16_8192, softmax, rmsnorm, swiglu, w8a16")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup

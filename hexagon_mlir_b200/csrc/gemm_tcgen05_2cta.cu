@@ -172,12 +172,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int m0 = m_blk * 256 + (int)rank * BM2;
         const int n0 = n_blk * BN_OUT;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (tile == pair) TR2(0, kb);
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 31, tile)) {
             ok = false;
             break;
           }
-          if (tile == pair) TR2(1, kb);
           const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);  // the leader's barrier
           remote_expect_tx(full, STAGE_BYTES);
 #pragma unroll
@@ -196,7 +194,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               tma_load_2d_pair(sb + SLAB_BYTES, &tmB, full, nb + 64, k0);
             }
           }
-          if (tile == pair) TR2(2, kb);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -212,18 +209,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
+      int tord = 0;
+      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++tord) {
+        TR2(0, tord);
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 32, tile)) break;
         tc_fence_after_sync();
+        TR2(1, tord);
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_MMA);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (tile == pair) TR2(3, kb);
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 33, tile)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          if (tile == pair) TR2(4, kb);
 #pragma unroll
           for (int sub = 0; sub < NSUB; ++sub) {
             const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * STAGE2_BYTES;
@@ -236,7 +234,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                            (kb | sub | k) != 0 ? 1u : 0u);
           }
           mma_commit_pair(bar_empty + 8 * stage);  // both producers may refill the stage
-          if (tile == pair) TR2(5, kb);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -244,6 +241,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         if (!ok) break;
         mma_commit_pair(bar_tfull + 8 * acc);  // accumulators complete in both CTAs
+        TR2(2, tord);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;
@@ -255,7 +253,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
+    int tord = 0;
+    for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++tord) {
       int m_blk, n_blk;
       tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
       const int m0 = m_blk * 256 + (int)rank * BM2, n0 = n_blk * BN_OUT;
@@ -263,6 +262,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
+      if (threadIdx.x == 64) TR2(3, tord);
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.m;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA);
@@ -279,6 +279,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
       tc_fence_before_sync();
       __syncwarp();
+      if (threadIdx.x == 64) TR2(4, tord);
       if (lane == 0) remote_arrive(map_to_cta(bar_tempty + 8 * acc, 0));  // the leader's barrier
       if (++acc == 2) {
         acc = 0;

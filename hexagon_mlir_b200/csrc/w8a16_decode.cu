@@ -135,6 +135,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p)
   __shared__ long long trace_s[8 * 64];
 #endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) TR(7, 0);
   // this CTA's channels, walked in passes of at most CH_PASS
   const int c_begin = (int)((int64_t)p.n * blockIdx.x / gridDim.x);
   const int c_end = (int)((int64_t)p.n * (blockIdx.x + 1) / gridDim.x);
@@ -162,6 +163,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p)
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_gen;
+  if (threadIdx.x == 0) TR(7, 1);
 
   // Every CTA needs the same activation tile for a given k chunk; each CTA starts
   // at its own step so that they do not all ask one L2 slice for the same lines at
@@ -254,10 +256,13 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p)
       for (int d = 0; d < D_AHEAD - 1; ++d) issue(d);
       for (int j = 0; j < steps; ++j, ++t) {
         const int b = t % NB;
+        if (tid == 0) TR(0, t);
         cp_async_wait<D_AHEAD - 2>();  // this thread's copies of step j have landed
+        if (tid == 0) TR(1, t);
         bool ok = mbar_wait(bar_free + 8 * b, (uint32_t)(((t / NB) & 1) ^ 1), abort_flag, p.status, 27, t);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) goto done;
+        if (tid == 0) TR(2, t);
         if (mine) {
           int st = j + rot;
           if (st >= steps) st -= steps;
@@ -277,6 +282,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p)
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_conv + 8 * b);
       }
+      if (tid == 0) TR(7, 2);
       cp_async_wait<0>();
       // end of K for this pass: read the accumulators out, add them, scale, round, store
       {
@@ -284,6 +290,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p)
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) goto done;
         tc_fence_after_sync();
+        if (tid == 0) TR(7, 3);
         if (warp < 4) {
           const int chl = q * 32 + lane;  // channel = TMEM lane
           const bool live = chl < ch;
@@ -311,6 +318,7 @@ w8a16_tc_kernel(const __grid_constant__ CUtensorMap tmA, const TcDecodeParams p)
             }
           }
         }
+        if (tid == 0) TR(7, 4);
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_aempty);

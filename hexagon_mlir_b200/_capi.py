@@ -56,6 +56,7 @@ _SIGNATURES = {
     "b200mlir_get_option": (c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_double)]),
     "matmul": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
     "klooped_matmul": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
+    "multispan_matmul": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
     "matmul_f32out": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
     "matmul_i8": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
     "softmax_kernel_float16": (None, [c_i64, _M2, c_i64, _M2] + _GRID),
@@ -116,6 +117,18 @@ _SIGNATURES = {
     "b200mlir_autotune_cache_clear": (None, []),
     "b200mlir_benchmark": (c_int, [ctypes.CFUNCTYPE(None, c_void_p), c_void_p, c_int,
                                    ctypes.POINTER(ctypes.c_double)]),
+    "b200mlir_benchmark_report": (c_int, [ctypes.CFUNCTYPE(None, c_void_p), c_void_p, c_int, ctypes.c_char_p,
+                                          ctypes.c_char_p, ctypes.POINTER(ctypes.c_double),
+                                          ctypes.POINTER(ctypes.c_longlong)]),
+    "b200mlir_perf_report_save": (c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_double, ctypes.c_char_p,
+                                          c_int, ctypes.c_longlong]),
+    "b200mlir_dtype_size": (c_int, [ctypes.c_int32]),
+    "b200mlir_tensor_dump": (c_int, [ctypes.c_char_p, ctypes.c_int32, c_i64, ctypes.POINTER(c_i64), c_void_p]),
+    "b200mlir_tensor_file_info": (c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(c_i64),
+                                          ctypes.POINTER(c_i64), ctypes.POINTER(c_i64)]),
+    "b200mlir_tensor_load": (c_int, [ctypes.c_char_p, c_int, c_void_p, c_i64]),
+    "b200mlir_manifest_json": (c_int, [ctypes.c_char_p, c_int]),
+    "b200mlir_manifest_reset": (None, []),
 }
 
 

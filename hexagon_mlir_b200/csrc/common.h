@@ -65,6 +65,10 @@ int workspace(size_t bytes, void **out);
 // Second, independent workspace for callers that hold the first.
 int workspace2(size_t bytes, void **out);
 
+// ---- manifest of planned matmuls (report.cu) ---------------------------------------
+struct GemmArgs;
+void manifest_record(const GemmArgs &g, int variant, const std::string &why);
+
 // ---- pointer classification / host staging -------------------------------------
 bool is_device_ptr(const void *p);
 

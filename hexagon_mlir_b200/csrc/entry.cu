@@ -225,6 +225,13 @@ void matmul(int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc
   matmul_impl(EPI_F16, ra, a, rb, b, rc, c, 0, nullptr);
 }
 
+void multispan_matmul(int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc, B200MemRef2D *c,
+                      B200_GRID_ARGS) {
+  // spans are a tiling the caller's kernel expresses; one call covers every span
+  ENTER_KERNEL();
+  matmul_impl(EPI_F16, ra, a, rb, b, rc, c, 0, nullptr);
+}
+
 void klooped_matmul(int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc,
                     B200MemRef2D *c, B200_GRID_ARGS) {
   ENTER_KERNEL();

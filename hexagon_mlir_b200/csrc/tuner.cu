@@ -383,7 +383,9 @@ int choose_gemm_variant(const GemmArgs &g, std::string *why) {
 int gemm_dispatch(const GemmArgs &g) {
   B200_TRY(ensure_ready());
   if (g.m <= 0 || g.n <= 0) return 0;
-  int v = choose_gemm_variant(g, nullptr);
+  std::string why;
+  int v = choose_gemm_variant(g, &why);
+  manifest_record(g, v, why);
   if (v >= 0) return launch_gemm_tc(v, g);
   return launch_gemm_simt(g);
 }

@@ -136,6 +136,7 @@ class Kernel:
 
 matmul = Kernel("matmul", (2, 2, 2))
 klooped_matmul = Kernel("klooped_matmul", (2, 2, 2), scalar_options={"BLOCK_K": "kloopBlockK"})
+multispan_matmul = Kernel("multispan_matmul", (2, 2, 2))  # test_matmul_multispan.py:82-107
 matmul_i8 = Kernel("matmul_i8", (2, 2, 2))
 softmax_kernel = Kernel("softmax_kernel", (2, 2), by_dtype=True)
 rms_norm_fwd_kernel = Kernel("rms_norm_fwd_kernel", (2, 2, 1), by_dtype=True,
@@ -340,6 +341,91 @@ def autotune_cache_load(path: str) -> None:
 
 def autotune_cache_clear() -> None:
     lib().b200mlir_autotune_cache_clear()
+
+
+# ---- the reference harness's file formats and manifest ------------------------------------
+
+# dtype ids of the raw tensor files (test/utils/dsp/include/tensor.h:26-38)
+DTYPE_IDS = {"bool": 0, "float16": 1, "float32": 2, "float64": 3, "int8": 4, "int16": 5, "int32": 6,
+             "int64": 7, "uint8": 8, "uint16": 9, "uint32": 10}
+_ID_TO_NP = {v: np.dtype(k) for k, v in DTYPE_IDS.items()}
+
+
+def _host_or_device(t):
+    """(pointer, numpy dtype, shape, keep-alive) of a contiguous numpy array or torch tensor."""
+    if isinstance(t, np.ndarray):
+        a = t if t.flags.c_contiguous else t.copy(order="C")  # (ascontiguousarray would promote rank 0)
+        return a.ctypes.data, a.dtype, a.shape, a
+    if torch is not None and isinstance(t, torch.Tensor):
+        c = t.contiguous()
+        return c.data_ptr(), np.dtype(str(c.dtype).replace("torch.", "")), tuple(c.shape), c
+    raise TypeError(f"unsupported tensor type {type(t)!r}")
+
+
+def tensor_dump(path, t) -> None:
+    """Write `t` as an output file of the reference's harness: header + data."""
+    ptr, dt, shape, keep = _host_or_device(t)
+    dims = (ctypes.c_int64 * max(1, len(shape)))(*shape)
+    if lib().b200mlir_tensor_dump(str(path).encode(), DTYPE_IDS[dt.name], len(shape), dims, ptr) != 0:
+        check()
+    del keep
+
+
+def tensor_file_info(path):
+    """(numpy dtype, shape) of an output file."""
+    dt, rank, nbytes = ctypes.c_int32(), ctypes.c_int64(), ctypes.c_int64()
+    dims = (ctypes.c_int64 * 8)()
+    if lib().b200mlir_tensor_file_info(str(path).encode(), ctypes.byref(dt), ctypes.byref(rank), dims,
+                                       ctypes.byref(nbytes)) != 0:
+        check()
+    return _ID_TO_NP[dt.value], tuple(dims[i] for i in range(rank.value))
+
+
+def tensor_load(path, out=None, has_header=True):
+    """Read a tensor file.  With a header (an output file) the result is allocated from it
+    unless `out` is given; without one (an input file) `out` supplies dtype, shape and place."""
+    if out is None:
+        if not has_header:
+            raise ValueError("an input file has no header: pass `out`")
+        dt, shape = tensor_file_info(path)
+        out = np.empty(shape, dt)
+    ptr, dt, shape, keep = _host_or_device(out)
+    if keep is not out and not (isinstance(out, np.ndarray) and keep.ctypes.data == out.ctypes.data):
+        raise ValueError("`out` must be contiguous")
+    nbytes = int(np.prod(shape, dtype=np.int64)) * dt.itemsize
+    if lib().b200mlir_tensor_load(str(path).encode(), 1 if has_header else 0, ptr, nbytes) != 0:
+        check()
+    return out
+
+
+def perf_report_save(path, name, perf, units="us", result="Pass", cycles=None) -> None:
+    code = {"Pass": 0, "Fail": 1}.get(result, 2)
+    if lib().b200mlir_perf_report_save(str(path).encode(), name.encode(), float(perf), units.encode(), code,
+                                       -1 if cycles is None else int(cycles)) != 0:
+        check()
+
+
+def benchmark_report(fn, iterations, name, path=None):
+    """One discarded call of `fn`, `iterations` timed ones; returns (mean us, mean SM cycles)
+    and writes perf.txt at `path` (hexagon_launcher_base.py:153-192)."""
+    thunk_t = ctypes.CFUNCTYPE(None, ctypes.c_void_p)
+    thunk = thunk_t(lambda _u: fn())
+    us, cyc = ctypes.c_double(), ctypes.c_longlong()
+    rc = lib().b200mlir_benchmark_report(thunk, None, int(iterations), name.encode(),
+                                         None if path is None else str(path).encode(),
+                                         ctypes.byref(us), ctypes.byref(cyc))
+    if rc != 0:
+        check()
+    return us.value, cyc.value
+
+
+def manifest() -> dict:
+    """{"matmuls": [{plan, reason, detail, shape_mnk, epilogue, variant, name, launches}]} since the last reset."""
+    return _json_call(lambda buf, cap: lib().b200mlir_manifest_json(buf, cap), cap=1 << 17)[1]
+
+
+def manifest_reset() -> None:
+    lib().b200mlir_manifest_reset()
 
 
 __all__ = [n for n in dir() if not n.startswith("_")] + ["B200Error"]

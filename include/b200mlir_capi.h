@@ -111,6 +111,12 @@ B200_API int b200mlir_get_option(const char *name, double *value);
  * mma, acc_store) and the pack/unpack leaves of hmx/src/HMXLayout.c. */
 B200_API void matmul(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B200MemRef2D *b,
                      int64_t rank_c, B200MemRef2D *c, B200_GRID_ARGS);
+/* The multi-span form: the kernel tiles M and N itself (BLOCK_M x BLOCK_N spans, whole K),
+ * each span stored to its own window of C with C's row stride
+ * (test/python/triton/test_matmul_multispan.py:82-107).  The span sizes are tl.constexpr
+ * and do not reach the ABI; one rounding per element, like `matmul`. */
+B200_API void multispan_matmul(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B200MemRef2D *b,
+                               int64_t rank_c, B200MemRef2D *c, B200_GRID_ARGS);
 /* Same contraction with the K-segmented accumulation of a K-looped tl.dot:
  * each BLOCK_K segment is read out as fp16, widened and added in fp32
  * (test/python/triton/test_matmul_kloop.py:27-34,87-98).  BLOCK_K = option
@@ -318,6 +324,39 @@ B200_API void b200mlir_autotune_cache_clear(void);
  * library's stream.  *mean_us receives the mean per call. */
 typedef void (*b200mlir_thunk)(void *user);
 B200_API int b200mlir_benchmark(b200mlir_thunk fn, void *user, int iterations, double *mean_us);
+
+/* The generated wrapper's timed section together with its report
+ * (backend/hexagon_launcher_base.py:153-192): one discarded call, `iterations` timed
+ * calls, then perf.txt at `path` (NULL: no file) — the Test_Info block of
+ * test/utils/dsp/include/test_report.h:43-66 followed by "PerfPcycles:<n>", both from
+ * the same pass, which backend/hmx_search.py:1074-1092 parses.  Cycles are SM clock
+ * cycles per call (two stamps on the stream; time x rated clock if they land on
+ * different SMs). */
+B200_API int b200mlir_benchmark_report(b200mlir_thunk fn, void *user, int iterations, const char *name,
+                                       const char *path, double *mean_us, long long *mean_cycles);
+/* result: 0 Pass, 1 Fail, other Unknown; cycles < 0 omits the PerfPcycles line. */
+B200_API int b200mlir_perf_report_save(const char *path, const char *name, double perf, const char *units,
+                                       int result, long long cycles);
+
+/* Raw tensor files of the reference's device harness
+ * (test/utils/dsp/include/tensor.h:219-259; dtype ids :26-38; host reader
+ * backend/hexagon_executor.py:200-216).  Output files: u32 dtype id, i64 rank,
+ * i64 dims[rank], data.  Input files: data only.  `data` / `dst` may be host or device
+ * pointers; rank <= 8. */
+B200_API int b200mlir_dtype_size(int32_t dtype_id);
+B200_API int b200mlir_tensor_dump(const char *path, int32_t dtype_id, int64_t rank, const int64_t *dims,
+                                  const void *data);
+B200_API int b200mlir_tensor_file_info(const char *path, int32_t *dtype_id, int64_t *rank, int64_t *dims,
+                                       int64_t *data_bytes);
+B200_API int b200mlir_tensor_load(const char *path, int has_header, void *dst, int64_t bytes);
+
+/* Manifest of the matmuls dispatched since the last reset, in the vocabulary of
+ * include/hexagon/Dialect/Hmx/Transforms/HmxManifest.h:81-111: plan "full-hmx"
+ * (tensor cores, whole tiles) / "hmx-tail" (tensor cores, edge tiles) / "hvx"
+ * (CUDA-core path) and the canonical reason; `detail` is this library's own wording.
+ * Returns the length of the JSON text. */
+B200_API int b200mlir_manifest_json(char *json, int cap);
+B200_API void b200mlir_manifest_reset(void);
 
 #ifdef __cplusplus
 }

@@ -64,6 +64,9 @@ int check_launch(const char *what);
 int workspace(size_t bytes, void **out);
 // Second, independent workspace for callers that hold the first.
 int workspace2(size_t bytes, void **out);
+// Device image of host tensors for the pipelined host-buffer GEMM, and its two copy streams.
+int staging_workspace(size_t bytes, void **out);
+int copy_streams(cudaStream_t *in, cudaStream_t *out);
 
 // ---- manifest of planned matmuls (report.cu) ---------------------------------------
 struct GemmArgs;

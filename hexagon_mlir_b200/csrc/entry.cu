@@ -3,6 +3,8 @@
 // backend/triton_hexagon_launcher.py:241-252).  Validates descriptors, stages
 // host tensors through device memory, and hands device pointers to the
 // dispatcher.  Nothing here computes on the CPU.
+#include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -120,6 +122,118 @@ int check_grid(int nx, int ny, int nz, int px, int py, int pz) {
   return 0;
 }
 
+// fp16 GEMM whose three tensors live in host memory, large enough that the PCIe transfers
+// dominate: A is cut into row panels and B into column panels, panels go up in the order
+// A0 B0 A1 B1 ..., the strips of C that a panel completes are computed as soon as it has landed and go
+// back down on a third stream while later panels are still on their way up.  The link is
+// full duplex, so the call approaches max(bytes up, bytes down) / link rate instead of their sum.
+constexpr size_t kPipelineMinBytes = 96u << 20;
+
+int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
+  const int64_t M = A.rows, K = A.cols, N = B.cols;
+  const int64_t P = std::max<int64_t>(2, std::min<int64_t>(16, std::min(M, N) / 1024));
+  // panel edges on multiples of 256 rows / columns (whole tiles of the widest variant)
+  const int64_t pm = ((M + P - 1) / P + 255) / 256 * 256, pn = ((N + P - 1) / P + 255) / 256 * 256;
+  const int64_t PM = (M + pm - 1) / pm, PN = (N + pn - 1) / pn;
+  cudaStream_t s_in, s_out, s = ctx().stream;
+  B200_TRY(copy_streams(&s_in, &s_out));
+  void *base = nullptr;
+  const size_t a_bytes = (size_t)M * K * 2, b_bytes = (size_t)K * N * 2, c_bytes = (size_t)M * N * 2;
+  B200_TRY(staging_workspace(a_bytes + b_bytes + c_bytes + 512, &base));
+  __half *dA = (__half *)base;
+  __half *dB = (__half *)((char *)base + ((a_bytes + 255) & ~(size_t)255));
+  __half *dC = (__half *)((char *)dB + ((b_bytes + 255) & ~(size_t)255));
+  std::vector<cudaEvent_t> ev;
+  auto new_event = [&](cudaEvent_t *e) -> cudaError_t {
+    cudaError_t r = cudaEventCreateWithFlags(e, cudaEventDisableTiming);
+    if (r == cudaSuccess) ev.push_back(*e);
+    return r;
+  };
+  int rc = 0;
+  cudaError_t e = cudaSuccess;
+  std::vector<cudaEvent_t> a_up(PM), b_up(PN);
+  cudaEvent_t start, done;
+#define PIPE_CUDA(expr)                                                                      \
+  if (rc == 0 && (e = (expr)) != cudaSuccess)                                                 \
+  rc = set_error(B200MLIR_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e))
+  // the copy streams start after whatever the caller queued before this call
+  cudaEvent_t t0 = nullptr;
+  if (getenv("B200MLIR_DEBUG")) { cudaEventCreate(&t0); cudaEventRecord(t0, s); }
+  PIPE_CUDA(new_event(&start));
+  PIPE_CUDA(cudaEventRecord(start, s));
+  PIPE_CUDA(cudaStreamWaitEvent(s_in, start, 0));
+  PIPE_CUDA(cudaStreamWaitEvent(s_out, start, 0));
+  for (int64_t d = 0; d < std::max(PM, PN) && rc == 0; ++d) {
+    if (d < PM) {
+      const int64_t r0 = d * pm, rows = std::min(pm, M - r0);
+      PIPE_CUDA(cudaMemcpy2DAsync(dA + r0 * K, (size_t)K * 2, (const __half *)A.p + r0 * A.ld, (size_t)A.ld * 2,
+                                  (size_t)K * 2, (size_t)rows, cudaMemcpyHostToDevice, s_in));
+      PIPE_CUDA(new_event(&a_up[d]));
+      PIPE_CUDA(cudaEventRecord(a_up[d], s_in));
+    }
+    if (d < PN) {
+      const int64_t c0 = d * pn, cols = std::min(pn, N - c0);
+      PIPE_CUDA(cudaMemcpy2DAsync(dB + c0, (size_t)N * 2, (const __half *)B.p + c0, (size_t)B.ld * 2,
+                                  (size_t)cols * 2, (size_t)K, cudaMemcpyHostToDevice, s_in));
+      PIPE_CUDA(new_event(&b_up[d]));
+      PIPE_CUDA(cudaEventRecord(b_up[d], s_in));
+    }
+    // what panel d completes: the row strip (row panel d x column panels 0..d) and the column
+    // strip (row panels 0..d-1 x column panel d); one GEMM and one copy down for each
+    for (int strip = 0; strip < 2 && rc == 0; ++strip) {
+      int64_t r0, rows, c0, cols;
+      if (strip == 0) {
+        if (d >= PM) continue;
+        r0 = d * pm; rows = std::min(pm, M - r0);
+        c0 = 0; cols = std::min((d + 1) * pn, N);
+      } else {
+        if (d >= PN || d == 0) continue;
+        r0 = 0; rows = std::min(d * pm, M);
+        c0 = d * pn; cols = std::min(pn, N - c0);
+      }
+      if (rows <= 0 || cols <= 0) continue;
+      if (d < PM) PIPE_CUDA(cudaStreamWaitEvent(s, a_up[d], 0));
+      if (d < PN) PIPE_CUDA(cudaStreamWaitEvent(s, b_up[d], 0));
+      GemmArgs g;
+      g.a = dA + r0 * K; g.b = dB + c0; g.c = dC + r0 * N + c0;
+      g.m = rows; g.n = cols; g.k = K;
+      g.lda = K; g.ldb = N; g.ldc = N;
+      g.epilogue = EPI_F16;
+      if (rc == 0) rc = gemm_dispatch(g);
+      cudaEvent_t blk;
+      PIPE_CUDA(new_event(&blk));
+      PIPE_CUDA(cudaEventRecord(blk, s));
+      PIPE_CUDA(cudaStreamWaitEvent(s_out, blk, 0));
+      PIPE_CUDA(cudaMemcpy2DAsync((__half *)C.p + r0 * C.ld + c0, (size_t)C.ld * 2, dC + r0 * N + c0, (size_t)N * 2,
+                                  (size_t)cols * 2, (size_t)rows, cudaMemcpyDeviceToHost, s_out));
+    }
+  }
+  cudaEvent_t t_up = nullptr, t_mm = nullptr, t_down = nullptr;
+  const bool debug = t0 != nullptr;
+  if (debug) {
+    cudaEventCreate(&t_up); cudaEventCreate(&t_mm); cudaEventCreate(&t_down);
+    cudaEventRecord(t_up, s_in); cudaEventRecord(t_mm, s); cudaEventRecord(t_down, s_out);
+  }
+  // the caller's stream continues after the last copy down; the call itself waits for it
+  PIPE_CUDA(new_event(&done));
+  PIPE_CUDA(cudaEventRecord(done, s_out));
+  PIPE_CUDA(cudaStreamWaitEvent(s, done, 0));
+#undef PIPE_CUDA
+  cudaError_t e1 = cudaStreamSynchronize(s_in), e2 = cudaStreamSynchronize(s_out), e3 = cudaStreamSynchronize(s);
+  if (debug) {  // B200MLIR_DEBUG: when each of the three streams finished
+    float a = 0, b = 0, c = 0;
+    cudaEventElapsedTime(&a, t0, t_up); cudaEventElapsedTime(&b, t0, t_mm); cudaEventElapsedTime(&c, t0, t_down);
+    fprintf(stderr, "[b200mlir] pipelined host GEMM %lldx%lldx%lld P=%lld: up done %.2f ms, compute done %.2f ms, down done %.2f ms\n",
+            (long long)M, (long long)N, (long long)K, (long long)P, a, b, c);
+    cudaEventDestroy(t0); cudaEventDestroy(t_up); cudaEventDestroy(t_mm); cudaEventDestroy(t_down);
+  }
+  for (cudaEvent_t x : ev) cudaEventDestroy(x);
+  if (rc == 0 && (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess))
+    rc = set_error(B200MLIR_ERR_CUDA, "pipelined host GEMM: %s",
+                   cudaGetErrorString(e1 != cudaSuccess ? e1 : e2 != cudaSuccess ? e2 : e3));
+  return rc;
+}
+
 int matmul_impl(int epilogue, int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t rc,
                 B200MemRef2D *c, int64_t rr, B200MemRef2D *res) {
   B200_TRY(ensure_ready());
@@ -137,6 +251,10 @@ int matmul_impl(int epilogue, int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRe
   if (has_res && (R.rows != C.rows || R.cols != C.cols))
     return set_error(B200MLIR_ERR_BAD_ARG, "matmul: residual shape differs from C");
   if (C.rows == 0 || C.cols == 0) return 0;
+  if (epilogue == EPI_F16 && A.cols > 0 && std::min(A.rows, B.cols) >= 4096 && A.cols % 8 == 0 && B.cols % 8 == 0 &&
+      A.span(2) + B.span(2) + C.span(2) >= kPipelineMinBytes && !is_device_ptr(A.p) && !is_device_ptr(B.p) &&
+      !is_device_ptr(C.p))
+    return matmul_host_pipelined(A, B, C);
   Stager st;
   GemmArgs g;
   B200_TRY(st.in(A.p, A.span(2), &g.a));

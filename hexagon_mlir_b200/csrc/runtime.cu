@@ -89,13 +89,13 @@ int check_launch(const char *what) {
   return 0;
 }
 
-// Two grow-only workspaces.  Growing frees and reallocates, so it must not
+// Grow-only workspaces (two for kernels' intermediates, one for staged host tensors).  Growing frees and reallocates, so it must not
 // happen inside a stream capture: callers warm up once outside any capture.
 struct Arena {
   void *p = nullptr;
   size_t cap = 0;
 };
-static Arena g_ws[2];
+static Arena g_ws[3];
 
 static int ws_get(int which, size_t bytes, void **out) {
   Arena &a = g_ws[which];
@@ -115,6 +115,17 @@ static int ws_get(int which, size_t bytes, void **out) {
 }
 int workspace(size_t bytes, void **out) { return ws_get(0, bytes, out); }
 int workspace2(size_t bytes, void **out) { return ws_get(1, bytes, out); }
+int staging_workspace(size_t bytes, void **out) { return ws_get(2, bytes, out); }
+
+int copy_streams(cudaStream_t *in, cudaStream_t *out) {
+  static cudaStream_t s_in = nullptr, s_out = nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!s_in) B200_CUDA(cudaStreamCreateWithFlags(&s_in, cudaStreamNonBlocking));
+  if (!s_out) B200_CUDA(cudaStreamCreateWithFlags(&s_out, cudaStreamNonBlocking));
+  *in = s_in;
+  *out = s_out;
+  return 0;
+}
 
 bool is_device_ptr(const void *p) {
   if (!p) return false;

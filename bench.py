@@ -348,6 +348,7 @@ def mlp_extra(torch, hm, dist, rank, world):
             mode = f"eager ({type(exc).__name__})"
     ms = timed(torch, step, 20, 5, dist if world > 1 else None)
     flops = 6.0 * t * d * f
+    block.release()  # the captured graph holds NCCL work: drop it before the process group goes
     return {"ms": ms, "tokens_per_s": t / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
             "parallelism": f"tp{world}", "allreduce_bytes": t * d * 2 if world > 1 else 0, "launch": mode}
 
@@ -463,7 +464,13 @@ def run_product_arm(args):
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     if multi:
+        # The line is out; tear down, but never let a stuck teardown hold the launcher.
+        import threading
+        threading.Timer(60.0, lambda: os._exit(0)).start()
+        torch.cuda.synchronize()
+        dist.barrier()
         dist.destroy_process_group()
+        os._exit(0)
     return 0
 
 

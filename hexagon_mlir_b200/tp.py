@@ -40,29 +40,25 @@ def _device_mlp(x, gain, wg, wu, wd, out, eps, add_residual):
     _l.mlp_block[(1,)](x, gain, wg, wu, wd, out, eps=eps, add_residual=add_residual)
 
 
-def _device_add(a, b, out):
-    _l.add_kernel[(1,)](a.reshape(-1), b.reshape(-1), out.reshape(-1))
-
-
 class TensorParallelMLP:
     """out = x + down(swiglu(gate(h), up(h))), h = rmsnorm(x)·gain, hidden dimension sharded.
 
     Each rank holds Wg[:, lo:hi], Wu[:, lo:hi], Wd[lo:hi, :] and computes a partial
-    [T, D] output; the partials are summed with one all-reduce and the residual is added
-    afterwards on every rank.  The token dimension is cut into `chunks` pieces so that the
-    all-reduce of piece i runs while piece i+1 is computed.  `compute` / `add` default to
-    the library's kernels; the CPU tests of the partitioning logic inject stand-ins.
+    [T, D] output (rank 0's includes the residual); the partials are summed with one
+    all-reduce per chunk.  The token dimension can be cut into `chunks` pieces so that the
+    all-reduce of piece i runs while piece i+1 is computed; at 2048 tokens one piece is best
+    (a 512-token piece leaves most SM pairs without a 256x256 tile).  `compute` defaults to
+    the library's kernel; the CPU tests of the partitioning logic inject a stand-in.
     """
 
-    def __init__(self, gain, wg, wu, wd, eps=1e-6, group=None, chunks=4, compute=None, add=None):
+    def __init__(self, gain, wg, wu, wd, eps=1e-6, group=None, chunks=1, compute=None):
         self.gain, self.wg, self.wu, self.wd = gain, wg, wu, wd
         self.eps = float(eps)
         self.group = group
         self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
         self.chunks = max(1, int(chunks))
         self.compute = compute or _device_mlp
-        self.add = add or _device_add
-        self._partial = None
         self._graph = None
         self._graph_key = None
 
@@ -91,23 +87,31 @@ class TensorParallelMLP:
         self._graph.replay()
         return out
 
+    def release(self):
+        """Drop the captured graph (it holds the collective's work objects).  Call this before
+        the process group is destroyed: tearing the group down under a live graph can block."""
+        if self._graph is not None:
+            torch.cuda.synchronize()
+            self._graph = None
+            self._graph_key = None
+
     def __call__(self, x, out):
         if self.world == 1:
             self.compute(x, self.gain, self.wg, self.wu, self.wd, out, self.eps, True)
             return out
-        if self._partial is None or self._partial.shape != x.shape or self._partial.device != x.device:
-            self._partial = torch.empty_like(x)
+        # rank 0's partial carries the residual (added in its down-projection's epilogue), so the
+        # all-reduce delivers the finished block: no partial buffer, no separate add pass
+        fold = self.rank == 0
         t = x.shape[0]
         step = -(-t // self.chunks)
         works = []
         for r0 in range(0, t, step):
             r1 = min(t, r0 + step)
-            part = self._partial[r0:r1]
-            self.compute(x[r0:r1], self.gain, self.wg, self.wu, self.wd, part, self.eps, False)
+            part = out[r0:r1]
+            self.compute(x[r0:r1], self.gain, self.wg, self.wu, self.wd, part, self.eps, fold)
             works.append(dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group, async_op=True))
         for w in works:
             w.wait()
-        self.add(self._partial, x, out)
         return out
 
 

@@ -41,7 +41,7 @@ def _worker(rank, world, port, q):
     x, gain, wg, wu, wd = _problem()
     T = lambda a: torch.from_numpy(a).cuda()
     block = tp.TensorParallelMLP(T(gain), tp.shard_columns(T(wg), rank, world), tp.shard_columns(T(wu), rank, world),
-                                 tp.shard_rows(T(wd), rank, world), eps=1e-6, group=dist.group.WORLD, chunks=4)
+                                 tp.shard_rows(T(wd), rank, world), eps=1e-6, group=dist.group.WORLD, chunks=2)
     xt = T(x)
     out = torch.zeros_like(xt)
     for _ in range(2):

@@ -48,13 +48,10 @@ def worker(rank, world, port, q):
             y = oracle.add_f16(y, xn, threads=1)
         out.copy_(torch.from_numpy(y))
 
-    def add(a, b, out):
-        out.copy_(torch.from_numpy(oracle.add_f16(a.numpy(), b.numpy(), threads=1)))
-
     T = torch.from_numpy
     block = tp.TensorParallelMLP(T(gain), tp.shard_columns(T(wg), rank, world), tp.shard_columns(T(wu), rank, world),
                                  tp.shard_rows(T(wd), rank, world), eps=1e-6, group=dist.group.WORLD, chunks=3,
-                                 compute=compute, add=add)
+                                 compute=compute)
     out = torch.zeros_like(T(x))
     block(T(x), out)
     # column-sharded GEMM: every rank owns a column block, results are disjoint

@@ -39,6 +39,7 @@ struct Options {
   double gemm_variant = -1;        // -1: dispatcher chooses
   double kloop_block_k = 64;
   double w8a16_variant = -1;
+  double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
 };
 
 struct Context {
@@ -67,6 +68,31 @@ int workspace2(size_t bytes, void **out);
 // Device image of host tensors for the pipelined host-buffer GEMM, and its two copy streams.
 int staging_workspace(size_t bytes, void **out);
 int copy_streams(cudaStream_t *in, cudaStream_t *out);
+
+// ---- programmatic dependent launch ---------------------------------------------------
+// A kernel launched this way may start while its predecessor in the stream drains: its
+// CTAs become resident and run up to their `pdl_wait()`, which returns once the
+// predecessor has completed and its writes are visible.  Kernels call `pdl_trigger()` first
+// so that their own successor can do the same.  Both are no-ops for a plain launch.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                              Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = ctx().opt.enable_pdl != 0 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 
 // ---- manifest of planned matmuls (report.cu) ---------------------------------------
 struct GemmArgs;
@@ -143,7 +169,7 @@ int pair_variant_smem_bytes();
 struct W8A16Weight {
   const void *src = nullptr;     // caller's row-major int8 [K,N] (identity key)
   const void *scales = nullptr;  // fp16 [N]
-  void *image = nullptr;         // pre-swizzled device image
+  void *image = nullptr;         // resident device image: [k/128][channel][128 B, pieces swizzled]
   void *scales_dev = nullptr;
   int64_t k = 0, n = 0;
   size_t image_bytes = 0;
@@ -152,10 +178,10 @@ struct W8A16Weight {
 int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
 int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
                  int64_t ldc);
-// w8a16_decode.cu
-int w8a16_build_block_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
-int launch_w8a16_decode(const __half *a, const void *block_image, const __half *scales_dev, int64_t k,
-                        int64_t n, __half *c, int64_t m, int64_t lda, int64_t ldc);
+// w8a16_tmem.cu
+int w8a16_build_tmem_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
+int launch_w8a16_tmem(const __half *a, const void *image, const __half *scales_dev, int64_t k, int64_t n,
+                      __half *c, int64_t m, int64_t lda, int64_t ldc);
 
 // dispatch.cpp
 int gemm_dispatch(const GemmArgs &g);  // picks a variant (option / cache / heuristic) and launches

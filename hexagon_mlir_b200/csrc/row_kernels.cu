@@ -58,10 +58,12 @@ softmax_f16_kernel(const __half *__restrict__ x, __half *__restrict__ y, int64_t
   const int lane = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
   const int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + (TPR > 32 ? 0 : (threadIdx.x >> 5));
   const bool live = row < rows;  // dead warps still take part in no block-level sync (TPR==32)
+  pdl_trigger();
   if (TPR == 32 && !live) return;
   const int nvec = cols >> 3;
   const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * ldx);
   uint4 *yr = reinterpret_cast<uint4 *>(y + row * ldy);
+  pdl_wait();
 
   H8 v[VPL];
 #pragma unroll
@@ -170,11 +172,13 @@ rmsnorm_f16_kernel(const __half *__restrict__ x, const __half *__restrict__ w,
   constexpr int ROWS_PER_BLOCK = TPR > 32 ? 1 : 256 / 32;
   const int lane = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
   const int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + (TPR > 32 ? 0 : (threadIdx.x >> 5));
+  pdl_trigger();
   if (TPR == 32 && row >= rows) return;
   const int nvec = cols >> 3;
   const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * ldx);
   const uint4 *wr = reinterpret_cast<const uint4 *>(w);
   uint4 *yr = reinterpret_cast<uint4 *>(y + row * ldy);
+  pdl_wait();
   H8 v[VPL];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
@@ -265,6 +269,8 @@ ew_f16_kernel(const __half *__restrict__ a, const __half *__restrict__ b, __half
   const uint4 *av = reinterpret_cast<const uint4 *>(a);
   const uint4 *bv = reinterpret_cast<const uint4 *>(b);
   uint4 *yv = reinterpret_cast<uint4 *>(y);
+  pdl_trigger();
+  pdl_wait();
   H8 va[UNROLL], vb[UNROLL];
 #pragma unroll
   for (int i = 0; i < UNROLL; ++i) {
@@ -317,7 +323,7 @@ int launch_ew(const __half *a, const __half *b, __half *y, int64_t n, const char
     int64_t nvec = n >> 3;
     int64_t blocks = (nvec + 256 * UNROLL - 1) / (256 * UNROLL);
     if (blocks < 1) blocks = 1;
-    ew_f16_kernel<OP, UNROLL><<<(unsigned)blocks, 256, 0, s>>>(a, b, y, n);
+    launch_pdl(ew_f16_kernel<OP, UNROLL>, dim3((unsigned)blocks), dim3(256), 0, s, a, b, y, n);
   } else {
     int64_t blocks = (n + 255) / 256;
     int64_t cap = (int64_t)ctx().sm_count * 16;
@@ -332,21 +338,21 @@ int launch_ew(const __half *a, const __half *b, __half *y, int64_t n, const char
 #define ROW_DISPATCH(KERNEL, ...)                                                        \
   do {                                                                                   \
     if (cols <= 256) {                                                                   \
-      KERNEL<32, 1><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(__VA_ARGS__);             \
+      launch_pdl(KERNEL<32, 1>, dim3((unsigned)(((rows + 7) / 8))), dim3(256), 0, s, __VA_ARGS__);             \
     } else if (cols <= 512) {                                                            \
-      KERNEL<32, 2><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(__VA_ARGS__);             \
+      launch_pdl(KERNEL<32, 2>, dim3((unsigned)(((rows + 7) / 8))), dim3(256), 0, s, __VA_ARGS__);             \
     } else if (cols <= 1024) {                                                           \
-      KERNEL<32, 4><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(__VA_ARGS__);             \
+      launch_pdl(KERNEL<32, 4>, dim3((unsigned)(((rows + 7) / 8))), dim3(256), 0, s, __VA_ARGS__);             \
     } else if (cols <= 2048) {                                                           \
-      KERNEL<32, 8><<<(unsigned)((rows + 7) / 8), 256, 0, s>>>(__VA_ARGS__);             \
+      launch_pdl(KERNEL<32, 8>, dim3((unsigned)(((rows + 7) / 8))), dim3(256), 0, s, __VA_ARGS__);             \
     } else if (cols <= 4096) {                                                           \
-      KERNEL<128, 4><<<(unsigned)rows, 128, 0, s>>>(__VA_ARGS__);                        \
+      launch_pdl(KERNEL<128, 4>, dim3((unsigned)(rows)), dim3(128), 0, s, __VA_ARGS__);                        \
     } else if (cols <= 8192) {                                                           \
-      KERNEL<256, 4><<<(unsigned)rows, 256, 0, s>>>(__VA_ARGS__);                        \
+      launch_pdl(KERNEL<256, 4>, dim3((unsigned)(rows)), dim3(256), 0, s, __VA_ARGS__);                        \
     } else if (cols <= 16384) {                                                          \
-      KERNEL<512, 4><<<(unsigned)rows, 512, 0, s>>>(__VA_ARGS__);                        \
+      launch_pdl(KERNEL<512, 4>, dim3((unsigned)(rows)), dim3(512), 0, s, __VA_ARGS__);                        \
     } else {                                                                             \
-      KERNEL<1024, 4><<<(unsigned)rows, 1024, 0, s>>>(__VA_ARGS__);                      \
+      launch_pdl(KERNEL<1024, 4>, dim3((unsigned)(rows)), dim3(1024), 0, s, __VA_ARGS__);                      \
     }                                                                                    \
   } while (0)
 

@@ -8,17 +8,17 @@
 // by every later launch (lib/Dialect/Hmx/Transforms/WeightResidentPass.cpp:9-93,
 // backend/hmx_weight_prepack.py:124-212).
 //
-// Resident image: [strip = n/32][kstep = k/16][lane 0..31][16 bytes].  The 16
-// bytes of a lane are exactly the B fragments of four m16n8k16 MMAs (four n8
-// tiles of the strip) for one k16 step, stored as q+128 so that two bytes
-// become two fp16 values with one byte-permute and one subtract — the dequant
-// happens in registers and the row-major weight is never read again.  A warp
-// streams one strip: 512 contiguous bytes per k-step.
+// The product path (`w8a16_matmul`, the registry's resident image) is the tcgen05 kernel of
+// w8a16_tmem.cu; this file holds the row-pass loop around it and the one entry point that
+// may not allocate, which keeps its own kernels:
 //
-// Decode shapes are HBM-bound, so the work list (n-block, k-step) is cut into
-// equal contiguous ranges over 2 CTAs per SM (no tail wave); partial sums go to
-// an fp32 scratch with red.add and a small second kernel scales, rounds and
-// re-zeroes it.
+// Caller-built image of that entry: [strip = n/32][kstep = k/16][lane 0..31][16 bytes].  The
+// 16 bytes of a lane are exactly the B fragments of four m16n8k16 MMAs (four n8 tiles of the
+// strip) for one k16 step, stored as q+128 so that two bytes become two fp16 values with one
+// byte-permute and one subtract.  A warp streams one strip: 512 contiguous bytes per k-step;
+// the work list (n-block, k-step) is cut into equal contiguous ranges over 2 CTAs per SM,
+// partial sums go to the fixed fp32 scratch with red.add and a small second kernel scales,
+// rounds and re-zeroes it.
 #include <mma.h>
 
 #include <mutex>
@@ -186,7 +186,7 @@ w8a16_finalize_kernel(float *__restrict__ ws, const __half *__restrict__ scales,
 }  // namespace
 
 int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes) {
-  return w8a16_build_block_image(wq_dev, k, n, image, bytes);
+  return w8a16_build_tmem_image(wq_dev, k, n, image, bytes);
 }
 
 int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
@@ -197,11 +197,11 @@ int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, in
     return set_error(B200MLIR_ERR_BAD_ARG,
                      "w8a16: activations must be 16-byte aligned with a row stride multiple of 8");
   if (w.k % 8) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16: K must be a multiple of 8");
-  // Rows go through the tensor-core kernel in passes of at most 64.
-  for (int64_t m0 = 0; m0 < m; m0 += 64) {
-    const int64_t mp = (m - m0) < 64 ? (m - m0) : 64;
-    B200_TRY(launch_w8a16_decode(a + m0 * lda, w.image, (const __half *)w.scales_dev, w.k, w.n,
-                                 c + m0 * ldc, mp, lda, ldc));
+  // rows in passes of at most 128 (the widest activation tile the kernel holds)
+  for (int64_t m0 = 0; m0 < m; m0 += 128) {
+    const int64_t mp = (m - m0) < 128 ? (m - m0) : 128;
+    B200_TRY(launch_w8a16_tmem(a + m0 * lda, w.image, (const __half *)w.scales_dev, w.k, w.n, c + m0 * ldc, mp,
+                               lda, ldc));
   }
   return 0;
 }

@@ -48,6 +48,37 @@ def test_w8a16_edge_shapes_host_buffers(hm, oracle, mkn):
     assert max_abs_rel(c, oracle.w8a16(a, wq, s)) <= TOL_GEMM
 
 
+@pytest.mark.parametrize("mkn", [(16, 512, 32000), (40, 512, 20000), (70, 256, 20000), (200, 384, 1408), (128, 128, 2048),
+                                 (3, 128, 2048), (16, 64, 4096)])
+def test_w8a16_wide_ranges_row_passes_and_reproducibility(hm, oracle, cuda, mkn):
+    """More than 128 channels per CTA (two channel passes), more than 128 rows (two row passes),
+    K of one step, and every activation-tile width (16/64/128 rows): each CTA owns its channels
+    for all of K and the ring slots have fixed owners, so repeated launches agree bit for bit —
+    also right after a different kernel has run (a converter getting a ring turn ahead would
+    show here as a run-to-run difference)."""
+    m, k, n = mkn
+    rng = philox(52)
+    a = rng.normal(0, 1, (m, k)).astype(np.float16)
+    wq = rng.integers(-127, 128, (k, n), dtype=np.int8)
+    s = rng.uniform(0.001, 0.02, n).astype(np.float16)
+    want = oracle.w8a16(a, wq, s)
+    at, wt, st = (cuda.from_numpy(x).cuda() for x in (a, wq, s))
+    x = cuda.randn((1024, 1024), device="cuda").half()
+    y = cuda.empty_like(x)
+    outs = []
+    for rep in range(4):
+        if rep % 2:
+            hm.softmax_kernel[(1,)](x, y)  # another kernel in between
+        ct = cuda.full((m, n), 7.0, dtype=cuda.float16, device="cuda")
+        hm.w8a16_matmul[(1,)](at, wt, st, ct)
+        outs.append(ct.cpu().numpy())
+    assert hm.device_status() == 0
+    assert max_abs_rel(outs[0], want) <= TOL_GEMM
+    for o in outs[1:]:
+        assert np.array_equal(o.view(np.uint16), outs[0].view(np.uint16))
+    hm.unregister_w8a16_weight(wt)
+
+
 def test_w8a16_integer_core_is_exact(hm, oracle):
     """Unit scales and integer activations: fp32 accumulation of int8 products is exact."""
     rng = philox(51)

@@ -92,6 +92,10 @@ class ClockSampler:
 
 # ---- the reference arm / CPU baseline: the oracle on host cores -----------------------------
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the 16384x16384x8192 launch (one ncu capture)
+HEADLINE_DRAM_BYTES_PER_LAUNCH = 8.371e9 + 0.532e9
+
+
 def cpu_gemm_sample(target_s: float = 12.0):
     """Times the CPU restatement on a slab of M rows (full N, K) sized to about target_s."""
     import oracle
@@ -451,7 +455,10 @@ def run_product_arm(args):
                        "l2": "inputs larger than L2 (A 268 MB per rank)", "variant": plan["name"],
                        "accumulate": "fp32 in TMEM, one fp16 rounding"},
             "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
-                         "frac": kernel_tflops / peak, "traffic": None,
+                         "frac": kernel_tflops / peak,
+                         # DRAM read + write bytes of one whole-problem launch (ncu capture summarised in
+                         # profiles/bench_gemm_16384x16384x8192_launches.md); scales with the shard at N > 1
+                         "traffic": HEADLINE_DRAM_BYTES_PER_LAUNCH / world if world > 1 else HEADLINE_DRAM_BYTES_PER_LAUNCH,
                          "peak_source": f"{peak_kind} cuBLAS bf16 burst; sustained {peaks.get('bf16_tflops_sustained')}",
                          "frac_of_sustained": kernel_tflops / peaks.get("bf16_tflops_sustained", peak),
                          "frac_of_nominal_2250": kernel_tflops / 2250.0,

@@ -39,6 +39,7 @@ struct Options {
   double gemm_variant = -1;        // -1: dispatcher chooses
   double kloop_block_k = 64;
   double w8a16_variant = -1;
+  double gemm_group_m = 0;         // 0: the kernels' default band height
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
 };
 

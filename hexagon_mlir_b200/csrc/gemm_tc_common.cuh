@@ -11,7 +11,7 @@
 namespace b200 {
 namespace {
 
-constexpr int GROUP_M = 8;
+constexpr int GROUP_M = 8;  // default height, in tiles, of the band the tile walk sweeps (option gemmGroupM)
 
 struct TcParams {
   void *c;
@@ -19,15 +19,16 @@ struct TcParams {
   int64_t ldc, ldres;
   int m, n, k;
   int m_blocks, n_blocks, num_tiles, k_blocks;
+  int group_m;
   int *status;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int &m_blk,
+__device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int group_m, int &m_blk,
                                             int &n_blk) {
-  const int per_group = GROUP_M * n_blocks;
+  const int per_group = group_m * n_blocks;
   const int group = tile / per_group;
-  const int first_m = group * GROUP_M;
-  const int gsz = min(m_blocks - first_m, GROUP_M);
+  const int first_m = group * group_m;
+  const int gsz = min(m_blocks - first_m, group_m);
   const int in_group = tile - group * per_group;
   m_blk = first_m + in_group % gsz;
   n_blk = in_group / gsz;

@@ -96,7 +96,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
+        tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, m_blk, n_blk);
         const int m0 = m_blk * BM, n0 = n_blk * BN_OUT;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, p.status, 1, tile)) {
@@ -172,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
+      tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, m_blk, n_blk);
       const int m0 = m_blk * BM, n0 = n_blk * BN_OUT;
       bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 4, tile);
       ok = __all_sync(0xffffffffu, ok);  // the loads below need the warp converged
@@ -261,6 +261,7 @@ int launch_one(const GemmArgs &g, const TcVariantInfo &vi) {
   p.n_blocks = (int)((g.n + BN_OUT - 1) / BN_OUT);
   p.num_tiles = p.m_blocks * p.n_blocks;
   p.k_blocks = (int)((g.k + BK - 1) / BK);
+  p.group_m = ctx().opt.gemm_group_m >= 1 ? (int)ctx().opt.gemm_group_m : GROUP_M;
   p.status = c.d_status;
   auto kern = gemm_tc_kernel<BN_MMA, STAGES, EPI>;
   static bool attr_set = false;  // one per template instantiation

@@ -168,7 +168,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       bool ok = true;
       for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs) {
         int m_blk, n_blk;
-        tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
+        tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, m_blk, n_blk);
         const int m0 = m_blk * 256 + (int)rank * BM2;
         const int n0 = n_blk * BN_OUT;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
@@ -256,7 +256,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     int tord = 0;
     for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++tord) {
       int m_blk, n_blk;
-      tile_coords(tile, p.m_blocks, p.n_blocks, m_blk, n_blk);
+      tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, m_blk, n_blk);
       const int m0 = m_blk * 256 + (int)rank * BM2, n0 = n_blk * BN_OUT;
       bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 34, tile);
       ok = __all_sync(0xffffffffu, ok);
@@ -331,6 +331,7 @@ int launch_pair(const GemmArgs &g, const char *name) {
   p.n_blocks = (int)((g.n + BN_OUT - 1) / BN_OUT);
   p.num_tiles = p.m_blocks * p.n_blocks;
   p.k_blocks = (int)((g.k + NSUB * BK2 - 1) / (NSUB * BK2));
+  p.group_m = ctx().opt.gemm_group_m >= 1 ? (int)ctx().opt.gemm_group_m : GROUP_M;
   p.status = c.d_status;
   auto kern = gemm_tc2_kernel<STAGES, NSUB, EPI>;
   static int max_pairs = 0;  // one per template instantiation

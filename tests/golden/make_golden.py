@@ -1,6 +1,6 @@
 """Generates the committed golden fixtures from the reference itself.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where the reference checkout is available (its location: HEXMLIR_REFERENCE_ROOT):
 
     python tests/golden/make_golden.py
 

@@ -259,6 +259,19 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         gbs = 2 * 4096 * 1024 * 2 / (ms * 1e-3) / 1e9
         out["softmax_f16_4096x1024"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
         del X, Y
+        # the same kernel where the launch and the first-byte latency no longer dominate: 8x the rows
+        X = [(torch.randn((32768, 1024), generator=g, device=dev) * 3).half() for _ in range(3)]
+        Y = [torch.empty_like(X[0]) for _ in range(3)]
+        state = {"i": 0}
+
+        def sm_big():
+            i = state["i"] % 3
+            state["i"] += 1
+            hm.softmax_kernel[(1,)](X[i], Y[i])
+        ms = graph_timed(torch, sm_big, reps=10, inner=6)
+        gbs = 2 * 32768 * 1024 * 2 / (ms * 1e-3) / 1e9
+        out["softmax_f16_32768x1024"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+        del X, Y
     if want("rmsnorm"):
         # RMSNorm / SwiGLU at the MLP's shapes
         x = torch.randn((2048, 4096), generator=g, device=dev).half()
@@ -457,8 +470,8 @@ def run_product_arm(args):
             "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
                          "frac": kernel_tflops / peak,
                          # DRAM read + write bytes of one whole-problem launch (ncu capture summarised in
-                         # profiles/bench_gemm_16384x16384x8192_launches.md); scales with the shard at N > 1
-                         "traffic": HEADLINE_DRAM_BYTES_PER_LAUNCH / world if world > 1 else HEADLINE_DRAM_BYTES_PER_LAUNCH,
+                         # profiles/bench_gemm_16384x16384x8192_launches.md); not captured for the shards at N > 1
+                         "traffic": HEADLINE_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
                          "peak_source": f"{peak_kind} cuBLAS bf16 burst; sustained {peaks.get('bf16_tflops_sustained')}",
                          "frac_of_sustained": kernel_tflops / peaks.get("bf16_tflops_sustained", peak),
                          "frac_of_nominal_2250": kernel_tflops / 2250.0,

@@ -40,6 +40,7 @@ struct Options {
   double kloop_block_k = 64;
   double w8a16_variant = -1;
   double gemm_group_m = 0;         // 0: the kernels' default band height
+  double w8a16_dependent_launch = 1;  // programmatic dependent launch of the w8a16 kernel (measured: -7 % per call in a chain)
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
 };
 

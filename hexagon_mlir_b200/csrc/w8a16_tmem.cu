@@ -166,6 +166,10 @@ w8a16_tmem_kernel(const __grid_constant__ CUtensorMap tmA, const StreamParams p)
 #endif
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) TR(7, 0);
+  // Launched as a programmatic dependent of the previous kernel in the stream (option
+  // w8a16DependentLaunch): let OUR successor start as early, and wait for our predecessor only
+  // where its data is touched — the activations and C.  The weight stream does not wait.
+  pdl_trigger();
   // this CTA's channels, walked in passes of at most SLOT / 128
   constexpr int CH_MAX = SLOT / CH_BYTES;
   const int c_begin = (int)((int64_t)p.n * blockIdx.x / gridDim.x);
@@ -222,6 +226,7 @@ w8a16_tmem_kernel(const __grid_constant__ CUtensorMap tmA, const StreamParams p)
     __syncwarp();
     asm volatile("bar.arrive 1, %0;" ::"n"(THREADS) : "memory");
     if (lane == 0) {
+      pdl_wait();  // the activations may be the previous kernel's output
       Cursor c{0, 0};
       for (int i = 0; i < DA && i < nsteps; ++i, c.advance(1, ksteps)) {
         const uint32_t full = bar_afull + 8 * i, dst = act0 + i * A_BYTES;
@@ -432,6 +437,7 @@ w8a16_tmem_kernel(const __grid_constant__ CUtensorMap tmA, const StreamParams p)
       const float sc = live ? __half2float(p.scales[ch0 + cl]) : 0.0f;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
       const int pass_first = pass * ksteps;
+      pdl_wait();  // C may be something the previous kernel still reads
 #pragma unroll 1
       for (int m0 = 0; m0 < NM; m0 += 16) {
         if (m0 >= p.m) break;  // uniform across the warp
@@ -540,7 +546,21 @@ int launch_tmem(const CUtensorMap &tmA, const StreamParams &p, int grid) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     attr_set = true;
   }
-  kern<<<grid, THREADS, smem, ctx().stream>>>(tmA, p);
+  if (ctx().opt.w8a16_dependent_launch != 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx().stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    B200_CUDA(cudaLaunchKernelEx(&cfg, kern, tmA, p));
+  } else {
+    kern<<<grid, THREADS, smem, ctx().stream>>>(tmA, p);
+  }
   return check_launch("w8a16_tmem");
 }
 

@@ -243,6 +243,16 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
         out[f"gemm_f16_{n}^3"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                                   "variant": hm.gemm_explain(n, n, n)["name"]}
+        if n == 4096:
+            # the K-looped form (fp16 read-out per 64-deep segment, fp32 running sum in the read-out warps)
+            def fk():
+                i = state["i"] % sets
+                state["i"] += 1
+                hm.klooped_matmul[(1,)](A[i], B[i], C[i], BLOCK_K=64)
+            ms = timed(torch, fk, 20, 3)
+            tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
+            out[f"gemm_f16_kloop64_{n}^3"] = {"us": ms * 1e3, "tflops": tf,
+                                              "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"]}
         del A, B, C
     if want("softmax"):
         # C2 softmax [4096,1024]: 16 MiB in + out per launch; 12 buffer pairs (201 MB) rotate past L2

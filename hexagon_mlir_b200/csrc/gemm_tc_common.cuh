@@ -20,6 +20,7 @@ struct TcParams {
   int m, n, k;
   int m_blocks, n_blocks, num_tiles, k_blocks;
   int group_m;
+  int seg_kb;  // K-looped form: k-blocks per segment
   int *status;
 };
 

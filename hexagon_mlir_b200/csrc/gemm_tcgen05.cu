@@ -131,10 +131,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 2, tile)) break;
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_MMA);
+        // Whole-K form: one accumulator per tile.  K-looped form: one per K segment of
+        // p.seg_kb k-blocks, started with accumulate off — the read-out warps round each to
+        // fp16 and keep the running sum themselves (test_matmul_kloop.py:87-98).
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          const bool seg_start = EPI == EPI_KLOOP_F16 ? (kb % p.seg_kb) == 0 : kb == 0;
+          if (seg_start) {
+            if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 2, tile)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+          }
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_MMA);
           if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 3, tile)) {
             ok = false;
             break;
@@ -149,19 +158,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             // B: MN-major, 64-column slabs B_SLAB_BYTES apart, 8-k groups 1024 B apart;
             // one K=16 step is 16 rows of 128 bytes
             const uint64_t bdesc = smem_desc_sw128(sb + k * 2048, B_SLAB_BYTES, 1024);
-            mma_f16_ss(d_tmem, adesc, bdesc, IDESC, (kb | k) != 0 ? 1u : 0u);
+            mma_f16_ss(d_tmem, adesc, bdesc, IDESC, (seg_start && k == 0) ? 0u : 1u);
           }
           mma_commit(bar_empty + 8 * stage);  // frees the stage once these MMAs have read it
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
-        }
-        if (!ok) break;
-        mma_commit(bar_tfull + 8 * acc);  // accumulator complete
-        if (++acc == 2) {
-          acc = 0;
-          acc_phase ^= 1u;
+          const bool seg_end = EPI == EPI_KLOOP_F16 ? ((kb + 1) % p.seg_kb == 0 || kb + 1 == p.k_blocks)
+                                                    : kb + 1 == p.k_blocks;
+          if (seg_end) {
+            mma_commit(bar_tfull + 8 * acc);  // accumulator complete
+            if (++acc == 2) {
+              acc = 0;
+              acc_phase ^= 1u;
+            }
+          }
         }
       }
     }
@@ -174,30 +186,71 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int m_blk, n_blk;
       tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, m_blk, n_blk);
       const int m0 = m_blk * BM, n0 = n_blk * BN_OUT;
-      bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 4, tile);
-      ok = __all_sync(0xffffffffu, ok);  // the loads below need the warp converged
-      if (!ok) break;
-      tc_fence_after_sync();
       const int row = m0 + q * 32 + lane;
       const bool row_ok = row < p.m;
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA);
+      if constexpr (EPI == EPI_KLOOP_F16) {
+        // running fp32 sums of this row's BN_MMA columns; every segment is rounded to fp16 first
+        float sum[BN_MMA];
+#pragma unroll
+        for (int e = 0; e < BN_MMA; ++e) sum[e] = 0.0f;
+        const int segs = (p.k_blocks + p.seg_kb - 1) / p.seg_kb;
+        bool ok = true;
+        for (int sg = 0; sg < segs; ++sg) {
+          ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 4, tile);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA);
+#pragma unroll
+          for (int c = 0; c < BN_MMA / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e)
+              sum[c * 32 + e] += __half2float(__float2half_rn(__uint_as_float(r[e])));
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < BN_MMA / 32; ++c) {
+          uint32_t r[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(sum[c * 32 + e]);
+          const int col0 = n0 + c * 32;
+          if (row_ok && col0 < p.n) epilogue_store_chunk<EPI_F16>(r, r, row, col0, p);
+        }
+      } else {
+        bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 4, tile);
+        ok = __all_sync(0xffffffffu, ok);  // the loads below need the warp converged
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA);
 #pragma unroll 1
-      for (int c = 0; c < BN_OUT / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_row + c * 32, r);
-        uint32_t r2[32];
-        if (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + BN_OUT + c * 32, r2);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.n) continue;
-        epilogue_store_chunk<EPI>(r, r2, row, col0, p);
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
-      if (++acc == 2) {
-        acc = 0;
-        acc_phase ^= 1u;
+        for (int c = 0; c < BN_OUT / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          uint32_t r2[32];
+          if (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + BN_OUT + c * 32, r2);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (!row_ok || col0 >= p.n) continue;
+          epilogue_store_chunk<EPI>(r, r2, row, col0, p);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
       }
     }
   }
@@ -262,6 +315,7 @@ int launch_one(const GemmArgs &g, const TcVariantInfo &vi) {
   p.num_tiles = p.m_blocks * p.n_blocks;
   p.k_blocks = (int)((g.k + BK - 1) / BK);
   p.group_m = ctx().opt.gemm_group_m >= 1 ? (int)ctx().opt.gemm_group_m : GROUP_M;
+  p.seg_kb = g.block_k >= BK ? g.block_k / BK : 1;
   p.status = c.d_status;
   auto kern = gemm_tc_kernel<BN_MMA, STAGES, EPI>;
   static bool attr_set = false;  // one per template instantiation
@@ -283,6 +337,10 @@ int launch_epi(const GemmArgs &g, const TcVariantInfo &vi) {
     case EPI_SWIGLU:
       if constexpr (BN_MMA >= 128) return launch_one<BN_MMA, STAGES, EPI_SWIGLU>(g, vi);
       return set_error(B200MLIR_ERR_UNSUPPORTED, "swiglu epilogue needs a variant with BN >= 128");
+    case EPI_KLOOP_F16:
+      // the read-out warps hold a row's running sums in registers: 128 columns is what fits
+      if constexpr (BN_MMA == 128) return launch_one<BN_MMA, STAGES, EPI_KLOOP_F16>(g, vi);
+      return set_error(B200MLIR_ERR_UNSUPPORTED, "k-looped read-out is built for the 128x128 variant only");
     default:
       return set_error(B200MLIR_ERR_UNSUPPORTED, "tensor-core gemm: epilogue %d not built",
                        g.epilogue);
@@ -315,7 +373,10 @@ const char *tc_variant_verdict(int v, const GemmArgs &g) {
   }
   if (g.epilogue == EPI_SWIGLU && (!g.b2 || !al16(g.b2))) return "tile-alignment";
   if (g.epilogue == EPI_SWIGLU && vi.bn < 128) return "epilogue-unsupported";
-  if (g.epilogue == EPI_KLOOP_F16) return "epilogue-unsupported";
+  // K-looped accumulation: segments of whole k-blocks, on the variant whose read-out warps
+  // can hold a row of running sums (anything else stays on the CUDA-core path)
+  if (g.epilogue == EPI_KLOOP_F16 && (vi.cta_group != 1 || vi.bn != 128 || g.block_k < BK || g.block_k % BK))
+    return "epilogue-unsupported";
   if (g.m > 0x7fffffff || g.n > 0x7fffffff || g.k > 0x7fffffff) return "extent-range";
   if (((g.m + BM - 1) / BM) * ((g.n + 31) / 32) > 0x3fffffff) return "extent-range";
   if (vi.smem_bytes > 227 * 1024) return "smem-budget";

@@ -120,7 +120,8 @@ B200_API void multispan_matmul(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, 
 /* Same contraction with the K-segmented accumulation of a K-looped tl.dot:
  * each BLOCK_K segment is read out as fp16, widened and added in fp32
  * (test/python/triton/test_matmul_kloop.py:27-34,87-98).  BLOCK_K = option
- * "kloopBlockK" (default 64). */
+ * "kloopBlockK" (default 64).  Multiples of 64 run on the tensor cores (one
+ * accumulator per segment), other values on the CUDA-core path; same arithmetic. */
 B200_API void klooped_matmul(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B200MemRef2D *b,
                              int64_t rank_c, B200MemRef2D *c, B200_GRID_ARGS);
 /* fp32 read-out with optional fp32 residual: C32 = f32(f16(A·B)) [+ R]

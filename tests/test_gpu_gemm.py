@@ -100,6 +100,32 @@ def test_klooped_matmul(hm, oracle, block_k):
     assert (got.view(np.uint16) != want.view(np.uint16)).mean() < 0.05
 
 
+@pytest.mark.parametrize("mnk,block_k", [((1024, 1024, 1024), 64), ((512, 384, 1000), 128), ((300, 520, 456), 64),
+                                         ((2048, 1024, 2048), 256), ((128, 128, 192), 192)])
+def test_klooped_matmul_on_tensor_cores(hm, oracle, mnk, block_k):
+    """Segments of whole 64-deep k-blocks run on tcgen05: one accumulator per segment, rounded to
+    fp16 by the read-out warps, which keep the fp32 running sum (HMXLayout.c:880-901).  Same
+    arithmetic as the CUDA-core path, so the two must agree bit for bit almost everywhere and
+    both with the oracle."""
+    m, n, k = mnk
+    rng = philox(48)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float16)
+    hm.manifest_reset()
+    got = run_matmul(hm, a, b, kernel=hm.klooped_matmul, BLOCK_K=block_k)
+    (row,) = hm.manifest()["matmuls"]
+    assert row["epilogue"] == "kloop-f16" and row["plan"] in ("full-hmx", "hmx-tail"), row
+    want = oracle.gemm_f16(a, b, block_k=block_k)
+    assert max_abs_rel(got, want) <= TOL_GEMM
+    assert (got.view(np.uint16) != want.view(np.uint16)).mean() < 0.05
+    simt = run_matmul(hm, a, b, variant=SIMT, kernel=hm.klooped_matmul, BLOCK_K=block_k)
+    assert (got.view(np.uint16) != simt.view(np.uint16)).mean() < 0.05
+    # the whole-K product differs: the segment roundings are really applied
+    if k // block_k >= 4:
+        whole = oracle.gemm_f16(a, b)
+        assert (got.view(np.uint16) != whole.view(np.uint16)).mean() > 0.05
+
+
 @pytest.mark.parametrize("variant", [SIMT, 0, 3])
 def test_f32_readout_with_residual(hm, oracle, variant):
     rng = philox(45)

@@ -376,7 +376,20 @@ def mlp_extra(torch, hm, dist, rank, world):
     ms = timed(torch, step, 20, 5, dist if world > 1 else None)
     flops = 6.0 * t * d * f
     block.release()  # the captured graph holds NCCL work: drop it before the process group goes
-    return {"ms": ms, "tokens_per_s": t / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
+    reduction = "nccl all-reduce" if world > 1 else "none"
+    forms = {}
+    if world > 1:
+        # the same block with the reduction fused into the kernels (peer stores over NVLink)
+        forms["nccl_all_reduce_ms"] = ms
+        try:
+            fused = tp.FusedTensorParallelMLP(gain, wg, wu, wd, tokens=t, eps=1e-6, group=dist.group.WORLD)
+            fms = timed(torch, lambda: fused(x), 20, 5, dist)
+            forms["fused_peer_store_ms"] = fms
+            if fms < ms:
+                ms, reduction, mode = fms, "fused: read-out pushes partial rows to their owners", "eager"
+        except Exception as exc:  # symmetric memory is a property of the box, not of this code
+            forms["fused_peer_store_ms"] = f"unavailable ({type(exc).__name__})"
+    return {"ms": ms, "reduction": reduction, **forms, "tokens_per_s": t / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
             "parallelism": f"tp{world}", "allreduce_bytes": t * d * 2 if world > 1 else 0, "launch": mode}
 
 

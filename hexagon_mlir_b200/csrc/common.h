@@ -117,6 +117,9 @@ int launch_silu_f16(const __half *x, __half *y, int64_t n);
 int launch_silu_f32(const float *x, float *y, int64_t n);
 int launch_swiglu_f16(const __half *g, const __half *u, __half *y, int64_t n);
 int launch_add_f16(const __half *a, const __half *b, __half *y, int64_t n);
+// out rows of this rank = f16(sum_w f32(recv[w]) + f32(residual)), stored to every rank's out
+int launch_reduce_rows_push(const __half *recv, const __half *residual, int64_t ldres, void *const *peer_out,
+                            int world, int rank, int64_t rows_per_rank, int64_t cols);
 
 // layout.cu
 int launch_pack_weight_f16(const uint16_t *src, uint16_t *dst, int64_t k, int64_t n, int64_t ld);
@@ -131,7 +134,18 @@ enum Epilogue : int {
   EPI_F32_RES = 1,    // C32 = f32(f16(acc)) [+ R32]
   EPI_KLOOP_F16 = 2,  // C16 = f16(sum_seg f32(f16(acc_seg)))
   EPI_F16_RES16 = 3,  // C16 = f16(f32(f16(acc)) + f32(R16))
-  EPI_SWIGLU = 4      // B holds [Wg | Wu] interleaved per tile; C16 = swiglu
+  EPI_SWIGLU = 4,     // B holds [Wg | Wu] interleaved per tile; C16 = swiglu
+  EPI_PUSH16 = 5      // f16(acc) stored into the row owner's receive slot on another GPU (PushTargets)
+};
+
+// Where EPI_PUSH16 stores: row r of the partial product belongs to rank r / rows_per_rank, whose
+// receive buffer is [world][rows_per_rank][N] fp16; this rank writes slot `rank` of it.  The
+// pointers are peer-mapped device addresses (one per rank, this rank's own included).
+constexpr int kMaxPushRanks = 8;
+struct PushTargets {
+  void *recv[kMaxPushRanks] = {};
+  int world = 0, rank = 0;
+  int64_t rows_per_rank = 0;
 };
 
 struct GemmArgs {
@@ -144,6 +158,7 @@ struct GemmArgs {
   int64_t lda = 0, ldb = 0, ldc = 0, ldres = 0;
   int epilogue = EPI_F16;
   int block_k = 0;  // EPI_KLOOP_F16 only
+  const PushTargets *push = nullptr;  // EPI_PUSH16 only
 };
 
 // gemm_simt.cu — any-shape fallback ("hmx-tail"/"hvx" plans of the reference)

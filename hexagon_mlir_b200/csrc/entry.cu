@@ -569,29 +569,31 @@ void w8a16_matmul(int64_t ra, B200MemRef2D *a, int64_t rw, B200MemRef2D *wq, int
   }
 }
 
-void mlp_block_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
-                       B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
-                       int64_t ro, B200MemRef2D *out, float eps, int add_residual, B200_GRID_ARGS) {
-  ENTER_KERNEL();
+// rmsnorm -> gate/up GEMM with SwiGLU read-out -> down GEMM.  The down GEMM either writes
+// `out` (with the residual when asked) or, given push targets, stores its fp16 partial rows
+// into the receive slots of the ranks that own them.
+static void mlp_block_impl(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
+                           B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
+                           int64_t ro, B200MemRef2D *out, float eps, int add_residual, const PushTargets *push) {
   if (ensure_ready()) return;
-  View2 X, WG, WU, WD, O;
+  View2 X, WG, WU, WD, O{nullptr, 0, 0, 0};
   View1 G;
   if (view2("x", rx, x, 2, &X) || view1("gain", rg, gain, 2, &G) || view2("Wg", rwg, wg, 2, &WG) ||
-      view2("Wu", rwu, wu, 2, &WU) || view2("Wd", rwd, wd, 2, &WD) || view2("out", ro, out, 2, &O))
+      view2("Wu", rwu, wu, 2, &WU) || view2("Wd", rwd, wd, 2, &WD) || (!push && view2("out", ro, out, 2, &O)))
     return;
   const int64_t T = X.rows, D = X.cols, F = WG.cols;
   if (G.n != D || WG.rows != D || WU.rows != D || WU.cols != F || WD.rows != F || WD.cols != D ||
-      O.rows != T || O.cols != D || WU.ld != WG.ld) {
+      (!push && (O.rows != T || O.cols != D)) || WU.ld != WG.ld) {
     set_error(B200MLIR_ERR_BAD_ARG, "mlp_block: shapes do not agree");
     return;
   }
   if (T == 0 || D == 0) return;
   Stager st;
   const void *dx, *dg, *dwg, *dwu, *dwd;
-  void *dout;
+  void *dout = nullptr;
   if (st.in(X.p, X.span(2), &dx) || st.in(G.p, (size_t)D * 2, &dg) || st.in(WG.p, WG.span(2), &dwg) ||
       st.in(WU.p, WU.span(2), &dwu) || st.in(WD.p, WD.span(2), &dwd) ||
-      st.out(O.p, O.span(2), &dout, O.ld != O.cols))
+      (!push && st.out(O.p, O.span(2), &dout, O.ld != O.cols)))
     return;
   void *h = nullptr, *act = nullptr;
   if (workspace((size_t)T * D * 2, &h) || workspace2((size_t)T * F * 2, &act)) return;
@@ -603,17 +605,60 @@ void mlp_block_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *ga
   g1.m = T; g1.n = F; g1.k = D; g1.lda = D; g1.ldb = WG.ld; g1.ldc = F;
   g1.epilogue = EPI_SWIGLU;
   if (gemm_dispatch(g1)) return;
-  // 3. out = act·Wd (+ x through the f32 residual read-out)
+  // 3. out = act·Wd (+ x through the f32 residual read-out), or the partial rows pushed to their owners
   GemmArgs g2;
   g2.a = act; g2.b = dwd; g2.c = dout;
-  g2.m = T; g2.n = D; g2.k = F; g2.lda = F; g2.ldb = WD.ld; g2.ldc = O.ld;
-  if (add_residual) {
+  g2.m = T; g2.n = D; g2.k = F; g2.lda = F; g2.ldb = WD.ld; g2.ldc = push ? D : O.ld;
+  if (push) {
+    g2.epilogue = EPI_PUSH16;
+    g2.push = push;
+  } else if (add_residual) {
     g2.epilogue = EPI_F16_RES16;
     g2.res = dx;
     g2.ldres = X.ld;
   }
   if (gemm_dispatch(g2)) return;
   st.finish();
+}
+
+void mlp_block_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
+                       B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
+                       int64_t ro, B200MemRef2D *out, float eps, int add_residual, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, add_residual, nullptr);
+}
+
+static int fill_push(PushTargets *pt, void *const *peer_recv, int world, int rank, int64_t rows) {
+  if (!peer_recv || world < 1 || world > kMaxPushRanks || rank < 0 || rank >= world || rows < 1 || rows % world)
+    return set_error(B200MLIR_ERR_BAD_ARG, "tensor-parallel push: world 1..%d, rank inside it, rows divisible by world",
+                     kMaxPushRanks);
+  for (int i = 0; i < world; ++i) {
+    if (!peer_recv[i]) return set_error(B200MLIR_ERR_BAD_ARG, "tensor-parallel push: receive pointer %d is null", i);
+    pt->recv[i] = peer_recv[i];
+  }
+  pt->world = world;
+  pt->rank = rank;
+  pt->rows_per_rank = rows / world;
+  return 0;
+}
+
+void mlp_block_push_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
+                            B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
+                            void *const *peer_recv, int world, int rank, float eps, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  PushTargets pt;
+  if (!x || fill_push(&pt, peer_recv, world, rank, x->sizes[0])) return;
+  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, 0, nullptr, eps, 0, &pt);
+}
+
+int b200mlir_tp_reduce_rows_float16(const void *recv, const void *residual, int64_t ldres, void *const *peer_out,
+                                    int world, int rank, int64_t rows_per_rank, int64_t cols) {
+  clear_error();
+  B200_TRY(ensure_ready());
+  if (!recv || !peer_out || !is_device_ptr(recv))
+    return set_error(B200MLIR_ERR_BAD_ARG, "tp_reduce_rows: device buffers required");
+  return launch_reduce_rows_push((const __half *)recv, (const __half *)residual, ldres, peer_out, world, rank,
+                                 rows_per_rank, cols);
 }
 
 int b200mlir_pack_weight_f16(const void *src, void *dst, int64_t k, int64_t n, int64_t ld) {

@@ -21,6 +21,8 @@ struct TcParams {
   int m_blocks, n_blocks, num_tiles, k_blocks;
   int group_m;
   int seg_kb;  // K-looped form: k-blocks per segment
+  void *push_recv[kMaxPushRanks];  // EPI_PUSH16: receive buffers, by owner rank
+  int push_rank, push_rows;
   int *status;
 };
 
@@ -88,6 +90,22 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
       }
       *reinterpret_cast<uint4 *>(cp + v * 8) = o;
     }
+  } else if (EPI == EPI_PUSH16) {
+    // the row's owner holds [world][rows][N]; this rank fills slot push_rank (stores cross NVLink)
+    const int owner = row / p.push_rows;
+    const int lr = row - owner * p.push_rows;
+    __half *cp = reinterpret_cast<__half *>(p.push_recv[owner]) +
+                 ((int64_t)p.push_rank * p.push_rows + lr) * p.ldc + col0;
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      if (col0 + v * 8 >= p.n) break;  // N is a multiple of 8
+      uint4 o;
+      uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        ow[j] = pack_h2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+      *reinterpret_cast<uint4 *>(cp + v * 8) = o;
+    }
   } else if (EPI == EPI_F32_RES) {
     float *cp = reinterpret_cast<float *>(p.c) + (int64_t)row * p.ldc + col0;
     const float *rp = reinterpret_cast<const float *>(p.res) + (int64_t)row * p.ldres + col0;
@@ -106,6 +124,13 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
       *reinterpret_cast<float4 *>(cp + v * 4) = o;
     }
   }
+}
+
+// Fills the EPI_PUSH16 part of the kernel parameters.
+inline void set_push_params(TcParams &p, const GemmArgs &g) {
+  for (int i = 0; i < kMaxPushRanks; ++i) p.push_recv[i] = g.push ? g.push->recv[i] : nullptr;
+  p.push_rank = g.push ? g.push->rank : 0;
+  p.push_rows = g.push ? (int)g.push->rows_per_rank : 1;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,

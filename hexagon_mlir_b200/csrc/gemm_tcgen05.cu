@@ -316,6 +316,7 @@ int launch_one(const GemmArgs &g, const TcVariantInfo &vi) {
   p.k_blocks = (int)((g.k + BK - 1) / BK);
   p.group_m = ctx().opt.gemm_group_m >= 1 ? (int)ctx().opt.gemm_group_m : GROUP_M;
   p.seg_kb = g.block_k >= BK ? g.block_k / BK : 1;
+  set_push_params(p, g);
   p.status = c.d_status;
   auto kern = gemm_tc_kernel<BN_MMA, STAGES, EPI>;
   static bool attr_set = false;  // one per template instantiation
@@ -334,6 +335,7 @@ int launch_epi(const GemmArgs &g, const TcVariantInfo &vi) {
     case EPI_F16: return launch_one<BN_MMA, STAGES, EPI_F16>(g, vi);
     case EPI_F32_RES: return launch_one<BN_MMA, STAGES, EPI_F32_RES>(g, vi);
     case EPI_F16_RES16: return launch_one<BN_MMA, STAGES, EPI_F16_RES16>(g, vi);
+    case EPI_PUSH16: return launch_one<BN_MMA, STAGES, EPI_PUSH16>(g, vi);
     case EPI_SWIGLU:
       if constexpr (BN_MMA >= 128) return launch_one<BN_MMA, STAGES, EPI_SWIGLU>(g, vi);
       return set_error(B200MLIR_ERR_UNSUPPORTED, "swiglu epilogue needs a variant with BN >= 128");
@@ -364,7 +366,16 @@ const char *tc_variant_verdict(int v, const GemmArgs &g) {
   if (g.m <= 4) return "min-rows";  // HmxTarget.h:100,201 — decode rows go to the vector path
   if (g.k < 8 || g.n < 8) return "tile-alignment";
   if (g.k % 8 || g.n % 8 || g.lda % 8 || g.ldb % 8) return "tile-alignment";
-  if (!al16(g.a) || !al16(g.b) || !al16(g.c)) return "tile-alignment";
+  if (g.epilogue == EPI_PUSH16) {
+    if (!g.push || g.push->world < 1 || g.push->world > kMaxPushRanks || g.push->rows_per_rank < 1 ||
+        g.push->rows_per_rank * g.push->world != g.m)
+      return "epilogue-unsupported";
+    for (int i = 0; i < g.push->world; ++i)
+      if (!g.push->recv[i] || !al16(g.push->recv[i])) return "tile-alignment";
+    if (!al16(g.a) || !al16(g.b)) return "tile-alignment";
+  } else if (!al16(g.a) || !al16(g.b) || !al16(g.c)) {
+    return "tile-alignment";
+  }
   if (g.epilogue == EPI_F32_RES) {
     if (g.ldc % 4 || (g.res && (g.ldres % 4 || !al16(g.res)))) return "tile-alignment";
   } else {

@@ -332,6 +332,8 @@ int launch_pair(const GemmArgs &g, const char *name) {
   p.num_tiles = p.m_blocks * p.n_blocks;
   p.k_blocks = (int)((g.k + NSUB * BK2 - 1) / (NSUB * BK2));
   p.group_m = ctx().opt.gemm_group_m >= 1 ? (int)ctx().opt.gemm_group_m : GROUP_M;
+  p.seg_kb = 1;
+  set_push_params(p, g);
   p.status = c.d_status;
   auto kern = gemm_tc2_kernel<STAGES, NSUB, EPI>;
   static int max_pairs = 0;  // one per template instantiation
@@ -371,6 +373,7 @@ int launch_pair_epi(const GemmArgs &g, const char *name) {
     case EPI_F16: return launch_pair<STAGES, NSUB, EPI_F16>(g, name);
     case EPI_F32_RES: return launch_pair<STAGES, NSUB, EPI_F32_RES>(g, name);
     case EPI_F16_RES16: return launch_pair<STAGES, NSUB, EPI_F16_RES16>(g, name);
+    case EPI_PUSH16: return launch_pair<STAGES, NSUB, EPI_PUSH16>(g, name);
     case EPI_SWIGLU: return launch_pair<STAGES, NSUB, EPI_SWIGLU>(g, name);
     default: return set_error(B200MLIR_ERR_UNSUPPORTED, "2-CTA gemm: epilogue %d not built", g.epilogue);
   }

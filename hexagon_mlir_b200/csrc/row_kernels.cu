@@ -313,6 +313,75 @@ silu_f32_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t n) {
 
 bool aligned16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
 
+// Second half of the tensor-parallel block's reduction: this rank owns `rows` rows; their W
+// fp16 partials sit in its receive buffer [W][rows][cols].  out = f16(sum_w f32(partial_w) +
+// f32(residual)), written to the same rows of EVERY rank's output (peer stores over NVLink).
+struct ReducePushParams {
+  const __half *recv;
+  const __half *residual;  // this rank's rows of the block input, or null
+  int64_t ldres;
+  __half *out[kMaxPushRanks];  // by rank: base of the [T][cols] output
+  int world, rank;
+  int64_t rows, cols;
+};
+
+template <int WORLD>
+__global__ void __launch_bounds__(256)
+reduce_rows_push_kernel(const ReducePushParams p) {
+  // every thread owns UNR 16-byte pieces; all their loads are issued before any arithmetic
+  constexpr int UNR = 4;
+  constexpr int WMAX = WORLD > 0 ? WORLD : kMaxPushRanks;
+  const int64_t vec_per_row = p.cols >> 3;
+  const int64_t total = p.rows * vec_per_row;
+  const int64_t slot = p.rows * p.cols;
+  const int world = WORLD > 0 ? WORLD : p.world;
+  for (int64_t base = ((int64_t)blockIdx.x * 256) * UNR + threadIdx.x; base < total;
+       base += (int64_t)gridDim.x * 256 * UNR) {
+    H8 part[UNR][WMAX], res[UNR];
+    int64_t off[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t i = base + (int64_t)u * 256;
+      off[u] = 0;
+      if (i < total) {
+        const int64_t r = i / vec_per_row, c = (i - r * vec_per_row) << 3;
+        off[u] = r * p.cols + c;
+#pragma unroll
+        for (int w = 0; w < WMAX; ++w)
+          if (w < world) part[u][w].u = *reinterpret_cast<const uint4 *>(p.recv + w * slot + off[u]);
+        if (p.residual) res[u].u = __ldg(reinterpret_cast<const uint4 *>(p.residual + r * p.ldres + c));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t i = base + (int64_t)u * 256;
+      if (i >= total) continue;
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+#pragma unroll
+      for (int w = 0; w < WMAX; ++w)
+        if (w < world) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += __half2float(part[u][w].h[e]);
+        }
+      if (p.residual) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += __half2float(res[u].h[e]);
+      }
+      H8 o;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o.h[e] = __float2half_rn(acc[e]);
+      const int64_t dst = p.rank * slot + off[u];
+      // peers first: their stores cross NVLink and take longest to drain
+#pragma unroll
+      for (int w = 0; w < WMAX; ++w)
+        if (w < world && w != p.rank) *reinterpret_cast<uint4 *>(p.out[w] + dst) = o.u;
+      *reinterpret_cast<uint4 *>(p.out[p.rank] + dst) = o.u;
+    }
+  }
+}
+
 template <int OP>
 int launch_ew(const __half *a, const __half *b, __half *y, int64_t n, const char *what) {
   B200_TRY(ensure_ready());
@@ -355,6 +424,41 @@ int launch_ew(const __half *a, const __half *b, __half *y, int64_t n, const char
       launch_pdl(KERNEL<1024, 4>, dim3((unsigned)(rows)), dim3(1024), 0, s, __VA_ARGS__);                      \
     }                                                                                    \
   } while (0)
+
+int launch_reduce_rows_push(const __half *recv, const __half *residual, int64_t ldres, void *const *peer_out,
+                            int world, int rank, int64_t rows_per_rank, int64_t cols) {
+  B200_TRY(ensure_ready());
+  if (world < 1 || world > kMaxPushRanks || rank < 0 || rank >= world || rows_per_rank < 1 || cols < 8 || cols % 8 ||
+      !recv || !aligned16(recv) || (residual && (!aligned16(residual) || ldres % 8)))
+    return set_error(B200MLIR_ERR_BAD_ARG,
+                     "reduce_rows_push: bad argument (world <= 8, cols a multiple of 8, 16-byte aligned)");
+  ReducePushParams p;
+  p.recv = recv;
+  p.residual = residual;
+  p.ldres = ldres;
+  for (int w = 0; w < kMaxPushRanks; ++w) {
+    p.out[w] = w < world ? (__half *)peer_out[w] : nullptr;
+    if (w < world && (!p.out[w] || !aligned16(p.out[w])))
+      return set_error(B200MLIR_ERR_BAD_ARG, "reduce_rows_push: output pointer %d missing or unaligned", w);
+  }
+  p.world = world;
+  p.rank = rank;
+  p.rows = rows_per_rank;
+  p.cols = cols;
+  const int64_t total = rows_per_rank * (cols >> 3);
+  int64_t blocks = (total + 256 * 4 - 1) / (256 * 4);
+  const int64_t cap = (int64_t)ctx().sm_count * 8;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  const unsigned g = (unsigned)blocks;
+  switch (world) {
+    case 2: reduce_rows_push_kernel<2><<<g, 256, 0, ctx().stream>>>(p); break;
+    case 4: reduce_rows_push_kernel<4><<<g, 256, 0, ctx().stream>>>(p); break;
+    case 8: reduce_rows_push_kernel<8><<<g, 256, 0, ctx().stream>>>(p); break;
+    default: reduce_rows_push_kernel<0><<<g, 256, 0, ctx().stream>>>(p); break;
+  }
+  return check_launch("reduce_rows_push");
+}
 
 static bool row_fast_path(const void *x, const void *y, int64_t cols, int64_t ldx, int64_t ldy) {
   return cols % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0 && aligned16(x) && aligned16(y) &&

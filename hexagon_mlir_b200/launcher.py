@@ -167,6 +167,32 @@ def matmul_f32out(a, b, c32, res32=None):
     check()
 
 
+def mlp_block_push(x, gain, wg, wu, wd, peer_recv, world, rank, eps=1e-6):
+    """The MLP block whose down projection stores its partial rows into the owners' receive
+    buffers (`peer_recv`: one peer-mapped device address per rank)."""
+    descs = [_desc(x, 2), _desc(gain, 1), _desc(wg, 2), _desc(wu, 2), _desc(wd, 2)]
+    _sync_stream([x, gain, wg, wu, wd])
+    ptrs = (ctypes.c_void_p * world)(*[int(p) for p in peer_recv])
+    args = []
+    for d, r in zip(descs, (2, 1, 2, 2, 2)):
+        args += [r, ctypes.byref(d)]
+    lib().mlp_block_push_float16(*args, ptrs, int(world), int(rank), ctypes.c_float(float(eps)), 1, 1, 1, 0, 0, 0)
+    check()
+
+
+def tp_reduce_rows(recv, residual_rows, peer_out, world, rank):
+    """This rank's rows of the block output: sum of the `world` slots of `recv` plus the residual
+    rows, stored into every rank's output (`peer_out`: one peer-mapped address per rank)."""
+    _sync_stream([recv])
+    rows, cols = int(recv.shape[1]), int(recv.shape[2])
+    ptrs = (ctypes.c_void_p * world)(*[int(p) for p in peer_out])
+    res_ptr = None if residual_rows is None else residual_rows.data_ptr()
+    ld = 0 if residual_rows is None else int(residual_rows.stride(0))
+    if lib().b200mlir_tp_reduce_rows_float16(recv.data_ptr(), res_ptr, ld, ptrs, int(world), int(rank), rows,
+                                             cols) != 0:
+        check()
+
+
 # ---- library management -----------------------------------------------------------------
 
 def init(device: int = 0) -> None:

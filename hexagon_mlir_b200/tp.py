@@ -115,6 +115,52 @@ class TensorParallelMLP:
         return out
 
 
+class FusedTensorParallelMLP:
+    """The same block with the reduction fused into the kernels instead of an all-reduce.
+
+    The ranks' buffers are mapped into each other's address space (torch symmetric memory over
+    NVLink).  The down projection's read-out stores each fp16 partial row straight into the
+    receive slot of the rank that owns the row (rows are dealt out in `world` contiguous
+    blocks), so the reduce-scatter half of the exchange runs under the GEMM; after a barrier a
+    small kernel sums each owner's `world` slots in fp32, adds the residual rows and stores the
+    finished rows into every rank's output; a second barrier and every rank holds the block
+    output.  Partials are rounded to fp16 once and summed in fp32, so the result is at least
+    as close to the single-GPU block as the all-reduce form.  Needs tokens divisible by the
+    world size and a world of at most 8.
+    """
+
+    def __init__(self, gain, wg, wu, wd, tokens, eps=1e-6, group=None, timeout_ms=10000):
+        import torch.distributed._symmetric_memory as symm
+        if group is None:
+            group = dist.group.WORLD
+        self.gain, self.wg, self.wu, self.wd = gain, wg, wu, wd
+        self.eps = float(eps)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.tokens, self.width = int(tokens), int(wd.shape[1])
+        if self.tokens % self.world or self.world > 8:
+            raise ValueError("tokens must be divisible by the world size (<= 8)")
+        self.rows = self.tokens // self.world
+        self.timeout_ms = int(timeout_ms)
+        dev = wd.device
+        self.recv = symm.empty((self.world, self.rows, self.width), dtype=torch.float16, device=dev)
+        self.out = symm.empty((self.tokens, self.width), dtype=torch.float16, device=dev)
+        self._h_recv = symm.rendezvous(self.recv, group)
+        self._h_out = symm.rendezvous(self.out, group)
+        self._recv_ptrs = [int(p) for p in self._h_recv.buffer_ptrs]
+        self._out_ptrs = [int(p) for p in self._h_out.buffer_ptrs]
+
+    def __call__(self, x):
+        """Returns the block output (a buffer this object owns; valid until the next call)."""
+        if tuple(x.shape) != (self.tokens, self.width):
+            raise ValueError(f"expected x of shape {(self.tokens, self.width)}")
+        _l.mlp_block_push(x, self.gain, self.wg, self.wu, self.wd, self._recv_ptrs, self.world, self.rank, self.eps)
+        self._h_recv.barrier(channel=0, timeout_ms=self.timeout_ms)  # every rank's partial rows have landed
+        lo = self.rank * self.rows
+        _l.tp_reduce_rows(self.recv, x[lo:lo + self.rows], self._out_ptrs, self.world, self.rank)
+        self._h_out.barrier(channel=1, timeout_ms=self.timeout_ms)   # every rank's finished rows have landed
+        return self.out
+
+
 class ColumnShardedGemm:
     """C[:, lo:hi] = A · B[:, lo:hi] on each rank; A replicated; no collective."""
 

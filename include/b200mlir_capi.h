@@ -182,6 +182,24 @@ B200_API void mlp_block_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_ga
                                 int64_t rank_wu, B200MemRef2D *wu, int64_t rank_wd,
                                 B200MemRef2D *wd, int64_t rank_o, B200MemRef2D *out,
                                 float eps, int add_residual, B200_GRID_ARGS);
+/* The same block with the reduction over ranks fused in, for `world` GPUs of one node whose
+ * buffers are mapped into each other's address space (peer access / symmetric memory).  The
+ * down projection's read-out stores this rank's fp16 partial rows straight into the receive
+ * buffer of the rank that owns them: row r belongs to rank r / (T/world), whose buffer is
+ * [world][T/world][D] fp16 and is filled at slot `rank`; peer_recv[i] is rank i's buffer as
+ * mapped here.  After every rank's call has completed (a barrier the caller provides),
+ * b200mlir_tp_reduce_rows_float16 sums the owner's `world` slots, adds the residual rows and
+ * stores the finished rows into every rank's [T][D] output (peer_out[i]); after a second
+ * barrier all ranks hold the block output.  No reference counterpart (the reference is a
+ * single device); it replaces the all-reduce of the tensor-parallel form above.  Needs T
+ * divisible by world, world <= 8, D a multiple of 8. */
+B200_API void mlp_block_push_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_gain, B200MemRef1D *gain,
+                                     int64_t rank_wg, B200MemRef2D *wg, int64_t rank_wu, B200MemRef2D *wu,
+                                     int64_t rank_wd, B200MemRef2D *wd, void *const *peer_recv, int world,
+                                     int rank, float eps, B200_GRID_ARGS);
+B200_API int b200mlir_tp_reduce_rows_float16(const void *recv, const void *residual_rows, int64_t ld_residual,
+                                             void *const *peer_out, int world, int rank, int64_t rows_per_rank,
+                                             int64_t cols);
 
 /* ---- seam 2: runtime ---------------------------------------------------------
  * qcom_hexagon_backend/bin/runtime/include/HexagonCAPI.h:26-68.  `isVtcm`

@@ -52,9 +52,19 @@ def _worker(rank, world, port, q):
     cshard = torch.zeros((x.shape[0], hi - lo), dtype=torch.float16, device="cuda")
     tp.ColumnShardedGemm(rank, world)(xt, tp.shard_columns(T(wg), rank, world), cshard)
     torch.cuda.synchronize()
-    q.put((rank, status, out.cpu().numpy(), lo, hi, cshard.cpu().numpy()))
+    # the same block with the reduction fused into the kernels (peer stores over NVLink)
+    fused = tp.FusedTensorParallelMLP(T(gain), tp.shard_columns(T(wg), rank, world), tp.shard_columns(T(wu), rank, world),
+                                      tp.shard_rows(T(wd), rank, world), tokens=x.shape[0], eps=1e-6,
+                                      group=dist.group.WORLD, timeout_ms=20000)
+    runs = [fused(xt).clone() for _ in range(3)]
+    torch.cuda.synchronize()
+    status = status or hm.device_status()
+    fused_same = all(torch.equal(r, runs[0]) for r in runs)
+    q.put((rank, status, out.cpu().numpy(), lo, hi, cshard.cpu().numpy(), runs[0].cpu().numpy(), fused_same))
     dist.barrier()
-    dist.destroy_process_group()
+    q.close()
+    q.join_thread()  # results flushed to the parent
+    os._exit(0)      # (tearing the group down under live symmetric-memory mappings can block)
 
 
 @pytest.mark.parametrize("world", [2])
@@ -75,11 +85,16 @@ def test_tensor_parallel_mlp_on_gpus(oracle, cuda, world):
     x, gain, wg, wu, wd = _problem()
     want = oracle.mlp(x, gain, wg, wu, wd, 1e-6).astype(np.float32)
     full = np.zeros((x.shape[0], wg.shape[1]), np.float16)
-    for rank, status, out, lo, hi, cshard in results:
+    for rank, status, out, lo, hi, cshard, fused_out, fused_same in results:
         assert status == 0
         err = np.abs(out.astype(np.float32) - want).max() / np.abs(want).max()
         assert err <= 1e-2, (rank, err)
         full[:, lo:hi] = cshard
+        # fused form: fp16 partials summed in fp32 by the row owner; every rank ends with the same bytes
+        ferr = np.abs(fused_out.astype(np.float32) - want).max() / np.abs(want).max()
+        assert ferr <= 1e-2, (rank, ferr)
+        assert fused_same
+    assert np.array_equal(results[0][6], results[1][6])
     assert np.array_equal(results[0][2], results[1][2])
     ref = oracle.gemm_f16(x, wg).astype(np.float32)
     assert np.abs(full.astype(np.float32) - ref).max() / np.abs(ref).max() <= 1e-2

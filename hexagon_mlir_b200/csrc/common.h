@@ -40,6 +40,7 @@ struct Options {
   double kloop_block_k = 64;
   double w8a16_variant = -1;
   double gemm_group_m = 0;         // 0: the kernels' default band height
+  double gemm_dependent_launch = 1;   // programmatic dependent launch of the tcgen05 GEMM kernels
   double w8a16_dependent_launch = 1;  // programmatic dependent launch of the w8a16 kernel (measured: -7 % per call in a chain)
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
 };
@@ -89,6 +90,22 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at;
   cfg.numAttrs = ctx().opt.enable_pdl != 0 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+// The same for any kernel, switched by `dependent` (the GEMM kernels use option gemmDependentLaunch).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_maybe_dependent(bool dependent, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                          cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = dependent ? 1 : 0;
   return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 #ifdef __CUDACC__

@@ -63,6 +63,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_gen + 16 * STAGES + 36);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // A programmatic dependent of the previous kernel in the stream: our own successor may start
+  // now; we touch what the predecessor wrote only after the producer's griddepcontrol.wait
+  // (every other access of the CTA is ordered after it through the mbarriers).
+  pdl_trigger();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -91,6 +95,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
+      pdl_wait();
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -325,7 +330,8 @@ int launch_one(const GemmArgs &g, const TcVariantInfo &vi) {
     attr_set = true;
   }
   int grid = p.num_tiles < c.sm_count ? p.num_tiles : c.sm_count;
-  kern<<<grid, NUM_THREADS, vi.smem_bytes, c.stream>>>(tmA, tmB, tmB2, p);
+  B200_CUDA(launch_maybe_dependent(c.opt.gemm_dependent_launch != 0, kern, dim3((unsigned)grid), dim3(NUM_THREADS),
+                                   (size_t)vi.smem_bytes, c.stream, tmA, tmB, tmB2, p));
   return check_launch(vi.name);
 }
 

@@ -134,6 +134,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const uint32_t rank = cluster_rank();
   const bool leader = rank == 0;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  // A programmatic dependent of the previous kernel in the stream: our own successor may start
+  // now; what the predecessor wrote is touched only after the producers' griddepcontrol.wait
+  // (every other access of the pair is ordered after it through the mbarriers).
+  pdl_trigger();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -163,6 +167,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 0) {
     // ---------------- TMA producer: this CTA's 128 rows of A and 128 columns of B ----------------
     if (lane == 0) {
+      pdl_wait();  // (see the note at the kernel's top)
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -353,7 +358,8 @@ int launch_pair(const GemmArgs &g, const char *name) {
     if (getenv("B200MLIR_DEBUG")) fprintf(stderr, "[b200mlir] 2-CTA gemm: %d resident pairs (occupancy query %d)\n", max_pairs, clusters);
   }
   int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
-  kern<<<2 * pairs, THREADS2, kSmem2, c.stream>>>(tmA, tmB, tmB2, p);
+  B200_CUDA(launch_maybe_dependent(c.opt.gemm_dependent_launch != 0, kern, dim3((unsigned)(2 * pairs)), dim3(THREADS2),
+                                   (size_t)kSmem2, c.stream, tmA, tmB, tmB2, p));
   return check_launch(name);
 }
 

@@ -7,8 +7,11 @@ Run where the reference checkout is available (its location: HEXMLIR_REFERENCE_R
 It (1) runs the reference's own layout leaves (HMXLayout.c, compiled by
 oracle/Makefile target "ref") on seeded inputs and stores inputs + outputs, and
 (2) imports the reference's stdlib-only backend/hmx_search.py and stores what
-its search-loop functions return on scripted measurements.  The tests read the
-fixtures only; nothing at test time touches the reference.
+its search-loop functions return on scripted measurements, and (3) evaluates the
+expected values of the reference's own device tests — the torch call each test
+compares its kernel against, on that test's shapes — and stores inputs and
+expectations.  The tests read the fixtures only; nothing at test time touches
+the reference.
 """
 import importlib.util
 import json
@@ -124,7 +127,49 @@ def search_fixture():
         json.dump(g, f, indent=1, sort_keys=True)
 
 
+def device_test_fixture():
+    """What the reference's device tests expect of each kernel: same shapes and input
+    distributions (torch.rand), the same torch call as the expected value.  The tolerance each
+    test applies is recorded beside it.  Sources: test/python/triton/test_softmax.py:18-19,71,
+    90-93; test_rms_norm.py:17-24,62-64,82-86; test_silu.py:18,21,51,68-69; test_matmul.py:17,
+    69-70,87-88; test_matmul_kloop.py:60-69,100-103,153-158."""
+    import torch
+    out = {}
+    # (the fp32 cases run on the widened fp16 inputs, so that each input is stored once)
+    torch.manual_seed(11)
+    x = torch.rand(128, 128, dtype=torch.float16)
+    out["softmax_x"] = x.numpy()
+    out["softmax_f16_expected"] = torch.nn.functional.softmax(x, dim=1, dtype=torch.float16).numpy()
+    out["softmax_f32_expected"] = torch.nn.functional.softmax(x.float(), dim=1, dtype=torch.float32).numpy()
+    torch.manual_seed(12)
+    x = torch.rand(127, 513, dtype=torch.float16)
+    w = torch.rand(513, dtype=torch.float16)
+    out["rmsnorm_x"], out["rmsnorm_w"] = x.numpy(), w.numpy()
+    out["rmsnorm_f16_expected"] = torch.nn.functional.rms_norm(x, (513,), weight=w, eps=1e-5).numpy()
+    out["rmsnorm_f32_expected"] = torch.nn.functional.rms_norm(x.float(), (513,), weight=w.float(), eps=1e-5).numpy()
+    torch.manual_seed(13)
+    x = torch.rand(16384, dtype=torch.float16)
+    out["silu_x"] = x.numpy()
+    out["silu_f16_expected"] = torch.nn.functional.silu(x).numpy()
+    out["silu_f32_expected"] = torch.nn.functional.silu(x.float()).numpy()
+    torch.manual_seed(14)
+    a = torch.rand((1024, 64), dtype=torch.float16)
+    b = torch.rand((64, 512), dtype=torch.float16)
+    out["matmul_a"], out["matmul_b"] = a.numpy(), b.numpy()
+    out["matmul_expected_rows_0_4"] = torch.matmul(a, b).numpy()[0::4]  # every fourth row
+    torch.manual_seed(0)  # the K-looped test seeds itself
+    a = torch.rand((256, 512), dtype=torch.float16)
+    b = torch.rand((512, 256), dtype=torch.float16)
+    out["kloop_a"], out["kloop_b"] = a.numpy(), b.numpy()
+    out["kloop_expected_f32"] = torch.matmul(a.float(), b.float()).numpy()
+    out["tolerances"] = np.array(json.dumps({
+        "softmax_f16_atol": 1e-3, "softmax_f32_atol": 1e-5, "rmsnorm_atol": 1e-2, "silu_atol": 1e-2,
+        "matmul_atol": 2e-1, "kloop_rel": 2e-3, "kloop_block_k": 256}))
+    np.savez_compressed(os.path.join(HERE, "device_tests_golden.npz"), **out)
+
+
 if __name__ == "__main__":
     layout_fixture()
     search_fixture()
+    device_test_fixture()
     print("wrote", sorted(os.listdir(HERE)))

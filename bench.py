@@ -224,9 +224,9 @@ def extras_single_gpu(torch, hm, peaks, only=None):
     def rand_h(shape, lo=-1.0, hi=1.0):
         return (torch.rand(shape, generator=g, device=dev) * (hi - lo) + lo).half()
 
-    for n in (1024, 4096, 8192):
-        if not want(f"gemm_f16_{n}") or (n == 8192 and only is None):
-            continue  # 8192^3 runs only when asked for by name (the 2-CTA kernel's capture)
+    for n in (512, 1024, 2048, 4096, 8192):  # the square sweep of the large-GEMM config
+        if not want(f"gemm_f16_{n}"):
+            continue
         # rotate over enough operand sets to exceed L2 between launches
         sets = max(2, int(np.ceil(3 * 126e6 / (3 * n * n * 2))))
         sets = min(sets, 24)
@@ -239,10 +239,18 @@ def extras_single_gpu(torch, hm, peaks, only=None):
             i = state["i"] % sets
             state["i"] += 1
             hm.matmul[(1,)](A[i], B[i], C[i])
-        ms = graph_timed(torch, fn, reps=5, inner=sets * 2) if n <= 1024 else timed(torch, fn, 40, 5)
+        ms = graph_timed(torch, fn, reps=5, inner=sets * 2) if n <= 1024 else timed(torch, fn, 40 if n <= 4096 else 10, 5)
         tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
         out[f"gemm_f16_{n}^3"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
                                   "variant": hm.gemm_explain(n, n, n)["name"]}
+        if only is None:
+            # what the on-device search (enumerate, verify, measure, gate, canary) picks for the shape
+            hm.autotune_cache_clear()
+            rep = hm.gemm_autotune(n, n, n)
+            names = {v["variant"]: v["name"] for v in hm.gemm_variants()}
+            out[f"gemm_f16_{n}^3"]["search"] = {"verdict": rep.get("round_verdict"),
+                                               "champion": names.get(rep.get("champion_variant"), None)}
+            hm.autotune_cache_clear()
         if n == 4096:
             # the K-looped form (fp16 read-out per 64-deep segment, fp32 running sum in the read-out warps)
             def fk():

@@ -205,6 +205,7 @@ struct W8A16Weight {
   const void *scales = nullptr;  // fp16 [N]
   void *image = nullptr;         // resident device image: [k/128][channel][128 B, pieces swizzled]
   void *scales_dev = nullptr;
+  void *w16 = nullptr;           // row-major fp16 f16(q*s), built on the first many-row call (see kW8A16ExpandRows)
   int64_t k = 0, n = 0;
   size_t image_bytes = 0;
   bool l2_persist = false;
@@ -212,7 +213,12 @@ struct W8A16Weight {
 int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
 int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
                  int64_t ldc);
+// Above this many activation rows a w8a16 product is compute-bound and every CTA of the streaming
+// kernel would re-read all activations from L2: the weight is expanded once to fp16 (2 bytes per
+// weight, kept with the registry entry) and the product goes through the fp16 GEMM.
+constexpr int64_t kW8A16ExpandRows = 128;
 // w8a16_tmem.cu
+int w8a16_expand_f16(const void *image, const __half *scales_dev, int64_t k, int64_t n, void **w16);
 int w8a16_build_tmem_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
 int launch_w8a16_tmem(const __half *a, const void *image, const __half *scales_dev, int64_t k, int64_t n,
                       __half *c, int64_t m, int64_t lda, int64_t ldc);

@@ -515,6 +515,7 @@ int b200mlir_w8a16_unregister_weight(const void *wq) {
   if (it == g_weights.end()) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 unregister: unknown weight");
   cudaStreamSynchronize(ctx().stream);
   cudaFree(it->second.image);
+  cudaFree(it->second.w16);
   cudaFree(it->second.scales_dev);
   g_weights.erase(it);
   return 0;
@@ -544,6 +545,9 @@ void w8a16_matmul(int64_t ra, B200MemRef2D *a, int64_t rw, B200MemRef2D *wq, int
     std::lock_guard<std::mutex> lk(g_w_mu);
     if (resident) {
       if (register_weight_locked(W.p, S.p, W.rows, W.cols, 0, &w)) return;
+      if (A.rows > kW8A16ExpandRows && !w->w16 &&
+          w8a16_expand_f16(w->image, (const __half *)w->scales_dev, w->k, w->n, &w->w16))
+        return;
       local = *w;
     }
   }

@@ -197,6 +197,15 @@ int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, in
     return set_error(B200MLIR_ERR_BAD_ARG,
                      "w8a16: activations must be 16-byte aligned with a row stride multiple of 8");
   if (w.k % 8) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16: K must be a multiple of 8");
+  if (m > kW8A16ExpandRows && w.w16) {
+    // many rows: compute-bound; the expanded fp16 weight goes through the fp16 GEMM
+    GemmArgs g;
+    g.a = a; g.b = w.w16; g.c = c;
+    g.m = m; g.n = w.n; g.k = w.k;
+    g.lda = lda; g.ldb = w.n; g.ldc = ldc;
+    g.epilogue = EPI_F16;
+    return gemm_dispatch(g);
+  }
   // rows in passes of at most 128 (the widest activation tile the kernel holds)
   for (int64_t m0 = 0; m0 < m; m0 += 128) {
     const int64_t mp = (m - m0) < 128 ? (m - m0) : 128;

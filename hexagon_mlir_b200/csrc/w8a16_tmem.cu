@@ -510,6 +510,31 @@ w8a16_tmem_image_kernel(const int8_t *__restrict__ wq, uint4 *__restrict__ image
   }
 }
 
+// resident image -> row-major fp16 [K,N], w16[k][n] = f16(f32(q) * f32(s[n])) (the oracle's dequantised
+// weight); one 16-byte piece (16 k of one channel) per thread, consecutive threads consecutive channels
+__global__ void __launch_bounds__(256)
+w8a16_expand_kernel(const uint4 *__restrict__ image, const __half *__restrict__ scales, __half *__restrict__ w16, int K,
+                    int N, int ksteps) {
+  const int64_t total = (int64_t)ksteps * N * 8;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const int n = (int)(i % N);
+    const int64_t r = i / N;
+    const int j = (int)(r & 7);
+    const int ks = (int)(r >> 3);
+    const uint4 v = image[((int64_t)ks * N + n) * 8 + (j ^ (n & 7))];
+    const float sc = __half2float(scales[n]);
+    const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const int k = ks * STEP_K + j * 16 + e;
+      if (k < K) {
+        const int q = (int)((words[e >> 2] >> (8 * (e & 3))) & 0xffu) - 128;
+        w16[(int64_t)k * N + n] = __float2half_rn((float)q * sc);
+      }
+    }
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -571,6 +596,25 @@ extern "C" __attribute__((visibility("default"))) int b200mlir_debug_get_trace3(
   return (int)cudaMemcpyFromSymbol(host, g_trace3_buf, sizeof(long long) * 8 * 64);
 }
 #endif
+
+int w8a16_expand_f16(const void *image, const __half *scales_dev, int64_t k, int64_t n, void **w16) {
+  B200_TRY(ensure_ready());
+  const int ksteps = (int)((k + STEP_K - 1) / STEP_K);
+  void *out = nullptr;
+  B200_CUDA(cudaMalloc(&out, (size_t)k * n * 2));
+  int64_t blocks = ((int64_t)ksteps * n * 8 + 255) / 256;
+  const int64_t cap = (int64_t)ctx().sm_count * 32;
+  if (blocks > cap) blocks = cap;
+  w8a16_expand_kernel<<<(unsigned)blocks, 256, 0, ctx().stream>>>((const uint4 *)image, scales_dev, (__half *)out, (int)k,
+                                                                (int)n, ksteps);
+  int rc = check_launch("w8a16_expand");
+  if (rc) {
+    cudaFree(out);
+    return rc;
+  }
+  *w16 = out;
+  return 0;
+}
 
 int w8a16_build_tmem_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes) {
   B200_TRY(ensure_ready());

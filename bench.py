@@ -352,6 +352,28 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         for wq_ in Wq:
             hm.unregister_w8a16_weight(wq_)
         del Wq
+        # the same kernel on a wider weight (a vocabulary projection): twice the bytes per CTA per launch,
+        # so the ~6 us a launch costs before and after its streaming phase weigh half as much
+        k, n = 4096, 32000
+        Wq = [torch.randint(-127, 128, (k, n), generator=g, device=dev, dtype=torch.int8) for _ in range(2)]
+        S = (torch.rand(n, generator=g, device=dev) * 0.019 + 0.001).half()
+        a = torch.randn((1, k), generator=g, device=dev).half()
+        c = torch.empty((1, n), dtype=torch.float16, device=dev)
+        state = {"i": 0}
+
+        def wide():
+            i = state["i"] % 2
+            state["i"] += 1
+            hm.w8a16_matmul[(1,)](a, Wq[i], S, c)
+        for _ in range(2):
+            wide()
+        ms = graph_timed(torch, wide, reps=10, inner=4)
+        bytes_ = k * n + 2 * n + 2 * k + 2 * n
+        out["w8a16_m1_4096x32000"] = {"us": ms * 1e3, "gbs": bytes_ / (ms * 1e-3) / 1e9,
+                                      "frac_of_measured_hbm": bytes_ / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+        for wq_ in Wq:
+            hm.unregister_w8a16_weight(wq_)
+        del Wq
     return out
 
 

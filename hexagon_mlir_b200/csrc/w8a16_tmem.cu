@@ -202,10 +202,8 @@ w8a16_tmem_kernel(const __grid_constant__ CUtensorMap tmA, const StreamParams p)
   // waiting) and start the first copies while the rest of the CTA is still setting up.
   if (warp >= W_WPROD && warp < W_APROD) {
     const int r = warp - W_WPROD;  // this producer's steps: r, r + WPRODS, ...
-    if (lane == 0) {
-      for (int i = r; i < DEPTH; i += WPRODS) mbar_init(bar_wfull + 8 * i, 1);
-      fence_barrier_init();
-    }
+    if (lane < DEPTH && lane % WPRODS == r) mbar_init(bar_wfull + 8 * lane, 1);
+    fence_barrier_init();
     __syncwarp();
     asm volatile("bar.arrive 1, %0;" ::"n"(THREADS) : "memory");
     if (lane == 0) {
@@ -219,10 +217,8 @@ w8a16_tmem_kernel(const __grid_constant__ CUtensorMap tmA, const StreamParams p)
     }
   }
   if (warp == W_APROD) {
-    if (lane == 0) {
-      for (int i = 0; i < DA; ++i) mbar_init(bar_afull + 8 * i, 1);
-      fence_barrier_init();
-    }
+    if (lane < DA) mbar_init(bar_afull + 8 * lane, 1);
+    fence_barrier_init();
     __syncwarp();
     asm volatile("bar.arrive 1, %0;" ::"n"(THREADS) : "memory");
     if (lane == 0) {
@@ -237,16 +233,19 @@ w8a16_tmem_kernel(const __grid_constant__ CUtensorMap tmA, const StreamParams p)
       }
     }
   }
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < DEPTH; ++i) mbar_init(bar_wfree + 8 * i, 4);
-    for (int i = 0; i < DA; ++i) mbar_init(bar_afree + 8 * i, 1);
-    for (int i = 0; i < TB; ++i) {
-      mbar_init(bar_tfull + 8 * i, 4);
-      mbar_init(bar_done + 8 * i, 1);
+  if (warp == 0) {
+    // the remaining ~40 barriers, one lane each (a lone thread needs ~1000 clocks for them)
+    if (lane < DEPTH) mbar_init(bar_wfree + 8 * lane, 4);
+    if (lane < DA) mbar_init(bar_afree + 8 * lane, 1);
+    if (lane < TB) {
+      mbar_init(bar_tfull + 8 * lane, 4);
+      mbar_init(bar_done + 8 * lane, 1);
     }
-    mbar_init(bar_accfull, ISS);
-    mbar_init(bar_accfree, EPI_W);
-    *abort_flag = 0;
+    if (lane == 0) {
+      mbar_init(bar_accfull, ISS);
+      mbar_init(bar_accfree, EPI_W);
+      *abort_flag = 0;
+    }
     fence_barrier_init();
   }
   if (warp == W_MMA0) {

@@ -149,6 +149,33 @@ class FusedTensorParallelMLP:
         self._recv_ptrs = [int(p) for p in self._h_recv.buffer_ptrs]
         self._out_ptrs = [int(p) for p in self._h_out.buffer_ptrs]
 
+    def captured(self, x):
+        """The same step replayed from a CUDA graph captured on first use for this `x` (kernels and
+        both barriers); refill `x` in place between replays."""
+        key = (x.data_ptr(), tuple(x.shape))
+        if getattr(self, "_graph", None) is None or self._graph_key != key:
+            self(x)
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                self(x)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    self(x)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self._graph, self._graph_key = graph, key
+        self._graph.replay()
+        return self.out
+
+    def release(self):
+        """Drop the captured graph before the process group or the symmetric buffers go."""
+        if getattr(self, "_graph", None) is not None:
+            torch.cuda.synchronize()
+            self._graph = None
+
     def __call__(self, x):
         """Returns the block output (a buffer this object owns; valid until the next call)."""
         if tuple(x.shape) != (self.tokens, self.width):

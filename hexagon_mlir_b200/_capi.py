@@ -81,6 +81,8 @@ _SIGNATURES = {
     "hexagon_runtime_free_2d": (None, [c_void_p]),
     "hexagon_runtime_copy": (None, [c_void_p, c_void_p, ctypes.c_size_t, ctypes.c_bool,
                                     ctypes.c_bool]),
+    "hexagon_runtime_build_crouton": (c_void_p, [c_void_p, ctypes.c_size_t]),
+    "hexagon_runtime_get_contiguous_memref": (c_void_p, [c_void_p]),
     "hexagon_runtime_resident_scope_enter_v2": (ctypes.c_int32, [ctypes.c_uint64, ctypes.c_uint64]),
     "hexagon_runtime_workspace_resident_v2": (c_void_p, [ctypes.c_uint64, ctypes.c_uint32,
                                                          ctypes.c_uint32, ctypes.c_uint32]),

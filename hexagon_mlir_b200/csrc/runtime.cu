@@ -299,8 +299,14 @@ void *hexagon_runtime_alloc_1d(size_t bytes, uint64_t alignment, bool isVtcm) {
   return p;
 }
 
+static std::unordered_map<void *, void *> g_alias;  // tile-pointer table -> its contiguous source
+
 void hexagon_runtime_free_1d(void *ptr) {
   clear_error();
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_alias.erase(ptr);  // freeing a tile-pointer table ends the alias, not the source
+  }
   if (ptr && cudaFree(ptr) != cudaSuccess)
     set_error(B200MLIR_ERR_CUDA, "free_1d failed: %s", cudaGetErrorString(cudaGetLastError()));
 }
@@ -330,6 +336,42 @@ void hexagon_runtime_copy(void *dst, void *src, size_t nbytes, bool, bool) {
   if (e == cudaSuccess && !(is_device_ptr(dst) && is_device_ptr(src)))
     e = cudaStreamSynchronize(ctx().stream);  // host side must observe completion
   if (e != cudaSuccess) set_error(B200MLIR_ERR_CUDA, "copy failed: %s", cudaGetErrorString(e));
+}
+
+// Buffer alias (bin/runtime/include/HexagonCAPI.h:34-37, src/HexagonCAPI.cpp:113-126): a table of
+// pointers to the 2048-byte tiles of a contiguous buffer, and the way back from the table.
+void *hexagon_runtime_build_crouton(void *source, size_t nbytes) {
+  clear_error();
+  if (ensure_ready()) return nullptr;
+  if (!source || nbytes == 0 || nbytes % 2048 != 0) {
+    set_error(B200MLIR_ERR_BAD_ARG, "build_crouton: size must be a positive multiple of 2048 bytes");
+    return nullptr;
+  }
+  const size_t n = nbytes / 2048;
+  std::vector<void *> host(n);
+  for (size_t i = 0; i < n; ++i) host[i] = (char *)source + i * 2048;
+  void *table = nullptr;
+  cudaError_t e = cudaMalloc(&table, n * sizeof(void *));
+  if (e == cudaSuccess) e = cudaMemcpy(table, host.data(), n * sizeof(void *), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    if (table) cudaFree(table);
+    set_error(B200MLIR_ERR_CUDA, "build_crouton: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_alias[table] = source;
+  return table;
+}
+
+void *hexagon_runtime_get_contiguous_memref(void *table) {
+  clear_error();
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_alias.find(table);
+  if (it == g_alias.end()) {
+    set_error(B200MLIR_ERR_BAD_ARG, "get_contiguous_memref: not a table built by build_crouton");
+    return nullptr;
+  }
+  return it->second;
 }
 
 // ---- seam 2: residency ---------------------------------------------------------------------

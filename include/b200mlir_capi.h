@@ -217,6 +217,14 @@ B200_API void *hexagon_runtime_alloc_2d(size_t numBlocks, size_t blockSize, uint
 B200_API void hexagon_runtime_free_2d(void *ptr);
 B200_API void hexagon_runtime_copy(void *dst, void *src, size_t nbytes, bool isDstVtcm,
                                    bool isSrcVtcm);
+/* Tile-pointer alias of a contiguous buffer (HexagonCAPI.h:34-37; impl
+ * bin/runtime/src/HexagonCAPI.cpp:113-126).  build_crouton returns a device table of
+ * nbytes/2048 pointers, entry i = source + i*2048 (nbytes must be a positive multiple of 2048,
+ * otherwise NULL with the error recorded, where the reference asserts);
+ * get_contiguous_memref maps such a table back to its source, NULL for any other pointer.
+ * The table is released with hexagon_runtime_free_1d, which leaves the source untouched. */
+B200_API void *hexagon_runtime_build_crouton(void *source, size_t nbytes);
+B200_API void *hexagon_runtime_get_contiguous_memref(void *source);
 /* Residency (HexagonCAPI.h:39-57; impl bin/runtime/src/HexagonCAPI.cpp:132-206).
  * One immutable scope per process; requests before scope entry fail; a weight
  * is identified by its source address and exact (bytes, alignment) descriptor

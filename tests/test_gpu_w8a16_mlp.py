@@ -166,6 +166,16 @@ def test_runtime_seam_on_device(hm, cuda):
     lib.hexagon_runtime_copy(p, src.ctypes.data, 4096, True, False)
     lib.hexagon_runtime_copy(dst.ctypes.data, p, 4096, False, True)
     assert np.array_equal(src, dst)
+    # tile-pointer alias: entry i points at byte i*2048 of the source, and maps back to it
+    tab = lib.hexagon_runtime_build_crouton(p, 4096)
+    assert tab and lib.hexagon_runtime_get_contiguous_memref(tab) == p
+    ptrs = np.zeros(2, np.uint64)
+    lib.hexagon_runtime_copy(ptrs.ctypes.data, tab, 16, False, True)
+    assert ptrs.tolist() == [p, p + 2048]
+    assert lib.hexagon_runtime_build_crouton(p, 4000) is None and hm._capi.last_error()[0] == 2
+    assert lib.hexagon_runtime_get_contiguous_memref(p) is None
+    lib.hexagon_runtime_free_1d(tab)
+    assert lib.hexagon_runtime_get_contiguous_memref(tab) is None
     lib.hexagon_runtime_free_1d(p)
     assert lib.hexagon_runtime_alloc_1d(0, 128, False) is None and hm._capi.last_error()[0] == 2
     # workspace residency: same (key, instance) -> same address; instances are separate

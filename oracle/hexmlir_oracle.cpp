@@ -306,6 +306,93 @@ void oracle_mlp_f16(const f16 *X, const f16 *Gain, const f16 *Wg, const f16 *Wu,
   oracle_add_f16(d.data(), X, Y, T * D, nthreads);
 }
 
+// Attention block (QK·softmax·PV), one row of queries at a time, in the order of the
+// reference's flash-attention kernel (test/python/triton/test_flash_attention.py:43-113 is
+// the loop over key blocks, :172-195 the prologue and the final division):
+//   qk_scale = sm_scale * 1.44269504;  m = -99999999999999, l = 1, acc = 0
+//   per BLOCK_N keys:  qk = q·kᵀ;  m' = max(m, max_j(qk)·qk_scale);  p = exp2(qk·qk_scale − m');
+//                      alpha = exp2(m − m');  l = l·alpha + Σp;  acc = acc·alpha + p·v;  m = m'
+//   out = acc / l
+// Both products take fp16 operands with a wide accumulate: Q, K, V arrive as fp16 (an fp32
+// tensor is rounded by the pack leaf, same file :239-246) and p is rounded to fp16 before p·v.
+// flags bit 0: each product's read-out is rounded to fp16 before it is used in fp32, as the
+//              engine's read-out tile is (include/hexagon/Dialect/Hmx/IR/HmxOps.td:308-316);
+// flags bit 1: p stays fp32 (what the kernel source computes when no operand is quantised;
+//              used to pin this function against the kernel run by Triton's interpreter).
+// Q, K, V: [BH, N, D] contiguous; O: [BH, N, D] fp32.
+void oracle_attention_f16(const f16 *Q, const f16 *K, const f16 *V, float *O, int64_t BH,
+                          int64_t N, int64_t D, double sm_scale, int block_n, int flags,
+                          int nthreads) {
+  const float qk_scale = (float)(sm_scale * 1.44269504);
+  const bool round_out = flags & 1, p_f32 = flags & 2;
+  parallel_for(BH * N, nthreads, [&](int64_t lo, int64_t hi) {
+    std::vector<float> qk(block_n), p(block_n), acc(D), pv(D), qf(D);
+    for (int64_t row = lo; row < hi; ++row) {
+      const int64_t bh = row / N;
+      const f16 *q = Q + row * D;
+      const f16 *Kb = K + bh * N * D, *Vb = V + bh * N * D;
+      for (int64_t d = 0; d < D; ++d) qf[d] = (float)q[d];
+      float m = -99999999999999.0f, l = 1.0f;
+      std::fill(acc.begin(), acc.end(), 0.0f);
+      for (int64_t n0 = 0; n0 < N; n0 += block_n) {
+        const int64_t nb = std::min<int64_t>(block_n, N - n0);
+        float mx = -INFINITY;
+        for (int64_t j = 0; j < nb; ++j) {
+          const f16 *kr = Kb + (n0 + j) * D;
+          float a = 0.0f;
+          for (int64_t d = 0; d < D; ++d) a += qf[d] * (float)kr[d];
+          if (round_out) a = (float)(f16)a;
+          qk[j] = a;
+          mx = std::max(mx, a);
+        }
+        const float m_new = std::max(m, mx * qk_scale);
+        float lsum = 0.0f;
+        for (int64_t j = 0; j < nb; ++j) {
+          const float e = exp2f(qk[j] * qk_scale - m_new);
+          lsum += e;
+          p[j] = p_f32 ? e : (float)(f16)e;
+        }
+        const float alpha = exp2f(m - m_new);
+        l = l * alpha + lsum;
+        std::fill(pv.begin(), pv.end(), 0.0f);
+        for (int64_t j = 0; j < nb; ++j) {
+          const f16 *vr = Vb + (n0 + j) * D;
+          const float pj = p[j];
+          for (int64_t d = 0; d < D; ++d) pv[d] += pj * (float)vr[d];
+        }
+        for (int64_t d = 0; d < D; ++d)
+          acc[d] = acc[d] * alpha + (round_out ? (float)(f16)pv[d] : pv[d]);
+        m = m_new;
+      }
+      float *o = O + row * D;
+      for (int64_t d = 0; d < D; ++d) o[d] = acc[d] / l;
+    }
+  });
+}
+
+// Two-phase ("online") softmax over column blocks, fp32
+// (test/python/triton/test_online_softmax.py:27-77): phase 1 keeps a running maximum m and a
+// running sum l = l·exp(m − m') + Σ exp(x − m') per block; phase 2 writes exp(x − m)/l.
+void oracle_online_softmax_f32(const float *X, float *Y, int64_t rows, int64_t cols,
+                               int64_t block_cols, int nthreads) {
+  parallel_for(rows, nthreads, [&](int64_t lo, int64_t hi) {
+    for (int64_t r = lo; r < hi; ++r) {
+      const float *x = X + r * cols;
+      float m = -INFINITY, l = 0.0f;
+      for (int64_t c0 = 0; c0 < cols; c0 += block_cols) {
+        const int64_t c1 = std::min(cols, c0 + block_cols);
+        float mx = m;
+        for (int64_t c = c0; c < c1; ++c) mx = std::max(mx, x[c]);
+        float s = 0.0f;
+        for (int64_t c = c0; c < c1; ++c) s += expf(x[c] - mx);
+        l = l * expf(m - mx) + s;
+        m = mx;
+      }
+      for (int64_t c = 0; c < cols; ++c) Y[r * cols + c] = expf(x[c] - m) / l;
+    }
+  });
+}
+
 // ---- tile ("crouton") layout -------------------------------------------
 // One 32x32 fp16 tile is 2048 bytes; element (r, c) lives at byte
 //   128*(r>>1) + 4*c + 2*(r&1)

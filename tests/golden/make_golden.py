@@ -11,7 +11,9 @@ its search-loop functions return on scripted measurements, and (3) evaluates the
 expected values of the reference's own device tests — the torch call each test
 compares its kernel against, on that test's shapes — and stores inputs and
 expectations.  The tests read the fixtures only; nothing at test time touches
-the reference.
+the reference.  (4) runs the reference's flash-attention and online-softmax kernel
+sources (test/python/triton/test_flash_attention.py, test_online_softmax.py) with
+Triton's CPU interpreter on seeded inputs and stores inputs and outputs.
 """
 import importlib.util
 import json
@@ -168,8 +170,61 @@ def device_test_fixture():
     np.savez_compressed(os.path.join(HERE, "device_tests_golden.npz"), **out)
 
 
+def attention_fixture():
+    """Outputs of the reference's own kernel sources, executed by Triton's interpreter (numpy on
+    the CPU, every value fp32): attention_fwd_kernel (test_flash_attention.py:116-195) and
+    online_softmax (test_online_softmax.py:27-77).  Inputs are torch.rand rounded to fp16 and
+    stored as fp16, so that an implementation with fp16 operands starts from the same numbers."""
+    os.environ["TRITON_INTERPRET"] = "1"
+    assert "triton" not in sys.modules, "the interpreter switch is read when triton is imported"
+    import torch
+
+    def load(name):
+        path = os.path.join(REF, "test", "python", "triton", name + ".py")
+        src = open(path).read().replace("from .. import parameterize_func_name", "")
+        mod = type(sys)("ref_" + name)
+        mod.__file__ = path
+        import linecache
+        linecache.cache[path] = (len(src), None, src.splitlines(True), path)  # the jit reads sources
+        exec(compile(src, path, "exec"), mod.__dict__)
+        return mod
+
+    fa = load("test_flash_attention")
+    out = {}
+    for tag, (n_ctx, block_n, seed) in {"a": (256, 64, 21), "b": (128, 32, 22)}.items():
+        torch.manual_seed(seed)
+        q, k, v = (torch.rand(1, 1, n_ctx, fa.D_HEAD).half() for _ in range(3))
+        o = torch.zeros(1, 1, n_ctx, fa.D_HEAD)
+        fa.attention_fwd_kernel[(1,)](
+            pid1=0, Q=q.float(), K=k.float(), V=v.float(), sm_scale=fa.SCALE, Out=o, H=1, N_CTX=n_ctx,
+            BLOCK_M=n_ctx, BLOCK_DMODEL=fa.D_HEAD, BLOCK_N=block_n, STAGE=fa.STAGE,
+            stride_0=n_ctx * fa.D_HEAD, stride_1=n_ctx * fa.D_HEAD, stride_2=fa.D_HEAD, stride_3=1)
+        out[f"attn_{tag}_q"], out[f"attn_{tag}_k"], out[f"attn_{tag}_v"] = q.numpy(), k.numpy(), v.numpy()
+        out[f"attn_{tag}_out"] = o.numpy()
+        out[f"attn_{tag}_block_n"] = np.array(block_n)
+    out["attn_scale"] = np.array(fa.SCALE)
+    out["attn_rel_tolerance"] = np.array(5e-3)  # test_flash_attention.py:248-249
+    os_ = load("test_online_softmax")
+    torch.manual_seed(23)
+    rows, cols = os_.CONSTANTS["NUM_ROWS"], os_.CONSTANTS["NUM_COLS"]
+    x = torch.rand(rows, cols)
+    out["online_x"] = x.numpy()
+    for threads in (1, 4):  # test_online_softmax.py:80-92: row and column blocks are rows/threads, cols/threads
+        y = torch.empty_like(x)
+        os_.online_softmax[(threads,)](x, y, NUM_ROWS=rows, NUM_COLS=cols, BLOCK_ROW_SIZE=rows // threads,
+                                       BLOCK_COL_SIZE=cols // threads)
+        out[f"online_y_threads{threads}"] = y.numpy()
+    out["online_atol"] = np.array(os_.ATOL)
+    np.savez_compressed(os.path.join(HERE, "attention_golden.npz"), **out)
+
+
 if __name__ == "__main__":
+    if len(sys.argv) > 1 and sys.argv[1] == "attention":  # needs a process in which triton is not yet imported
+        attention_fixture()
+        sys.exit(0)
     layout_fixture()
     search_fixture()
     device_test_fixture()
+    import subprocess
+    subprocess.run([sys.executable, os.path.abspath(__file__), "attention"], check=True)
     print("wrote", sorted(os.listdir(HERE)))

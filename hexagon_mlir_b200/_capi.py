@@ -30,6 +30,11 @@ class MemRef2D(ctypes.Structure):
                 ("sizes", c_i64 * 2), ("strides", c_i64 * 2)]
 
 
+class MemRef4D(ctypes.Structure):
+    _fields_ = [("allocated", c_void_p), ("aligned", c_void_p), ("offset", c_i64),
+                ("sizes", c_i64 * 4), ("strides", c_i64 * 4)]
+
+
 class B200Error(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"b200mlir error {code}: {message}")
@@ -42,6 +47,7 @@ _lib = None
 _GRID = [c_int] * 6
 _M2 = ctypes.POINTER(MemRef2D)
 _M1 = ctypes.POINTER(MemRef1D)
+_M4 = ctypes.POINTER(MemRef4D)
 
 _SIGNATURES = {
     "b200mlir_init": (c_int, [c_int]),
@@ -59,6 +65,8 @@ _SIGNATURES = {
     "multispan_matmul": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
     "matmul_f32out": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
     "matmul_i8": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
+    "attention_fwd_kernel_float16": (None, [c_i64, _M4] * 4 + [ctypes.c_float] + _GRID),
+    "attention_fwd_kernel_float32": (None, [c_i64, _M4] * 4 + [ctypes.c_float] + _GRID),
     "softmax_kernel_float16": (None, [c_i64, _M2, c_i64, _M2] + _GRID),
     "softmax_kernel_float32": (None, [c_i64, _M2, c_i64, _M2] + _GRID),
     "rms_norm_fwd_kernel_float16": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M1] + _GRID),

@@ -13,7 +13,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200mlir.so")
 
 SOURCES = ["runtime.cu", "row_kernels.cu", "layout.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu",
-           "w8a16.cu", "w8a16_tmem.cu", "tuner.cu", "report.cu", "entry.cu"]
+           "w8a16.cu", "w8a16_tmem.cu", "attention_tmem.cu", "tuner.cu", "report.cu", "entry.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

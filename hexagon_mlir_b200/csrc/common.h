@@ -42,6 +42,7 @@ struct Options {
   double gemm_group_m = 0;         // 0: the kernels' default band height
   double gemm_dependent_launch = 1;   // programmatic dependent launch of the tcgen05 GEMM kernels
   double w8a16_dependent_launch = 1;  // programmatic dependent launch of the w8a16 kernel (measured: -7 % per call in a chain)
+  double attention_tiles = 0;      // query tiles per CTA of the attention kernel: 0 chooses by size, 1 or 2
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
 };
 
@@ -222,6 +223,13 @@ int w8a16_expand_f16(const void *image, const __half *scales_dev, int64_t k, int
 int w8a16_build_tmem_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
 int launch_w8a16_tmem(const __half *a, const void *image, const __half *scales_dev, int64_t k, int64_t n,
                       __half *c, int64_t m, int64_t lda, int64_t ldc);
+
+// attention_tmem.cu — softmax(Q·Kᵀ·sm_scale)·V per (batch, head); q, k, v share one stride set
+// (elements; the head dimension is contiguous), out has its own; f32 = fp32 tensors (operands are
+// rounded to fp16 first), else fp16
+int launch_attention(const void *q, const void *k, const void *v, void *out, bool f32, int64_t z, int64_t h,
+                     int64_t n, int64_t d, int64_t sz, int64_t sh, int64_t sn, int64_t soz, int64_t soh,
+                     int64_t son, double sm_scale);
 
 // dispatch.cpp
 int gemm_dispatch(const GemmArgs &g);  // picks a variant (option / cache / heuristic) and launches

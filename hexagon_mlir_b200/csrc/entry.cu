@@ -499,6 +499,68 @@ void add_kernel_float16(int64_t rx, B200MemRef1D *x, int64_t ry, B200MemRef1D *y
   ew_impl(3, rx, x, ry, y, ro, o);
 }
 
+// ---- attention block ---------------------------------------------------------------------------
+struct View4 {
+  void *p;
+  int64_t z, h, n, d, sz, sh, sn;
+  size_t span(size_t esz) const { return (size_t)((z - 1) * sz + (h - 1) * sh + (n - 1) * sn + d) * esz; }
+};
+static int view4(const char *what, int64_t rank, const B200MemRef4D *m, size_t esz, View4 *v) {
+  if (rank != 4 || !m)
+    return set_error(B200MLIR_ERR_BAD_ARG, "%s: expected a rank-4 memref descriptor (got rank %lld)", what, (long long)rank);
+  for (int i = 0; i < 4; ++i)
+    if (m->sizes[i] < 1 || m->strides[i] < 0)
+      return set_error(B200MLIR_ERR_BAD_ARG, "%s: extent %d is %lld", what, i, (long long)m->sizes[i]);
+  if (m->strides[3] != 1) return set_error(B200MLIR_ERR_BAD_ARG, "%s: innermost stride must be 1", what);
+  if (!m->aligned) return set_error(B200MLIR_ERR_BAD_ARG, "%s: null data pointer", what);
+  v->p = (char *)m->aligned + m->offset * (int64_t)esz;
+  v->z = m->sizes[0], v->h = m->sizes[1], v->n = m->sizes[2], v->d = m->sizes[3];
+  v->sn = v->n > 1 ? m->strides[2] : v->d;
+  v->sh = v->h > 1 ? m->strides[1] : v->n * v->sn;
+  v->sz = v->z > 1 ? m->strides[0] : std::max(v->h * v->sh, v->n * v->sn);
+  return 0;
+}
+static void attention_impl(bool f32, int64_t rq, B200MemRef4D *q, int64_t rk, B200MemRef4D *k, int64_t rv,
+                           B200MemRef4D *v, int64_t ro, B200MemRef4D *out, float sm_scale) {
+  if (ensure_ready()) return;
+  const size_t esz = f32 ? 4 : 2;
+  View4 Q, K, V, O;
+  if (view4("Q", rq, q, esz, &Q) || view4("K", rk, k, esz, &K) || view4("V", rv, v, esz, &V) ||
+      view4("Out", ro, out, esz, &O))
+    return;
+  for (const View4 *t : {&K, &V, &O})
+    if (t->z != Q.z || t->h != Q.h || t->n != Q.n || t->d != Q.d) {
+      set_error(B200MLIR_ERR_BAD_ARG, "attention: Q, K, V and Out must have one shape [Z, H, N_CTX, D_HEAD]");
+      return;
+    }
+  for (const View4 *t : {&K, &V})
+    if (t->sz != Q.sz || t->sh != Q.sh || t->sn != Q.sn) {
+      // the reference kernel takes one stride set for all of its tensors (test_flash_attention.py:31-34)
+      set_error(B200MLIR_ERR_BAD_ARG, "attention: Q, K and V must share their strides");
+      return;
+    }
+  Stager st;
+  const void *dq, *dk, *dv;
+  void *dout;
+  if (st.in(Q.p, Q.span(esz), &dq) || st.in(K.p, K.span(esz), &dk) || st.in(V.p, V.span(esz), &dv) ||
+      st.out(O.p, O.span(esz), &dout, O.span(esz) != (size_t)(O.z * O.h * O.n * O.d) * esz))
+    return;
+  if (launch_attention(dq, dk, dv, dout, f32, Q.z, Q.h, Q.n, Q.d, Q.sz, Q.sh, Q.sn, O.sz, O.sh, O.sn, (double)sm_scale))
+    return;
+  st.finish();
+}
+
+void attention_fwd_kernel_float16(int64_t rq, B200MemRef4D *q, int64_t rk, B200MemRef4D *k, int64_t rv,
+                                  B200MemRef4D *v, int64_t ro, B200MemRef4D *out, float sm_scale, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  attention_impl(false, rq, q, rk, k, rv, v, ro, out, sm_scale);
+}
+void attention_fwd_kernel_float32(int64_t rq, B200MemRef4D *q, int64_t rk, B200MemRef4D *k, int64_t rv,
+                                  B200MemRef4D *v, int64_t ro, B200MemRef4D *out, float sm_scale, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  attention_impl(true, rq, q, rk, k, rv, v, ro, out, sm_scale);
+}
+
 int b200mlir_w8a16_register_weight(const void *wq, const void *scales, int64_t k, int64_t n, int l2_persist) {
   clear_error();
   B200_TRY(ensure_ready());

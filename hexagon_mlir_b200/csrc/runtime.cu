@@ -253,6 +253,7 @@ static double *option_slot(const char *name) {
   if (!strcmp(name, "gemmGroupM")) return &o.gemm_group_m;
   if (!strcmp(name, "w8a16DependentLaunch")) return &o.w8a16_dependent_launch;
   if (!strcmp(name, "gemmDependentLaunch")) return &o.gemm_dependent_launch;
+  if (!strcmp(name, "attentionTiles")) return &o.attention_tiles;
   return nullptr;
 }
 

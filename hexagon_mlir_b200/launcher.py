@@ -18,7 +18,7 @@ import json
 import numpy as np
 
 from . import _capi
-from ._capi import B200Error, MemRef1D, MemRef2D, check, lib
+from ._capi import B200Error, MemRef1D, MemRef2D, MemRef4D, check, lib
 
 try:  # torch is plumbing (device memory, streams); numpy tensors work without it
     import torch
@@ -60,7 +60,7 @@ def _desc(t, rank):
     if len(shape) != rank:
         # the reference hands the kernel the tensor's own rank; a mismatch is the caller's bug
         raise ValueError(f"expected a rank-{rank} tensor, got shape {shape}")
-    d = (MemRef1D if rank == 1 else MemRef2D)()
+    d = {1: MemRef1D, 2: MemRef2D, 4: MemRef4D}[rank]()
     d.allocated = ptr
     d.aligned = ptr
     d.offset = 0
@@ -151,6 +151,42 @@ mlp_block = Kernel(
                                 int(bool(opts.get("add_residual", True)))])
 mlp_block.scalar_options = {}
 _ACCEPTED |= {"eps", "add_residual"}
+
+
+class _AttentionKernel(Kernel):
+    """``attention_fwd_kernel[grid](pid1=0, Q=q, K=k, V=v, sm_scale=s, Out=o, H=h, ...)`` as the
+    reference launches it (test/python/triton/test_flash_attention.py:212-236): tensors are
+    [Z, H, N_CTX, D_HEAD], every argument may be given by keyword, the tl.constexpr extras are
+    accepted and not passed on.  With ``pid1`` given only that (batch, head) is computed, as in
+    the reference kernel (off_hz = pid1, :133-137); without it, all of them in one launch."""
+
+    def __getitem__(self, grid):
+        def run(*args, **kw):
+            names = ("pid1", "Q", "K", "V", "sm_scale", "Out", "H")
+            for n, a in zip(names, args):
+                kw[n] = a
+            q, k, v, out = (kw.pop(n) for n in ("Q", "K", "V", "Out"))
+            sm_scale = float(kw.pop("sm_scale"))
+            pid1 = kw.pop("pid1", None)
+            kw.pop("H", None)
+            if pid1 is not None:
+                z, h = divmod(int(pid1), q.shape[1])
+                q, k, v, out = (t[z:z + 1, h:h + 1] for t in (q, k, v, out))
+            launch = _Launch(self, 1)
+            launch(q, k, v, out, sm_scale=sm_scale, **kw)
+        return run
+
+
+attention_fwd_kernel = _AttentionKernel(
+    "attention_fwd_kernel", (4, 4, 4, 4), by_dtype=True,
+    scalars=lambda args, opts: [ctypes.c_float(float(opts["sm_scale"]))])
+_ACCEPTED |= {"sm_scale", "enableVectorization", "stride_0", "stride_1", "stride_2", "stride_3"}
+
+
+def attention(q, k, v, out, sm_scale):
+    """out = softmax(q·kᵀ·sm_scale)·v for every (batch, head) of [Z, H, N_CTX, D_HEAD] tensors."""
+    attention_fwd_kernel[(1,)](Q=q, K=k, V=v, Out=out, sm_scale=sm_scale)
+    return out
 
 
 def matmul_f32out(a, b, c32, res32=None):

@@ -57,6 +57,14 @@ typedef struct {
   int64_t strides[2];
 } B200MemRef2D;
 
+typedef struct {
+  void *allocated;
+  void *aligned;
+  int64_t offset;
+  int64_t sizes[4];
+  int64_t strides[4];
+} B200MemRef4D;
+
 enum {
   B200MLIR_OK = 0,
   B200MLIR_ERR_NO_DEVICE = 1,   /* no CUDA device / driver, or not sm_100 */
@@ -88,7 +96,8 @@ B200_API int b200mlir_device_status(void);
  * the reference's: "enableWeightResident", "iterations", plus
  * "rmsNormEpsilon" (a tl.constexpr in the reference kernel,
  * test/python/triton/test_rms_norm.py:17,39), "gemmVariant" (-1 = dispatcher's
- * choice) and "kloopBlockK".  Returns 0, or B200MLIR_ERR_BAD_ARG for an
+ * choice), "kloopBlockK" and "attentionTiles" (query tiles per CTA of the
+ * attention kernel: 0 = by size, 1 or 2).  Returns 0, or B200MLIR_ERR_BAD_ARG for an
  * unknown name. */
 B200_API int b200mlir_set_option(const char *name, double value);
 B200_API int b200mlir_get_option(const char *name, double *value);
@@ -203,6 +212,22 @@ B200_API void mlp_block_push_float16(int64_t rank_x, B200MemRef2D *x, int64_t ra
 B200_API int b200mlir_tp_reduce_rows_float16(const void *recv, const void *residual_rows, int64_t ld_residual,
                                              void *const *peer_out, int world, int rank, int64_t rows_per_rank,
                                              int64_t cols);
+
+/* Attention block, softmax(Q·K^T·sm_scale)·V per (batch, head): the reference's flash-attention
+ * kernel (test/python/triton/test_flash_attention.py:116-195, loop over key blocks :43-113;
+ * launched at :198-236).  Q, K, V, Out are [Z, H, N_CTX, D_HEAD] with the head dimension
+ * contiguous; Q, K and V share one stride set as in the reference (:31-34), Out may have its own.
+ * sm_scale is a tl.constexpr in the reference kernel and an argument here; it must be positive.
+ * Both products take fp16 operands with fp32 accumulation (the float32 entry rounds Q, K, V to
+ * fp16 first, as the engine's pack leaf does, :239-246); the running maximum, the row sums and
+ * the output accumulator are fp32.  D_HEAD is 64 or 128, strides multiples of 8 elements, any
+ * N_CTX (a short last key block is masked); non-causal, as the reference (STAGE = 1). */
+B200_API void attention_fwd_kernel_float16(int64_t rank_q, B200MemRef4D *q, int64_t rank_k, B200MemRef4D *k,
+                                           int64_t rank_v, B200MemRef4D *v, int64_t rank_o, B200MemRef4D *out,
+                                           float sm_scale, B200_GRID_ARGS);
+B200_API void attention_fwd_kernel_float32(int64_t rank_q, B200MemRef4D *q, int64_t rank_k, B200MemRef4D *k,
+                                           int64_t rank_v, B200MemRef4D *v, int64_t rank_o, B200MemRef4D *out,
+                                           float sm_scale, B200_GRID_ARGS);
 
 /* ---- seam 2: runtime ---------------------------------------------------------
  * qcom_hexagon_backend/bin/runtime/include/HexagonCAPI.h:26-68.  `isVtcm`

@@ -1,0 +1,115 @@
+"""Attention block through the C ABI against the oracle and the fixtures made from the
+reference's own kernel source.  Tolerance: the reference test's relative Frobenius error
+below 5e-3 (test/python/triton/test_flash_attention.py:248-249); this kernel keeps S and P·V in
+fp32, so it is also held to 3e-4 against the oracle's fp16-operand form."""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import philox
+
+pytestmark = pytest.mark.gpu
+
+REF_TOL = 5e-3
+TIGHT = 3e-4
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "attention_golden.npz"))
+
+
+def _rel(got, want):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    return float(np.linalg.norm(got - want) / np.linalg.norm(want))
+
+
+def test_reference_case_float32(hm, oracle, cuda):
+    """Z=H=1, N_CTX=1024, D_HEAD=64, fp32 tensors of torch.rand, sm_scale 0.5, launched as the reference does."""
+    cuda.manual_seed(0)
+    q, k, v = (cuda.rand(1, 1, 1024, 64, device="cuda") for _ in range(3))
+    out = cuda.zeros_like(q)
+    hm.attention_fwd_kernel[(1,)](pid1=0, Q=q, K=k, V=v, sm_scale=0.5, Out=out, H=1, N_CTX=1024, BLOCK_M=1024,
+                                  BLOCK_DMODEL=64, BLOCK_N=64, STAGE=1, stride_0=65536, stride_1=65536,
+                                  stride_2=64, stride_3=1, enableVectorization=True, enableMultiThreading=True,
+                                  enableConvertToHexagonmem=True, enableHexagonmemCopyToDMA=False)
+    want = cuda.nn.functional.scaled_dot_product_attention(q, k, v, scale=0.5)
+    rel = float((out - want).norm() / want.norm())
+    assert rel < REF_TOL
+    o = oracle.attention(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), 0.5, block_n=64)
+    assert _rel(out.cpu().numpy(), o) < TIGHT
+    assert hm.device_status() == 0
+
+
+def test_golden_from_reference_kernel(hm):
+    for tag in "ab":
+        q, k, v = (GOLD[f"attn_{tag}_{n}"] for n in "qkv")  # fp16, host
+        out = np.zeros(q.shape, np.float16)
+        hm.attention(q, k, v, out, float(GOLD["attn_scale"]))
+        assert _rel(out, GOLD[f"attn_{tag}_out"]) < 6e-4  # fp16 output rounding included
+        out32 = np.zeros(q.shape, np.float32)
+        hm.attention(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), out32, float(GOLD["attn_scale"]))
+        assert _rel(out32, GOLD[f"attn_{tag}_out"]) < TIGHT
+
+
+@pytest.mark.parametrize("shape,tiles", [((2, 3, 200, 64), 0), ((2, 3, 200, 64), 2), ((1, 2, 384, 128), 1),
+                                         ((1, 2, 384, 128), 2), ((1, 1, 1, 64), 0), ((1, 5, 129, 64), 2),
+                                         ((3, 1, 72, 128), 0), ((1, 2, 1000, 64), 1)])
+def test_shapes_ragged_and_both_tilings(hm, oracle, cuda, shape, tiles):
+    rng = philox(31)
+    q, k, v = (rng.normal(0, 1, shape).astype(np.float16) for _ in range(3))
+    scale = 1.0 / np.sqrt(shape[-1])
+    want = oracle.attention(q, k, v, scale, block_n=64)
+    hm.set_option("attentionTiles", tiles)
+    try:
+        qt, kt, vt = (cuda.from_numpy(t).cuda() for t in (q, k, v))
+        out = cuda.zeros_like(qt)
+        hm.attention(qt, kt, vt, out, scale)
+        got = out.cpu().numpy()
+    finally:
+        hm.set_option("attentionTiles", 0)
+    assert _rel(got, want) < 8e-4  # fp16 output
+    assert hm.device_status() == 0
+
+
+def test_strided_heads_and_pid1(hm, oracle, cuda):
+    """[Z, N, H, D] storage viewed as [Z, H, N, D]; and one (batch, head) per call through pid1."""
+    rng = philox(32)
+    z, h, n, d = 2, 4, 320, 64
+    base = [rng.normal(0, 1, (z, n, h, d)).astype(np.float16) for _ in range(3)]
+    q, k, v = (cuda.from_numpy(t).cuda().permute(0, 2, 1, 3) for t in base)
+    want = oracle.attention(*(np.ascontiguousarray(t.transpose(0, 2, 1, 3)) for t in base), 0.25, block_n=64)
+    out = cuda.zeros(z, h, n, d, dtype=cuda.float16, device="cuda")
+    hm.attention(q, k, v, out, 0.25)
+    assert _rel(out.cpu().numpy(), want) < 8e-4
+    out2 = cuda.zeros(z, n, h, d, dtype=cuda.float16, device="cuda").permute(0, 2, 1, 3)
+    for pid1 in range(z * h):
+        hm.attention_fwd_kernel[(1,)](pid1, q, k, v, 0.25, out2, h)
+    assert cuda.equal(out2, out)
+
+
+def test_large_against_torch_and_repeatable(hm, cuda):
+    cuda.manual_seed(3)
+    q, k, v = (cuda.randn(2, 8, 2048, 64, device="cuda", dtype=cuda.float16) for _ in range(3))
+    out = cuda.zeros_like(q)
+    hm.attention(q, k, v, out, 0.125)
+    want = cuda.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float(), scale=0.125)
+    assert float((out.float() - want).norm() / want.norm()) < 8e-4
+    again = cuda.zeros_like(q)
+    hm.attention(q, k, v, again, 0.125)
+    assert cuda.equal(out, again)
+    # rows of softmax(QK)·1 are 1: V of ones gives ones, whatever the scores
+    ones = cuda.ones_like(v)
+    hm.attention(q, k, ones, out, 0.125)
+    assert float((out.float() - 1).abs().max()) < 2e-3
+
+
+def test_refusals(hm, cuda):
+    q = cuda.zeros(1, 1, 64, 32, device="cuda", dtype=cuda.float16)
+    with pytest.raises(hm.B200Error) as e:
+        hm.attention(q, q, q, cuda.zeros_like(q), 0.5)
+    assert e.value.code == 6  # head size
+    q = cuda.zeros(1, 1, 64, 64, device="cuda", dtype=cuda.float16)
+    with pytest.raises(hm.B200Error) as e:
+        hm.attention(q, q, q, cuda.zeros_like(q), -1.0)
+    assert e.value.code == 2
+    with pytest.raises(hm.B200Error) as e:
+        hm.attention(q, q[:, :, :32], q, cuda.zeros_like(q), 0.5)
+    assert e.value.code == 2

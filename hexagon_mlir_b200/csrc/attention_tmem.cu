@@ -45,6 +45,11 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
 __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -71,173 +76,224 @@ struct AttParams {
   int *status;
 };
 
+// Region stamps for timeline debugging (the analogue of the reference's light-weight profiling
+// regions, lib/Transforms/HexagonLWPInstrumentation.cpp): compiled in only with
+// -DB200MLIR_ATT_TRACE; CTA (0,0,0) records clock64() per role and key block.
+#ifdef B200MLIR_ATT_TRACE
+__device__ long long g_att_trace[8 * 32];
+#define ATR(role, u) do { if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (u) < 32) trace_s[(role) * 32 + (u)] = clock64(); } while (0)
+#else
+#define ATR(role, u) do { } while (0)
+#endif
+
 // status sites of this kernel
 constexpr int ATT_SITE = 60;
 
-template <int D, int BN, int TILES, int STAGES, bool OUT32>
-__global__ void __launch_bounds__(128 * TILES + 64, 1)
+// Block: TILES softmax warpgroups and one warpgroup that holds the MMA-issue warps (one per tile)
+// and the load warp.  With two tiles the register file gives 12 warps 168 registers each; the last
+// warpgroup hands most of its share back (setmaxnreg) and the softmax warpgroups take 232.
+constexpr int att_threads(int tiles) { return tiles == 2 ? 384 : 192; }
+constexpr int ATT_BN = 64;  // keys per block
+
+// Pipeline of one tile (block i, S buffer b = i & 1):
+//   MMA warp:  QK(0), QK(1);  then per i:  wait P(i) -> QK(i+2) into buffer b -> PV(i)
+//              (head size 128: PV(i) first, because P(i) sits inside that buffer)
+//   softmax:   wait S(i) -> max, exponentials, P(i) -> signal -> O = O·alpha + PV(i-1)
+// so the next S is complete before the softmax group asks for it, and the group never waits for
+// the tensor cores in steady state.
+template <int D, int TILES, int KST, bool OUT32>
+__global__ void __launch_bounds__(att_threads(TILES), 1)
     attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const AttParams p) {
   static_assert(D == 64 || D == 128, "head size");
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 128, "key block");
+  constexpr int BN = ATT_BN;
+  constexpr bool ALIAS = D == 128;         // P(i) overwrites the first half of S(i) instead of its own columns
   constexpr int SLABS = D / 64;            // 64-column (128-byte) slabs of a tile row
   constexpr int Q_SLAB = ATT_BM * 128;     // bytes of one slab of a Q tile
   constexpr int Q_BYTES = SLABS * Q_SLAB;
   constexpr int KV_SLAB = BN * 128;
   constexpr int KV_BYTES = SLABS * KV_SLAB;
-  constexpr int TCOLS = BN + BN / 2 + D;   // TMEM columns of one tile: S, P, PV
-  constexpr int TMEM_COLS = TILES * TCOLS <= 256 ? 256 : 512;
-  static_assert(TILES * TCOLS <= 512, "TMEM budget");
-  constexpr int MMA_WARP = 4 * TILES, LOAD_WARP = 4 * TILES + 1;
+  // TMEM columns of one tile: S0 [0,64), S1 [64,128); D=64: P0 [128,160), P1 [160,192), PV [192,256);
+  // D=128: PV [128,256)
+  constexpr int TCOLS = 256;
+  constexpr int COL_P = 128, COL_PV = ALIAS ? 128 : 192;
+  constexpr int TMEM_COLS = TILES * TCOLS;
+  constexpr int MMA_WARP0 = 4 * TILES, LOAD_WARP = 5 * TILES;
   constexpr uint32_t IDESC_QK = make_idesc(/*D f32*/ 1, /*A f16*/ 0, /*B f16*/ 0, /*A K-major*/ 0,
                                            /*B K-major*/ 0, ATT_BM, BN);
   constexpr uint32_t IDESC_PV = make_idesc(/*D f32*/ 1, /*A f16*/ 0, /*B f16*/ 0, /*A K-major*/ 0,
                                            /*B MN-major*/ 1, ATT_BM, D);
 
   extern __shared__ uint8_t smem_raw[];
+#ifdef B200MLIR_ATT_TRACE
+  __shared__ long long trace_s[8 * 32];
+#endif
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t q_smem = base;
   const uint32_t k_smem = q_smem + TILES * Q_BYTES;
-  const uint32_t v_smem = k_smem + STAGES * KV_BYTES;
-  const uint32_t ctrl = v_smem + STAGES * KV_BYTES;
-  const uint32_t bar_qfull = ctrl;            // TILES: Q tile landed
-  const uint32_t bar_kfull = ctrl + 16;       // STAGES: K block landed
-  const uint32_t bar_kempty = ctrl + 48;      // STAGES: every QK product that reads the stage is complete
-  const uint32_t bar_vfull = ctrl + 80;       // STAGES
-  const uint32_t bar_vempty = ctrl + 112;     // STAGES
-  const uint32_t bar_sfull = ctrl + 144;      // TILES: S of the tile complete
-  const uint32_t bar_pfull = ctrl + 160;      // TILES: P written (and S no longer needed), 4 warps
-  const uint32_t bar_pvfull = ctrl + 176;     // TILES: P·V complete
-  const uint32_t bar_pvfree = ctrl + 192;     // TILES: P·V read out, 4 warps
-  const uint32_t tmem_slot = ctrl + 208;
+  const uint32_t v_smem = k_smem + KST * KV_BYTES;
+  const uint32_t ctrl = v_smem + KST * KV_BYTES;
+  const uint32_t bar_qfull = ctrl;            // [tile] Q tile landed
+  const uint32_t bar_kfull = ctrl + 16;       // [stage] K block landed
+  const uint32_t bar_kempty = ctrl + 48;      // [stage] every tile's QK product of the block is complete
+  const uint32_t bar_vfull = ctrl + 80;       // [stage]
+  const uint32_t bar_vempty = ctrl + 112;     // [stage] every tile's P·V of the block is complete
+  const uint32_t bar_sfull = ctrl + 144;      // [tile][buffer] S complete
+  const uint32_t bar_pfull = ctrl + 176;      // [tile] P written (and S read), 4 warps
+  const uint32_t bar_pvfull = ctrl + 192;     // [tile] P·V complete
+  const uint32_t bar_pvfree = ctrl + 208;     // [tile] P·V read out, 4 warps
+  const uint32_t tmem_slot = ctrl + 224;
   uint8_t *ctrl_ptr = smem_raw + (ctrl - smem_u32(smem_raw));
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_ptr + 212);
-  static_assert(STAGES <= 4, "barrier table");
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_ptr + 228);
+  static_assert(KST <= 4 && KST >= 3, "barrier table; K(i+2) is loaded while K(i+1) is in use");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * (TILES * ATT_BM);
   const int hh = blockIdx.y, zz = blockIdx.z;
+  const int nb = p.n_blocks;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int t = 0; t < TILES; ++t) {
       mbar_init(bar_qfull + 8 * t, 1);
-      mbar_init(bar_sfull + 8 * t, 1);
+      mbar_init(bar_sfull + 16 * t, 1);
+      mbar_init(bar_sfull + 16 * t + 8, 1);
       mbar_init(bar_pfull + 8 * t, 4);
       mbar_init(bar_pvfull + 8 * t, 1);
       mbar_init(bar_pvfree + 8 * t, 4);
     }
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < KST; ++s) {
       mbar_init(bar_kfull + 8 * s, 1);
-      mbar_init(bar_kempty + 8 * s, 1);
+      mbar_init(bar_kempty + 8 * s, TILES);
       mbar_init(bar_vfull + 8 * s, 1);
-      mbar_init(bar_vempty + 8 * s, 1);
+      mbar_init(bar_vempty + 8 * s, TILES);
     }
     fence_barrier_init();
   }
-  if (warp == MMA_WARP) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == MMA_WARP0) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(ctrl_ptr + 208);
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(ctrl_ptr + 224);
 
+  if (TILES == 2) {
+    if (warp < 4 * TILES)
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    else
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+  }
   if (warp < 4 * TILES) {
     // ---------------- softmax group of tile t: one thread per query row ----------------
     const int t = warp >> 2, q4 = warp & 3;
-    const uint32_t t_s = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(t * TCOLS);
-    const uint32_t t_p = t_s + BN;
-    const uint32_t t_pv = t_p + BN / 2;
+    const uint32_t t_row = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(t * TCOLS);
+    const uint32_t t_pv = t_row + COL_PV;
     const float c2 = p.scale2;
     float o[D];
 #pragma unroll
     for (int e = 0; e < D; ++e) o[e] = 0.0f;
     float m = -1.0e30f, l = 0.0f, alpha_prev = 0.0f;
     bool ok = true;
-    for (int i = 0; i < p.n_blocks; ++i) {
-      const uint32_t par = (uint32_t)(i & 1);
-      if (i > 0) {
-        // P·V of the previous block: it was issued before this block's S, so it is complete first
-        ok = mbar_wait(bar_pvfull + 8 * t, par ^ 1u, abort_flag, p.status, ATT_SITE + 1, i);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_pv + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha_prev, __uint_as_float(r[e]));
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_pvfree + 8 * t);
-      }
-      ok = mbar_wait(bar_sfull + 8 * t, par, abort_flag, p.status, ATT_SITE + 2, i);
+    for (int i = 0; i < nb; ++i) {
+      const int b = i & 1;
+      ok = mbar_wait(bar_sfull + 16 * t + 8 * b, (uint32_t)((i >> 1) & 1), abort_flag, p.status, ATT_SITE + 2, i);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if (threadIdx.x == 0) ATR(4, i);
       tc_fence_after_sync();
+      const uint32_t t_s = t_row + (uint32_t)(b * 64);
+      const uint32_t t_p = ALIAS ? t_s : t_row + (uint32_t)(COL_P + b * 32);
+      // the row's 64 scores stay in registers for both passes
+      uint32_t s0[32], s1[32];
+      tmem_ld_32x32(t_s, s0);
+      tmem_ld_32x32(t_s + 32, s1);
+      tmem_ld_wait();
       const int n_valid = p.n_ctx - i * BN;  // keys of this block that exist (the last block may be short)
-      float mx = -INFINITY;
+      if (n_valid < BN) {
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + c * 32, r);
-        tmem_ld_wait();
-        if (n_valid >= BN) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (c * 32 + e < n_valid) mx = fmaxf(mx, __uint_as_float(r[e]));
+        for (int e = 0; e < 32; ++e) {
+          if (e >= n_valid) s0[e] = 0xff800000u;  // -inf: no weight
+          if (32 + e >= n_valid) s1[e] = 0xff800000u;
         }
       }
-      const float m_new = fmaxf(m, mx * c2);
-      const float alpha = ex2(m - m_new);
-      float lsum = 0.0f;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_s + c * 32, r);
-        tmem_ld_wait();
+      for (int e = 0; e < 32; e += 4) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mx[j] = max3(mx[j], __uint_as_float(s0[e + j]), __uint_as_float(s1[e + j]));
+      }
+      const float m_new = fmaxf(m, max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * c2);
+      const float alpha = ex2(m - m_new);
+      float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          float e0 = ex2(fmaf(__uint_as_float(r[2 * e]), c2, -m_new));
-          float e1 = ex2(fmaf(__uint_as_float(r[2 * e + 1]), c2, -m_new));
-          if (n_valid < BN) {
-            if (c * 32 + 2 * e >= n_valid) e0 = 0.0f;
-            if (c * 32 + 2 * e + 1 >= n_valid) e1 = 0.0f;
-          }
-          lsum += e0 + e1;
-          pk[e] = pack_h2(e0, e1);
+          const float a0 = ex2(fmaf(__uint_as_float(s0[2 * e]), c2, -m_new));
+          const float a1 = ex2(fmaf(__uint_as_float(s0[2 * e + 1]), c2, -m_new));
+          ls[0] += a0;
+          ls[1] += a1;
+          pk[e] = pack_h2(a0, a1);
         }
-        tmem_st_x16(t_p + c * 16, pk);
+        tmem_st_x16(t_p, pk);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const float a0 = ex2(fmaf(__uint_as_float(s1[2 * e]), c2, -m_new));
+          const float a1 = ex2(fmaf(__uint_as_float(s1[2 * e + 1]), c2, -m_new));
+          ls[2] += a0;
+          ls[3] += a1;
+          pk[e] = pack_h2(a0, a1);
+        }
+        tmem_st_x16(t_p + 16, pk);
       }
       tmem_st_wait_all();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pfull + 8 * t);
-      l = fmaf(l, alpha, lsum);
+      if (threadIdx.x == 0) ATR(5, i);
+      l = fmaf(l, alpha, (ls[0] + ls[1]) + (ls[2] + ls[3]));
+      if (i > 0) {
+        // P·V of the previous block, issued a whole block ago
+        ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 1, i);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (threadIdx.x == 0) ATR(6, i);
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t_pv + c * 64, r0);
+          tmem_ld_32x32(t_pv + c * 64 + 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            o[c * 64 + e] = fmaf(o[c * 64 + e], alpha_prev, __uint_as_float(r0[e]));
+            o[c * 64 + 32 + e] = fmaf(o[c * 64 + 32 + e], alpha_prev, __uint_as_float(r1[e]));
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_pvfree + 8 * t);
+        if (threadIdx.x == 0) ATR(7, i);
+      }
       alpha_prev = alpha;
       m = m_new;
     }
     if (ok) {
-      ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((p.n_blocks - 1) & 1), abort_flag, p.status, ATT_SITE + 3, 0);
+      ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((nb - 1) & 1), abort_flag, p.status, ATT_SITE + 3, 0);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       tc_fence_after_sync();
       const int row = m0 + t * ATT_BM + q4 * 32 + lane;
       const int64_t off = (int64_t)zz * p.so_z + (int64_t)hh * p.so_h + (int64_t)row * p.so_n;
+      const float inv_l = 1.0f / l;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32(t_pv + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
-        for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha_prev, __uint_as_float(r[e])) / l;
+        for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha_prev, __uint_as_float(r[e])) * inv_l;
         if (row < p.n_ctx) {
           if (OUT32) {
             float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + off + c * 32);
@@ -257,77 +313,82 @@ __global__ void __launch_bounds__(128 * TILES + 64, 1)
         }
       }
     }
-  } else if (warp == MMA_WARP) {
-    // ---------------- MMA issue ----------------
+  } else if (warp >= MMA_WARP0 && warp < MMA_WARP0 + TILES) {
+    // ---------------- MMA issue, one warp per tile ----------------
     if (lane == 0) {
-      bool ok = true;
-      for (int t = 0; t < TILES && ok; ++t)
-        ok = mbar_wait(bar_qfull + 8 * t, 0u, abort_flag, p.status, ATT_SITE + 4, t);
-      auto issue_qk = [&](int t, int stage) {
-        const uint32_t qa = q_smem + t * Q_BYTES, ka = k_smem + stage * KV_BYTES;
-#pragma unroll
-        for (int j = 0; j < D / 16; ++j) {
-          // both operands K-major: 8-row groups 1024 B apart, one K=16 step is 32 bytes inside the swizzle row
-          const uint32_t in_row = (uint32_t)((j & 3) * 32);
-          const uint64_t adesc = smem_desc_sw128(qa + (j >> 2) * Q_SLAB + in_row, 16, 1024);
-          const uint64_t bdesc = smem_desc_sw128(ka + (j >> 2) * KV_SLAB + in_row, 16, 1024);
-          mma_f16_ss(tmem_base + (uint32_t)(t * TCOLS), adesc, bdesc, IDESC_QK, j ? 1u : 0u);
-        }
-        mma_commit(bar_sfull + 8 * t);
-      };
-      auto issue_pv = [&](int t, int stage) {
-        const uint32_t va = v_smem + stage * KV_BYTES;
-        const uint32_t t_p = tmem_base + (uint32_t)(t * TCOLS + BN);
-#pragma unroll
-        for (int j = 0; j < BN / 16; ++j) {
-          // V is MN-major: 64-column slabs KV_SLAB apart, 8-key groups 1024 B apart, one K=16 step is 16 rows
-          const uint64_t bdesc = smem_desc_sw128(va + j * 2048, KV_SLAB, 1024);
-          mma_f16_ts_att(t_p + BN / 2, t_p + (uint32_t)(j * 8), bdesc, IDESC_PV, j ? 1u : 0u);
-        }
-        mma_commit(bar_pvfull + 8 * t);
-      };
+      const int t = warp - MMA_WARP0;
+      const uint32_t tm = tmem_base + (uint32_t)(t * TCOLS);
+      bool ok = mbar_wait(bar_qfull + 8 * t, 0u, abort_flag, p.status, ATT_SITE + 4, t);
+      // descriptors without their start address; a K=16 step adds a constant to the address field
+      const uint64_t qdesc = smem_desc_sw128(q_smem + t * Q_BYTES, 16, 1024);
+      const uint64_t kdesc0 = smem_desc_sw128(k_smem, 16, 1024);
+      const uint64_t vdesc0 = smem_desc_sw128(v_smem, KV_SLAB, 1024);
       int ks = 0, vs = 0;
       uint32_t kph = 0, vph = 0;
-      if (ok) ok = mbar_wait(bar_kfull, 0u, abort_flag, p.status, ATT_SITE + 5, 0);
-      if (ok) {
+      // S[buf] = Q·K(block)ᵀ for the next block of the K ring
+      auto issue_qk = [&](int buf, int blk) -> bool {
+        if (!mbar_wait(bar_kfull + 8 * ks, kph, abort_flag, p.status, ATT_SITE + 5, blk)) return false;
         tc_fence_after_sync();
-        for (int t = 0; t < TILES; ++t) issue_qk(t, 0);
-        mma_commit(bar_kempty);
-        if (++ks == STAGES) {
+        const uint64_t kd = kdesc0 + (uint64_t)((ks * KV_BYTES) >> 4);
+#pragma unroll
+        for (int j = 0; j < D / 16; ++j) {
+          // both operands K-major: 8-row groups 1024 B apart, a K=16 step is 32 bytes inside the swizzle row
+          const uint64_t qo = (uint64_t)(((j >> 2) * Q_SLAB + (j & 3) * 32) >> 4);
+          const uint64_t ko = (uint64_t)(((j >> 2) * KV_SLAB + (j & 3) * 32) >> 4);
+          mma_f16_ss(tm + (uint32_t)(buf * 64), qdesc + qo, kd + ko, IDESC_QK, j ? 1u : 0u);
+        }
+        mma_commit(bar_sfull + 16 * t + 8 * buf);
+        mma_commit(bar_kempty + 8 * ks);
+        if (++ks == KST) {
           ks = 0;
           kph ^= 1u;
         }
-      }
-      for (int i = 0; i < p.n_blocks && ok; ++i) {
-        const bool more = i + 1 < p.n_blocks;
-        ok = mbar_wait(bar_vfull + 8 * vs, vph, abort_flag, p.status, ATT_SITE + 6, i);
-        if (ok && more) ok = mbar_wait(bar_kfull + 8 * ks, kph, abort_flag, p.status, ATT_SITE + 7, i);
-        for (int t = 0; t < TILES && ok; ++t) {
-          ok = mbar_wait(bar_pfull + 8 * t, (uint32_t)(i & 1), abort_flag, p.status, ATT_SITE + 8, i);
-          if (ok && i > 0)
-            ok = mbar_wait(bar_pvfree + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 9, i);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_pv(t, vs);
-          if (more) issue_qk(t, ks);
-        }
+        return true;
+      };
+      if (ok) ok = issue_qk(0, 0);
+      if (ok && nb > 1) ok = issue_qk(1, 1);
+      for (int i = 0; i < nb && ok; ++i) {
+        const int b = i & 1;
+        ok = mbar_wait(bar_pfull + 8 * t, (uint32_t)b, abort_flag, p.status, ATT_SITE + 8, i);
         if (!ok) break;
+        if (t == 0) ATR(0, i);
+        // S(i) is read: with P in columns of its own the product after next can start at once,
+        // ahead of P·V(i), which still waits for the softmax group to take P·V(i-1)
+        if (!ALIAS && i + 2 < nb) {
+          ok = issue_qk(b, i + 2);
+          if (!ok) break;
+          if (t == 0) ATR(2, i);
+        }
+        ok = mbar_wait(bar_vfull + 8 * vs, vph, abort_flag, p.status, ATT_SITE + 6, i);
+        if (ok && i > 0)
+          ok = mbar_wait(bar_pvfree + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 9, i);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t a_tmem = tm + (uint32_t)(ALIAS ? b * 64 : COL_P + b * 32);
+        const uint64_t vd = vdesc0 + (uint64_t)((vs * KV_BYTES) >> 4);
+#pragma unroll
+        for (int j = 0; j < BN / 16; ++j) {
+          // V is MN-major: 64-column slabs KV_SLAB apart, 8-key groups 1024 B apart, a K=16 step is 16 rows
+          mma_f16_ts_att(tm + COL_PV, a_tmem + (uint32_t)(j * 8), vd + (uint64_t)(j * 128), IDESC_PV, j ? 1u : 0u);
+        }
+        mma_commit(bar_pvfull + 8 * t);
         mma_commit(bar_vempty + 8 * vs);
-        if (++vs == STAGES) {
+        if (++vs == KST) {
           vs = 0;
           vph ^= 1u;
         }
-        if (more) {
-          mma_commit(bar_kempty + 8 * ks);
-          if (++ks == STAGES) {
-            ks = 0;
-            kph ^= 1u;
-          }
+        if (t == 0) ATR(1, i);
+        if (ALIAS && i + 2 < nb) {
+          // P(i) lives in the S buffer the next product overwrites: P·V(i) must have read it
+          ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)b, abort_flag, p.status, ATT_SITE + 7, i);
+          if (!ok) break;
+          ok = issue_qk(b, i + 2);
+          if (t == 0) ATR(2, i);
         }
       }
     }
   } else if (warp == LOAD_WARP) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer: Q, then K(0), K(1), V(0), K(2), V(1), K(3), ... ----------------
     if (lane == 0) {
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
@@ -338,33 +399,46 @@ __global__ void __launch_bounds__(128 * TILES + 64, 1)
         for (int s = 0; s < SLABS; ++s)
           tma_load_4d(q_smem + t * Q_BYTES + s * Q_SLAB, &tmQ, bar_qfull + 8 * t, s * 64, m0 + t * ATT_BM, hh, zz);
       }
-      int st = 0;
-      uint32_t ph = 0;
+      int ks = 0, vs = 0;
+      uint32_t kph = 0, vph = 0;
       bool ok = true;
-      for (int i = 0; i < p.n_blocks; ++i) {
-        ok = mbar_wait(bar_kempty + 8 * st, ph ^ 1u, abort_flag, p.status, ATT_SITE + 10, i);
-        if (!ok) break;
-        mbar_expect_tx(bar_kfull + 8 * st, KV_BYTES);
+      auto load_k = [&](int blk) {
+        ok = mbar_wait(bar_kempty + 8 * ks, kph ^ 1u, abort_flag, p.status, ATT_SITE + 10, blk);
+        if (!ok) return;
+        mbar_expect_tx(bar_kfull + 8 * ks, KV_BYTES);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
-          tma_load_4d(k_smem + st * KV_BYTES + s * KV_SLAB, &tmK, bar_kfull + 8 * st, s * 64, i * BN, hh, zz);
-        ok = mbar_wait(bar_vempty + 8 * st, ph ^ 1u, abort_flag, p.status, ATT_SITE + 11, i);
-        if (!ok) break;
-        mbar_expect_tx(bar_vfull + 8 * st, KV_BYTES);
-#pragma unroll
-        for (int s = 0; s < SLABS; ++s)
-          tma_load_4d(v_smem + st * KV_BYTES + s * KV_SLAB, &tmV, bar_vfull + 8 * st, s * 64, i * BN, hh, zz);
-        if (++st == STAGES) {
-          st = 0;
-          ph ^= 1u;
+          tma_load_4d(k_smem + ks * KV_BYTES + s * KV_SLAB, &tmK, bar_kfull + 8 * ks, s * 64, blk * BN, hh, zz);
+        if (++ks == KST) {
+          ks = 0;
+          kph ^= 1u;
         }
+      };
+      load_k(0);
+      if (ok && nb > 1) load_k(1);
+      for (int i = 0; i < nb && ok; ++i) {
+        ok = mbar_wait(bar_vempty + 8 * vs, vph ^ 1u, abort_flag, p.status, ATT_SITE + 11, i);
+        if (!ok) break;
+        mbar_expect_tx(bar_vfull + 8 * vs, KV_BYTES);
+#pragma unroll
+        for (int s = 0; s < SLABS; ++s)
+          tma_load_4d(v_smem + vs * KV_BYTES + s * KV_SLAB, &tmV, bar_vfull + 8 * vs, s * 64, i * BN, hh, zz);
+        if (++vs == KST) {
+          vs = 0;
+          vph ^= 1u;
+        }
+        if (i + 2 < nb) load_k(i + 2);
       }
     }
   }
   // every role ends here; the accumulators are read, so TMEM can go back
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == MMA_WARP) {
+#ifdef B200MLIR_ATT_TRACE
+  if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0)
+    for (int i = threadIdx.x; i < 8 * 32; i += blockDim.x) g_att_trace[i] = trace_s[i];
+#endif
+  if (warp == MMA_WARP0) {
     tc_fence_after_sync();
     __syncwarp();
     tmem_dealloc(tmem_base, TMEM_COLS);
@@ -414,12 +488,13 @@ struct AttShape {
   int64_t z, h, n, d, sz, sh, sn;
 };
 
-template <int D, int BN, int TILES, int STAGES, bool OUT32>
+template <int D, int TILES, int KST, bool OUT32>
 int launch_attention_variant(const void *q, const void *k, const void *v, void *out, const AttShape &in,
                              const AttShape &os, double sm_scale) {
-  constexpr int SMEM = TILES * (D / 64) * ATT_BM * 128 + 2 * STAGES * (D / 64) * BN * 128 + 256 + 1024;
+  constexpr int BN = ATT_BN;
+  constexpr int SMEM = TILES * (D / 64) * ATT_BM * 128 + 2 * KST * (D / 64) * BN * 128 + 256 + 1024;
   static bool attr_set = false;
-  auto kern = attention_kernel<D, BN, TILES, STAGES, OUT32>;
+  auto kern = attention_kernel<D, TILES, KST, OUT32>;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     attr_set = true;
@@ -438,12 +513,18 @@ int launch_attention_variant(const void *q, const void *k, const void *v, void *
   p.scale2 = (float)(sm_scale * 1.44269504);  // the kernel source's own constant for 1/ln 2
   p.status = ctx().d_status;
   dim3 grid((unsigned)((in.n + TILES * ATT_BM - 1) / (TILES * ATT_BM)), (unsigned)in.h, (unsigned)in.z);
-  kern<<<grid, 128 * TILES + 64, SMEM, ctx().stream>>>(tmQ, tmK, tmV, p);
+  kern<<<grid, att_threads(TILES), SMEM, ctx().stream>>>(tmQ, tmK, tmV, p);
   count_launch();
   return check_launch("attention_kernel");
 }
 
 }  // namespace
+
+#ifdef B200MLIR_ATT_TRACE
+extern "C" __attribute__((visibility("default"))) int b200mlir_debug_get_att_trace(long long *host) {
+  return (int)cudaMemcpyFromSymbol(host, g_att_trace, sizeof(long long) * 8 * 32);
+}
+#endif
 
 int launch_attention(const void *q, const void *k, const void *v, void *out, bool f32, int64_t z, int64_t h,
                      int64_t n, int64_t d, int64_t sz, int64_t sh, int64_t sn, int64_t soz, int64_t soh,
@@ -484,13 +565,13 @@ int launch_attention(const void *q, const void *k, const void *v, void *out, boo
   int two = tiles > c.sm_count ? 1 : 0;
   if (c.opt.attention_tiles == 1) two = 0;
   if (c.opt.attention_tiles == 2) two = 1;
-#define ATT_GO(D_, BN_, T_, O_) launch_attention_variant<D_, BN_, T_, 3, O_>(q, k, v, out, in, os, sm_scale)
+#define ATT_GO(D_, T_, K_, O_) launch_attention_variant<D_, T_, K_, O_>(q, k, v, out, in, os, sm_scale)
   if (d == 64) {
-    if (two) return f32 ? ATT_GO(64, 128, 2, true) : ATT_GO(64, 128, 2, false);
-    return f32 ? ATT_GO(64, 128, 1, true) : ATT_GO(64, 128, 1, false);
+    if (two) return f32 ? ATT_GO(64, 2, 4, true) : ATT_GO(64, 2, 4, false);
+    return f32 ? ATT_GO(64, 1, 4, true) : ATT_GO(64, 1, 4, false);
   }
-  if (two) return f32 ? ATT_GO(128, 64, 2, true) : ATT_GO(128, 64, 2, false);
-  return f32 ? ATT_GO(128, 64, 1, true) : ATT_GO(128, 64, 1, false);
+  if (two) return f32 ? ATT_GO(128, 2, 3, true) : ATT_GO(128, 2, 3, false);
+  return f32 ? ATT_GO(128, 1, 3, true) : ATT_GO(128, 1, 3, false);
 #undef ATT_GO
 }
 

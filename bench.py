@@ -374,6 +374,29 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         for wq_ in Wq:
             hm.unregister_w8a16_weight(wq_)
         del Wq
+    # attention block: the reference's own case (one head of 1024 x 64, fp32 tensors, sm_scale 0.5:
+    # test/python/triton/test_flash_attention.py:17,37) and head counts / lengths that fill the device
+    for name, (z, h, n, d, f32) in {"attention_f32_1x1x1024x64": (1, 1, 1024, 64, True),
+                                    "attention_f16_4x16x4096x64": (4, 16, 4096, 64, False),
+                                    "attention_f16_4x16x4096x128": (4, 16, 4096, 128, False)}.items():
+        if not want(name):
+            continue
+        dt = torch.float32 if f32 else torch.float16
+        sets = 2 if z * h > 1 else 8  # 4 x 16 x 4096 x 128: 67 MB per tensor, two sets exceed L2
+        Q, K, V = ([torch.rand((z, h, n, d), generator=g, device=dev).to(dt) for _ in range(sets)] for _ in range(3))
+        O = [torch.empty_like(Q[0]) for _ in range(sets)]
+        state = {"i": 0}
+        scale = 0.5 if f32 else d ** -0.5
+
+        def att():
+            i = state["i"] % sets
+            state["i"] += 1
+            hm.attention(Q[i], K[i], V[i], O[i], scale)
+        ms = graph_timed(torch, att, reps=5, inner=sets * (1 if z * h > 1 else 4))
+        flops = 4.0 * z * h * n * n * d
+        out[name] = {"us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12,
+                     "frac_of_measured_bf16_burst": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+        del Q, K, V, O
     return out
 
 
@@ -566,7 +589,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--case", default="", help="run one case of `extra` only (profiling captures): gemm_f16_1024, "
-                                               "gemm_f16_4096, gemm_f16_8192, softmax, rmsnorm, swiglu, w8a16")
+                                               "gemm_f16_4096, gemm_f16_8192, softmax, rmsnorm, swiglu, w8a16, attention_f16_4x16x4096x64, ...")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup

@@ -6,16 +6,17 @@
 // l = l·exp2(m − m') + ΣP; O = O·exp2(m − m') + P·V; at the end O / l, with c = sm_scale·log2(e).
 // Q, K, V and P are fp16 operands of the tensor cores, every sum is fp32.
 //
-// One CTA owns TILES tiles of 128 queries of one (batch, head).  Roles:
-//   warps [4t, 4t+4)   softmax group of tile t: thread = one query row.  Reads S from TMEM twice
-//                      (row maximum, then exponentials), writes P as packed fp16 back to TMEM, and
-//                      keeps the row's O[D] in registers: O = O·alpha + (P·V read from TMEM).
-//   warp 4·TILES       lane 0 issues every MMA: S_t = Q_t·Kᵀ (operands in shared memory) and
-//                      PV_t = P_t·V (P from TMEM, V from shared memory), in the order
-//                      PV(t,i), QK(t,i+1) so that a group's next S is on its way while the other
-//                      group computes.
-//   warp 4·TILES+1     lane 0 loads Q once and the K and V blocks into two rings with TMA.
-// TMEM per tile: S [128 x BN] fp32, P [128 x BN] fp16 (BN/2 columns), PV [128 x D] fp32.
+// The kernel keeps m lazily: O lives in TMEM scaled by exp2(-m) and m moves only when the row
+// maximum has grown by more than 2^8, in which case O and l are rescaled; O / l is the same.
+//
+// One CTA owns TILES tiles of 128 queries of one (batch, head); key blocks of 64.  Roles:
+//   warps [4t, 4t+4)     softmax group of tile t: thread = one query row.  Reads the row of S from
+//                        TMEM once, takes the maximum, writes P as packed fp16 back to TMEM.
+//   warp 4·TILES + t     lane 0 issues tile t's MMAs: S = Q·Kᵀ (both operands in shared memory)
+//                        two blocks ahead, and O += P·V (P from TMEM, V from shared memory).
+//   warp 5·TILES         lane 0 loads Q once and the K and V blocks into two rings with TMA.
+// TMEM per tile (256 columns): S0, S1 [128 x 64] fp32; head size 64: P0, P1 (32 columns each) and
+// O [128 x 64] fp32; head size 128: O [128 x 128] fp32 and P(i) written over the read half of S(i).
 // Every wait is bounded; a wait that runs out sets the CTA's abort flag and the device status.
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -58,6 +59,17 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[
         "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait_all() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // D[tmem] (+)= A[tmem] · B[smem descriptor]
 __device__ __forceinline__ void mma_f16_ts_att(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
@@ -89,18 +101,16 @@ __device__ long long g_att_trace[8 * 32];
 // status sites of this kernel
 constexpr int ATT_SITE = 60;
 
-// Block: TILES softmax warpgroups and one warpgroup that holds the MMA-issue warps (one per tile)
-// and the load warp.  With two tiles the register file gives 12 warps 168 registers each; the last
-// warpgroup hands most of its share back (setmaxnreg) and the softmax warpgroups take 232.
+// Block: TILES softmax warpgroups, then the MMA-issue warps (one per tile) and the load warp.
 constexpr int att_threads(int tiles) { return tiles == 2 ? 384 : 192; }
 constexpr int ATT_BN = 64;  // keys per block
 
 // Pipeline of one tile (block i, S buffer b = i & 1):
-//   MMA warp:  QK(0), QK(1);  then per i:  wait P(i) -> QK(i+2) into buffer b -> PV(i)
-//              (head size 128: PV(i) first, because P(i) sits inside that buffer)
-//   softmax:   wait S(i) -> max, exponentials, P(i) -> signal -> O = O·alpha + PV(i-1)
-// so the next S is complete before the softmax group asks for it, and the group never waits for
-// the tensor cores in steady state.
+//   MMA warp:  QK(0), QK(1);  then per i:  wait P(i) -> O += P(i)·V(i) -> QK(i+2) into buffer b
+//   softmax:   wait S(i) -> max -> (rarely: rescale O in TMEM) -> exponentials, P(i) -> signal
+// O accumulates in TMEM over all blocks (P·V with accumulate), so the softmax thread holds only
+// the row's scores; the next S is complete before the softmax group asks for it, and the group
+// never waits for the tensor cores in steady state.
 template <int D, int TILES, int KST, bool OUT32>
 __global__ void __launch_bounds__(att_threads(TILES), 1)
     attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -140,8 +150,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
   const uint32_t bar_vempty = ctrl + 112;     // [stage] every tile's P·V of the block is complete
   const uint32_t bar_sfull = ctrl + 144;      // [tile][buffer] S complete
   const uint32_t bar_pfull = ctrl + 176;      // [tile] P written (and S read), 4 warps
-  const uint32_t bar_pvfull = ctrl + 192;     // [tile] P·V complete
-  const uint32_t bar_pvfree = ctrl + 208;     // [tile] P·V read out, 4 warps
+  const uint32_t bar_pvfull = ctrl + 192;     // [tile] O += P·V of a block complete
   const uint32_t tmem_slot = ctrl + 224;
   uint8_t *ctrl_ptr = smem_raw + (ctrl - smem_u32(smem_raw));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_ptr + 228);
@@ -160,7 +169,6 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
       mbar_init(bar_sfull + 16 * t + 8, 1);
       mbar_init(bar_pfull + 8 * t, 4);
       mbar_init(bar_pvfull + 8 * t, 1);
-      mbar_init(bar_pvfree + 8 * t, 4);
     }
     for (int s = 0; s < KST; ++s) {
       mbar_init(bar_kfull + 8 * s, 1);
@@ -176,22 +184,18 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
   tc_fence_after_sync();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(ctrl_ptr + 224);
 
-  if (TILES == 2) {
-    if (warp < 4 * TILES)
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
-    else
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
-  }
   if (warp < 4 * TILES) {
     // ---------------- softmax group of tile t: one thread per query row ----------------
     const int t = warp >> 2, q4 = warp & 3;
     const uint32_t t_row = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(t * TCOLS);
-    const uint32_t t_pv = t_row + COL_PV;
+    const uint32_t t_o = t_row + COL_PV;
     const float c2 = p.scale2;
-    float o[D];
-#pragma unroll
-    for (int e = 0; e < D; ++e) o[e] = 0.0f;
-    float m = -1.0e30f, l = 0.0f, alpha_prev = 0.0f;
+    // O accumulates in TMEM across blocks, scaled by exp2(-m): m follows the row maximum lazily.
+    // It moves only when the maximum has grown by more than kSlack (then P would leave fp16's
+    // comfortable range): O and l are multiplied by exp2(m_old - m_new).  O / l does not depend
+    // on which m was used, so the result is the reference's up to rounding.
+    constexpr float kSlack = 8.0f;
+    float m = -1.0e30f, l = 0.0f;
     bool ok = true;
     for (int i = 0; i < nb; ++i) {
       const int b = i & 1;
@@ -221,15 +225,39 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
 #pragma unroll
         for (int j = 0; j < 4; ++j) mx[j] = max3(mx[j], __uint_as_float(s0[e + j]), __uint_as_float(s1[e + j]));
       }
-      const float m_new = fmaxf(m, max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * c2);
-      const float alpha = ex2(m - m_new);
+      const float cur = max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * c2;
+      bool took_pv = i == 0;  // whether this block's turn at the P·V barrier is done
+      if (__any_sync(0xffffffffu, cur > m + kSlack)) {
+        const float m_new = fmaxf(m, cur);
+        const float alpha = ex2(m - m_new);  // 0 on the first block, 1 for a row whose maximum stayed
+        l *= alpha;
+        m = m_new;
+        if (i > 0) {
+          // O must hold every product issued so far before it is rescaled
+          ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 1, i);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          took_pv = true;
+          tc_fence_after_sync();
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_o + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+            tmem_st_x32(t_o + c * 32, r);
+          }
+        }
+      }
+      const float neg_m = -m;
       float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       {
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float a0 = ex2(fmaf(__uint_as_float(s0[2 * e]), c2, -m_new));
-          const float a1 = ex2(fmaf(__uint_as_float(s0[2 * e + 1]), c2, -m_new));
+          const float a0 = ex2(fmaf(__uint_as_float(s0[2 * e]), c2, neg_m));
+          const float a1 = ex2(fmaf(__uint_as_float(s0[2 * e + 1]), c2, neg_m));
           ls[0] += a0;
           ls[1] += a1;
           pk[e] = pack_h2(a0, a1);
@@ -237,46 +265,29 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         tmem_st_x16(t_p, pk);
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float a0 = ex2(fmaf(__uint_as_float(s1[2 * e]), c2, -m_new));
-          const float a1 = ex2(fmaf(__uint_as_float(s1[2 * e + 1]), c2, -m_new));
+          const float a0 = ex2(fmaf(__uint_as_float(s1[2 * e]), c2, neg_m));
+          const float a1 = ex2(fmaf(__uint_as_float(s1[2 * e + 1]), c2, neg_m));
           ls[2] += a0;
           ls[3] += a1;
           pk[e] = pack_h2(a0, a1);
         }
         tmem_st_x16(t_p + 16, pk);
       }
+      if (!took_pv) {
+        // Take every phase of the P·V barrier in order (a parity wait cannot skip one), and before
+        // P(i) is signalled, so that the barrier cannot run a phase ahead of this wait.  P·V(i-1)
+        // was issued a block ago; it also means P·V(i-2) has read the P buffer reused next.
+        ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 9, i);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (threadIdx.x == 0) ATR(6, i);
+      }
       tmem_st_wait_all();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pfull + 8 * t);
       if (threadIdx.x == 0) ATR(5, i);
-      l = fmaf(l, alpha, (ls[0] + ls[1]) + (ls[2] + ls[3]));
-      if (i > 0) {
-        // P·V of the previous block, issued a whole block ago
-        ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 1, i);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (threadIdx.x == 0) ATR(6, i);
-        tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < D / 64; ++c) {
-          uint32_t r0[32], r1[32];
-          tmem_ld_32x32(t_pv + c * 64, r0);
-          tmem_ld_32x32(t_pv + c * 64 + 32, r1);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            o[c * 64 + e] = fmaf(o[c * 64 + e], alpha_prev, __uint_as_float(r0[e]));
-            o[c * 64 + 32 + e] = fmaf(o[c * 64 + 32 + e], alpha_prev, __uint_as_float(r1[e]));
-          }
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_pvfree + 8 * t);
-        if (threadIdx.x == 0) ATR(7, i);
-      }
-      alpha_prev = alpha;
-      m = m_new;
+      l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
     }
     if (ok) {
       ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((nb - 1) & 1), abort_flag, p.status, ATT_SITE + 3, 0);
@@ -290,25 +301,22 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
-        tmem_ld_32x32(t_pv + c * 32, r);
+        tmem_ld_32x32(t_o + c * 32, r);
         tmem_ld_wait();
+        float o[32];
 #pragma unroll
-        for (int e = 0; e < 32; ++e) o[c * 32 + e] = fmaf(o[c * 32 + e], alpha_prev, __uint_as_float(r[e])) * inv_l;
+        for (int e = 0; e < 32; ++e) o[e] = __uint_as_float(r[e]) * inv_l;
         if (row < p.n_ctx) {
           if (OUT32) {
             float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(p.out) + off + c * 32);
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-              dst[e] = make_float4(o[c * 32 + 4 * e], o[c * 32 + 4 * e + 1], o[c * 32 + 4 * e + 2],
-                                   o[c * 32 + 4 * e + 3]);
+            for (int e = 0; e < 8; ++e) dst[e] = make_float4(o[4 * e], o[4 * e + 1], o[4 * e + 2], o[4 * e + 3]);
           } else {
             uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__half *>(p.out) + off + c * 32);
 #pragma unroll
             for (int e = 0; e < 4; ++e)
-              dst[e] = make_uint4(pack_h2(o[c * 32 + 8 * e], o[c * 32 + 8 * e + 1]),
-                                  pack_h2(o[c * 32 + 8 * e + 2], o[c * 32 + 8 * e + 3]),
-                                  pack_h2(o[c * 32 + 8 * e + 4], o[c * 32 + 8 * e + 5]),
-                                  pack_h2(o[c * 32 + 8 * e + 6], o[c * 32 + 8 * e + 7]));
+              dst[e] = make_uint4(pack_h2(o[8 * e], o[8 * e + 1]), pack_h2(o[8 * e + 2], o[8 * e + 3]),
+                                  pack_h2(o[8 * e + 4], o[8 * e + 5]), pack_h2(o[8 * e + 6], o[8 * e + 7]));
           }
         }
       }
@@ -352,16 +360,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         ok = mbar_wait(bar_pfull + 8 * t, (uint32_t)b, abort_flag, p.status, ATT_SITE + 8, i);
         if (!ok) break;
         if (t == 0) ATR(0, i);
-        // S(i) is read: with P in columns of its own the product after next can start at once,
-        // ahead of P·V(i), which still waits for the softmax group to take P·V(i-1)
-        if (!ALIAS && i + 2 < nb) {
-          ok = issue_qk(b, i + 2);
-          if (!ok) break;
-          if (t == 0) ATR(2, i);
-        }
         ok = mbar_wait(bar_vfull + 8 * vs, vph, abort_flag, p.status, ATT_SITE + 6, i);
-        if (ok && i > 0)
-          ok = mbar_wait(bar_pvfree + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 9, i);
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t a_tmem = tm + (uint32_t)(ALIAS ? b * 64 : COL_P + b * 32);
@@ -369,7 +368,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
 #pragma unroll
         for (int j = 0; j < BN / 16; ++j) {
           // V is MN-major: 64-column slabs KV_SLAB apart, 8-key groups 1024 B apart, a K=16 step is 16 rows
-          mma_f16_ts_att(tm + COL_PV, a_tmem + (uint32_t)(j * 8), vd + (uint64_t)(j * 128), IDESC_PV, j ? 1u : 0u);
+          mma_f16_ts_att(tm + COL_PV, a_tmem + (uint32_t)(j * 8), vd + (uint64_t)(j * 128), IDESC_PV, (i | j) ? 1u : 0u);
         }
         mma_commit(bar_pvfull + 8 * t);
         mma_commit(bar_vempty + 8 * vs);
@@ -378,10 +377,12 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
           vph ^= 1u;
         }
         if (t == 0) ATR(1, i);
-        if (ALIAS && i + 2 < nb) {
-          // P(i) lives in the S buffer the next product overwrites: P·V(i) must have read it
-          ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)b, abort_flag, p.status, ATT_SITE + 7, i);
-          if (!ok) break;
+        if (i + 2 < nb) {
+          if (ALIAS) {
+            // P(i) lives in the S buffer the next product overwrites: P·V(i) must have read it
+            ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)b, abort_flag, p.status, ATT_SITE + 7, i);
+            if (!ok) break;
+          }
           ok = issue_qk(b, i + 2);
           if (t == 0) ATR(2, i);
         }

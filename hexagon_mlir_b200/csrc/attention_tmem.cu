@@ -12,9 +12,10 @@
 // One CTA owns TILES tiles of 128 queries of one (batch, head); key blocks of 64.  Roles:
 //   warps [4t, 4t+4)     softmax group of tile t: thread = one query row.  Reads the row of S from
 //                        TMEM once, takes the maximum, writes P as packed fp16 back to TMEM.
-//   warp 4·TILES + t     lane 0 issues tile t's MMAs: S = Q·Kᵀ (both operands in shared memory)
-//                        two blocks ahead, and O += P·V (P from TMEM, V from shared memory).
-//   warp 5·TILES         lane 0 loads Q once and the K and V blocks into two rings with TMA.
+//   warp 4·TILES + t     lane 0 issues tile t's score products S = Q·Kᵀ (both operands in shared
+//                        memory), two blocks ahead of the softmax group.
+//   warp 5·TILES + t     lane 0 issues tile t's O += P·V (P from TMEM, V from shared memory).
+//   warp 6·TILES         lane 0 loads Q once and the K and V blocks into two rings with TMA.
 // TMEM per tile (256 columns): S0, S1 [128 x 64] fp32; head size 64: P0, P1 (32 columns each) and
 // O [128 x 64] fp32; head size 128: O [128 x 128] fp32 and P(i) written over the read half of S(i).
 // Every wait is bounded; a wait that runs out sets the CTA's abort flag and the device status.
@@ -101,17 +102,19 @@ __device__ long long g_att_trace[8 * 32];
 // status sites of this kernel
 constexpr int ATT_SITE = 60;
 
-// Block: TILES softmax warpgroups, then the MMA-issue warps (one per tile) and the load warp.
-constexpr int att_threads(int tiles) { return tiles == 2 ? 384 : 192; }
+// Block: TILES softmax warpgroups, then per tile one warp that issues the score products and one
+// that issues P·V, then the load warp.
+constexpr int att_threads(int tiles) { return 32 * (6 * tiles + 1); }
 constexpr int ATT_BN = 64;  // keys per block
 
 // Pipeline of one tile (block i, S buffer b = i & 1):
-//   MMA warp:  QK(0), QK(1);  then per i:  wait P(i) -> O += P(i)·V(i) -> QK(i+2) into buffer b
+//   score warp: QK(0), QK(1);  then per i:  wait P(i) -> QK(i+2) into buffer b
+//   P·V warp:   per i:  wait P(i) -> O += P(i)·V(i)
 //   softmax:   wait S(i) -> max -> (rarely: rescale O in TMEM) -> exponentials, P(i) -> signal
 // O accumulates in TMEM over all blocks (P·V with accumulate), so the softmax thread holds only
 // the row's scores; the next S is complete before the softmax group asks for it, and the group
 // never waits for the tensor cores in steady state.
-template <int D, int TILES, int KST, bool OUT32>
+template <int D, int TILES, int KST, int VST, bool OUT32>
 __global__ void __launch_bounds__(att_threads(TILES), 1)
     attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const AttParams p) {
@@ -128,7 +131,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
   constexpr int TCOLS = 256;
   constexpr int COL_P = 128, COL_PV = ALIAS ? 128 : 192;
   constexpr int TMEM_COLS = TILES * TCOLS;
-  constexpr int MMA_WARP0 = 4 * TILES, LOAD_WARP = 5 * TILES;
+  constexpr int QK_WARP0 = 4 * TILES, PV_WARP0 = 5 * TILES, LOAD_WARP = 6 * TILES;
   constexpr uint32_t IDESC_QK = make_idesc(/*D f32*/ 1, /*A f16*/ 0, /*B f16*/ 0, /*A K-major*/ 0,
                                            /*B K-major*/ 0, ATT_BM, BN);
   constexpr uint32_t IDESC_PV = make_idesc(/*D f32*/ 1, /*A f16*/ 0, /*B f16*/ 0, /*A K-major*/ 0,
@@ -142,19 +145,19 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
   const uint32_t q_smem = base;
   const uint32_t k_smem = q_smem + TILES * Q_BYTES;
   const uint32_t v_smem = k_smem + KST * KV_BYTES;
-  const uint32_t ctrl = v_smem + KST * KV_BYTES;
+  const uint32_t ctrl = v_smem + VST * KV_BYTES;
   const uint32_t bar_qfull = ctrl;            // [tile] Q tile landed
   const uint32_t bar_kfull = ctrl + 16;       // [stage] K block landed
   const uint32_t bar_kempty = ctrl + 48;      // [stage] every tile's QK product of the block is complete
   const uint32_t bar_vfull = ctrl + 80;       // [stage]
   const uint32_t bar_vempty = ctrl + 112;     // [stage] every tile's P·V of the block is complete
   const uint32_t bar_sfull = ctrl + 144;      // [tile][buffer] S complete
-  const uint32_t bar_pfull = ctrl + 176;      // [tile] P written (and S read), 4 warps
-  const uint32_t bar_pvfull = ctrl + 192;     // [tile] O += P·V of a block complete
-  const uint32_t tmem_slot = ctrl + 224;
+  const uint32_t bar_pfull = ctrl + 176;      // [tile][block parity] P written (and S read), 4 warps
+  const uint32_t bar_pvfull = ctrl + 208;     // [tile][block parity] O += P·V of a block complete
+  const uint32_t tmem_slot = ctrl + 240;
   uint8_t *ctrl_ptr = smem_raw + (ctrl - smem_u32(smem_raw));
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_ptr + 228);
-  static_assert(KST <= 4 && KST >= 3, "barrier table; K(i+2) is loaded while K(i+1) is in use");
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(ctrl_ptr + 244);
+  static_assert(KST <= 4 && KST >= 2 && VST <= 4 && VST >= 2, "barrier table; K(i), K(i+1) are resident together");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * (TILES * ATT_BM);
@@ -167,22 +170,26 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
       mbar_init(bar_qfull + 8 * t, 1);
       mbar_init(bar_sfull + 16 * t, 1);
       mbar_init(bar_sfull + 16 * t + 8, 1);
-      mbar_init(bar_pfull + 8 * t, 4);
-      mbar_init(bar_pvfull + 8 * t, 1);
+      mbar_init(bar_pfull + 16 * t, 4);
+      mbar_init(bar_pfull + 16 * t + 8, 4);
+      mbar_init(bar_pvfull + 16 * t, 1);
+      mbar_init(bar_pvfull + 16 * t + 8, 1);
     }
     for (int s = 0; s < KST; ++s) {
       mbar_init(bar_kfull + 8 * s, 1);
       mbar_init(bar_kempty + 8 * s, TILES);
+    }
+    for (int s = 0; s < VST; ++s) {
       mbar_init(bar_vfull + 8 * s, 1);
       mbar_init(bar_vempty + 8 * s, TILES);
     }
     fence_barrier_init();
   }
-  if (warp == MMA_WARP0) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == QK_WARP0) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(ctrl_ptr + 224);
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(ctrl_ptr + 240);
 
   if (warp < 4 * TILES) {
     // ---------------- softmax group of tile t: one thread per query row ----------------
@@ -199,7 +206,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
     bool ok = true;
     for (int i = 0; i < nb; ++i) {
       const int b = i & 1;
-      ok = mbar_wait(bar_sfull + 16 * t + 8 * b, (uint32_t)((i >> 1) & 1), abort_flag, p.status, ATT_SITE + 2, i);
+      ok = mbar_wait_parked(bar_sfull + 16 * t + 8 * b, (uint32_t)((i >> 1) & 1), abort_flag, p.status, ATT_SITE + 2, i);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       if (threadIdx.x == 0) ATR(4, i);
@@ -226,7 +233,6 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         for (int j = 0; j < 4; ++j) mx[j] = max3(mx[j], __uint_as_float(s0[e + j]), __uint_as_float(s1[e + j]));
       }
       const float cur = max3(mx[0], mx[1], fmaxf(mx[2], mx[3])) * c2;
-      bool took_pv = i == 0;  // whether this block's turn at the P·V barrier is done
       if (__any_sync(0xffffffffu, cur > m + kSlack)) {
         const float m_new = fmaxf(m, cur);
         const float alpha = ex2(m - m_new);  // 0 on the first block, 1 for a row whose maximum stayed
@@ -234,10 +240,10 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         m = m_new;
         if (i > 0) {
           // O must hold every product issued so far before it is rescaled
-          ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 1, i);
+          ok = mbar_wait_parked(bar_pvfull + 16 * t + 8 * ((i - 1) & 1), (uint32_t)(((i - 1) >> 1) & 1), abort_flag, p.status,
+                         ATT_SITE + 1, i);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          took_pv = true;
           tc_fence_after_sync();
 #pragma unroll 1
           for (int c = 0; c < D / 32; ++c) {
@@ -249,6 +255,15 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
             tmem_st_x32(t_o + c * 32, r);
           }
         }
+      }
+      if (i >= 2) {
+        // P(i) goes where P(i-2) was: the product that read it, two blocks old, is complete.  Every
+        // barrier of this kernel belongs to a block parity, so its next phase cannot start before
+        // each of its waiters has seen this one.
+        ok = mbar_wait_parked(bar_pvfull + 16 * t + 8 * b, (uint32_t)(((i - 2) >> 1) & 1), abort_flag, p.status, ATT_SITE + 9, i);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (threadIdx.x == 0) ATR(6, i);
       }
       const float neg_m = -m;
       float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -273,24 +288,16 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         }
         tmem_st_x16(t_p + 16, pk);
       }
-      if (!took_pv) {
-        // Take every phase of the P·V barrier in order (a parity wait cannot skip one), and before
-        // P(i) is signalled, so that the barrier cannot run a phase ahead of this wait.  P·V(i-1)
-        // was issued a block ago; it also means P·V(i-2) has read the P buffer reused next.
-        ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((i - 1) & 1), abort_flag, p.status, ATT_SITE + 9, i);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (threadIdx.x == 0) ATR(6, i);
-      }
       tmem_st_wait_all();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_pfull + 8 * t);
+      if (lane == 0) mbar_arrive(bar_pfull + 16 * t + 8 * b);
       if (threadIdx.x == 0) ATR(5, i);
       l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
     }
     if (ok) {
-      ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)((nb - 1) & 1), abort_flag, p.status, ATT_SITE + 3, 0);
+      ok = mbar_wait_parked(bar_pvfull + 16 * t + 8 * ((nb - 1) & 1), (uint32_t)(((nb - 1) >> 1) & 1), abort_flag, p.status,
+                     ATT_SITE + 3, 0);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
@@ -321,21 +328,19 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         }
       }
     }
-  } else if (warp >= MMA_WARP0 && warp < MMA_WARP0 + TILES) {
-    // ---------------- MMA issue, one warp per tile ----------------
+  } else if (warp >= QK_WARP0 && warp < QK_WARP0 + TILES) {
+    // ---------------- score products of tile t: S(i+2) = Q·K(i+2)ᵀ as soon as S(i) is read ----------------
     if (lane == 0) {
-      const int t = warp - MMA_WARP0;
+      const int t = warp - QK_WARP0;
       const uint32_t tm = tmem_base + (uint32_t)(t * TCOLS);
-      bool ok = mbar_wait(bar_qfull + 8 * t, 0u, abort_flag, p.status, ATT_SITE + 4, t);
-      // descriptors without their start address; a K=16 step adds a constant to the address field
+      bool ok = mbar_wait_parked(bar_qfull + 8 * t, 0u, abort_flag, p.status, ATT_SITE + 4, t);
+      // descriptors of the ring's first stage; a stage or a K=16 step adds a constant to the address field
       const uint64_t qdesc = smem_desc_sw128(q_smem + t * Q_BYTES, 16, 1024);
       const uint64_t kdesc0 = smem_desc_sw128(k_smem, 16, 1024);
-      const uint64_t vdesc0 = smem_desc_sw128(v_smem, KV_SLAB, 1024);
-      int ks = 0, vs = 0;
-      uint32_t kph = 0, vph = 0;
-      // S[buf] = Q·K(block)ᵀ for the next block of the K ring
+      int ks = 0;
+      uint32_t kph = 0;
       auto issue_qk = [&](int buf, int blk) -> bool {
-        if (!mbar_wait(bar_kfull + 8 * ks, kph, abort_flag, p.status, ATT_SITE + 5, blk)) return false;
+        if (!mbar_wait_parked(bar_kfull + 8 * ks, kph, abort_flag, p.status, ATT_SITE + 5, blk)) return false;
         tc_fence_after_sync();
         const uint64_t kd = kdesc0 + (uint64_t)((ks * KV_BYTES) >> 4);
 #pragma unroll
@@ -355,13 +360,33 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
       };
       if (ok) ok = issue_qk(0, 0);
       if (ok && nb > 1) ok = issue_qk(1, 1);
+      for (int i = 0; i + 2 < nb && ok; ++i) {
+        const int b = i & 1;
+        const uint32_t ph = (uint32_t)((i >> 1) & 1);
+        ok = mbar_wait_parked(bar_pfull + 16 * t + 8 * b, ph, abort_flag, p.status, ATT_SITE + 8, i);
+        if (ok && ALIAS)  // P(i) lives in the S buffer this product overwrites: P·V(i) must have read it
+          ok = mbar_wait_parked(bar_pvfull + 16 * t + 8 * b, ph, abort_flag, p.status, ATT_SITE + 7, i);
+        if (!ok) break;
+        if (t == 0) ATR(3, i);
+        ok = issue_qk(b, i + 2);
+        if (t == 0) ATR(2, i);
+      }
+    }
+  } else if (warp >= PV_WARP0 && warp < PV_WARP0 + TILES) {
+    // ---------------- O += P(i)·V(i) of tile t ----------------
+    if (lane == 0) {
+      const int t = warp - PV_WARP0;
+      const uint32_t tm = tmem_base + (uint32_t)(t * TCOLS);
+      const uint64_t vdesc0 = smem_desc_sw128(v_smem, KV_SLAB, 1024);
+      int vs = 0;
+      uint32_t vph = 0;
+      bool ok = true;
       for (int i = 0; i < nb && ok; ++i) {
         const int b = i & 1;
-        ok = mbar_wait(bar_pfull + 8 * t, (uint32_t)b, abort_flag, p.status, ATT_SITE + 8, i);
+        ok = mbar_wait_parked(bar_pfull + 16 * t + 8 * b, (uint32_t)((i >> 1) & 1), abort_flag, p.status, ATT_SITE + 12, i);
+        if (ok) ok = mbar_wait_parked(bar_vfull + 8 * vs, vph, abort_flag, p.status, ATT_SITE + 6, i);
         if (!ok) break;
         if (t == 0) ATR(0, i);
-        ok = mbar_wait(bar_vfull + 8 * vs, vph, abort_flag, p.status, ATT_SITE + 6, i);
-        if (!ok) break;
         tc_fence_after_sync();
         const uint32_t a_tmem = tm + (uint32_t)(ALIAS ? b * 64 : COL_P + b * 32);
         const uint64_t vd = vdesc0 + (uint64_t)((vs * KV_BYTES) >> 4);
@@ -370,22 +395,13 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
           // V is MN-major: 64-column slabs KV_SLAB apart, 8-key groups 1024 B apart, a K=16 step is 16 rows
           mma_f16_ts_att(tm + COL_PV, a_tmem + (uint32_t)(j * 8), vd + (uint64_t)(j * 128), IDESC_PV, (i | j) ? 1u : 0u);
         }
-        mma_commit(bar_pvfull + 8 * t);
+        mma_commit(bar_pvfull + 16 * t + 8 * b);
         mma_commit(bar_vempty + 8 * vs);
-        if (++vs == KST) {
+        if (++vs == VST) {
           vs = 0;
           vph ^= 1u;
         }
         if (t == 0) ATR(1, i);
-        if (i + 2 < nb) {
-          if (ALIAS) {
-            // P(i) lives in the S buffer the next product overwrites: P·V(i) must have read it
-            ok = mbar_wait(bar_pvfull + 8 * t, (uint32_t)b, abort_flag, p.status, ATT_SITE + 7, i);
-            if (!ok) break;
-          }
-          ok = issue_qk(b, i + 2);
-          if (t == 0) ATR(2, i);
-        }
       }
     }
   } else if (warp == LOAD_WARP) {
@@ -404,7 +420,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
       uint32_t kph = 0, vph = 0;
       bool ok = true;
       auto load_k = [&](int blk) {
-        ok = mbar_wait(bar_kempty + 8 * ks, kph ^ 1u, abort_flag, p.status, ATT_SITE + 10, blk);
+        ok = mbar_wait_parked(bar_kempty + 8 * ks, kph ^ 1u, abort_flag, p.status, ATT_SITE + 10, blk);
         if (!ok) return;
         mbar_expect_tx(bar_kfull + 8 * ks, KV_BYTES);
 #pragma unroll
@@ -418,13 +434,13 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
       load_k(0);
       if (ok && nb > 1) load_k(1);
       for (int i = 0; i < nb && ok; ++i) {
-        ok = mbar_wait(bar_vempty + 8 * vs, vph ^ 1u, abort_flag, p.status, ATT_SITE + 11, i);
+        ok = mbar_wait_parked(bar_vempty + 8 * vs, vph ^ 1u, abort_flag, p.status, ATT_SITE + 11, i);
         if (!ok) break;
         mbar_expect_tx(bar_vfull + 8 * vs, KV_BYTES);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
           tma_load_4d(v_smem + vs * KV_BYTES + s * KV_SLAB, &tmV, bar_vfull + 8 * vs, s * 64, i * BN, hh, zz);
-        if (++vs == KST) {
+        if (++vs == VST) {
           vs = 0;
           vph ^= 1u;
         }
@@ -439,7 +455,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
   if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0)
     for (int i = threadIdx.x; i < 8 * 32; i += blockDim.x) g_att_trace[i] = trace_s[i];
 #endif
-  if (warp == MMA_WARP0) {
+  if (warp == QK_WARP0) {
     tc_fence_after_sync();
     __syncwarp();
     tmem_dealloc(tmem_base, TMEM_COLS);
@@ -489,13 +505,13 @@ struct AttShape {
   int64_t z, h, n, d, sz, sh, sn;
 };
 
-template <int D, int TILES, int KST, bool OUT32>
+template <int D, int TILES, int KST, int VST, bool OUT32>
 int launch_attention_variant(const void *q, const void *k, const void *v, void *out, const AttShape &in,
                              const AttShape &os, double sm_scale) {
   constexpr int BN = ATT_BN;
-  constexpr int SMEM = TILES * (D / 64) * ATT_BM * 128 + 2 * KST * (D / 64) * BN * 128 + 256 + 1024;
+  constexpr int SMEM = TILES * (D / 64) * ATT_BM * 128 + (KST + VST) * (D / 64) * BN * 128 + 256 + 1024;
   static bool attr_set = false;
-  auto kern = attention_kernel<D, TILES, KST, OUT32>;
+  auto kern = attention_kernel<D, TILES, KST, VST, OUT32>;
   if (!attr_set) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     attr_set = true;
@@ -568,13 +584,13 @@ int launch_attention(const void *q, const void *k, const void *v, void *out, boo
   int two = d == 128 && tiles > c.sm_count ? 1 : 0;
   if (c.opt.attention_tiles == 1) two = 0;
   if (c.opt.attention_tiles == 2) two = 1;
-#define ATT_GO(D_, T_, K_, O_) launch_attention_variant<D_, T_, K_, O_>(q, k, v, out, in, os, sm_scale)
+#define ATT_GO(D_, T_, K_, V_, O_) launch_attention_variant<D_, T_, K_, V_, O_>(q, k, v, out, in, os, sm_scale)
   if (d == 64) {
-    if (two) return f32 ? ATT_GO(64, 2, 4, true) : ATT_GO(64, 2, 4, false);
-    return f32 ? ATT_GO(64, 1, 4, true) : ATT_GO(64, 1, 4, false);
+    if (two) return f32 ? ATT_GO(64, 2, 4, 4, true) : ATT_GO(64, 2, 4, 4, false);
+    return f32 ? ATT_GO(64, 1, 4, 4, true) : ATT_GO(64, 1, 4, 4, false);
   }
-  if (two) return f32 ? ATT_GO(128, 2, 3, true) : ATT_GO(128, 2, 3, false);
-  return f32 ? ATT_GO(128, 1, 3, true) : ATT_GO(128, 1, 3, false);
+  if (two) return f32 ? ATT_GO(128, 2, 3, 3, true) : ATT_GO(128, 2, 3, 3, false);
+  return f32 ? ATT_GO(128, 1, 2, 2, true) : ATT_GO(128, 1, 2, 2, false);
 #undef ATT_GO
 }
 

@@ -66,6 +66,35 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same wait for a thread that should not take issue slots from its neighbours while it
+// waits: try_wait is given a suspend-time hint, so the hardware parks the thread until the phase
+// completes or the hint (nanoseconds) runs out; the clock budget is checked between attempts.
+__device__ __forceinline__ bool mbar_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                                 int *status, int site, int detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait_parked(bar, parity, 20000u)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      if (atomicCAS(status, 0, site) == 0) status[1] = detail;
+      return false;
+    }
+  }
+}
+
 // 2-D tiled TMA load into this CTA's shared memory, completion on an mbarrier.
 // c0 is the innermost coordinate and must keep c0 * elemsize a multiple of 16.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar,

@@ -464,8 +464,12 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
 
 // fp32 [z,h,n,d] with the caller's strides -> contiguous fp16 (round to nearest even, as the
 // engine's pack leaf does: bin/runtime/hmx/src/HMXLayout.c:257-264).
-__global__ void attention_cast_kernel(const float *__restrict__ src, __half *__restrict__ dst, int64_t total4,
-                                      int d4, int n, int h, int64_t sz, int64_t sh, int64_t sn) {
+__global__ void attention_cast_kernel(const float *__restrict__ q, const float *__restrict__ k,
+                                      const float *__restrict__ v, __half *__restrict__ dst, int64_t total4, int d4,
+                                      int n, int h, int64_t sz, int64_t sh, int64_t sn) {
+  // blockIdx.y picks the operand; the three results are stored one after the other
+  const float *src = blockIdx.y == 0 ? q : blockIdx.y == 1 ? k : v;
+  dst += (int64_t)blockIdx.y * total4 * 4;
   for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total4; i += (int64_t)gridDim.x * blockDim.x) {
     const int c = (int)(i % d4);
     int64_t r = i / d4;
@@ -473,10 +477,10 @@ __global__ void attention_cast_kernel(const float *__restrict__ src, __half *__r
     r /= n;
     const int hh = (int)(r % h);
     const int64_t zz = r / h;
-    const float4 v = *reinterpret_cast<const float4 *>(src + zz * sz + hh * sh + (int64_t)row * sn + c * 4);
+    const float4 x = *reinterpret_cast<const float4 *>(src + zz * sz + hh * sh + (int64_t)row * sn + c * 4);
     uint2 o;
-    o.x = pack_h2(v.x, v.y);
-    o.y = pack_h2(v.z, v.w);
+    o.x = pack_h2(x.x, x.y);
+    o.y = pack_h2(x.z, x.w);
     *reinterpret_cast<uint2 *>(dst + i * 4) = o;
   }
 }
@@ -563,27 +567,22 @@ int launch_attention(const void *q, const void *k, const void *v, void *out, boo
     const size_t each = (size_t)z * h * n * d;
     void *ws = nullptr;
     B200_TRY(workspace(3 * each * sizeof(__half), &ws));
-    const void *src[3] = {q, k, v};
     __half *dst = (__half *)ws;
     const int64_t total4 = (int64_t)each / 4;
     const int blocks = (int)std::min<int64_t>((total4 + 255) / 256, (int64_t)c.sm_count * 8);
-    for (int i = 0; i < 3; ++i) {
-      attention_cast_kernel<<<blocks, 256, 0, c.stream>>>((const float *)src[i], dst + i * each, total4, (int)(d / 4),
-                                                          (int)n, (int)h, sz, sh, sn);
-      count_launch();
-    }
+    attention_cast_kernel<<<dim3(blocks, 3), 256, 0, c.stream>>>((const float *)q, (const float *)k, (const float *)v,
+                                                                 dst, total4, (int)(d / 4), (int)n, (int)h, sz, sh, sn);
+    count_launch();
     B200_TRY(check_launch("attention_cast_kernel"));
     q = dst;
     k = dst + each;
     v = dst + 2 * each;
     in = AttShape{z, h, n, d, h * n * d, n * d, d};
   }
-  // Two tiles per CTA pay at head size 128 once there are more tiles than SMs; at head size 64 one
-  // tile per CTA measured faster at every size (620 against 576 TFLOP/s at 4 x 16 x 4096).
-  const int64_t tiles = z * h * ((n + ATT_BM - 1) / ATT_BM);
-  int two = d == 128 && tiles > c.sm_count ? 1 : 0;
-  if (c.opt.attention_tiles == 1) two = 0;
-  if (c.opt.attention_tiles == 2) two = 1;
+  // One tile per CTA and two CTAs per SM measured as fast as or faster than two tiles in one CTA
+  // at both head sizes (4 x 16 x 4096: 679 against 597 TFLOP/s at 64, 1075 against 1062 at 128);
+  // option attentionTiles = 2 selects the two-tile form.
+  const int two = c.opt.attention_tiles == 2 ? 1 : 0;
 #define ATT_GO(D_, T_, K_, V_, O_) launch_attention_variant<D_, T_, K_, V_, O_>(q, k, v, out, in, os, sm_scale)
   if (d == 64) {
     if (two) return f32 ? ATT_GO(64, 2, 4, 4, true) : ATT_GO(64, 2, 4, 4, false);

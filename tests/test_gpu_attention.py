@@ -101,6 +101,36 @@ def test_large_against_torch_and_repeatable(hm, cuda):
     assert float((out.float() - 1).abs().max()) < 2e-3
 
 
+@pytest.mark.parametrize("d,tiles", [(64, 0), (64, 2), (128, 0), (128, 2)])
+def test_scores_that_grow_block_by_block(hm, oracle, cuda, d, tiles):
+    """The kernel keeps O in TMEM scaled by a lazily updated maximum and rescales it only when a
+    row's maximum grows by more than 2^8: keys whose scores rise by ~11.5 (in log2) per 64-key
+    block force that on every block, for the rows of the second half of each tile only."""
+    rng = philox(33)
+    n = 576  # nine blocks
+    q = rng.uniform(-0.02, 0.02, (2, 2, n, d)).astype(np.float16)
+    q[:, :, np.arange(n) % 128 >= 64] += np.float16(16.0 / d)   # these rows see the growing scores
+    k = (np.arange(n) // 64 * 0.5)[None, None, :, None] + rng.uniform(-0.05, 0.05, (2, 2, n, d))
+    k = k.astype(np.float16)
+    v = rng.normal(0, 1, (2, 2, n, d)).astype(np.float16)
+    want = oracle.attention(q, k, v, 1.0, block_n=64)
+    hm.set_option("attentionTiles", tiles)
+    try:
+        out = np.zeros_like(q)
+        hm.attention(q, k, v, out, 1.0)
+    finally:
+        hm.set_option("attentionTiles", 0)
+    assert np.isfinite(out.astype(np.float32)).all()
+    assert _rel(out, want) < 8e-4
+    assert hm.device_status() == 0
+    # and the other way round: the largest scores first, nothing to rescale afterwards
+    k2 = np.ascontiguousarray(k[:, :, ::-1])
+    want2 = oracle.attention(q, k2, v, 1.0, block_n=64)
+    out2 = np.zeros_like(q)
+    hm.attention(q, k2, v, out2, 1.0)
+    assert _rel(out2, want2) < 8e-4
+
+
 def test_refusals(hm, cuda):
     q = cuda.zeros(1, 1, 64, 32, device="cuda", dtype=cuda.float16)
     with pytest.raises(hm.B200Error) as e:

@@ -67,6 +67,7 @@ _SIGNATURES = {
     "matmul_i8": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M2] + _GRID),
     "attention_fwd_kernel_float16": (None, [c_i64, _M4] * 4 + [ctypes.c_float] + _GRID),
     "attention_fwd_kernel_float32": (None, [c_i64, _M4] * 4 + [ctypes.c_float] + _GRID),
+    "online_softmax": (None, [c_i64, _M2, c_i64, _M2] + _GRID),
     "softmax_kernel_float16": (None, [c_i64, _M2, c_i64, _M2] + _GRID),
     "softmax_kernel_float32": (None, [c_i64, _M2, c_i64, _M2] + _GRID),
     "rms_norm_fwd_kernel_float16": (None, [c_i64, _M2, c_i64, _M2, c_i64, _M1] + _GRID),

@@ -550,6 +550,10 @@ static void attention_impl(bool f32, int64_t rq, B200MemRef4D *q, int64_t rk, B2
   st.finish();
 }
 
+void online_softmax(int64_t rx, B200MemRef2D *x, int64_t ry, B200MemRef2D *y, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  softmax_impl(false, rx, x, ry, y);
+}
 void attention_fwd_kernel_float16(int64_t rq, B200MemRef4D *q, int64_t rk, B200MemRef4D *k, int64_t rv,
                                   B200MemRef4D *v, int64_t ro, B200MemRef4D *out, float sm_scale, B200_GRID_ARGS) {
   ENTER_KERNEL();

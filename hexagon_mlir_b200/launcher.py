@@ -139,6 +139,7 @@ klooped_matmul = Kernel("klooped_matmul", (2, 2, 2), scalar_options={"BLOCK_K": 
 multispan_matmul = Kernel("multispan_matmul", (2, 2, 2))  # test_matmul_multispan.py:82-107
 matmul_i8 = Kernel("matmul_i8", (2, 2, 2))
 softmax_kernel = Kernel("softmax_kernel", (2, 2), by_dtype=True)
+online_softmax = Kernel("online_softmax", (2, 2))  # test_online_softmax.py:27-77, fp32
 rms_norm_fwd_kernel = Kernel("rms_norm_fwd_kernel", (2, 2, 1), by_dtype=True,
                              scalar_options={"EPSILON": "rmsNormEpsilon"})
 silu_kernel = Kernel("silu_kernel", (1, 1), by_dtype=True)

@@ -213,6 +213,13 @@ B200_API int b200mlir_tp_reduce_rows_float16(const void *recv, const void *resid
                                              void *const *peer_out, int world, int rank, int64_t rows_per_rank,
                                              int64_t cols);
 
+/* The two-phase ("online") softmax of test/python/triton/test_online_softmax.py:27-77, fp32 rows:
+ * running maximum and running sum over column blocks, then exp(x - m) / l.  The block sizes are
+ * tl.constexpr there and do not change the result beyond fp32 round-off (the test's tolerance is
+ * 1e-5 against a plain softmax), so this entry runs the row-softmax kernel: one pass, row in
+ * registers.  The symbol has no dtype suffix because the reference kernel has none. */
+B200_API void online_softmax(int64_t rank_x, B200MemRef2D *x, int64_t rank_y, B200MemRef2D *y, B200_GRID_ARGS);
+
 /* Attention block, softmax(Q·K^T·sm_scale)·V per (batch, head): the reference's flash-attention
  * kernel (test/python/triton/test_flash_attention.py:116-195, loop over key blocks :43-113;
  * launched at :198-236).  Q, K, V, Out are [Z, H, N_CTX, D_HEAD] with the head dimension

@@ -131,6 +131,23 @@ def test_scores_that_grow_block_by_block(hm, oracle, cuda, d, tiles):
     assert _rel(out2, want2) < 8e-4
 
 
+def test_online_softmax_as_the_reference_launches_it(hm, oracle, cuda):
+    """test_online_softmax.py:80-110: 128 x 128 fp32, 1 and 4 programs, atol 1e-5 against torch."""
+    x = GOLD["online_x"]
+    for threads in (1, 4):
+        xt = cuda.from_numpy(x).cuda()
+        out = cuda.empty_like(xt)
+        hm.online_softmax[(threads,)](xt, out, NUM_ROWS=128, NUM_COLS=128, BLOCK_ROW_SIZE=128 // threads,
+                                      BLOCK_COL_SIZE=128 // threads, enableMultiThreading=threads == 1,
+                                      enableVTCMTiling=threads == 1, enableConvertToHexagonmem=threads == 1,
+                                      enableHexagonmemCopyToDMA=threads == 1)
+        got = out.cpu().numpy()
+        atol = float(GOLD["online_atol"])
+        assert np.abs(got - GOLD[f"online_y_threads{threads}"]).max() < atol  # the reference kernel's own output
+        assert np.abs(got - oracle.online_softmax(x, 128 // threads)).max() < atol
+        assert cuda.allclose(out, cuda.nn.functional.softmax(xt, dim=1), atol=atol)
+
+
 def test_refusals(hm, cuda):
     q = cuda.zeros(1, 1, 64, 32, device="cuda", dtype=cuda.float16)
     with pytest.raises(hm.B200Error) as e:

@@ -47,6 +47,21 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two fp32 lanes per instruction (sm_100): {d0, d1} = {a0, a1} * {b, b} + {c, c}, and a packed add.
+__device__ __forceinline__ void fma2(float &d0, float &d1, float a0, float a1, float b, float c) {
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float &d0, float &d1, float a0, float a1) {
+  asm("{\n\t.reg .b64 ra, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\t"
+      "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "+f"(d0), "+f"(d1)
+      : "f"(a0), "f"(a1));
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float y;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
@@ -271,19 +286,21 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         uint32_t pk[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float a0 = ex2(fmaf(__uint_as_float(s0[2 * e]), c2, neg_m));
-          const float a1 = ex2(fmaf(__uint_as_float(s0[2 * e + 1]), c2, neg_m));
-          ls[0] += a0;
-          ls[1] += a1;
+          float a0, a1;
+          fma2(a0, a1, __uint_as_float(s0[2 * e]), __uint_as_float(s0[2 * e + 1]), c2, neg_m);
+          a0 = ex2(a0);
+          a1 = ex2(a1);
+          add2(ls[0], ls[1], a0, a1);
           pk[e] = pack_h2(a0, a1);
         }
         tmem_st_x16(t_p, pk);
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const float a0 = ex2(fmaf(__uint_as_float(s1[2 * e]), c2, neg_m));
-          const float a1 = ex2(fmaf(__uint_as_float(s1[2 * e + 1]), c2, neg_m));
-          ls[2] += a0;
-          ls[3] += a1;
+          float a0, a1;
+          fma2(a0, a1, __uint_as_float(s1[2 * e]), __uint_as_float(s1[2 * e + 1]), c2, neg_m);
+          a0 = ex2(a0);
+          a1 = ex2(a1);
+          add2(ls[2], ls[3], a0, a1);
           pk[e] = pack_h2(a0, a1);
         }
         tmem_st_x16(t_p + 16, pk);

@@ -42,6 +42,7 @@ struct Options {
   double gemm_group_m = 0;         // 0: the kernels' default band height
   double gemm_dependent_launch = 1;   // programmatic dependent launch of the tcgen05 GEMM kernels
   double w8a16_dependent_launch = 1;  // programmatic dependent launch of the w8a16 kernel (measured: -7 % per call in a chain)
+  double w8a16_expand_rows = 64;   // above this many activation rows a w8a16 product takes the expanded fp16 weight
   double attention_tiles = 0;      // query tiles per CTA of the attention kernel: 0 chooses by size, 1 or 2
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
 };
@@ -206,7 +207,7 @@ struct W8A16Weight {
   const void *scales = nullptr;  // fp16 [N]
   void *image = nullptr;         // resident device image: [k/128][channel][128 B, pieces swizzled]
   void *scales_dev = nullptr;
-  void *w16 = nullptr;           // row-major fp16 f16(q*s), built on the first many-row call (see kW8A16ExpandRows)
+  void *w16 = nullptr;           // row-major fp16 f16(q*s), built on the first many-row call (option w8a16ExpandRows)
   int64_t k = 0, n = 0;
   size_t image_bytes = 0;
   bool l2_persist = false;
@@ -214,10 +215,11 @@ struct W8A16Weight {
 int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
 int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
                  int64_t ldc);
-// Above this many activation rows a w8a16 product is compute-bound and every CTA of the streaming
-// kernel would re-read all activations from L2: the weight is expanded once to fp16 (2 bytes per
-// weight, kept with the registry entry) and the product goes through the fp16 GEMM.
-constexpr int64_t kW8A16ExpandRows = 128;
+// Above option w8a16ExpandRows activation rows (default 64) every CTA of the streaming kernel
+// re-reads so many activations from L2 that it falls behind the fp16 GEMM (measured on
+// 4096x11008: 96 rows 26.8 against 24.5 us, 128 rows 28.3 against 25.1; 64 rows 18.2 against
+// 24.2): the weight is expanded once to fp16 (2 bytes per weight, kept with the registry entry)
+// and the product goes through the fp16 GEMM.
 // w8a16_tmem.cu
 int w8a16_expand_f16(const void *image, const __half *scales_dev, int64_t k, int64_t n, void **w16);
 int w8a16_build_tmem_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);

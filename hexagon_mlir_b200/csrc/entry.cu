@@ -611,7 +611,7 @@ void w8a16_matmul(int64_t ra, B200MemRef2D *a, int64_t rw, B200MemRef2D *wq, int
     std::lock_guard<std::mutex> lk(g_w_mu);
     if (resident) {
       if (register_weight_locked(W.p, S.p, W.rows, W.cols, 0, &w)) return;
-      if (A.rows > kW8A16ExpandRows && !w->w16 &&
+      if (A.rows > (int64_t)ctx().opt.w8a16_expand_rows && !w->w16 &&
           w8a16_expand_f16(w->image, (const __half *)w->scales_dev, w->k, w->n, &w->w16))
         return;
       local = *w;

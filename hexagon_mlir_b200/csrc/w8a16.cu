@@ -197,7 +197,7 @@ int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, in
     return set_error(B200MLIR_ERR_BAD_ARG,
                      "w8a16: activations must be 16-byte aligned with a row stride multiple of 8");
   if (w.k % 8) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16: K must be a multiple of 8");
-  if (m > kW8A16ExpandRows && w.w16) {
+  if (m > (int64_t)ctx().opt.w8a16_expand_rows && w.w16) {
     // many rows: compute-bound; the expanded fp16 weight goes through the fp16 GEMM
     GemmArgs g;
     g.a = a; g.b = w.w16; g.c = c;

@@ -177,9 +177,9 @@ B200_API void swiglu_kernel_float16(int64_t rank_g, B200MemRef1D *gate, int64_t 
                                     B200_GRID_ARGS);
 /* C[M,N] = A[M,K] · dequant(Wq[K,N], s[N]); Wq int8 row-major, s fp16 per
  * output channel, fp32 accumulate, fp16 out.  No reference function (HMX admits
- * f16/f32 only: include/hexagon/Dialect/Hmx/IR/HmxDType.h:59,69).  Up to 128 rows
- * stream the resident int8 image; a call with more rows expands the weight once to
- * fp16 (2 bytes per weight, kept until the weight is unregistered) and runs the
+ * f16/f32 only: include/hexagon/Dialect/Hmx/IR/HmxDType.h:59,69).  Up to 64 rows
+ * (option "w8a16ExpandRows") stream the resident int8 image; a call with more rows expands the
+ * weight once to fp16 (2 bytes per weight, kept until the weight is unregistered) and runs the
  * fp16 GEMM. */
 B200_API void w8a16_matmul(int64_t rank_a, B200MemRef2D *a, int64_t rank_w, B200MemRef2D *wq,
                            int64_t rank_s, B200MemRef1D *scales, int64_t rank_c,

@@ -102,6 +102,11 @@ struct AttParams {
   int n_ctx, n_blocks;    // keys, and key blocks of BN
   float scale2;           // sm_scale · log2(e)
   int *status;
+  // Short problems: the key blocks are split over `splits` CTAs per tile; each writes its
+  // unnormalised O (fp32) and its (m, l) per row, and attention_combine_kernel merges them.
+  int splits, rows_pad;   // rows_pad: rows of a (batch, head) rounded up to whole CTAs
+  float *part_o;          // [z][h][split][rows_pad][D]
+  float *part_ml;         // [z][h][split][rows_pad][2]
 };
 
 // Region stamps for timeline debugging (the analogue of the reference's light-weight profiling
@@ -175,9 +180,11 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
   static_assert(KST <= 4 && KST >= 2 && VST <= 4 && VST >= 2, "barrier table; K(i), K(i+1) are resident together");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * (TILES * ATT_BM);
+  const int split = (int)blockIdx.x % p.splits;
+  const int m0 = ((int)blockIdx.x / p.splits) * (TILES * ATT_BM);
   const int hh = blockIdx.y, zz = blockIdx.z;
-  const int nb = p.n_blocks;
+  const int blk0 = p.n_blocks * split / p.splits;                    // this CTA's key blocks: [blk0, blk0 + nb)
+  const int nb = p.n_blocks * (split + 1) / p.splits - blk0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -233,7 +240,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
       tmem_ld_32x32(t_s, s0);
       tmem_ld_32x32(t_s + 32, s1);
       tmem_ld_wait();
-      const int n_valid = p.n_ctx - i * BN;  // keys of this block that exist (the last block may be short)
+      const int n_valid = p.n_ctx - (blk0 + i) * BN;  // keys of this block that exist (the last block may be short)
       if (n_valid < BN) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
@@ -321,6 +328,22 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
       tc_fence_after_sync();
       const int row = m0 + t * ATT_BM + q4 * 32 + lane;
       const int64_t off = (int64_t)zz * p.so_z + (int64_t)hh * p.so_h + (int64_t)row * p.so_n;
+      if (p.splits > 1) {
+        // partial result of this key range: O as it stands (scaled by exp2(-m)), and (m, l)
+        const int64_t prow = (((int64_t)zz * gridDim.y + hh) * p.splits + split) * p.rows_pad + row;
+        float4 *dst = reinterpret_cast<float4 *>(p.part_o + prow * D);
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_o + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            dst[c * 8 + e] = make_float4(__uint_as_float(r[4 * e]), __uint_as_float(r[4 * e + 1]),
+                                         __uint_as_float(r[4 * e + 2]), __uint_as_float(r[4 * e + 3]));
+        }
+        *reinterpret_cast<float2 *>(p.part_ml + prow * 2) = make_float2(m, l);
+      } else {
       const float inv_l = 1.0f / l;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -343,6 +366,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
                                   pack_h2(o[8 * e + 4], o[8 * e + 5]), pack_h2(o[8 * e + 6], o[8 * e + 7]));
           }
         }
+      }
       }
     }
   } else if (warp >= QK_WARP0 && warp < QK_WARP0 + TILES) {
@@ -442,7 +466,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         mbar_expect_tx(bar_kfull + 8 * ks, KV_BYTES);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
-          tma_load_4d(k_smem + ks * KV_BYTES + s * KV_SLAB, &tmK, bar_kfull + 8 * ks, s * 64, blk * BN, hh, zz);
+          tma_load_4d(k_smem + ks * KV_BYTES + s * KV_SLAB, &tmK, bar_kfull + 8 * ks, s * 64, (blk0 + blk) * BN, hh, zz);
         if (++ks == KST) {
           ks = 0;
           kph ^= 1u;
@@ -456,7 +480,7 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         mbar_expect_tx(bar_vfull + 8 * vs, KV_BYTES);
 #pragma unroll
         for (int s = 0; s < SLABS; ++s)
-          tma_load_4d(v_smem + vs * KV_BYTES + s * KV_SLAB, &tmV, bar_vfull + 8 * vs, s * 64, i * BN, hh, zz);
+          tma_load_4d(v_smem + vs * KV_BYTES + s * KV_SLAB, &tmV, bar_vfull + 8 * vs, s * 64, (blk0 + i) * BN, hh, zz);
         if (++vs == VST) {
           vs = 0;
           vph ^= 1u;
@@ -476,6 +500,45 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
     tc_fence_after_sync();
     __syncwarp();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// Merges the partial results of a split attention: per row M = max_s m_s,
+// out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).  One thread per (row, 8 columns).
+template <bool OUT32>
+__global__ void attention_combine_kernel(const float *__restrict__ part_o, const float *__restrict__ part_ml, void *out,
+                                         int64_t total, int splits, int rows_pad, int n_ctx, int d, int h,
+                                         int64_t so_z, int64_t so_h, int64_t so_n) {
+  const int groups = d / 8;
+  const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int g = (int)(idx % groups);
+  const int64_t rr = idx / groups;
+  const int row = (int)(rr % n_ctx);
+  const int64_t zh = rr / n_ctx;
+  const int64_t base = zh * splits * rows_pad + row;
+  float mx = -INFINITY;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(base + (int64_t)s * rows_pad) * 2]);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, lsum = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    const int64_t pr = base + (int64_t)s * rows_pad;
+    const float w = exp2f(part_ml[pr * 2] - mx);
+    lsum = fmaf(part_ml[pr * 2 + 1], w, lsum);
+    const float4 a = *reinterpret_cast<const float4 *>(part_o + pr * d + g * 8);
+    const float4 b = *reinterpret_cast<const float4 *>(part_o + pr * d + g * 8 + 4);
+    acc[0] = fmaf(a.x, w, acc[0]); acc[1] = fmaf(a.y, w, acc[1]); acc[2] = fmaf(a.z, w, acc[2]); acc[3] = fmaf(a.w, w, acc[3]);
+    acc[4] = fmaf(b.x, w, acc[4]); acc[5] = fmaf(b.y, w, acc[5]); acc[6] = fmaf(b.z, w, acc[6]); acc[7] = fmaf(b.w, w, acc[7]);
+  }
+  const float inv = 1.0f / lsum;
+  const int64_t off = (zh / h) * so_z + (zh % h) * so_h + (int64_t)row * so_n + g * 8;
+  if (OUT32) {
+    float4 *dst = reinterpret_cast<float4 *>(reinterpret_cast<float *>(out) + off);
+    dst[0] = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    dst[1] = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+  } else {
+    *reinterpret_cast<uint4 *>(reinterpret_cast<__half *>(out) + off) =
+        make_uint4(pack_h2(acc[0] * inv, acc[1] * inv), pack_h2(acc[2] * inv, acc[3] * inv),
+                   pack_h2(acc[4] * inv, acc[5] * inv), pack_h2(acc[6] * inv, acc[7] * inv));
   }
 }
 
@@ -550,9 +613,36 @@ int launch_attention_variant(const void *q, const void *k, const void *v, void *
   p.n_blocks = (int)((in.n + BN - 1) / BN);
   p.scale2 = (float)(sm_scale * 1.44269504);  // the kernel source's own constant for 1/ln 2
   p.status = ctx().d_status;
-  dim3 grid((unsigned)((in.n + TILES * ATT_BM - 1) / (TILES * ATT_BM)), (unsigned)in.h, (unsigned)in.z);
+  // Few tiles and many key blocks: split the keys so that more SMs work.  Two CTAs fit an SM, so
+  // there are 2 x SMs places; a split keeps at least four blocks, and problems with fewer than 16
+  // blocks are not worth the merge (measured: 1x1x1024x64 14.4 -> 10.3 us, 1x2x4096x64 46.6 -> 23.4,
+  // 2x8x512x64 9.3 -> 10.3 when split).  Option attentionSplits overrides (0 = this rule).
+  const int grid_m = (int)((in.n + TILES * ATT_BM - 1) / (TILES * ATT_BM));
+  const int64_t ctas = (int64_t)grid_m * in.h * in.z;
+  int splits = 1;
+  if (ctas * 2 <= ctx().sm_count && p.n_blocks >= 16)
+    splits = (int)std::min<int64_t>(std::min<int64_t>(p.n_blocks / 4, 2 * ctx().sm_count / ctas), 8);
+  if (ctx().opt.attention_splits >= 1) splits = (int)std::min<double>(ctx().opt.attention_splits, (double)p.n_blocks);
+  p.splits = splits;
+  p.rows_pad = grid_m * TILES * ATT_BM;
+  p.part_o = nullptr;
+  p.part_ml = nullptr;
+  if (splits > 1) {
+    const size_t rows = (size_t)in.z * in.h * splits * p.rows_pad;
+    void *ws = nullptr;
+    B200_TRY(workspace2(rows * (D + 2) * sizeof(float), &ws));
+    p.part_o = (float *)ws;
+    p.part_ml = p.part_o + rows * D;
+  }
+  dim3 grid((unsigned)(grid_m * splits), (unsigned)in.h, (unsigned)in.z);
   kern<<<grid, att_threads(TILES), SMEM, ctx().stream>>>(tmQ, tmK, tmV, p);
-  count_launch();
+  if (splits > 1) {
+    B200_TRY(check_launch("attention_kernel"));
+    const int64_t total = (int64_t)in.z * in.h * in.n * (D / 8);
+    attention_combine_kernel<OUT32><<<(unsigned)((total + 127) / 128), 128, 0, ctx().stream>>>(
+        p.part_o, p.part_ml, out, total, splits, p.rows_pad, (int)in.n, D, (int)in.h, os.sz, os.sh, os.sn);
+    return check_launch("attention_combine_kernel");
+  }
   return check_launch("attention_kernel");
 }
 
@@ -589,7 +679,6 @@ int launch_attention(const void *q, const void *k, const void *v, void *out, boo
     const int blocks = (int)std::min<int64_t>((total4 + 255) / 256, (int64_t)c.sm_count * 8);
     attention_cast_kernel<<<dim3(blocks, 3), 256, 0, c.stream>>>((const float *)q, (const float *)k, (const float *)v,
                                                                  dst, total4, (int)(d / 4), (int)n, (int)h, sz, sh, sn);
-    count_launch();
     B200_TRY(check_launch("attention_cast_kernel"));
     q = dst;
     k = dst + each;

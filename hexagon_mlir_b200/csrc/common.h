@@ -43,6 +43,7 @@ struct Options {
   double gemm_dependent_launch = 1;   // programmatic dependent launch of the tcgen05 GEMM kernels
   double w8a16_dependent_launch = 1;  // programmatic dependent launch of the w8a16 kernel (measured: -7 % per call in a chain)
   double w8a16_expand_rows = 64;   // above this many activation rows a w8a16 product takes the expanded fp16 weight
+  double attention_splits = 0;     // key splits of the attention kernel: 0 chooses by size
   double attention_tiles = 0;      // query tiles per CTA of the attention kernel: 0 chooses by size, 1 or 2
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
 };

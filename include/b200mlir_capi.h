@@ -96,8 +96,9 @@ B200_API int b200mlir_device_status(void);
  * the reference's: "enableWeightResident", "iterations", plus
  * "rmsNormEpsilon" (a tl.constexpr in the reference kernel,
  * test/python/triton/test_rms_norm.py:17,39), "gemmVariant" (-1 = dispatcher's
- * choice), "kloopBlockK" and "attentionTiles" (query tiles per CTA of the
- * attention kernel: 0 = by size, 1 or 2).  Returns 0, or B200MLIR_ERR_BAD_ARG for an
+ * choice), "kloopBlockK", "attentionTiles" (query tiles per CTA of the
+ * attention kernel: 0 = by size, 1 or 2), "attentionSplits" (CTAs that share the keys of one
+ * query tile, merged by a second kernel: 0 = by size) and "w8a16ExpandRows".  Returns 0, or B200MLIR_ERR_BAD_ARG for an
  * unknown name. */
 B200_API int b200mlir_set_option(const char *name, double value);
 B200_API int b200mlir_get_option(const char *name, double *value);

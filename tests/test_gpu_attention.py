@@ -131,6 +131,33 @@ def test_scores_that_grow_block_by_block(hm, oracle, cuda, d, tiles):
     assert _rel(out2, want2) < 8e-4
 
 
+@pytest.mark.parametrize("shape,splits", [((1, 1, 1024, 64), 0), ((1, 1, 1024, 64), 8), ((1, 2, 1000, 128), 3),
+                                          ((2, 1, 520, 64), 9), ((1, 1, 2048, 128), 0)])
+def test_keys_split_over_ctas(hm, oracle, cuda, shape, splits):
+    """Few query tiles: the key blocks are shared out over several CTAs per tile and merged by a
+    second kernel (automatically, or with option attentionSplits)."""
+    rng = philox(34)
+    q, k, v = (rng.normal(0, 1, shape).astype(np.float16) for _ in range(3))
+    k[..., shape[2] // 2:, :] *= np.float16(3.0)  # the later splits see larger maxima
+    scale = 1.0 / np.sqrt(shape[-1])
+    want = oracle.attention(q, k, v, scale, block_n=64)
+    hm.set_option("attentionSplits", splits)
+    try:
+        out = cuda.zeros(shape, dtype=cuda.float16, device="cuda")
+        qt, kt, vt = (cuda.from_numpy(t).cuda() for t in (q, k, v))
+        before = hm.launch_count()
+        hm.attention(qt, kt, vt, out, scale)
+        launches = hm.launch_count() - before
+        out32 = np.zeros(shape, np.float32)
+        hm.attention(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), out32, scale)
+    finally:
+        hm.set_option("attentionSplits", 0)
+    assert launches == 2  # the split kernel and the merge
+    assert _rel(out.cpu().numpy(), want) < 8e-4
+    assert _rel(out32, want) < TIGHT
+    assert hm.device_status() == 0
+
+
 def test_online_softmax_as_the_reference_launches_it(hm, oracle, cuda):
     """test_online_softmax.py:80-110: 128 x 128 fp32, 1 and 4 programs, atol 1e-5 against torch."""
     x = GOLD["online_x"]

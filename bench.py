@@ -374,6 +374,21 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         for wq_ in Wq:
             hm.unregister_w8a16_weight(wq_)
         del Wq
+    if want("gemm_i8_4096"):
+        n = 4096
+        a8 = [torch.randint(-128, 128, (n, n), generator=g, device=dev, dtype=torch.int8) for _ in range(4)]
+        b8 = [torch.randint(-128, 128, (n, n), generator=g, device=dev, dtype=torch.int8) for _ in range(4)]
+        c32 = torch.empty((n, n), dtype=torch.int32, device=dev)
+        state = {"i": 0}
+
+        def i8():
+            i = state["i"] % 4
+            state["i"] += 1
+            hm.matmul_i8[(1,)](a8[i], b8[i], c32)
+        ms = graph_timed(torch, i8, reps=5, inner=8)
+        out["gemm_i8_4096^3"] = {"us": ms * 1e3, "tops": 2.0 * n ** 3 / (ms * 1e-3) / 1e12,
+                                 "note": "int32 sums, exact; includes the transpose of B"}
+        del a8, b8, c32
     # attention block: the reference's own case (one head of 1024 x 64, fp32 tensors, sm_scale 0.5:
     # test/python/triton/test_flash_attention.py:17,37) and head counts / lengths that fill the device
     for name, (z, h, n, d, f32) in {"attention_f32_1x1x1024x64": (1, 1, 1024, 64, True),

@@ -142,6 +142,7 @@ int launch_reduce_rows_push(const __half *recv, const __half *residual, int64_t 
                             int world, int rank, int64_t rows_per_rank, int64_t cols);
 
 // layout.cu
+int launch_transpose_i8(const int8_t *src, int8_t *dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst);
 int launch_pack_weight_f16(const uint16_t *src, uint16_t *dst, int64_t k, int64_t n, int64_t ld);
 int launch_pack_act_f16(const uint16_t *src, uint16_t *dst, int64_t rows, int64_t cols,
                         int64_t ld);
@@ -155,7 +156,8 @@ enum Epilogue : int {
   EPI_KLOOP_F16 = 2,  // C16 = f16(sum_seg f32(f16(acc_seg)))
   EPI_F16_RES16 = 3,  // C16 = f16(f32(f16(acc)) + f32(R16))
   EPI_SWIGLU = 4,     // B holds [Wg | Wu] interleaved per tile; C16 = swiglu
-  EPI_PUSH16 = 5      // f16(acc) stored into the row owner's receive slot on another GPU (PushTargets)
+  EPI_PUSH16 = 5,     // f16(acc) stored into the row owner's receive slot on another GPU (PushTargets)
+  EPI_I32 = 6         // int8 operands (B given transposed, [N,K]), C32 = the exact int32 sums
 };
 
 // Where EPI_PUSH16 stores: row r of the partial product belongs to rank r / rows_per_rank, whose
@@ -198,6 +200,9 @@ const TcVariantInfo &tc_variant_info(int v);
 // "ok" or a refusal reason for variant v on (m,n,k) with the given epilogue.
 const char *tc_variant_verdict(int v, const GemmArgs &g);
 int launch_gemm_tc(int v, const GemmArgs &g);
+// int8 x int8 -> int32 on the tensor cores (kind::i8); bt is B transposed, [N,K] row-major
+int launch_gemm_i8_tc(const int8_t *a, const int8_t *bt, int32_t *c, int64_t m, int64_t n, int64_t k, int64_t lda,
+                      int64_t ldbt, int64_t ldc);
 // gemm_tcgen05_2cta.cu
 int launch_gemm_tc_pair(const GemmArgs &g, bool deep_k);
 int pair_variant_smem_bytes();

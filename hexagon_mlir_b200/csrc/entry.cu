@@ -377,9 +377,21 @@ void matmul_i8(int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRef2D *b, int64_t
   const void *da, *db;
   void *dc;
   if (st.in(A.p, A.span(1), &da) || st.in(B.p, B.span(1), &db) || st.out(C.p, C.span(4), &dc, C.ld != C.cols)) return;
-  if (launch_gemm_i8_simt((const int8_t *)da, (const int8_t *)db, (int32_t *)dc, A.rows, B.cols, A.cols, A.ld,
-                          B.ld, C.ld))
+  // Tensor cores (kind::i8, exact int32 sums) when the operands meet the TMA alignment and the
+  // problem fills a few tiles; B is transposed once into the workspace because both int8 operands
+  // are read K-major.  Everything else takes the CUDA-core loop.  Both are exact.
+  const int64_t M = A.rows, N = B.cols, K = A.cols;
+  const bool tc = ctx().opt.gemm_variant != -2 && M >= 64 && N >= 64 && K >= 64 && N % 4 == 0 && A.ld % 16 == 0 &&
+                  C.ld % 4 == 0 && ((uintptr_t)da & 15) == 0 && ((uintptr_t)dc & 15) == 0;
+  if (tc) {
+    const int64_t ldbt = (K + 15) / 16 * 16;
+    void *bt = nullptr;
+    if (workspace((size_t)N * ldbt, &bt)) return;
+    if (launch_transpose_i8((const int8_t *)db, (int8_t *)bt, K, N, B.ld, ldbt)) return;
+    if (launch_gemm_i8_tc((const int8_t *)da, (const int8_t *)bt, (int32_t *)dc, M, N, K, A.ld, ldbt, C.ld)) return;
+  } else if (launch_gemm_i8_simt((const int8_t *)da, (const int8_t *)db, (int32_t *)dc, M, N, K, A.ld, B.ld, C.ld)) {
     return;
+  }
   st.finish();
 }
 

@@ -106,6 +106,14 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
         ow[j] = pack_h2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
       *reinterpret_cast<uint4 *>(cp + v * 8) = o;
     }
+  } else if (EPI == EPI_I32) {
+    int32_t *cp = reinterpret_cast<int32_t *>(p.c) + (int64_t)row * p.ldc + col0;
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      if (col0 + v * 4 >= p.n) break;  // N is a multiple of 4
+      *reinterpret_cast<int4 *>(cp + v * 4) =
+          make_int4((int)r[v * 4], (int)r[v * 4 + 1], (int)r[v * 4 + 2], (int)r[v * 4 + 3]);
+    }
   } else if (EPI == EPI_F32_RES) {
     float *cp = reinterpret_cast<float *>(p.c) + (int64_t)row * p.ldc + col0;
     const float *rp = reinterpret_cast<const float *>(p.res) + (int64_t)row * p.ldres + col0;

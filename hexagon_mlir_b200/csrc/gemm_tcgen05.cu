@@ -46,8 +46,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int B_STAGE_BYTES = N_SLABS * B_SLAB_BYTES;
   constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   constexpr int TMEM_COLS = 2 * BN_MMA <= 32 ? 32 : 2 * BN_MMA;  // power of two by construction
-  constexpr uint32_t IDESC = make_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, /*A K-major*/ 0,
-                                        /*B MN-major*/ 1, BM, BN_MMA);
+  // int8 form (EPI_I32): both operands K-major (B arrives transposed), 128 int8 per swizzle row,
+  // K = 32 per instruction: the same bytes per stage and per step as the fp16 form
+  constexpr bool I8 = EPI == EPI_I32;
+  constexpr uint32_t IDESC = I8 ? make_idesc(/*D=s32*/ 2, /*A=s8*/ 1, /*B=s8*/ 1, /*A K-major*/ 0, /*B K-major*/ 0,
+                                             BM, BN_MMA)
+                                : make_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, /*A K-major*/ 0,
+                                             /*B MN-major*/ 1, BM, BN_MMA);
+  constexpr int KSTEP = I8 ? 128 : BK;  // elements of K per stage
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -112,9 +118,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_STAGE_BYTES;
           mbar_expect_tx(full, STAGE_BYTES);
-          tma_load_2d(sa, &tmA, full, kb * BK, m0);
+          tma_load_2d(sa, &tmA, full, kb * KSTEP, m0);
+          if (I8) tma_load_2d(sb, &tmB, full, kb * KSTEP, n0);  // [BN_MMA rows of Bᵀ] x 128 bytes
 #pragma unroll
-          for (int s = 0; s < N_SLABS; ++s) {
+          for (int s = 0; s < (I8 ? 0 : N_SLABS); ++s) {
             if (EPI == EPI_SWIGLU && s >= N_SLABS / 2)
               tma_load_2d(sb + s * B_SLAB_BYTES, &tmB2, full, n0 + (s - N_SLABS / 2) * 64, kb * BK);
             else
@@ -162,6 +169,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t adesc = smem_desc_sw128(sa + k * 32, 16, 1024);
             // B: MN-major, 64-column slabs B_SLAB_BYTES apart, 8-k groups 1024 B apart;
             // one K=16 step is 16 rows of 128 bytes
+            if (I8) {
+              mma_i8_ss(d_tmem, adesc, smem_desc_sw128(sb + k * 32, 16, 1024), IDESC, (seg_start && k == 0) ? 0u : 1u);
+              continue;
+            }
             const uint64_t bdesc = smem_desc_sw128(sb + k * 2048, B_SLAB_BYTES, 1024);
             mma_f16_ss(d_tmem, adesc, bdesc, IDESC, (seg_start && k == 0) ? 0u : 1u);
           }
@@ -358,6 +369,46 @@ int launch_epi(const GemmArgs &g, const TcVariantInfo &vi) {
 bool al16(const void *p) { return ((uintptr_t)p & 15u) == 0; }
 
 }  // namespace
+
+int launch_gemm_i8_tc(const int8_t *a, const int8_t *bt, int32_t *c, int64_t m, int64_t n, int64_t k, int64_t lda,
+                      int64_t ldbt, int64_t ldc) {
+  B200_TRY(ensure_ready());
+  constexpr int BN_MMA = 128, STAGES = 6;
+  if (!al16(a) || !al16(bt) || !al16(c) || lda % 16 || ldbt % 16 || ldc % 4 || n % 4 || m < 1 || n < 1 || k < 1)
+    return set_error(B200MLIR_ERR_UNSUPPORTED, "int8 tensor-core gemm: alignment (rows 16-byte aligned, N a multiple of 4)");
+  Context &c_ = ctx();
+  const TcVariantInfo &vi = kVariants[1];  // 128x128, six stages of 32 KiB: the same ring
+  CUtensorMap tmA, tmB;
+  B200_TRY(make_map_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k, m, lda, 128, BM));
+  B200_TRY(make_map_2d(&tmB, bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k, n, ldbt, 128, BN_MMA));
+  TcParams p;
+  p.c = c;
+  p.res = nullptr;
+  p.ldc = ldc;
+  p.ldres = 0;
+  p.m = (int)m;
+  p.n = (int)n;
+  p.k = (int)k;
+  p.m_blocks = (int)((m + BM - 1) / BM);
+  p.n_blocks = (int)((n + BN_MMA - 1) / BN_MMA);
+  p.num_tiles = p.m_blocks * p.n_blocks;
+  p.k_blocks = (int)((k + 127) / 128);
+  p.group_m = GROUP_M;
+  p.seg_kb = 1;
+  GemmArgs none;
+  set_push_params(p, none);
+  p.status = c_.d_status;
+  auto kern = gemm_tc_kernel<BN_MMA, STAGES, EPI_I32>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, vi.smem_bytes));
+    attr_set = true;
+  }
+  const int grid = p.num_tiles < c_.sm_count ? p.num_tiles : c_.sm_count;
+  B200_CUDA(launch_maybe_dependent(false, kern, dim3((unsigned)grid), dim3(NUM_THREADS), (size_t)vi.smem_bytes, c_.stream,
+                                   tmA, tmB, tmB, p));
+  return check_launch("gemm_tc_i8_128x128");
+}
 
 int tc_variant_count() { return kNumVariants; }
 const TcVariantInfo &tc_variant_info(int v) { return kVariants[v]; }

@@ -71,7 +71,52 @@ unsigned grid_for(int64_t words) {
   return (unsigned)blocks;
 }
 
+// int8 [rows, cols] -> [cols, ld_dst] (transposed; columns rows..ld_dst-1 of every output row are
+// zero).  64 x 64 byte tiles through shared memory, four bytes per thread and access.
+template <bool VEC>
+__global__ void transpose_i8_kernel(const int8_t *__restrict__ src, int8_t *__restrict__ dst, int64_t rows,
+                                    int64_t cols, int64_t ld_src, int64_t ld_dst) {
+  __shared__ int8_t t[64][68];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16 threads
+  const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t r = r0 + ty + 16 * i, c = c0 + tx * 4;
+    if (VEC && r < rows && c + 3 < cols) {
+      *reinterpret_cast<uint32_t *>(&t[ty + 16 * i][tx * 4]) = *reinterpret_cast<const uint32_t *>(src + r * ld_src + c);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        t[ty + 16 * i][tx * 4 + j] = (r < rows && c + j < cols) ? src[r * ld_src + c + j] : (int8_t)0;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t orow = c0 + ty + 16 * i, ocol = r0 + tx * 4;  // output row = input column
+    if (orow >= cols || ocol >= ld_dst) continue;                // ld_dst is a multiple of 16
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) w |= (uint32_t)(uint8_t)t[tx * 4 + j][ty + 16 * i] << (8 * j);
+    *reinterpret_cast<uint32_t *>(dst + orow * ld_dst + ocol) = w;
+  }
+}
+
 }  // namespace
+
+int launch_transpose_i8(const int8_t *src, int8_t *dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst) {
+  B200_TRY(ensure_ready());
+  if (rows <= 0 || cols <= 0) return 0;
+  const int64_t gy = (ld_dst + 63) / 64, gx = (cols + 63) / 64;
+  if (gy > 65535) return set_error(B200MLIR_ERR_UNSUPPORTED, "transpose_i8: more than 4 M rows");
+  if (ld_dst % 16 || ((uintptr_t)dst & 3)) return set_error(B200MLIR_ERR_BAD_ARG, "transpose_i8: output rows must be 16-byte multiples");
+  const dim3 grid((unsigned)gx, (unsigned)gy);
+  if (ld_src % 4 == 0 && ((uintptr_t)src & 3) == 0)
+    transpose_i8_kernel<true><<<grid, 256, 0, ctx().stream>>>(src, dst, rows, cols, ld_src, ld_dst);
+  else
+    transpose_i8_kernel<false><<<grid, 256, 0, ctx().stream>>>(src, dst, rows, cols, ld_src, ld_dst);
+  return check_launch("transpose_i8");
+}
 
 int launch_pack_weight_f16(const uint16_t *src, uint16_t *dst, int64_t k, int64_t n, int64_t ld) {
   B200_TRY(ensure_ready());

@@ -156,6 +156,34 @@ def test_int8_accumulation_bit_exact(hm, oracle, mnk):
     assert np.array_equal(c, oracle.gemm_i8_i32(a, b))
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 384), (128, 128, 4096), (1000, 1028, 2064), (64, 64, 64),
+                                   (300, 132, 208), (2048, 2048, 2048)])
+def test_matmul_i8_on_tensor_cores_is_exact(hm, oracle, cuda, m, n, k):
+    """int8 x int8 -> int32 through tcgen05 kind::i8 (B transposed on the way): the exact sums,
+    equal to the CUDA-core loop and to the oracle, full range operands (-128 included)."""
+    rng = philox(41)
+    a = rng.integers(-128, 128, (m, k), dtype=np.int8)
+    b = rng.integers(-128, 128, (k, n), dtype=np.int8)
+    a[0, :] = -128
+    b[:, 0] = -128  # the largest magnitude a sum can reach: k * 16384
+    at, bt = cuda.from_numpy(a).cuda(), cuda.from_numpy(b).cuda()
+    ct = cuda.zeros((m, n), dtype=cuda.int32, device="cuda")
+    before = hm.launch_count()
+    hm.matmul_i8[(1,)](at, bt, ct)
+    assert hm.launch_count() - before == 2  # transpose + tensor-core kernel
+    assert hm.device_status() == 0
+    got = ct.cpu().numpy()
+    want = a.astype(np.int32) @ b.astype(np.int32) if m * n * k > 2 ** 30 else oracle.gemm_i8_i32(a, b)
+    assert np.array_equal(got, want)
+    hm.set_option("gemmVariant", -2)  # the CUDA-core loop
+    try:
+        c2 = cuda.zeros_like(ct)
+        hm.matmul_i8[(1,)](at, bt, c2)
+    finally:
+        hm.set_option("gemmVariant", -1)
+    assert cuda.equal(ct, c2)
+
+
 def test_empty_and_bad_shapes(hm):
     a = np.zeros((0, 64), np.float16)
     hm.matmul[(1,)](a, np.zeros((64, 32), np.float16), np.zeros((0, 32), np.float16))

@@ -393,7 +393,8 @@ def extras_single_gpu(torch, hm, peaks, only=None):
     # test/python/triton/test_flash_attention.py:17,37) and head counts / lengths that fill the device
     for name, (z, h, n, d, f32) in {"attention_f32_1x1x1024x64": (1, 1, 1024, 64, True),
                                     "attention_f16_4x16x4096x64": (4, 16, 4096, 64, False),
-                                    "attention_f16_4x16x4096x128": (4, 16, 4096, 128, False)}.items():
+                                    "attention_f16_4x16x4096x128": (4, 16, 4096, 128, False),
+                                    "attention_f16_causal_4x16x4096x128": (4, 16, 4096, 128, False)}.items():
         if not want(name):
             continue
         dt = torch.float32 if f32 else torch.float16
@@ -406,9 +407,9 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         def att():
             i = state["i"] % sets
             state["i"] += 1
-            hm.attention(Q[i], K[i], V[i], O[i], scale)
+            hm.attention(Q[i], K[i], V[i], O[i], scale, causal="causal" in name)
         ms = graph_timed(torch, att, reps=5, inner=sets * (1 if z * h > 1 else 4))
-        flops = 4.0 * z * h * n * n * d
+        flops = 4.0 * z * h * n * n * d * (0.5 if "causal" in name else 1.0)
         out[name] = {"us": ms * 1e3, "tflops": flops / (ms * 1e-3) / 1e12,
                      "frac_of_measured_bf16_burst": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
         del Q, K, V, O

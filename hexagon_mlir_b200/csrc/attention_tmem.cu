@@ -105,6 +105,7 @@ struct AttParams {
   // Short problems: the key blocks are split over `splits` CTAs per tile; each writes its
   // unnormalised O (fp32) and its (m, l) per row, and attention_combine_kernel merges them.
   int splits, rows_pad;   // rows_pad: rows of a (batch, head) rounded up to whole CTAs
+  int causal;             // query i sees keys 0..i only (one tile per CTA, no key splits)
   float *part_o;          // [z][h][split][rows_pad][D]
   float *part_ml;         // [z][h][split][rows_pad][2]
 };
@@ -181,10 +182,14 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = (int)blockIdx.x % p.splits;
-  const int m0 = ((int)blockIdx.x / p.splits) * (TILES * ATT_BM);
+  // causal: the last tiles have the most key blocks, so they are handed out first
+  const int mt = (int)blockIdx.x / p.splits;
+  const int m0 = (p.causal ? (int)gridDim.x / p.splits - 1 - mt : mt) * (TILES * ATT_BM);
   const int hh = blockIdx.y, zz = blockIdx.z;
-  const int blk0 = p.n_blocks * split / p.splits;                    // this CTA's key blocks: [blk0, blk0 + nb)
-  const int nb = p.n_blocks * (split + 1) / p.splits - blk0;
+  // causal: the tile's last row m0 + 127 sees keys up to itself, later blocks are skipped altogether
+  const int nb_tile = p.causal ? min(p.n_blocks, (m0 + TILES * ATT_BM - 1) / ATT_BN + 1) : p.n_blocks;
+  const int blk0 = nb_tile * split / p.splits;                       // this CTA's key blocks: [blk0, blk0 + nb)
+  const int nb = nb_tile * (split + 1) / p.splits - blk0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -246,6 +251,15 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
         for (int e = 0; e < 32; ++e) {
           if (e >= n_valid) s0[e] = 0xff800000u;  // -inf: no weight
           if (32 + e >= n_valid) s1[e] = 0xff800000u;
+        }
+      }
+      if (p.causal && (blk0 + i) * BN + BN > m0) {
+        // a block on the diagonal: keys after the thread's own row carry no weight
+        const int over = m0 + t * ATT_BM + q4 * 32 + lane - (blk0 + i) * BN;  // last key offset this row may see
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          if (e > over) s0[e] = 0xff800000u;
+          if (32 + e > over) s1[e] = 0xff800000u;
         }
       }
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -591,7 +605,7 @@ struct AttShape {
 
 template <int D, int TILES, int KST, int VST, bool OUT32>
 int launch_attention_variant(const void *q, const void *k, const void *v, void *out, const AttShape &in,
-                             const AttShape &os, double sm_scale) {
+                             const AttShape &os, double sm_scale, bool causal) {
   constexpr int BN = ATT_BN;
   constexpr int SMEM = TILES * (D / 64) * ATT_BM * 128 + (KST + VST) * (D / 64) * BN * 128 + 256 + 1024;
   static bool attr_set = false;
@@ -623,6 +637,8 @@ int launch_attention_variant(const void *q, const void *k, const void *v, void *
   if (ctas * 2 <= ctx().sm_count && p.n_blocks >= 16)
     splits = (int)std::min<int64_t>(std::min<int64_t>(p.n_blocks / 4, 2 * ctx().sm_count / ctas), 8);
   if (ctx().opt.attention_splits >= 1) splits = (int)std::min<double>(ctx().opt.attention_splits, (double)p.n_blocks);
+  p.causal = causal ? 1 : 0;
+  if (causal) splits = 1;  // the tiles of a causal problem have different numbers of key blocks
   p.splits = splits;
   p.rows_pad = grid_m * TILES * ATT_BM;
   p.part_o = nullptr;
@@ -656,7 +672,7 @@ extern "C" __attribute__((visibility("default"))) int b200mlir_debug_get_att_tra
 
 int launch_attention(const void *q, const void *k, const void *v, void *out, bool f32, int64_t z, int64_t h,
                      int64_t n, int64_t d, int64_t sz, int64_t sh, int64_t sn, int64_t soz, int64_t soh,
-                     int64_t son, double sm_scale) {
+                     int64_t son, double sm_scale, bool causal) {
   Context &c = ctx();
   if (d != 64 && d != 128) return set_error(B200MLIR_ERR_UNSUPPORTED, "attention: head size %lld (64 or 128)", (long long)d);
   if (z < 1 || h < 1 || n < 1 || h > 65535 || z > 65535 || n > (1 << 30))
@@ -688,8 +704,8 @@ int launch_attention(const void *q, const void *k, const void *v, void *out, boo
   // One tile per CTA and two CTAs per SM measured as fast as or faster than two tiles in one CTA
   // at both head sizes (4 x 16 x 4096: 679 against 597 TFLOP/s at 64, 1075 against 1062 at 128);
   // option attentionTiles = 2 selects the two-tile form.
-  const int two = c.opt.attention_tiles == 2 ? 1 : 0;
-#define ATT_GO(D_, T_, K_, V_, O_) launch_attention_variant<D_, T_, K_, V_, O_>(q, k, v, out, in, os, sm_scale)
+  const int two = c.opt.attention_tiles == 2 && !causal ? 1 : 0;  // (causal: one tile per CTA)
+#define ATT_GO(D_, T_, K_, V_, O_) launch_attention_variant<D_, T_, K_, V_, O_>(q, k, v, out, in, os, sm_scale, causal)
   if (d == 64) {
     if (two) return f32 ? ATT_GO(64, 2, 4, 4, true) : ATT_GO(64, 2, 4, 4, false);
     return f32 ? ATT_GO(64, 1, 4, 4, true) : ATT_GO(64, 1, 4, 4, false);

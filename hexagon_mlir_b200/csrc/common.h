@@ -43,6 +43,7 @@ struct Options {
   double gemm_dependent_launch = 1;   // programmatic dependent launch of the tcgen05 GEMM kernels
   double w8a16_dependent_launch = 1;  // programmatic dependent launch of the w8a16 kernel (measured: -7 % per call in a chain)
   double w8a16_expand_rows = 64;   // above this many activation rows a w8a16 product takes the expanded fp16 weight
+  double attention_stage = 1;      // STAGE of the reference kernel's signature: 1 all keys, 3 causal
   double attention_splits = 0;     // key splits of the attention kernel: 0 chooses by size
   double attention_tiles = 0;      // query tiles per CTA of the attention kernel: 0 chooses by size, 1 or 2
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
@@ -237,7 +238,7 @@ int launch_w8a16_tmem(const __half *a, const void *image, const __half *scales_d
 // rounded to fp16 first), else fp16
 int launch_attention(const void *q, const void *k, const void *v, void *out, bool f32, int64_t z, int64_t h,
                      int64_t n, int64_t d, int64_t sz, int64_t sh, int64_t sn, int64_t soz, int64_t soh,
-                     int64_t son, double sm_scale);
+                     int64_t son, double sm_scale, bool causal);
 
 // dispatch.cpp
 int gemm_dispatch(const GemmArgs &g);  // picks a variant (option / cache / heuristic) and launches

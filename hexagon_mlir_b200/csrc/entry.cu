@@ -557,7 +557,8 @@ static void attention_impl(bool f32, int64_t rq, B200MemRef4D *q, int64_t rk, B2
   if (st.in(Q.p, Q.span(esz), &dq) || st.in(K.p, K.span(esz), &dk) || st.in(V.p, V.span(esz), &dv) ||
       st.out(O.p, O.span(esz), &dout, O.span(esz) != (size_t)(O.z * O.h * O.n * O.d) * esz))
     return;
-  if (launch_attention(dq, dk, dv, dout, f32, Q.z, Q.h, Q.n, Q.d, Q.sz, Q.sh, Q.sn, O.sz, O.sh, O.sn, (double)sm_scale))
+  if (launch_attention(dq, dk, dv, dout, f32, Q.z, Q.h, Q.n, Q.d, Q.sz, Q.sh, Q.sn, O.sz, O.sh, O.sn, (double)sm_scale,
+                       ctx().opt.attention_stage == 3))
     return;
   st.finish();
 }

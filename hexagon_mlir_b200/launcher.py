@@ -170,6 +170,9 @@ class _AttentionKernel(Kernel):
             sm_scale = float(kw.pop("sm_scale"))
             pid1 = kw.pop("pid1", None)
             kw.pop("H", None)
+            # STAGE is a tl.constexpr of the reference kernel (1: every key, 3: causal); it is set on
+            # every launch, so that one causal call does not change the next
+            lib().b200mlir_set_option(b"attentionStage", float(kw.pop("STAGE", 1)))
             if pid1 is not None:
                 z, h = divmod(int(pid1), q.shape[1])
                 q, k, v, out = (t[z:z + 1, h:h + 1] for t in (q, k, v, out))
@@ -184,9 +187,10 @@ attention_fwd_kernel = _AttentionKernel(
 _ACCEPTED |= {"sm_scale", "enableVectorization", "stride_0", "stride_1", "stride_2", "stride_3"}
 
 
-def attention(q, k, v, out, sm_scale):
-    """out = softmax(q·kᵀ·sm_scale)·v for every (batch, head) of [Z, H, N_CTX, D_HEAD] tensors."""
-    attention_fwd_kernel[(1,)](Q=q, K=k, V=v, Out=out, sm_scale=sm_scale)
+def attention(q, k, v, out, sm_scale, causal=False):
+    """out = softmax(q·kᵀ·sm_scale)·v for every (batch, head) of [Z, H, N_CTX, D_HEAD] tensors;
+    causal: query i attends to keys 0..i."""
+    attention_fwd_kernel[(1,)](Q=q, K=k, V=v, Out=out, sm_scale=sm_scale, STAGE=3 if causal else 1)
     return out
 
 

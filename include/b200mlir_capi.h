@@ -98,7 +98,8 @@ B200_API int b200mlir_device_status(void);
  * test/python/triton/test_rms_norm.py:17,39), "gemmVariant" (-1 = dispatcher's
  * choice), "kloopBlockK", "attentionTiles" (query tiles per CTA of the
  * attention kernel: 0 = by size, 1 or 2), "attentionSplits" (CTAs that share the keys of one
- * query tile, merged by a second kernel: 0 = by size) and "w8a16ExpandRows".  Returns 0, or B200MLIR_ERR_BAD_ARG for an
+ * query tile, merged by a second kernel: 0 = by size), "attentionStage" (1 or 3, see the
+ * attention entry) and "w8a16ExpandRows".  Returns 0, or B200MLIR_ERR_BAD_ARG for an
  * unknown name. */
 B200_API int b200mlir_set_option(const char *name, double value);
 B200_API int b200mlir_get_option(const char *name, double *value);
@@ -232,7 +233,10 @@ B200_API void online_softmax(int64_t rank_x, B200MemRef2D *x, int64_t rank_y, B2
  * Both products take fp16 operands with fp32 accumulation (the float32 entry rounds Q, K, V to
  * fp16 first, as the engine's pack leaf does, :239-246); the running maximum, the row sums and
  * the output accumulator are fp32.  D_HEAD is 64 or 128, strides multiples of 8 elements, any
- * N_CTX (a short last key block is masked); non-causal, as the reference (STAGE = 1). */
+ * N_CTX (a short last key block is masked).  Option "attentionStage" is the kernel's STAGE
+ * constexpr (:183-185): 1, the default and the only form the reference's loop implements, lets
+ * every query see every key; 3 is causal (query i sees keys 0..i; key blocks past the diagonal
+ * are skipped). */
 B200_API void attention_fwd_kernel_float16(int64_t rank_q, B200MemRef4D *q, int64_t rank_k, B200MemRef4D *k,
                                            int64_t rank_v, B200MemRef4D *v, int64_t rank_o, B200MemRef4D *out,
                                            float sm_scale, B200_GRID_ARGS);

@@ -182,7 +182,7 @@ def mlp(x, gain, wg, wu, wd, eps: float, threads: int = 0):
 
 
 def attention(q, k, v, sm_scale: float, block_n: int = 64, engine_rounding: bool = False,
-              p_f32: bool = False, threads: int = 0):
+              p_f32: bool = False, causal: bool = False, threads: int = 0):
     """Attention block in the reference kernel's order; q, k, v are [..., N, D] (fp32 inputs
     are rounded to fp16 first, as the engine's pack leaf does); returns fp32 of q's shape."""
     q, k, v = (_c(np.asarray(t).astype(np.float16), np.float16) for t in (q, k, v))
@@ -193,7 +193,7 @@ def attention(q, k, v, sm_scale: float, block_n: int = 64, engine_rounding: bool
     _f64 = ctypes.c_double
     lib().oracle_attention_f16(_ptr(q), _ptr(k), _ptr(v), _ptr(o), _i64(bh), _i64(n), _i64(d),
                                _f64(sm_scale), _int(block_n),
-                               _int((1 if engine_rounding else 0) | (2 if p_f32 else 0)),
+                               _int((1 if engine_rounding else 0) | (2 if p_f32 else 0) | (4 if causal else 0)),
                                _int(_nt(threads)))
     return o
 

@@ -319,12 +319,15 @@ void oracle_mlp_f16(const f16 *X, const f16 *Gain, const f16 *Wg, const f16 *Wu,
 //              engine's read-out tile is (include/hexagon/Dialect/Hmx/IR/HmxOps.td:308-316);
 // flags bit 1: p stays fp32 (what the kernel source computes when no operand is quantised;
 //              used to pin this function against the kernel run by Triton's interpreter).
+// flags bit 2: causal — query i sees keys 0..i only (STAGE = 3 of the kernel's signature,
+//              test_flash_attention.py:183-185; the reference's inner loop implements STAGE = 1 only,
+//              so this form has no reference output to pin against and is checked against torch).
 // Q, K, V: [BH, N, D] contiguous; O: [BH, N, D] fp32.
 void oracle_attention_f16(const f16 *Q, const f16 *K, const f16 *V, float *O, int64_t BH,
                           int64_t N, int64_t D, double sm_scale, int block_n, int flags,
                           int nthreads) {
   const float qk_scale = (float)(sm_scale * 1.44269504);
-  const bool round_out = flags & 1, p_f32 = flags & 2;
+  const bool round_out = flags & 1, p_f32 = flags & 2, causal = flags & 4;
   parallel_for(BH * N, nthreads, [&](int64_t lo, int64_t hi) {
     std::vector<float> qk(block_n), p(block_n), acc(D), pv(D), qf(D);
     for (int64_t row = lo; row < hi; ++row) {
@@ -334,8 +337,9 @@ void oracle_attention_f16(const f16 *Q, const f16 *K, const f16 *V, float *O, in
       for (int64_t d = 0; d < D; ++d) qf[d] = (float)q[d];
       float m = -99999999999999.0f, l = 1.0f;
       std::fill(acc.begin(), acc.end(), 0.0f);
-      for (int64_t n0 = 0; n0 < N; n0 += block_n) {
-        const int64_t nb = std::min<int64_t>(block_n, N - n0);
+      const int64_t last_key = causal ? row - bh * N : N - 1;
+      for (int64_t n0 = 0; n0 <= last_key; n0 += block_n) {
+        const int64_t nb = std::min<int64_t>(block_n, last_key + 1 - n0);
         float mx = -INFINITY;
         for (int64_t j = 0; j < nb; ++j) {
           const f16 *kr = Kb + (n0 + j) * D;

@@ -158,6 +158,30 @@ def test_keys_split_over_ctas(hm, oracle, cuda, shape, splits):
     assert hm.device_status() == 0
 
 
+@pytest.mark.parametrize("shape", [(2, 3, 200, 64), (1, 2, 1000, 128), (1, 1, 64, 64), (1, 4, 2048, 64)])
+def test_causal(hm, oracle, cuda, shape):
+    """STAGE = 3 of the reference kernel's signature: query i sees keys 0..i.  The reference's loop does
+    not implement it, so the oracle's causal form is itself checked against torch here."""
+    rng = philox(35)
+    q, k, v = (rng.normal(0, 1, shape).astype(np.float16) for _ in range(3))
+    scale = 1.0 / np.sqrt(shape[-1])
+    want = oracle.attention(q, k, v, scale, block_n=64, causal=True)
+    qt, kt, vt = (cuda.from_numpy(t).cuda() for t in (q, k, v))
+    ref = cuda.nn.functional.scaled_dot_product_attention(qt.float(), kt.float(), vt.float(), scale=scale, is_causal=True)
+    assert _rel(want, ref.cpu().numpy()) < 3e-4
+    out = cuda.zeros_like(qt)
+    hm.attention(qt, kt, vt, out, scale, causal=True)
+    assert _rel(out.cpu().numpy(), want) < 8e-4
+    out32 = np.zeros(shape, np.float32)
+    hm.attention_fwd_kernel[(1,)](Q=q.astype(np.float32), K=k.astype(np.float32), V=v.astype(np.float32), Out=out32,
+                                  sm_scale=scale, STAGE=3)
+    assert _rel(out32, want) < TIGHT
+    # the stage is per launch: the next plain call sees every key again
+    hm.attention(qt, kt, vt, out, scale)
+    assert _rel(out.cpu().numpy(), oracle.attention(q, k, v, scale, block_n=64)) < 8e-4
+    assert hm.device_status() == 0
+
+
 def test_online_softmax_as_the_reference_launches_it(hm, oracle, cuda):
     """test_online_softmax.py:80-110: 128 x 128 fp32, 1 and 4 programs, atol 1e-5 against torch."""
     x = GOLD["online_x"]

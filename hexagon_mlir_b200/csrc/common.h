@@ -205,6 +205,8 @@ int launch_gemm_tc(int v, const GemmArgs &g);
 int launch_gemm_i8_tc(const int8_t *a, const int8_t *bt, int32_t *c, int64_t m, int64_t n, int64_t k, int64_t lda,
                       int64_t ldbt, int64_t ldc);
 // gemm_tcgen05_2cta.cu
+int launch_gemm_i8_tc_pair(const int8_t *a, const int8_t *bt, int32_t *c, int64_t m, int64_t n, int64_t k, int64_t lda,
+                           int64_t ldbt, int64_t ldc);
 int launch_gemm_tc_pair(const GemmArgs &g, bool deep_k);
 int pair_variant_smem_bytes();
 

@@ -374,6 +374,10 @@ int launch_gemm_i8_tc(const int8_t *a, const int8_t *bt, int32_t *c, int64_t m, 
                       int64_t ldbt, int64_t ldc) {
   B200_TRY(ensure_ready());
   constexpr int BN_MMA = 128, STAGES = 6;
+  // enough 256 x 256 tiles for the SM pairs: the two-CTA form (option gemmVariant = 1 keeps this one)
+  if (m >= 512 && n >= 512 && (m / 256) * (n / 256) >= 32 && ctx().opt.gemm_variant != 1 && al16(a) && al16(bt) &&
+      al16(c) && lda % 16 == 0 && ldbt % 16 == 0 && ldc % 4 == 0 && n % 4 == 0)
+    return launch_gemm_i8_tc_pair(a, bt, c, m, n, k, lda, ldbt, ldc);
   if (!al16(a) || !al16(bt) || !al16(c) || lda % 16 || ldbt % 16 || ldc % 4 || n % 4 || m < 1 || n < 1 || k < 1)
     return set_error(B200MLIR_ERR_UNSUPPORTED, "int8 tensor-core gemm: alignment (rows 16-byte aligned, N a multiple of 4)");
   Context &c_ = ctx();

@@ -85,6 +85,15 @@ __device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_desc, u
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void mma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on the barrier at this offset in BOTH CTAs of the pair once the MMAs issued so far are done.
 __device__ __forceinline__ void mma_commit_pair(uint32_t bar) {
   const uint16_t mask = 3;
@@ -111,8 +120,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   constexpr int BN_MMA = 256;
   constexpr int BN_OUT = (EPI == EPI_SWIGLU) ? 128 : 256;
   constexpr int TMEM_COLS = 512;  // two accumulator stages of 256 columns
-  constexpr uint32_t IDESC = make_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, /*A K-major*/ 0,
-                                        /*B MN-major*/ 1, 256, BN_MMA);
+  // int8 form (EPI_I32): both operands K-major (B arrives transposed, this CTA loads its 128 rows
+  // of it), 128 int8 per swizzle row and K = 32 per instruction: the fp16 form's bytes per stage
+  constexpr bool I8 = EPI == EPI_I32;
+  constexpr uint32_t IDESC = I8 ? make_idesc(/*D=s32*/ 2, /*A=s8*/ 1, /*B=s8*/ 1, 0, /*B K-major*/ 0, 256, BN_MMA)
+                                : make_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, /*A K-major*/ 0,
+                                             /*B MN-major*/ 1, 256, BN_MMA);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   constexpr int STAGE_BYTES = NSUB * STAGE2_BYTES;
@@ -187,9 +200,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           for (int sub = 0; sub < NSUB; ++sub) {
             const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * STAGE2_BYTES;
             const uint32_t sb = sa + A2_BYTES;
-            const int k0 = kb * BKS + sub * BK2;
+            const int k0 = (kb * NSUB + sub) * (I8 ? 128 : BK2);  // in elements
             tma_load_2d_pair(sa, &tmA, full, k0, m0);
-            if (EPI == EPI_SWIGLU) {
+            if (I8) {
+              tma_load_2d_pair(sb, &tmB, full, k0, n0 + (int)rank * 128);  // 128 rows of Bᵀ x 128 bytes
+            } else if (EPI == EPI_SWIGLU) {
               const CUtensorMap *mb = leader ? &tmB : &tmB2;  // gate half / up half
               tma_load_2d_pair(sb, mb, full, n0, k0);
               tma_load_2d_pair(sb + SLAB_BYTES, mb, full, n0 + 64, k0);
@@ -232,11 +247,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * STAGE2_BYTES;
             const uint32_t sb = sa + A2_BYTES;
             const uint64_t adesc = smem_desc_sw128(sa, 16, 1024);
-            const uint64_t bdesc = smem_desc_sw128(sb, SLAB_BYTES, 1024);
+            const uint64_t bdesc = I8 ? smem_desc_sw128(sb, 16, 1024) : smem_desc_sw128(sb, SLAB_BYTES, 1024);
 #pragma unroll
-            for (int k = 0; k < BK2 / 16; ++k)
-              mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), IDESC,
-                           (kb | sub | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < BK2 / 16; ++k) {
+              if (I8)
+                mma_i8_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC,
+                            (kb | sub | k) != 0 ? 1u : 0u);
+              else
+                mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), IDESC,
+                             (kb | sub | k) != 0 ? 1u : 0u);
+            }
           }
           mma_commit_pair(bar_empty + 8 * stage);  // both producers may refill the stage
           if (++stage == STAGES) {
@@ -383,6 +403,53 @@ int launch_pair_epi(const GemmArgs &g, const char *name) {
     case EPI_SWIGLU: return launch_pair<STAGES, NSUB, EPI_SWIGLU>(g, name);
     default: return set_error(B200MLIR_ERR_UNSUPPORTED, "2-CTA gemm: epilogue %d not built", g.epilogue);
   }
+}
+
+// int8 x int8 -> int32 over SM pairs; bt is B transposed, [N,K] row-major
+int launch_gemm_i8_tc_pair(const int8_t *a, const int8_t *bt, int32_t *c, int64_t m, int64_t n, int64_t k, int64_t lda,
+                           int64_t ldbt, int64_t ldc) {
+  B200_TRY(ensure_ready());
+  constexpr int STAGES = 6, NSUB = 1;
+  Context &cx = ctx();
+  CUtensorMap tmA, tmB;
+  B200_TRY(make_map_2d(&tmA, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k, m, lda, 128, BM2));
+  B200_TRY(make_map_2d(&tmB, bt, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, k, n, ldbt, 128, 128));
+  TcParams p;
+  p.c = c;
+  p.res = nullptr;
+  p.ldc = ldc;
+  p.ldres = 0;
+  p.m = (int)m;
+  p.n = (int)n;
+  p.k = (int)k;
+  p.m_blocks = (int)((m + 255) / 256);
+  p.n_blocks = (int)((n + 255) / 256);
+  p.num_tiles = p.m_blocks * p.n_blocks;
+  p.k_blocks = (int)((k + 127) / 128);
+  p.group_m = GROUP_M;
+  p.seg_kb = 1;
+  GemmArgs none;
+  set_push_params(p, none);
+  p.status = cx.d_status;
+  auto kern = gemm_tc2_kernel<STAGES, NSUB, EPI_I32>;
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2));
+    cudaLaunchConfig_t q = {};
+    q.gridDim = dim3(2 * (cx.sm_count / 2));
+    q.blockDim = dim3(THREADS2);
+    q.dynamicSmemBytes = kSmem2;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &q) != cudaSuccess || clusters < 1) {
+      cudaGetLastError();
+      clusters = cx.sm_count / 2 - 4;
+    }
+    max_pairs = clusters < cx.sm_count / 2 ? clusters : cx.sm_count / 2;
+  }
+  const int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
+  B200_CUDA(launch_maybe_dependent(false, kern, dim3((unsigned)(2 * pairs)), dim3(THREADS2), (size_t)kSmem2, cx.stream,
+                                   tmA, tmB, tmB, p));
+  return check_launch("gemm_tc2_i8_256x256");
 }
 
 // deep_k: 128-deep stages (three of them) instead of six 64-deep ones

@@ -143,7 +143,7 @@ B200_API void matmul_f32out(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B20
                             B200MemRef2D *res32, B200_GRID_ARGS);
 /* int8 x int8 -> int32, exact (the reference routes integer matmuls to exact
  * vector loops: include/hexagon/Dialect/Hmx/Transforms/HmxTarget.h:198-200).  Runs on the tensor
- * cores (tcgen05 kind::i8, B transposed once into the workspace) when M, N, K >= 64, N is a
+ * cores (tcgen05 kind::i8, over SM pairs for large problems; B transposed once into the workspace) when M, N, K >= 64, N is a
  * multiple of 4 and the rows of A and C are 16-byte multiples; otherwise on CUDA cores.  Both are
  * bit-exact. */
 B200_API void matmul_i8(int64_t rank_a, B200MemRef2D *a, int64_t rank_b, B200MemRef2D *b,

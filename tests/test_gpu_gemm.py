@@ -157,7 +157,7 @@ def test_int8_accumulation_bit_exact(hm, oracle, mnk):
 
 
 @pytest.mark.parametrize("m,n,k", [(256, 512, 384), (128, 128, 4096), (1000, 1028, 2064), (64, 64, 64),
-                                   (300, 132, 208), (2048, 2048, 2048)])
+                                   (300, 132, 208), (2048, 2048, 2048), (2100, 2052, 1040)])
 def test_matmul_i8_on_tensor_cores_is_exact(hm, oracle, cuda, m, n, k):
     """int8 x int8 -> int32 through tcgen05 kind::i8 (B transposed on the way): the exact sums,
     equal to the CUDA-core loop and to the oracle, full range operands (-128 included)."""

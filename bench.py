@@ -262,6 +262,16 @@ def extras_single_gpu(torch, hm, peaks, only=None):
             tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
             out[f"gemm_f16_kloop64_{n}^3"] = {"us": ms * 1e3, "tflops": tf,
                                               "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"]}
+
+            # the same form with the reference test's own segment (test_matmul_kloop.py: BLOCK_K = 256)
+            def fk256():
+                i = state["i"] % sets
+                state["i"] += 1
+                hm.klooped_matmul[(1,)](A[i], B[i], C[i], BLOCK_K=256)
+            ms = timed(torch, fk256, 20, 3)
+            tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
+            out[f"gemm_f16_kloop256_{n}^3"] = {"us": ms * 1e3, "tflops": tf,
+                                               "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"]}
         del A, B, C
     if want("softmax"):
         # C2 softmax [4096,1024]: 16 MiB in + out per launch; 12 buffer pairs (201 MB) rotate past L2

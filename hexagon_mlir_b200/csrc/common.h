@@ -38,6 +38,7 @@ struct Options {
   double enable_weight_resident = 1;
   double gemm_variant = -1;        // -1: dispatcher chooses
   double kloop_block_k = 64;
+  double kloop_pairs = 1;          // K-looped matmul on the two-CTA kernel (eight read-out warps per CTA); 0 keeps it on the one-CTA kernel
   double w8a16_variant = -1;
   double gemm_group_m = 0;         // 0: the kernels' default band height
   double gemm_dependent_launch = 1;   // programmatic dependent launch of the tcgen05 GEMM kernels

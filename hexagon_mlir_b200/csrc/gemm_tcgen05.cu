@@ -447,7 +447,10 @@ const char *tc_variant_verdict(int v, const GemmArgs &g) {
   if (g.epilogue == EPI_SWIGLU && vi.bn < 128) return "epilogue-unsupported";
   // K-looped accumulation: segments of whole k-blocks, on the variant whose read-out warps
   // can hold a row of running sums (anything else stays on the CUDA-core path)
-  if (g.epilogue == EPI_KLOOP_F16 && (vi.cta_group != 1 || vi.bn != 128 || g.block_k < BK || g.block_k % BK))
+  // (the one-CTA 128x128 variant, and the two-CTA variant with 64-deep stages, whose eight read-out warps take 128 columns each)
+  if (g.epilogue == EPI_KLOOP_F16 &&
+      (!((vi.cta_group == 1 && vi.bn == 128) || (vi.cta_group == 2 && vi.bk == 64 && ctx().opt.kloop_pairs != 0)) ||
+       g.block_k < BK || g.block_k % BK))
     return "epilogue-unsupported";
   if (g.m > 0x7fffffff || g.n > 0x7fffffff || g.k > 0x7fffffff) return "extent-range";
   if (((g.m + BM - 1) / BM) * ((g.n + 31) / 32) > 0x3fffffff) return "extent-range";

@@ -113,8 +113,13 @@ __device__ long long g2_trace_buf[2 * 6 * 64];
 // EPI_SWIGLU: the pair's MMA N = 256 is [gate 128 | up 128]; CTA 0 loads the Wg tile,
 // CTA 1 the Wu tile, and each CTA's accumulator rows hold both halves.
 // NSUB: 64-deep K sub-tiles per stage (one barrier round trip and one commit per stage).
+// K-looped form (EPI_KLOOP_F16): one accumulator stage per K segment of p.seg_kb stages, started
+// with accumulate off; eight read-out warps per CTA (two per TMEM lane quadrant, 128 columns each)
+// round every segment to fp16 and keep the row's fp32 running sums in registers
+// (test/python/triton/test_matmul_kloop.py:87-98).
+constexpr int pair_threads(int epi) { return epi == EPI_KLOOP_F16 ? 320 : THREADS2; }
 template <int STAGES, int NSUB, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS2, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(EPI), 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmB2, const TcParams p) {
   constexpr int BN_MMA = 256;
@@ -159,7 +164,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, 8);  // four epilogue warps in each CTA
+      mbar_init(bar_tempty + 8 * s, EPI == EPI_KLOOP_F16 ? 16 : 8);  // the read-out warps of both CTAs
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -230,6 +235,58 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint32_t acc_phase = 0;
       bool ok = true;
       int tord = 0;
+      if constexpr (EPI == EPI_KLOOP_F16) {
+      for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++tord) {
+        TR2(0, tord);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          const bool seg_start = EPI == EPI_KLOOP_F16 ? (kb % p.seg_kb) == 0 : kb == 0;
+          if (seg_start) {
+            if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 32, tile)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+            TR2(1, tord);
+          }
+          const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN_MMA);
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 33, tile)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+#pragma unroll
+          for (int sub = 0; sub < NSUB; ++sub) {
+            const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * STAGE2_BYTES;
+            const uint32_t sb = sa + A2_BYTES;
+            const uint64_t adesc = smem_desc_sw128(sa, 16, 1024);
+            const uint64_t bdesc = I8 ? smem_desc_sw128(sb, 16, 1024) : smem_desc_sw128(sb, SLAB_BYTES, 1024);
+#pragma unroll
+            for (int k = 0; k < BK2 / 16; ++k) {
+              const uint32_t accum = (seg_start && sub == 0 && k == 0) ? 0u : 1u;
+              if (I8)
+                mma_i8_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, accum);
+              else
+                mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), IDESC, accum);
+            }
+          }
+          mma_commit_pair(bar_empty + 8 * stage);  // both producers may refill the stage
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+          const bool seg_end = EPI == EPI_KLOOP_F16 ? ((kb + 1) % p.seg_kb == 0 || kb + 1 == p.k_blocks)
+                                                    : kb + 1 == p.k_blocks;
+          if (seg_end) {
+            mma_commit_pair(bar_tfull + 8 * acc);  // accumulators complete in both CTAs
+            if (++acc == 2) {
+              acc = 0;
+              acc_phase ^= 1u;
+            }
+          }
+        }
+        TR2(2, tord);
+      }
+      } else {
       for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++tord) {
         TR2(0, tord);
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 32, tile)) break;
@@ -272,9 +329,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           acc_phase ^= 1u;
         }
       }
+      }
     }
   } else {
-    // ---------------- epilogue (warps 2..5): this CTA's 128 rows ----------------
+    // ---------------- epilogue (warps 2..5, K-looped form 2..9): this CTA's 128 rows ----------------
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -283,6 +341,48 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       int m_blk, n_blk;
       tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, m_blk, n_blk);
       const int m0 = m_blk * 256 + (int)rank * BM2, n0 = n_blk * BN_OUT;
+      if constexpr (EPI == EPI_KLOOP_F16) {
+        // this warp's half of the 256 columns: fp32 running sums of its row, every segment rounded to fp16 first
+        const int half = (warp - 2) >> 2;
+        const int row = m0 + q * 32 + lane;
+        float sum[128];
+#pragma unroll
+        for (int e = 0; e < 128; ++e) sum[e] = 0.0f;
+        const int segs = (p.k_blocks + p.seg_kb - 1) / p.seg_kb;
+        bool ok = true;
+        for (int sg = 0; sg < segs; ++sg) {
+          ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 34, tile);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA + half * 128);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sum[c * 32 + e] += __half2float(__float2half_rn(__uint_as_float(r[e])));
+          }
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) remote_arrive(map_to_cta(bar_tempty + 8 * acc, 0));  // the leader's barrier
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(sum[c * 32 + e]);
+          const int col0 = n0 + half * 128 + c * 32;
+          if (row < p.m && col0 < p.n) epilogue_store_chunk<EPI_F16>(r, r, row, col0, p);
+        }
+        continue;
+      }
       bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 34, tile);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -357,7 +457,7 @@ int launch_pair(const GemmArgs &g, const char *name) {
   p.num_tiles = p.m_blocks * p.n_blocks;
   p.k_blocks = (int)((g.k + NSUB * BK2 - 1) / (NSUB * BK2));
   p.group_m = ctx().opt.gemm_group_m >= 1 ? (int)ctx().opt.gemm_group_m : GROUP_M;
-  p.seg_kb = 1;
+  p.seg_kb = (EPI == EPI_KLOOP_F16 && g.block_k >= NSUB * BK2) ? g.block_k / (NSUB * BK2) : 1;
   set_push_params(p, g);
   p.status = c.d_status;
   auto kern = gemm_tc2_kernel<STAGES, NSUB, EPI>;
@@ -366,7 +466,7 @@ int launch_pair(const GemmArgs &g, const char *name) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2));
     cudaLaunchConfig_t q = {};
     q.gridDim = dim3(2 * (c.sm_count / 2));
-    q.blockDim = dim3(THREADS2);
+    q.blockDim = dim3(pair_threads(EPI));
     q.dynamicSmemBytes = kSmem2;
     int clusters = 0;
     // SMs pair up inside a GPC only: ask how many pairs can be resident at once
@@ -378,7 +478,7 @@ int launch_pair(const GemmArgs &g, const char *name) {
     if (getenv("B200MLIR_DEBUG")) fprintf(stderr, "[b200mlir] 2-CTA gemm: %d resident pairs (occupancy query %d)\n", max_pairs, clusters);
   }
   int pairs = p.num_tiles < max_pairs ? p.num_tiles : max_pairs;
-  B200_CUDA(launch_maybe_dependent(c.opt.gemm_dependent_launch != 0, kern, dim3((unsigned)(2 * pairs)), dim3(THREADS2),
+  B200_CUDA(launch_maybe_dependent(c.opt.gemm_dependent_launch != 0, kern, dim3((unsigned)(2 * pairs)), dim3(pair_threads(EPI)),
                                    (size_t)kSmem2, c.stream, tmA, tmB, tmB2, p));
   return check_launch(name);
 }
@@ -401,6 +501,9 @@ int launch_pair_epi(const GemmArgs &g, const char *name) {
     case EPI_F16_RES16: return launch_pair<STAGES, NSUB, EPI_F16_RES16>(g, name);
     case EPI_PUSH16: return launch_pair<STAGES, NSUB, EPI_PUSH16>(g, name);
     case EPI_SWIGLU: return launch_pair<STAGES, NSUB, EPI_SWIGLU>(g, name);
+    case EPI_KLOOP_F16:
+      if constexpr (NSUB == 1) return launch_pair<STAGES, NSUB, EPI_KLOOP_F16>(g, name);
+      return set_error(B200MLIR_ERR_UNSUPPORTED, "k-looped read-out is built for 64-deep stages");
     default: return set_error(B200MLIR_ERR_UNSUPPORTED, "2-CTA gemm: epilogue %d not built", g.epilogue);
   }
 }

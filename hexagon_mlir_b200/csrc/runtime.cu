@@ -248,6 +248,7 @@ static double *option_slot(const char *name) {
   if (!strcmp(name, "enableWeightResident")) return &o.enable_weight_resident;
   if (!strcmp(name, "gemmVariant")) return &o.gemm_variant;
   if (!strcmp(name, "kloopBlockK")) return &o.kloop_block_k;
+  if (!strcmp(name, "kloopPairs")) return &o.kloop_pairs;
   if (!strcmp(name, "w8a16Variant")) return &o.w8a16_variant;
   if (!strcmp(name, "enablePDL")) return &o.enable_pdl;
   if (!strcmp(name, "gemmGroupM")) return &o.gemm_group_m;

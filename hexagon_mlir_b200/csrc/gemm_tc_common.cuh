@@ -43,6 +43,17 @@ __device__ __forceinline__ __half silu_h(__half x) {
   return __float2half_rn(__fdividef(__half2float(x), __half2float(d)));
 }
 
+// {d0, d1} += {f32(f16(a0)), f32(f16(a1))}: one packed rounding, two widenings, one packed add
+// (the K-looped read-out: every segment is rounded to fp16 before it joins the fp32 running sum)
+__device__ __forceinline__ void add_rounded2(float &d0, float &d1, float a0, float a1) {
+  const float2 f = __half22float2(__floats2half2_rn(a0, a1));
+  asm("{\n\t.reg .b64 ra, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\tmov.b64 rd, {%0, %1};\n\t"
+      "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "+f"(d0), "+f"(d1)
+      : "f"(f.x), "f"(f.y));
+}
+
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t *>(&h);

@@ -362,7 +362,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tmem_ld_32x32(t_row + c * 32, r);
             tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) sum[c * 32 + e] += __half2float(__float2half_rn(__uint_as_float(r[e])));
+            for (int e = 0; e < 32; e += 2)
+              add_rounded2(sum[c * 32 + e], sum[c * 32 + e + 1], __uint_as_float(r[e]), __uint_as_float(r[e + 1]));
           }
           tc_fence_before_sync();
           __syncwarp();

@@ -225,7 +225,8 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         return (torch.rand(shape, generator=g, device=dev) * (hi - lo) + lo).half()
 
     for n in (512, 1024, 2048, 4096, 8192):  # the square sweep of the large-GEMM config
-        if not want(f"gemm_f16_{n}"):
+        kloop_only = only is not None and only.startswith("kloop")  # profiling captures of the K-looped form alone
+        if not want(f"gemm_f16_{n}") and not (kloop_only and n == 4096):
             continue
         # rotate over enough operand sets to exceed L2 between launches
         sets = max(2, int(np.ceil(3 * 126e6 / (3 * n * n * 2))))
@@ -240,10 +241,11 @@ def extras_single_gpu(torch, hm, peaks, only=None):
             state["i"] += 1
             hm.matmul[(1,)](A[i], B[i], C[i])
         # (launches of a few microseconds are replayed from a CUDA graph: issued from Python they are host-bound)
-        ms = graph_timed(torch, fn, reps=5, inner=sets * 2) if n <= 2048 else timed(torch, fn, 40 if n <= 4096 else 10, 5)
-        tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
-        out[f"gemm_f16_{n}^3"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
-                                  "variant": hm.gemm_explain(n, n, n)["name"]}
+        if not kloop_only:
+            ms = graph_timed(torch, fn, reps=5, inner=sets * 2) if n <= 2048 else timed(torch, fn, 40 if n <= 4096 else 10, 5)
+            tf = 2.0 * n ** 3 / (ms * 1e-3) / 1e12
+            out[f"gemm_f16_{n}^3"] = {"us": ms * 1e3, "tflops": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+                                      "variant": hm.gemm_explain(n, n, n)["name"]}
         if only is None:
             # what the on-device search (enumerate, verify, measure, gate, canary) picks for the shape
             hm.autotune_cache_clear()
@@ -615,7 +617,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--case", default="", help="run one case of `extra` only (profiling captures): gemm_f16_1024, "
-                                               "gemm_f16_4096, gemm_f16_8192, softmax, rmsnorm, swiglu, w8a16, attention_f16_4x16x4096x64, ...")
+                                               "gemm_f16_4096, gemm_f16_8192, kloop, gemm_i8, softmax, rmsnorm, swiglu, w8a16, attention_f16_4x16x4096x64, ...")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup

@@ -146,8 +146,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // Whole-K form: one accumulator per tile.  K-looped form: one per K segment of
         // p.seg_kb k-blocks, started with accumulate off — the read-out warps round each to
         // fp16 and keep the running sum themselves (test_matmul_kloop.py:87-98).
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          const bool seg_start = EPI == EPI_KLOOP_F16 ? (kb % p.seg_kb) == 0 : kb == 0;
+        // (position inside the K segment by counting: a division costs the lone issuing thread ~300 clocks)
+        for (int kb = 0, in_seg = 0; kb < p.k_blocks; ++kb) {
+          const bool seg_start = EPI == EPI_KLOOP_F16 ? in_seg == 0 : kb == 0;
           if (seg_start) {
             if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 2, tile)) {
               ok = false;
@@ -181,7 +182,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             stage = 0;
             phase ^= 1u;
           }
-          const bool seg_end = EPI == EPI_KLOOP_F16 ? ((kb + 1) % p.seg_kb == 0 || kb + 1 == p.k_blocks)
+          if (++in_seg == p.seg_kb) in_seg = 0;
+          const bool seg_end = EPI == EPI_KLOOP_F16 ? (in_seg == 0 || kb + 1 == p.k_blocks)
                                                     : kb + 1 == p.k_blocks;
           if (seg_end) {
             mma_commit(bar_tfull + 8 * acc);  // accumulator complete

@@ -238,8 +238,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       if constexpr (EPI == EPI_KLOOP_F16) {
       for (int tile = pair; ok && tile < p.num_tiles; tile += num_pairs, ++tord) {
         TR2(0, tord);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          const bool seg_start = EPI == EPI_KLOOP_F16 ? (kb % p.seg_kb) == 0 : kb == 0;
+        // (position inside the K segment by counting: a division costs the lone issuing thread ~300 clocks)
+        for (int kb = 0, in_seg = 0; kb < p.k_blocks; ++kb) {
+          const bool seg_start = EPI == EPI_KLOOP_F16 ? in_seg == 0 : kb == 0;
           if (seg_start) {
             if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1u, abort_flag, p.status, 32, tile)) {
               ok = false;
@@ -274,7 +275,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             stage = 0;
             phase ^= 1u;
           }
-          const bool seg_end = EPI == EPI_KLOOP_F16 ? ((kb + 1) % p.seg_kb == 0 || kb + 1 == p.k_blocks)
+          if (++in_seg == p.seg_kb) in_seg = 0;
+          const bool seg_end = EPI == EPI_KLOOP_F16 ? (in_seg == 0 || kb + 1 == p.k_blocks)
                                                     : kb + 1 == p.k_blocks;
           if (seg_end) {
             mma_commit_pair(bar_tfull + 8 * acc);  // accumulators complete in both CTAs

@@ -99,8 +99,9 @@ B200_API int b200mlir_device_status(void);
  * choice), "kloopBlockK", "attentionTiles" (query tiles per CTA of the
  * attention kernel: 0 = by size, 1 or 2), "attentionSplits" (CTAs that share the keys of one
  * query tile, merged by a second kernel: 0 = by size), "attentionStage" (1 or 3, see the
- * attention entry) and "w8a16ExpandRows".  Returns 0, or B200MLIR_ERR_BAD_ARG for an
- * unknown name. */
+ * attention entry), "w8a16ExpandRows" and "kloopPairs" (1: the K-looped matmul may take the
+ * two-CTA kernel, the default; 0: one-CTA kernel only).  Returns 0, or B200MLIR_ERR_BAD_ARG for
+ * an unknown name. */
 B200_API int b200mlir_set_option(const char *name, double value);
 B200_API int b200mlir_get_option(const char *name, double *value);
 

@@ -46,3 +46,20 @@ def test_online_softmax_oracle_matches_reference_kernel():
         got = oracle.online_softmax(x, x.shape[1] // threads)
         assert np.abs(got - GOLD[f"online_y_threads{threads}"]).max() < 1e-7
     assert np.abs(oracle.online_softmax(x, 32) - oracle.softmax(x)).max() < float(GOLD["online_atol"])
+
+
+def test_attention_oracle_causal_form():
+    """STAGE = 3 of the kernel's signature has no reference output (its loop implements STAGE = 1 only):
+    the oracle's causal form is checked against a float64 masked softmax."""
+    rng = np.random.default_rng(6)
+    q, k, v = (rng.normal(0, 1, (2, 2, 150, 64)).astype(np.float16) for _ in range(3))
+    got = oracle.attention(q, k, v, 0.125, block_n=64, causal=True)
+    s = np.einsum("bhnd,bhmd->bhnm", q.astype(np.float64), k.astype(np.float64)) * 0.125
+    s = np.where(np.tril(np.ones((150, 150), bool)), s, -np.inf)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    want = np.einsum("bhnm,bhmd->bhnd", p / p.sum(-1, keepdims=True), v.astype(np.float64))
+    assert _rel(got, want) < 2e-4
+    # the first query sees only the first key: its output is v[0]
+    assert np.allclose(got[..., 0, :], v[..., 0, :].astype(np.float32), atol=1e-6)
+    # block size does not matter beyond rounding
+    assert _rel(oracle.attention(q, k, v, 0.125, block_n=32, causal=True), got) < 1e-4

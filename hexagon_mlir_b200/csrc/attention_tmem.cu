@@ -18,6 +18,9 @@
 //   warp 6·TILES         lane 0 loads Q once and the K and V blocks into two rings with TMA.
 // TMEM per tile (256 columns): S0, S1 [128 x 64] fp32; head size 64: P0, P1 (32 columns each) and
 // O [128 x 64] fp32; head size 128: O [128 x 128] fp32 and P(i) written over the read half of S(i).
+// Short problems share a tile's key blocks among several CTAs (partial O, m, l per row; merged by
+// attention_combine_kernel); the causal form skips the blocks past a tile's diagonal and masks
+// the two blocks on it.
 // Every wait is bounded; a wait that runs out sets the CTA's abort flag and the device status.
 #include <cuda.h>
 #include <cuda_fp16.h>

@@ -120,6 +120,8 @@ struct StreamParams {
   __half *c;
   int64_t ldc;
   int m, n, ksteps;
+  int chan_q, chan_r;  // n = grid * chan_q + chan_r: CTA b owns chan_q channels, one more if b < chan_r
+  int rot_mul;         // (ksteps << 16) / grid: CTA b starts at k step (b * rot_mul) >> 16
   int *status;
 };
 
@@ -172,15 +174,17 @@ w8a16_tmem_kernel(const __grid_constant__ CUtensorMap tmA, const StreamParams p)
   pdl_trigger();
   // this CTA's channels, walked in passes of at most SLOT / 128
   constexpr int CH_MAX = SLOT / CH_BYTES;
-  const int c_begin = (int)((int64_t)p.n * blockIdx.x / gridDim.x);
-  const int c_end = (int)((int64_t)p.n * (blockIdx.x + 1) / gridDim.x);
+  // (no division here: the first weight copies wait for these, and a 64-bit division is a
+  // subroutine of several hundred clocks)
+  const int c_begin = (int)blockIdx.x * p.chan_q + min((int)blockIdx.x, p.chan_r);
+  const int c_end = c_begin + p.chan_q + ((int)blockIdx.x < p.chan_r ? 1 : 0);
   const int passes = (c_end - c_begin + CH_MAX - 1) / CH_MAX;
   const int ksteps = p.ksteps;
   const int nsteps = passes * ksteps;  // local steps: pass-major, then k
   // Owning all of K, a CTA is free to walk it in any order: each starts at its own k step, so
   // that at any moment the 148 CTAs read 148 different places of the image (all of them
   // asking for the same 1.4 MB row at once leaves most DRAM channels idle).
-  const int rot = (int)(((int64_t)blockIdx.x * ksteps) / gridDim.x);
+  const int rot = (int)(((unsigned)blockIdx.x * (unsigned)p.rot_mul) >> 16);
   // Position of a local step without divisions (a lone thread pays ~300 clocks for one): the
   // pass, the step inside the pass, and what they select.
   struct Cursor {
@@ -652,6 +656,9 @@ int launch_w8a16_tmem(const __half *a, const void *image, const __half *scales_d
   p.status = ctx().d_status;
   int grid = ctx().sm_count;
   if (grid > n) grid = (int)n;
+  p.chan_q = (int)(n / grid);
+  p.chan_r = (int)(n % grid);
+  p.rot_mul = (p.ksteps << 16) / grid;
   CUtensorMap tmA;
   B200_TRY(make_act_map(&tmA, a, m, k, lda, nm));
   // up to 80 channels per CTA take the deep ring of 10 KiB slots; wider ranges 16 KiB slots

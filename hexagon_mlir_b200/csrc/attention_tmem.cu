@@ -109,6 +109,7 @@ struct AttParams {
   // unnormalised O (fp32) and its (m, l) per row, and attention_combine_kernel merges them.
   int splits, rows_pad;   // rows_pad: rows of a (batch, head) rounded up to whole CTAs
   int causal;             // query i sees keys 0..i only (one tile per CTA, no key splits)
+  int split_blk[17];      // key-block boundaries of the splits (splits <= 16), so that no CTA divides
   float *part_o;          // [z][h][split][rows_pad][D]
   float *part_ml;         // [z][h][split][rows_pad][2]
 };
@@ -184,15 +185,16 @@ __global__ void __launch_bounds__(att_threads(TILES), 1)
   static_assert(KST <= 4 && KST >= 2 && VST <= 4 && VST >= 2, "barrier table; K(i), K(i+1) are resident together");
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int split = (int)blockIdx.x % p.splits;
+  // (divisions are kept off this path: the first loads wait for these numbers)
+  const int mt = p.splits == 1 ? (int)blockIdx.x : (int)blockIdx.x / p.splits;
+  const int split = (int)blockIdx.x - mt * p.splits;
   // causal: the last tiles have the most key blocks, so they are handed out first
-  const int mt = (int)blockIdx.x / p.splits;
   const int m0 = (p.causal ? (int)gridDim.x / p.splits - 1 - mt : mt) * (TILES * ATT_BM);
   const int hh = blockIdx.y, zz = blockIdx.z;
   // causal: the tile's last row m0 + 127 sees keys up to itself, later blocks are skipped altogether
   const int nb_tile = p.causal ? min(p.n_blocks, (m0 + TILES * ATT_BM - 1) / ATT_BN + 1) : p.n_blocks;
-  const int blk0 = nb_tile * split / p.splits;                       // this CTA's key blocks: [blk0, blk0 + nb)
-  const int nb = nb_tile * (split + 1) / p.splits - blk0;
+  const int blk0 = p.splits == 1 ? 0 : p.split_blk[split];           // this CTA's key blocks: [blk0, blk0 + nb)
+  const int nb = (p.splits == 1 ? nb_tile : p.split_blk[split + 1]) - blk0;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -642,7 +644,9 @@ int launch_attention_variant(const void *q, const void *k, const void *v, void *
   if (ctx().opt.attention_splits >= 1) splits = (int)std::min<double>(ctx().opt.attention_splits, (double)p.n_blocks);
   p.causal = causal ? 1 : 0;
   if (causal) splits = 1;  // the tiles of a causal problem have different numbers of key blocks
+  if (splits > 16) splits = 16;
   p.splits = splits;
+  for (int i = 0; i <= 16; ++i) p.split_blk[i] = i <= splits ? (int)((int64_t)p.n_blocks * i / splits) : p.n_blocks;
   p.rows_pad = grid_m * TILES * ATT_BM;
   p.part_o = nullptr;
   p.part_ml = nullptr;

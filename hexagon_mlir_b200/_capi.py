@@ -35,6 +35,15 @@ class MemRef4D(ctypes.Structure):
                 ("sizes", c_i64 * 4), ("strides", c_i64 * 4)]
 
 
+class HmxReadoutBatch(ctypes.Structure):
+    """HmxReadoutBatch (bin/runtime/include/HmxVectorExecutor.h:103-110 of the reference), 64-bit pointers."""
+    _fields_ = [("rowStart", ctypes.c_uint32), ("rowCount", ctypes.c_uint32), ("validRows", ctypes.c_uint32),
+                ("nCroutons", ctypes.c_uint32), ("ar", c_void_p), ("dst", c_void_p)]
+
+
+HmxReadoutFn = ctypes.CFUNCTYPE(None, ctypes.POINTER(HmxReadoutBatch), ctypes.c_uint32)
+
+
 class B200Error(RuntimeError):
     def __init__(self, code: int, message: str):
         super().__init__(f"b200mlir error {code}: {message}")
@@ -102,6 +111,11 @@ _SIGNATURES = {
     "hexagon_runtime_resident_free_v2": (ctypes.c_int32, [c_void_p, ctypes.c_uint32]),
     "hexagon_runtime_hmx_ensure": (None, []),
     "hexagon_runtime_hmx_unlock": (None, []),
+    "hexagon_runtime_hmx_exec_configure": (ctypes.c_int32, [HmxReadoutFn, ctypes.c_int32]),
+    "hexagon_runtime_hmx_exec_publish": (ctypes.c_uint32, [ctypes.POINTER(HmxReadoutBatch), ctypes.c_uint32]),
+    "hexagon_runtime_hmx_exec_drain": (None, []),
+    "hexagon_runtime_hmx_exec_shutdown": (None, []),
+    "b200mlir_hmx_exec_batches_run": (ctypes.c_uint64, []),
     "hexagon_runtime_dma_start": (ctypes.c_uint32, [c_void_p, c_int, c_void_p, c_int,
                                                     ctypes.c_uint32, ctypes.c_bool, ctypes.c_bool,
                                                     ctypes.POINTER(c_int)]),

@@ -13,7 +13,8 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200mlir.so")
 
 SOURCES = ["runtime.cu", "row_kernels.cu", "layout.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu",
-           "w8a16.cu", "w8a16_tmem.cu", "attention_tmem.cu", "tuner.cu", "report.cu", "entry.cu"]
+           "w8a16.cu", "w8a16_tmem.cu", "attention_tmem.cu", "tuner.cu", "report.cu", "entry.cu",
+           "readout_executor.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -45,7 +46,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
 
     def compile_one(src: str) -> str:
         s = os.path.join(CSRC, src)
-        o = os.path.join(OBJ, src.replace(".cu", ".o"))
+        o = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
         if force or _stale(o, [s] + headers):
             cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", s, "-o", o]
             r = subprocess.run(cmd, capture_output=True, text=True)

@@ -50,6 +50,15 @@ struct Options {
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
 };
 
+// The stream kernels are enqueued on is a property of the calling thread: b200mlir_set_stream
+// binds one to the thread that calls it, a thread that never did uses the legacy default
+// stream.  (Seam 1 lets several host threads call the same kernel symbol at once; a single
+// process-wide stream would make them race on it.)
+struct StreamSlot {
+  operator cudaStream_t() const;
+  StreamSlot &operator=(cudaStream_t s);
+};
+
 struct Context {
   bool ready = false;
   int device = -1;
@@ -58,7 +67,7 @@ struct Context {
   size_t l2_bytes = 0;
   size_t persisting_l2_max = 0;
   std::string gpu_name;
-  cudaStream_t stream = nullptr;
+  StreamSlot stream;
   int *d_status = nullptr;  // device status word: 0 clean, else first failure
   Options opt;
 };
@@ -76,6 +85,13 @@ int workspace2(size_t bytes, void **out);
 // Device image of host tensors for the pipelined host-buffer GEMM, and its two copy streams.
 int staging_workspace(size_t bytes, void **out);
 int copy_streams(cudaStream_t *in, cudaStream_t *out);
+// Workspace of the split-K GEMM variant (tile counters, then fp32 partial tiles); zero-filled when (re)allocated.
+int splitk_workspace(size_t bytes, void **out);
+// L2 persistence window over a resident weight image: set (raises the device's set-aside size,
+// never lowers it), clear when that image goes away, and apply to the calling thread's stream.
+int l2_window_set(const void *base, size_t bytes);
+void l2_window_clear(const void *base);
+void l2_window_apply();
 
 // ---- programmatic dependent launch ---------------------------------------------------
 // A kernel launched this way may start while its predecessor in the stream drains: its

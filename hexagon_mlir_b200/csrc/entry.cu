@@ -278,9 +278,24 @@ int register_weight_locked(const void *wq, const void *scales, int64_t k, int64_
                            W8A16Weight **out) {
   auto it = g_weights.find(wq);
   if (it != g_weights.end()) {
-    if (it->second.k != k || it->second.n != n)
+    W8A16Weight &e = it->second;
+    if (e.k != k || e.n != n)
       return set_error(B200MLIR_ERR_BAD_ARG, "w8a16: weight at %p re-registered with a different shape", wq);
-    if (out) *out = &it->second;
+    if (e.scales != scales) {
+      // same weight bytes under other scales: the image (scale-free) stays, the device copy of the
+      // scales is refreshed and the expanded fp16 weight, which has the scales folded in, is dropped
+      cudaError_t ce = cudaMemcpyAsync(e.scales_dev, scales, (size_t)n * 2, cudaMemcpyDefault, ctx().stream);
+      if (ce == cudaSuccess) ce = cudaStreamSynchronize(ctx().stream);
+      if (ce != cudaSuccess) return set_error(B200MLIR_ERR_CUDA, "w8a16: scales copy failed: %s", cudaGetErrorString(ce));
+      if (e.w16) cudaFree(e.w16);
+      e.w16 = nullptr;
+      e.scales = scales;
+    }
+    if (l2_persist && !e.l2_persist) {
+      e.l2_persist = true;
+      l2_window_set(e.image, e.image_bytes);
+    }
+    if (out) *out = &e;
     return 0;
   }
   Context &c = ctx();
@@ -306,20 +321,9 @@ int register_weight_locked(const void *wq, const void *scales, int64_t k, int64_
     if (w.scales_dev) cudaFree(w.scales_dev);
     return rc;
   }
-  if (w.l2_persist && c.persisting_l2_max > 0) {
-    // Decode GEMMs re-read the same image every call: pin as much of it as the
-    // device allows in L2.  The setting lives in this process's context only.
-    size_t want = w.image_bytes < c.persisting_l2_max ? w.image_bytes : c.persisting_l2_max;
-    cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, want);
-    cudaStreamAttrValue attr = {};
-    attr.accessPolicyWindow.base_ptr = w.image;
-    attr.accessPolicyWindow.num_bytes = want;
-    attr.accessPolicyWindow.hitRatio = 1.0f;
-    attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
-    attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
-    if (cudaStreamSetAttribute(c.stream, cudaStreamAttributeAccessPolicyWindow, &attr) != cudaSuccess)
-      cudaGetLastError();  // a hint; not having it is not an error
-  }
+  // Decode GEMMs re-read the same image every call: pin as much of it as the device allows in
+  // L2.  The window follows the calling thread's stream (b200mlir_set_stream re-applies it).
+  if (w.l2_persist) l2_window_set(w.image, w.image_bytes);
   auto ins = g_weights.emplace(wq, w);
   if (out) *out = &ins.first->second;
   return 0;
@@ -593,6 +597,7 @@ int b200mlir_w8a16_unregister_weight(const void *wq) {
   auto it = g_weights.find(wq);
   if (it == g_weights.end()) return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 unregister: unknown weight");
   cudaStreamSynchronize(ctx().stream);
+  if (it->second.l2_persist) l2_window_clear(it->second.image);
   cudaFree(it->second.image);
   cudaFree(it->second.w16);
   cudaFree(it->second.scales_dev);

@@ -36,9 +36,91 @@ Context &ctx() {
 
 static std::mutex g_mu;
 
+// ---- the calling thread's stream, and the L2 persistence window it carries ------------------
+static thread_local cudaStream_t t_stream = nullptr;
+static thread_local uint64_t t_window_gen = 0;       // generation of the window last applied by this thread ...
+static thread_local cudaStream_t t_window_stream = nullptr;  // ... and the stream it was applied to
+StreamSlot::operator cudaStream_t() const { return t_stream; }
+StreamSlot &StreamSlot::operator=(cudaStream_t s) {
+  t_stream = s;
+  return *this;
+}
+
+// An access-policy window is an attribute of ONE stream, and the set-aside L2 size is a device
+// limit: the library keeps one window (the most recently registered persisting weight), raises
+// the limit and never lowers it, and re-applies the window whenever a thread's stream is not the
+// one that carries the current generation.
+struct L2Window {
+  const void *base = nullptr;
+  size_t bytes = 0;
+  size_t limit = 0;     // cudaLimitPersistingL2CacheSize as set by this library
+  uint64_t gen = 0;     // bumped by every change
+};
+static L2Window g_window;
+
+void l2_window_apply() {
+  const void *base;
+  size_t bytes;
+  uint64_t gen;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    base = g_window.base;
+    bytes = g_window.bytes;
+    gen = g_window.gen;
+  }
+  if (gen == 0 || (t_window_gen == gen && t_window_stream == t_stream)) return;
+  cudaStreamAttrValue attr = {};
+  attr.accessPolicyWindow.base_ptr = const_cast<void *>(base);
+  attr.accessPolicyWindow.num_bytes = base ? bytes : 0;  // zero bytes switches the window off
+  attr.accessPolicyWindow.hitRatio = 1.0f;
+  attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+  attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+  if (cudaStreamSetAttribute(t_stream, cudaStreamAttributeAccessPolicyWindow, &attr) != cudaSuccess)
+    cudaGetLastError();  // a hint; not having it is not an error
+  t_window_gen = gen;
+  t_window_stream = t_stream;
+}
+
+int l2_window_set(const void *base, size_t bytes) {
+  Context &c = ctx();
+  if (c.persisting_l2_max == 0) return 0;
+  size_t want = bytes < c.persisting_l2_max ? bytes : c.persisting_l2_max;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (want > g_window.limit) {
+      if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, want) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+      }
+      g_window.limit = want;
+    }
+    g_window.base = base;
+    g_window.bytes = want;
+    ++g_window.gen;
+  }
+  l2_window_apply();
+  return 0;
+}
+
+void l2_window_clear(const void *base) {
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_window.base != base) return;
+    g_window.base = nullptr;
+    g_window.bytes = 0;
+    ++g_window.gen;
+  }
+  l2_window_apply();
+}
+
 static int init_locked(int device) {
   Context &c = ctx();
   if (c.ready && c.device == device) return 0;
+  // The status word, the workspaces, the copy streams, registered weights and the kernels'
+  // cached attributes all belong to the first device: one device per process.
+  if (c.ready)
+    return set_error(B200MLIR_ERR_BAD_ARG, "already initialised on device %d; one device per process (asked for %d)",
+                     c.device, device);
   int count = 0;
   cudaError_t e = cudaGetDeviceCount(&count);
   if (e != cudaSuccess || count == 0)
@@ -95,7 +177,7 @@ struct Arena {
   void *p = nullptr;
   size_t cap = 0;
 };
-static Arena g_ws[3];
+static Arena g_ws[4];
 
 static int ws_get(int which, size_t bytes, void **out) {
   Arena &a = g_ws[which];
@@ -116,6 +198,14 @@ static int ws_get(int which, size_t bytes, void **out) {
 int workspace(size_t bytes, void **out) { return ws_get(0, bytes, out); }
 int workspace2(size_t bytes, void **out) { return ws_get(1, bytes, out); }
 int staging_workspace(size_t bytes, void **out) { return ws_get(2, bytes, out); }
+int splitk_workspace(size_t bytes, void **out) {
+  const bool fresh = bytes > g_ws[3].cap;
+  B200_TRY(ws_get(3, bytes, out));
+  // the tile counters at its start must read zero before the first launch that uses them
+  // (every launch leaves them at zero again)
+  if (fresh) B200_CUDA(cudaMemsetAsync(g_ws[3].p, 0, g_ws[3].cap, ctx().stream));
+  return 0;
+}
 
 int copy_streams(cudaStream_t *in, cudaStream_t *out) {
   static cudaStream_t s_in = nullptr, s_out = nullptr;
@@ -198,7 +288,8 @@ int b200mlir_init(int device) {
 int b200mlir_set_stream(void *s) {
   clear_error();
   B200_TRY(ensure_ready());
-  ctx().stream = (cudaStream_t)s;
+  ctx().stream = (cudaStream_t)s;  // this thread's stream from now on
+  l2_window_apply();               // the persistence window travels with the stream in use
   return 0;
 }
 
@@ -279,32 +370,54 @@ int b200mlir_get_option(const char *name, double *value) {
 }
 
 // ---- seam 2: alloc / copy ----------------------------------------------------------------
-void *hexagon_runtime_alloc_1d(size_t bytes, uint64_t alignment, bool isVtcm) {
-  clear_error();
-  if (ensure_ready()) return nullptr;
-  if (bytes == 0 || (alignment & (alignment - 1)) != 0) {
-    set_error(B200MLIR_ERR_BAD_ARG, "alloc_1d: bytes=%zu alignment=%llu unsupported", bytes,
-              (unsigned long long)alignment);
+// cudaMalloc aligns to 256 bytes; the lowering keeps the op's requested alignment on every
+// on-chip allocation and tile buffers ask for 2048 (HexagonMemToLLVMPass.cpp:538-542), so
+// larger alignments are served by over-allocating and remembering the base.
+static std::unordered_map<void *, void *> g_alias;      // tile-pointer table -> its contiguous source
+static std::unordered_map<void *, void *> g_aligned;    // aligned pointer handed out -> cudaMalloc base
+static std::unordered_map<void *, void *> g_tables;     // block-pointer table (pinned host) -> device block storage
+
+static void *alloc_aligned(size_t bytes, uint64_t alignment, const char *what) {
+  if (bytes == 0 || alignment == 0 || (alignment & (alignment - 1)) != 0 || alignment > 2048) {
+    set_error(B200MLIR_ERR_BAD_ARG, "%s: bytes=%zu alignment=%llu unsupported (a power of two up to 2048)", what,
+              bytes, (unsigned long long)alignment);
     return nullptr;
   }
-  (void)isVtcm;
-  if (alignment > 256) {
-    set_error(B200MLIR_ERR_BAD_ARG,
-              "alloc_1d: alignment %llu above the 256-byte device allocation granule; use the "
-              "resident entry points for 2 KiB-aligned tiles",
-              (unsigned long long)alignment);
+  const size_t extra = alignment > 256 ? (size_t)alignment : 0;
+  void *base = nullptr;
+  if (cudaMalloc(&base, bytes + extra) != cudaSuccess) {
+    set_error(B200MLIR_ERR_CUDA, "%s(%zu) failed: %s", what, bytes, cudaGetErrorString(cudaGetLastError()));
     return nullptr;
   }
-  void *p = nullptr;
-  if (cudaMalloc(&p, bytes) != cudaSuccess) {
-    set_error(B200MLIR_ERR_CUDA, "alloc_1d(%zu) failed: %s", bytes,
-              cudaGetErrorString(cudaGetLastError()));
-    return nullptr;
+  if (!extra) return base;
+  void *p = (void *)(((uintptr_t)base + alignment - 1) & ~(uintptr_t)(alignment - 1));
+  if (p != base) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_aligned[p] = base;
   }
   return p;
 }
 
-static std::unordered_map<void *, void *> g_alias;  // tile-pointer table -> its contiguous source
+static void free_aligned(void *p) {
+  void *base = p;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_aligned.find(p);
+    if (it != g_aligned.end()) {
+      base = it->second;
+      g_aligned.erase(it);
+    }
+  }
+  if (base && cudaFree(base) != cudaSuccess)
+    set_error(B200MLIR_ERR_CUDA, "free failed: %s", cudaGetErrorString(cudaGetLastError()));
+}
+
+void *hexagon_runtime_alloc_1d(size_t bytes, uint64_t alignment, bool isVtcm) {
+  clear_error();
+  if (ensure_ready()) return nullptr;
+  (void)isVtcm;
+  return alloc_aligned(bytes, alignment, "alloc_1d");
+}
 
 void hexagon_runtime_free_1d(void *ptr) {
   clear_error();
@@ -312,22 +425,63 @@ void hexagon_runtime_free_1d(void *ptr) {
     std::lock_guard<std::mutex> lk(g_mu);
     g_alias.erase(ptr);  // freeing a tile-pointer table ends the alias, not the source
   }
-  if (ptr && cudaFree(ptr) != cudaSuccess)
-    set_error(B200MLIR_ERR_CUDA, "free_1d failed: %s", cudaGetErrorString(cudaGetLastError()));
+  free_aligned(ptr);
 }
 
+// The indirect-tensor form (bin/runtime/src/HexagonCAPI.cpp:89-94, src/HexagonBuffer.cpp:89-113):
+// ONE allocation holding numBlocks blocks at a stride of blockSize rounded up to the alignment,
+// and the call returns a TABLE of the block addresses, not the storage.  The reference's table
+// is ordinary memory of the processor that also runs the kernel; here it is pinned host memory
+// mapped into the device's address space, so host code and kernels index the same pointer.
 void *hexagon_runtime_alloc_2d(size_t numBlocks, size_t blockSize, uint64_t alignment,
                                bool isVtcm) {
-  // The reference returns a table of block pointers; on one flat HBM address
-  // space the blocks are one contiguous allocation, block i at i*blockSize.
+  clear_error();
+  if (ensure_ready()) return nullptr;
+  (void)isVtcm;
   if (numBlocks == 0 || blockSize == 0) {
     set_error(B200MLIR_ERR_BAD_ARG, "alloc_2d: zero-sized request");
     return nullptr;
   }
-  return hexagon_runtime_alloc_1d(numBlocks * blockSize, alignment, isVtcm);
+  if (alignment == 0 || (alignment & (alignment - 1)) != 0 || alignment > 2048) {
+    set_error(B200MLIR_ERR_BAD_ARG, "alloc_2d: alignment %llu unsupported", (unsigned long long)alignment);
+    return nullptr;
+  }
+  const size_t stride = (blockSize + alignment - 1) / alignment * alignment;
+  if (stride > SIZE_MAX / numBlocks) {
+    set_error(B200MLIR_ERR_BAD_ARG, "alloc_2d: %zu blocks of %zu bytes overflow", numBlocks, blockSize);
+    return nullptr;
+  }
+  void *storage = alloc_aligned(stride * numBlocks, alignment, "alloc_2d");
+  if (!storage) return nullptr;
+  void **table = nullptr;
+  if (cudaHostAlloc((void **)&table, numBlocks * sizeof(void *), cudaHostAllocMapped | cudaHostAllocPortable) !=
+      cudaSuccess) {
+    set_error(B200MLIR_ERR_CUDA, "alloc_2d: block table: %s", cudaGetErrorString(cudaGetLastError()));
+    free_aligned(storage);
+    return nullptr;
+  }
+  for (size_t i = 0; i < numBlocks; ++i) table[i] = (char *)storage + i * stride;
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_tables[table] = storage;
+  return table;
 }
 
-void hexagon_runtime_free_2d(void *ptr) { hexagon_runtime_free_1d(ptr); }
+void hexagon_runtime_free_2d(void *ptr) {
+  clear_error();
+  void *storage = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    auto it = g_tables.find(ptr);
+    if (it == g_tables.end()) {
+      set_error(B200MLIR_ERR_BAD_ARG, "free_2d: not a table returned by alloc_2d");
+      return;
+    }
+    storage = it->second;
+    g_tables.erase(it);
+  }
+  cudaFreeHost(ptr);
+  free_aligned(storage);
+}
 
 void hexagon_runtime_copy(void *dst, void *src, size_t nbytes, bool, bool) {
   clear_error();
@@ -514,13 +668,29 @@ static uint32_t dma_issue(void *src, void *dst, uint32_t width, uint32_t height,
   CopyRing &r = g_ring;
   if (!r.stream && cudaStreamCreateWithFlags(&r.stream, cudaStreamNonBlocking) != cudaSuccess)
     return refuse("copy stream creation failed");
+  // Slot allocation follows the reference ring (bin/runtime/UserDMA/RingBuffer.h:103-116):
+  // descriptors no longer in flight are reclaimed whether or not anybody waited on their token,
+  // and a full ring blocks on its oldest descriptor instead of refusing the start.
   int slot = -1;
-  for (int i = 0; i < CopyRing::kSlots; ++i)
-    if (!r.used[i]) {
-      slot = i;
-      break;
+  for (int i = 0; i < CopyRing::kSlots && slot < 0; ++i)
+    if (!r.used[i]) slot = i;
+  if (slot < 0) {
+    int oldest = 0;
+    for (int i = 0; i < CopyRing::kSlots; ++i) {
+      if (cudaEventQuery(r.ev[i]) == cudaSuccess) {
+        r.used[i] = false;
+        if (slot < 0) slot = i;
+      } else {
+        cudaGetLastError();  // cudaErrorNotReady is not an error here
+        if ((int32_t)(r.token_of[i] - r.token_of[oldest]) < 0) oldest = i;
+      }
     }
-  if (slot < 0) return refuse("descriptor ring full");
+    if (slot < 0) {
+      if (cudaEventSynchronize(r.ev[oldest]) != cudaSuccess) return refuse("waiting for the oldest descriptor failed");
+      r.used[oldest] = false;
+      slot = oldest;
+    }
+  }
   if (!r.ev[slot] &&
       cudaEventCreateWithFlags(&r.ev[slot], cudaEventDisableTiming) != cudaSuccess)
     return refuse("event creation failed");
@@ -568,7 +738,7 @@ void hexagon_runtime_dma_wait(uint32_t token) {
   cudaError_t e = cudaEventSynchronize(ev);
   if (e != cudaSuccess) set_error(B200MLIR_ERR_CUDA, "dma_wait: %s", cudaGetErrorString(e));
   std::lock_guard<std::mutex> lk(g_mu);
-  g_ring.used[slot] = false;
+  if (g_ring.token_of[slot] == token) g_ring.used[slot] = false;  // (a start may have reclaimed and reused the slot meanwhile)
 }
 
 int b200mlir_benchmark(b200mlir_thunk fn, void *user, int iterations, double *mean_us) {

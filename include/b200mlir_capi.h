@@ -248,9 +248,16 @@ B200_API void attention_fwd_kernel_float32(int64_t rank_q, B200MemRef4D *q, int6
 /* ---- seam 2: runtime ---------------------------------------------------------
  * qcom_hexagon_backend/bin/runtime/include/HexagonCAPI.h:26-68.  `isVtcm`
  * selected the 8 MiB on-chip scratch on Hexagon; here every allocation is HBM
- * and the flag only asks for 2 KiB alignment.  alloc never returns NULL for a
- * valid request on a working device; on failure it returns NULL and records
- * the error instead of aborting the process. */
+ * and the flag is accepted and ignored.  Alignment: any power of two up to 2048
+ * (tile buffers ask for 2048).  alloc never returns NULL for a valid request on
+ * a working device; on failure it returns NULL and records the error instead of
+ * aborting the process.
+ * alloc_2d is the indirect-tensor form (bin/runtime/src/HexagonCAPI.cpp:89-94,
+ * src/HexagonBuffer.cpp:89-113): one device allocation of numBlocks blocks at a
+ * stride of blockSize rounded up to the alignment, and the RETURN VALUE IS A
+ * TABLE of numBlocks block addresses (table[i] = block i), not the storage.  The
+ * table is pinned host memory mapped into the device's address space: host code
+ * and kernels may both index it.  free_2d takes the table and releases both. */
 B200_API void *hexagon_runtime_alloc_1d(size_t bytes, uint64_t alignment, bool isVtcm);
 B200_API void hexagon_runtime_free_1d(void *ptr);
 B200_API void *hexagon_runtime_alloc_2d(size_t numBlocks, size_t blockSize, uint64_t alignment,
@@ -283,6 +290,36 @@ B200_API int32_t hexagon_runtime_resident_free_v2(void *ptr, uint32_t bytes);
  * kept so that compiled callers link, and they do nothing. */
 B200_API void hexagon_runtime_hmx_ensure(void);
 B200_API void hexagon_runtime_hmx_unlock(void);
+/* Read-out executor (bin/runtime/include/HmxVectorExecutor.h:86-156): a resident host thread
+ * runs `fn` on groups of accumulator rows while the calling thread continues.  The descriptor has
+ * the reference's six fields in its order (pointers are 64-bit here, so 32 bytes instead of 24).
+ * configure returns 0, -1 (fn is NULL), -2 (numThreads other than 1 was asked for; one thread is
+ * used and the executor works), -3 (the thread would not start).  publish has one producer, never
+ * blocks and returns the number of batches accepted: fewer than `count` only when the 16-slot ring
+ * (15 usable) is full — THE CALLER MUST READ OUT THE REST ITSELF — and 0 before configure or after
+ * shutdown.  `fn` is called once per batch (count = 1), in publish order.  drain returns when every
+ * accepted batch has been read out; shutdown drains and releases the thread.  Inside this
+ * library's own GEMM kernels the split these calls implement is done by the epilogue warps. */
+typedef struct {
+  uint32_t rowStart;  /* first m-row in `ar` */
+  uint32_t rowCount;  /* rows in the group (G) */
+  uint32_t validRows; /* rows valid in the last row of the group */
+  uint32_t nCroutons; /* n-tiles per row */
+  void *ar;           /* accumulator array */
+  void *dst;          /* row-major destination, already offset to rowStart */
+} B200HmxReadoutBatch;
+typedef void (*B200HmxReadoutFn)(const B200HmxReadoutBatch *batch, uint32_t count);
+#define B200_HMX_EXEC_OK 0
+#define B200_HMX_EXEC_ERR_NULL_FN (-1)
+#define B200_HMX_EXEC_ERR_THREADS (-2)
+#define B200_HMX_EXEC_ERR_CREATE (-3)
+B200_API int32_t hexagon_runtime_hmx_exec_configure(B200HmxReadoutFn fn, int32_t numThreads);
+B200_API uint32_t hexagon_runtime_hmx_exec_publish(const B200HmxReadoutBatch *batches, uint32_t count);
+B200_API void hexagon_runtime_hmx_exec_drain(void);
+B200_API void hexagon_runtime_hmx_exec_shutdown(void);
+/* Batches the executor thread has run since the library was loaded (diagnostic counter, the
+ * `batchesRun` of the reference's executor). */
+B200_API uint64_t b200mlir_hmx_exec_batches_run(void);
 /* Asynchronous copies (bin/runtime/include/RuntimeDMA.h:39-51).  A refused
  * start returns 0xFFFFFFFF and sets *status = -1; waiting on that token
  * returns at once.  Strides, width in bytes. */

@@ -151,6 +151,9 @@ _SIGNATURES = {
                                           ctypes.POINTER(ctypes.c_longlong)]),
     "b200mlir_perf_report_save": (c_int, [ctypes.c_char_p, ctypes.c_char_p, ctypes.c_double, ctypes.c_char_p,
                                           c_int, ctypes.c_longlong]),
+    "b200mlir_fill_random": (c_int, [c_void_p, ctypes.c_int32, c_i64, ctypes.c_uint64, c_int, ctypes.c_double,
+                                     ctypes.c_double]),
+    "b200mlir_selftest_bounded_wait": (c_int, [c_int]),
     "b200mlir_dtype_size": (c_int, [ctypes.c_int32]),
     "b200mlir_tensor_dump": (c_int, [ctypes.c_char_p, ctypes.c_int32, c_i64, ctypes.POINTER(c_i64), c_void_p]),
     "b200mlir_tensor_file_info": (c_int, [ctypes.c_char_p, ctypes.POINTER(ctypes.c_int32), ctypes.POINTER(c_i64),

@@ -213,6 +213,7 @@ struct TcVariantInfo {
   int bm, bn, bk, stages, cta_group;
   int smem_bytes, tmem_cols;
   double model_eff;  // fraction of the tensor pipe this tiling sustained when measured
+  bool stream_k = false;  // work is dealt out in k-blocks, not whole tiles (gemm_tcgen05_streamk.cu)
 };
 const TcVariantInfo &tc_variant_info(int v);
 // "ok" or a refusal reason for variant v on (m,n,k) with the given epilogue.
@@ -226,6 +227,9 @@ int launch_gemm_i8_tc_pair(const int8_t *a, const int8_t *bt, int32_t *c, int64_
                            int64_t ldbt, int64_t ldc);
 int launch_gemm_tc_pair(const GemmArgs &g, bool deep_k);
 int pair_variant_smem_bytes();
+// gemm_tcgen05_streamk.cu — the pair kernel with the k-blocks of its tiles dealt out evenly over the pairs
+int launch_gemm_tc_streamk(const GemmArgs &g);
+bool streamk_shape_ok(const GemmArgs &g);
 
 // w8a16.cu
 struct W8A16Weight {

@@ -306,6 +306,8 @@ const TcVariantInfo kVariants[] = {
     // a pair of CTAs per 256 x 256 tile (gemm_tcgen05_2cta.cu)
     {"tc256x256x64_2cta_s6", 256, 256, 64, 6, 2, 6 * 32768 + 16 * 6 + 64 + 1024, 512, 0.85},
     {"tc256x256x128_2cta_s3", 256, 256, 128, 3, 2, 6 * 32768 + 16 * 6 + 64 + 1024, 512, 0.10},
+    // the same pair tile with the k-blocks of all tiles dealt out evenly (gemm_tcgen05_streamk.cu)
+    {"tc256x256x64_2cta_streamk", 256, 256, 64, 6, 2, 6 * 32768 + 16 * 6 + 64 + 1024, 512, 0.85, true},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -451,9 +453,14 @@ const char *tc_variant_verdict(int v, const GemmArgs &g) {
   // can hold a row of running sums (anything else stays on the CUDA-core path)
   // (the one-CTA 128x128 variant, and the two-CTA variant with 64-deep stages, whose eight read-out warps take 128 columns each)
   if (g.epilogue == EPI_KLOOP_F16 &&
-      (!((vi.cta_group == 1 && vi.bn == 128) || (vi.cta_group == 2 && vi.bk == 64 && ctx().opt.kloop_pairs != 0)) ||
+      (!((vi.cta_group == 1 && vi.bn == 128) ||
+         (vi.cta_group == 2 && vi.bk == 64 && !vi.stream_k && ctx().opt.kloop_pairs != 0)) ||
        g.block_k < BK || g.block_k % BK))
     return "epilogue-unsupported";
+  if (vi.stream_k) {
+    if (g.epilogue == EPI_KLOOP_F16 || g.epilogue == EPI_I32) return "epilogue-unsupported";
+    if (!streamk_shape_ok(g)) return "extent-range";
+  }
   if (g.m > 0x7fffffff || g.n > 0x7fffffff || g.k > 0x7fffffff) return "extent-range";
   if (((g.m + BM - 1) / BM) * ((g.n + 31) / 32) > 0x3fffffff) return "extent-range";
   if (vi.smem_bytes > 227 * 1024) return "smem-budget";
@@ -473,6 +480,7 @@ int launch_gemm_tc(int v, const GemmArgs &g) {
     case 2: return launch_epi<64, 8>(g, vi);
     case 3: return launch_gemm_tc_pair(g, false);
     case 4: return launch_gemm_tc_pair(g, true);
+    case 5: return launch_gemm_tc_streamk(g);
   }
   return set_error(B200MLIR_ERR_BAD_ARG, "no such gemm variant %d", v);
 }

@@ -49,7 +49,8 @@ constexpr long long kWaitLimitCycles = 2000000000LL;
 // role of the CTA: the first wait that runs out sets it, so the others leave
 // too.  `status` is the library's device status word ({site, detail}).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          int *status, int site, int detail) {
+                                          int *status, int site, int detail,
+                                          long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
@@ -57,7 +58,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         if (atomicCAS(status, 0, site) == 0) status[1] = detail;
         return false;

@@ -327,6 +327,8 @@ int b200mlir_device_status(void) {
     set_error(B200MLIR_ERR_DEVICE_WAIT, "a bounded device wait expired (site %d, detail %d)",
               h[0], h[1]);
     cudaMemset(ctx().d_status, 0, 256);
+    // a kernel that gave up may have left arrival counters of the split-K workspace non-zero
+    if (g_ws[3].p) cudaMemset(g_ws[3].p, 0, g_ws[3].cap < (1u << 20) ? g_ws[3].cap : (1u << 20));
   }
   return h[0];
 }

@@ -30,6 +30,8 @@ constexpr double kCvFactor = 3.0;       // hmx_search.py:1184
 constexpr double kMarginFloor = 0.15;   // hmx_search.py:1185
 constexpr int kReps = 3;                // hexagon_bench reps
 constexpr int kSimtVariant = -1;
+constexpr double kStreamKDrag = 1.05;     // modelled loss of the stream-K form per k-block against whole tiles
+constexpr double kStreamKFixup = 2500.0;  // clocks to combine one more contributor's partial of a cut tile
 
 std::mutex g_cache_mu;
 struct CacheEntry {
@@ -62,9 +64,18 @@ std::string cache_key(int64_t m, int64_t n, int64_t k, int epi) {
 double model_clocks(const TcVariantInfo &vi, int64_t m, int64_t n, int64_t k, int sms) {
   const double tiles = std::ceil((double)m / vi.bm) * std::ceil((double)n / vi.bn);
   const double slots = std::max(1, sms / vi.cta_group);
-  const double waves = std::ceil(tiles / slots);
   const double kblocks = std::ceil((double)k / vi.bk);
   const double per_block = (double)vi.bm * vi.bn * vi.bk * 2.0 / (8192.0 * vi.cta_group) / vi.model_eff;
+  if (vi.stream_k) {
+    // k-blocks dealt out evenly: no round is left part-filled, but every tile cut between pairs
+    // costs a trip of its fp32 partials through the workspace (kStreamKFixup clocks on the pair
+    // that combines them), and a pair that changes tile mid-range restarts its accumulator
+    const double units = tiles * kblocks, share = std::ceil(units / std::min(slots, units));
+    const bool cut = std::fmod(tiles, slots) != 0.0 || tiles < slots;
+    const double parts = std::max(1.0, std::ceil(std::min(slots, units) / tiles));  // contributors per cut tile
+    return share * per_block * kStreamKDrag + 1500.0 + (cut ? kStreamKFixup * parts : 0.0);
+  }
+  const double waves = std::ceil(tiles / slots);
   return waves * (kblocks * per_block + 1500.0);
 }
 

@@ -270,6 +270,29 @@ def device_status() -> int:
     return int(lib().b200mlir_device_status())
 
 
+def selftest_bounded_wait(limit_us: int = 1000) -> None:
+    """Run the one-CTA kernel whose wait nobody satisfies; afterwards `device_status()` reports
+    site 90 once and the word is clean again."""
+    if lib().b200mlir_selftest_bounded_wait(int(limit_us)) != 0:
+        check()
+
+
+UNIFORM, NORMAL, INTEGERS = 0, 1, 2
+
+
+def fill_random(t, seed: int, dist: int, p0: float, p1: float):
+    """Fill a contiguous float16 / float32 / int8 tensor (torch or numpy) from the library's
+    counter-based generator; the CPU twins beside the oracle give the same bytes."""
+    ptr, dt, shape, keep = _host_or_device(t)
+    if keep is not t and not (isinstance(t, np.ndarray) and keep.ctypes.data == t.ctypes.data):
+        raise ValueError("fill_random needs a contiguous tensor")
+    _sync_stream([t])
+    n = int(np.prod(shape, dtype=np.int64))
+    if lib().b200mlir_fill_random(ptr, DTYPE_IDS[dt.name], n, int(seed), int(dist), float(p0), float(p1)) != 0:
+        check()
+    return t
+
+
 # ---- weight residency --------------------------------------------------------------------
 
 def register_w8a16_weight(wq, scales, l2_persist: bool = False) -> None:

@@ -446,6 +446,22 @@ B200_API int b200mlir_benchmark_report(b200mlir_thunk fn, void *user, int iterat
 B200_API int b200mlir_perf_report_save(const char *path, const char *name, double perf, const char *units,
                                        int result, long long cycles);
 
+/* Synthetic inputs for the harness: fills `dst` (device or host pointer; n elements of dtype id
+ * 1 = float16, 2 = float32, 4 = int8, the ids of the raw tensor files below) from a counter-based
+ * generator (Philox4x32-10 keyed by `seed`; element i is drawn from its index alone).  dist 0:
+ * uniform [p0, p1); 1: normal(mean p0, sigma p1) as a sum of twelve uniforms (tails end at six
+ * sigma); 2: integers uniform in [p0, p1].  The same stream is implemented on the CPU beside the
+ * oracle, so a CPU check and this library see identical bytes for one seed.  No counterpart in
+ * the reference, whose tests draw their inputs in Python. */
+B200_API int b200mlir_fill_random(void *dst, int32_t dtype_id, int64_t n, uint64_t seed, int dist, double p0,
+                                  double p1);
+/* Self-test of the bounded device wait every kernel here relies on: a one-CTA kernel waits, with a
+ * budget of `limit_us` microseconds, on a barrier nothing arrives at; the wait gives up and the
+ * kernel returns.  Returns 0 when that happened; b200mlir_device_status() then reports site 90
+ * (and clears the word), exactly as after a real expiry.  The reference refuses instead of
+ * hanging in the same way (bin/runtime/include/RuntimeDMA.h:19-37). */
+B200_API int b200mlir_selftest_bounded_wait(int limit_us);
+
 /* Raw tensor files of the reference's device harness
  * (test/utils/dsp/include/tensor.h:219-259; dtype ids :26-38; host reader
  * backend/hexagon_executor.py:200-216).  Output files: u32 dtype id, i64 rank,

@@ -30,11 +30,12 @@ _f32 = ctypes.c_float
 _u32 = ctypes.c_uint
 
 
-def build(with_ref: bool = True) -> None:
-    """Compile ``liboracle.so`` and, if the reference tree exists, ``_ref/``."""
+def build(with_ref: bool = True, ref_root: str | None = None) -> None:
+    """Compile ``liboracle.so`` and, when a reference checkout is named (argument, else the
+    environment variable HEXMLIR_REFERENCE_ROOT) and exists, ``_ref/`` from its sources in place."""
     subprocess.run(["make", "-s", "-C", _HERE, "all"], check=True)
-    ref_root = os.environ.get("HEXMLIR_REFERENCE_ROOT", "/root/reference")
-    if with_ref and os.path.isdir(ref_root):
+    ref_root = ref_root or os.environ.get("HEXMLIR_REFERENCE_ROOT", "")
+    if with_ref and ref_root and os.path.isdir(ref_root):
         subprocess.run(["make", "-s", "-C", _HERE, "ref", f"REF={ref_root}"],
                        check=True, stderr=subprocess.DEVNULL)
 
@@ -294,3 +295,73 @@ def ref_unpack_acc_f32(tiles, rows, cols, res=None):
                               _u32(rows), _u32(cols), _u32(cols))
     assert rc == 0
     return out
+
+
+# ---- synthetic inputs: the counter-based generator (three implementations, one byte stream) ----
+
+_DTYPE_IDS = {np.dtype(np.float16): 1, np.dtype(np.float32): 2, np.dtype(np.int8): 4}
+UNIFORM, NORMAL, INTEGERS = 0, 1, 2
+
+
+def fill_random(shape, dtype, seed: int, dist: int, p0: float, p1: float, threads: int = 0):
+    """The C++ loop of the generator (see hexmlir_oracle.cpp: Philox4x32-10, element i = word i&3
+    of block i>>2)."""
+    out = np.empty(shape, dtype)
+    lib().oracle_fill_random(_ptr(out), _int(_DTYPE_IDS[out.dtype]), _i64(out.size), ctypes.c_uint64(seed),
+                             _int(dist), _f32(p0), _f32(p1), _int(_nt(threads)))
+    return out
+
+
+def _philox_np(c0, c1, c2, c3, k0, k1):
+    m0, m1 = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57)
+    mask, sh = np.uint64(0xFFFFFFFF), np.uint64(32)
+    k0, k1 = np.uint64(k0), np.uint64(k1)
+    for _ in range(10):
+        p0, p1 = m0 * c0, m1 * c2          # 32 x 32 -> 64 bits, held in uint64
+        c0, c1, c2, c3 = (p1 >> sh) ^ c1 ^ k0, p1 & mask, (p0 >> sh) ^ c3 ^ k1, p0 & mask
+        k0, k1 = (k0 + np.uint64(0x9E3779B9)) & mask, (k1 + np.uint64(0xBB67AE85)) & mask
+    return c0, c1, c2, c3
+
+
+def fill_random_numpy(shape, dtype, seed: int, dist: int, p0: float, p1: float, start: int = 0, index=None):
+    """numpy twin of the generator; `start` offsets the element index (or `index` names every
+    element's index outright), so any slice of a large tensor can be drawn without the rest —
+    what a counter-based generator is for."""
+    n = int(np.prod(shape))
+    i = np.arange(start, start + n, dtype=np.uint64) if index is None else np.asarray(index, np.uint64).reshape(-1)
+    assert i.size == n
+    k0, k1 = seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF
+    zero = np.zeros(n, np.uint64)
+    f32 = np.float32
+    if dist == NORMAL:
+        total = np.zeros(n, np.uint64)
+        for j in range(3):
+            w = _philox_np(i & np.uint64(0xFFFFFFFF), i >> np.uint64(32), zero + np.uint64(j), zero + np.uint64(1),
+                           k0, k1)
+            for x in w:
+                total += x >> np.uint64(12)
+        z = total.astype(f32) * f32(2.0 ** -20) - f32(6.0)
+        v = f32(p0) + f32(p1) * z
+    else:
+        blk = i >> np.uint64(2)
+        w = _philox_np(blk & np.uint64(0xFFFFFFFF), blk >> np.uint64(32), zero, zero, k0, k1)
+        x = np.choose((i & np.uint64(3)).astype(np.int64), w)
+        if dist == INTEGERS:
+            lo, hi = int(p0), int(p1)
+            v = (x % np.uint64(hi - lo + 1)).astype(np.int64) + lo
+        else:
+            u = (x >> np.uint64(8)).astype(f32) * f32(2.0 ** -24)
+            v = f32(p0) + u * (f32(p1) - f32(p0))
+    return np.asarray(v).astype(dtype).reshape(shape)
+
+
+def random_rows(r0: int, rows: int, ld: int, dtype, seed, dist, p0, p1):
+    """Rows [r0, r0 + rows) of a row-major [*, ld] tensor filled by the generator."""
+    return fill_random_numpy((rows, ld), dtype, seed, dist, p0, p1, start=r0 * ld)
+
+
+def random_cols(c0: int, cols: int, rows: int, ld: int, dtype, seed, dist, p0, p1):
+    """Columns [c0, c0 + cols) of a row-major [rows, ld] tensor filled by the generator."""
+    idx = (np.arange(rows, dtype=np.uint64)[:, None] * np.uint64(ld) + np.uint64(c0)
+           + np.arange(cols, dtype=np.uint64)[None, :])
+    return fill_random_numpy((rows, cols), dtype, seed, dist, p0, p1, index=idx)

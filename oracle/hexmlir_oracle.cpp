@@ -470,3 +470,62 @@ void oracle_unpack_acc_f16(const uint16_t *tiles, uint16_t *dst, int64_t rows,
 }
 
 }  // extern "C"
+
+// ---- synthetic inputs: one counter-based generator, the same bytes everywhere -------------
+// Philox4x32-10 (Salmon et al., SC'11).  Element i of a tensor takes word (i & 3) of the block
+// with counter (i >> 2, stream, lane) and key = seed; no state, so the GPU kernel of the library
+// (b200mlir_fill_random), this loop and the numpy twin in oracle/__init__.py produce identical
+// bytes for the same (seed, distribution, parameters).  No counterpart in the reference, whose
+// tests draw inputs with torch.rand/randn; BASELINE's shapes and distributions are kept.
+//   dist 0: uniform [p0, p1):  p0 + (w >> 8) * 2^-24 * (p1 - p0), unfused multiply then add
+//   dist 1: normal(p0, p1) as an Irwin-Hall sum of twelve 20-bit uniforms (exact integer sum S,
+//           z = S * 2^-20 - 6, tails end at 6 sigma), x = p0 + p1 * z
+//   dist 2: integers uniform in [p0, p1] (w mod range)
+static inline void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1,
+                                 uint32_t out[4]) {
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0, p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0, n1 = (uint32_t)p1;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1, n3 = (uint32_t)p0;
+    c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+static inline float fill_value(int64_t i, uint64_t seed, int dist, float p0, float p1) {
+  const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  const uint32_t blk_lo = (uint32_t)((uint64_t)i >> 2), blk_hi = (uint32_t)((uint64_t)i >> 34);
+  uint32_t w[4];
+  if (dist == 1) {
+    uint32_t sum = 0;
+    for (uint32_t j = 0; j < 3; ++j) {
+      philox4x32_10((uint32_t)((uint64_t)i), (uint32_t)((uint64_t)i >> 32), j, 1u, k0, k1, w);
+      sum += (w[0] >> 12) + (w[1] >> 12) + (w[2] >> 12) + (w[3] >> 12);
+    }
+    const float z = (float)sum * 9.5367431640625e-07f - 6.0f;  // 2^-20
+    const float t = p1 * z;
+    return p0 + t;
+  }
+  philox4x32_10(blk_lo, blk_hi, 0u, 0u, k0, k1, w);
+  const uint32_t x = w[i & 3];
+  if (dist == 2) {
+    const int lo = (int)p0, hi = (int)p1;
+    return (float)(lo + (int)(x % (uint32_t)(hi - lo + 1)));
+  }
+  const float u = (float)(x >> 8) * 5.9604644775390625e-08f;  // 2^-24
+  const float t = u * (p1 - p0);
+  return p0 + t;
+}
+
+extern "C" void oracle_fill_random(void *dst, int dtype_id, int64_t n, uint64_t seed, int dist, float p0, float p1,
+                                   int nthreads) {
+  parallel_for(n, nthreads, [&](int64_t lo, int64_t hi) {
+    for (int64_t i = lo; i < hi; ++i) {
+      const float v = fill_value(i, seed, dist, p0, p1);
+      if (dtype_id == 1) ((f16 *)dst)[i] = (f16)v;          // dtype ids of the raw tensor files: 1 f16
+      else if (dtype_id == 2) ((float *)dst)[i] = v;         // 2 f32
+      else ((int8_t *)dst)[i] = (int8_t)(int)v;              // 4 int8
+    }
+  });
+}

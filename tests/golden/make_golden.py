@@ -25,7 +25,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("HEXMLIR_REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("HEXMLIR_REFERENCE_ROOT") or sys.exit("set HEXMLIR_REFERENCE_ROOT to the reference checkout")
 
 import oracle  # noqa: E402
 

@@ -26,7 +26,7 @@ def n_variants(hm):
     return len(hm.gemm_variants())
 
 
-@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, 3, 4, -1])
+@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, 3, 4, 5, -1])
 def test_c1_config(hm, oracle, variant):
     """M=N=K=1024, U[-1,1], seed 0."""
     rng = philox(0)
@@ -52,7 +52,7 @@ def test_reference_test_shape(hm, oracle):
     assert max_abs_rel(got, oracle.gemm_f16(a, b)) <= TOL_GEMM
 
 
-@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4])
+@pytest.mark.parametrize("variant", [0, 1, 2, 3, 4, 5])
 @pytest.mark.parametrize("mnk", [(128, 256, 64), (128, 64, 128), (5, 8, 8), (129, 264, 72),
                                  (300, 520, 200), (256, 256, 4096), (1000, 1000, 1000),
                                  (64, 2048, 512), (2048, 64, 320)])
@@ -245,3 +245,73 @@ def test_host_buffers_take_the_pipelined_path(hm, oracle, mnk, pad):
     dc = torch.empty((m, n), dtype=torch.float16, device="cuda")
     hm.matmul[(1,)](da, db, dc)
     assert np.array_equal(dc.cpu().numpy().view(np.uint16), np.ascontiguousarray(c).view(np.uint16))
+
+
+STREAMK = 5
+
+
+@pytest.mark.parametrize("mnk", [(1024, 1024, 1024), (256, 11008, 4096), (2048, 4096, 1376), (2048, 1376, 4096),
+                                 (300, 520, 200), (512, 512, 8192), (256, 256, 64 * 148), (4096, 4096, 512)])
+def test_stream_k_cuts_tiles_between_pairs_and_stays_exact_in_order(hm, oracle, cuda, mnk):
+    """The k-blocks of all tiles dealt out evenly over the SM pairs: tiles cut between pairs are
+    combined from fp32 partials in a fixed order, so the result matches the oracle like any other
+    variant AND is bit-identical run to run (the reduction order is the partition's, not arrival's).
+    Shapes: the first config, the many-row w8a16 product, both GEMMs of a TP8 MLP shard (one with
+    a K tail), an odd shape, one tile cut 74 ways, K of exactly one block per pair, uncut tiles."""
+    m, n, k = mnk
+    rng = philox(61)
+    a = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+    b = rng.uniform(-1, 1, (k, n)).astype(np.float16)
+    assert hm.gemm_variant_verdict(STREAMK, m, n, k) == "ok"
+    want = oracle.gemm_f16(a, b)
+    da, db = cuda.from_numpy(a).cuda(), cuda.from_numpy(b).cuda()
+    outs = []
+    hm.set_option("gemmVariant", STREAMK)
+    try:
+        for _ in range(3):
+            c = cuda.full((m, n), 7.0, dtype=cuda.float16, device="cuda")
+            hm.matmul[(1,)](da, db, c)
+            outs.append(c)
+    finally:
+        hm.set_option("gemmVariant", -1)
+    assert hm.device_status() == 0
+    assert max_abs_rel(outs[0].cpu().numpy(), want) <= TOL_GEMM
+    assert cuda.equal(outs[0], outs[1]) and cuda.equal(outs[0], outs[2])
+    # and close to the whole-tile pair kernel: only the fp32 summation order differs
+    hm.set_option("gemmVariant", 3)
+    try:
+        c3 = cuda.empty((m, n), dtype=cuda.float16, device="cuda")
+        hm.matmul[(1,)](da, db, c3)
+    finally:
+        hm.set_option("gemmVariant", -1)
+    assert float((outs[0].float() - c3.float()).abs().max()) <= 2 * 2.0 ** -10 * max(1.0, float(c3.abs().max()))
+
+
+def test_stream_k_read_outs(hm, oracle):
+    """The fused read-outs behind a combined tile: fp32 + residual, and the MLP block's SwiGLU and
+    residual forms (both GEMMs of the block forced onto the variant)."""
+    rng = philox(62)
+    a = rng.uniform(-1, 1, (320, 4096)).astype(np.float16)
+    b = rng.uniform(-1, 1, (4096, 520)).astype(np.float16)
+    res = rng.normal(0, 1, (320, 520)).astype(np.float32)
+    c32 = np.zeros((320, 520), np.float32)
+    hm.set_option("gemmVariant", STREAMK)
+    try:
+        hm.matmul_f32out(a, b, c32, res)
+        want = oracle.gemm_f16_f32out(a, b, res)
+        assert max_abs_rel(c32, want) <= TOL_GEMM
+        t, d, f = 512, 1024, 1376
+        x = rng.normal(0, 1, (t, d)).astype(np.float16)
+        gain = rng.uniform(0.5, 1.5, d).astype(np.float16)
+        wg = rng.normal(0, 0.02, (d, f)).astype(np.float16)
+        wu = rng.normal(0, 0.02, (d, f)).astype(np.float16)
+        wd = rng.normal(0, 0.02, (f, d)).astype(np.float16)
+        y = np.zeros_like(x)
+        hm.manifest_reset()
+        hm.mlp_block[(1,)](x, gain, wg, wu, wd, y, eps=1e-6, add_residual=True)
+        names = [r["name"] for r in hm.manifest()["matmuls"]]
+    finally:
+        hm.set_option("gemmVariant", -1)
+    assert hm.device_status() == 0
+    assert names and all("streamk" in nm for nm in names), names
+    assert max_abs_rel(y, oracle.mlp(x, gain, wg, wu, wd, 1e-6)) <= TOL_GEMM

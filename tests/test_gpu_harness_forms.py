@@ -92,3 +92,42 @@ def test_tensor_dump_from_device_memory(hm, cuda, tmp_path):
     dst = cuda.zeros((64, 64), dtype=cuda.float16, device="cuda")
     hm.tensor_load(p, out=dst)
     assert bool((dst == t).all())
+
+
+@pytest.mark.parametrize("dist,p0,p1,dtype", [(0, -1.0, 1.0, np.float16), (1, 0.0, 3.0, np.float16),
+                                              (1, 0.0, 0.02, np.float16), (2, -127, 127, np.int8),
+                                              (0, 0.001, 0.02, np.float16), (1, 0.0, 1.0, np.float32)])
+def test_device_generator_gives_the_oracles_bytes(hm, oracle, cuda, dist, p0, p1, dtype):
+    """One counter-based generator, three implementations: the library's kernel must write the bytes
+    the C++ loop beside the oracle writes (device tensor and host tensor alike)."""
+    tdt = {np.float16: cuda.float16, np.float32: cuda.float32, np.int8: cuda.int8}[dtype]
+    t = cuda.empty((1031, 517), dtype=tdt, device="cuda")
+    hm.fill_random(t, 4, dist, p0, p1)
+    want = oracle.fill_random((1031, 517), dtype, 4, dist, p0, p1)
+    assert np.array_equal(t.cpu().numpy().view(np.uint8), want.view(np.uint8))
+    h = np.empty((33, 7), dtype)
+    hm.fill_random(h, 9, dist, p0, p1)
+    assert np.array_equal(h.view(np.uint8), oracle.fill_random((33, 7), dtype, 9, dist, p0, p1).view(np.uint8))
+
+
+def test_a_bounded_device_wait_runs_out_and_the_library_recovers(hm, oracle):
+    """A one-CTA kernel waits about a millisecond on a barrier nothing arrives at: the wait gives up,
+    the kernel returns, the host reads B200MLIR_ERR_DEVICE_WAIT with the site code, the status word
+    is clean afterwards and a normal GEMM then passes.  (Refusal with a status word instead of a
+    hang: bin/runtime/include/RuntimeDMA.h:19-37 of the reference.)"""
+    assert hm.device_status() == 0
+    hm.selftest_bounded_wait(1000)
+    assert hm.device_status() == 90                    # the self-test's site code
+    code, msg = hm._capi.last_error()
+    assert code == 5 and "site 90" in msg and "detail 7" in msg
+    assert hm.device_status() == 0                     # reading it cleared it
+    rng = np.random.Generator(np.random.Philox(7))
+    a = rng.uniform(-1, 1, (256, 512)).astype(np.float16)
+    b = rng.uniform(-1, 1, (512, 256)).astype(np.float16)
+    c = np.zeros((256, 256), np.float16)
+    hm.matmul[(1,)](a, b, c)
+    assert hm.device_status() == 0
+    want = oracle.gemm_f16(a, b).astype(np.float32)
+    assert np.abs(c.astype(np.float32) - want).max() / np.abs(want).max() <= 1e-2
+    with pytest.raises(hm.B200Error):
+        hm.selftest_bounded_wait(0)

@@ -153,8 +153,15 @@ static int init_locked(int device) {
 int ensure_ready() {
   Context &c = ctx();
   if (c.ready) {
+    // A host thread that calls in for the first time has no current context yet, and the
+    // driver-API calls made here (tensor-map encoding) need one: bind the device's primary context.
+    static thread_local bool t_bound = false;
     int cur = -1;
-    if (cudaGetDevice(&cur) == cudaSuccess && cur != c.device) cudaSetDevice(c.device);
+    if (!t_bound || (cudaGetDevice(&cur) == cudaSuccess && cur != c.device)) {
+      cudaSetDevice(c.device);
+      cudaFree(nullptr);
+      t_bound = true;
+    }
     return 0;
   }
   std::lock_guard<std::mutex> lk(g_mu);

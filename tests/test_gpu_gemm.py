@@ -244,7 +244,20 @@ def test_host_buffers_take_the_pipelined_path(hm, oracle, mnk, pad):
     da, db = torch.from_numpy(a).cuda(), torch.from_numpy(np.ascontiguousarray(b)).cuda()
     dc = torch.empty((m, n), dtype=torch.float16, device="cuda")
     hm.matmul[(1,)](da, db, dc)
-    assert np.array_equal(dc.cpu().numpy().view(np.uint16), np.ascontiguousarray(c).view(np.uint16))
+    # the strips and the whole problem may take different variants; where a variant cuts a tile's K
+    # between SM pairs the fp32 sum is associated differently, which can move the last fp16 bit
+    got_dev = dc.cpu().numpy()
+    same = got_dev.view(np.uint16) == np.ascontiguousarray(c).view(np.uint16)
+    assert same.mean() > 0.9
+    assert np.abs(got_dev.astype(np.float32) - c.astype(np.float32)).max() <= 2 * 2.0 ** -10 * np.abs(got_dev).max()
+    hm.set_option("gemmVariant", 3)      # one whole-tile variant for every strip and for the whole problem:
+    try:                                 # the same fp32 sums in the same order, so the same bytes
+        c2 = np.zeros((m, n), np.float16)
+        hm.matmul[(1,)](a, b, c2)
+        hm.matmul[(1,)](da, db, dc)
+    finally:
+        hm.set_option("gemmVariant", -1)
+    assert np.array_equal(dc.cpu().numpy().view(np.uint16), c2.view(np.uint16))
 
 
 STREAMK = 5

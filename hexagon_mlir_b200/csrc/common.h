@@ -198,6 +198,12 @@ struct GemmArgs {
   int64_t lda = 0, ldb = 0, ldc = 0, ldres = 0;
   int epilogue = EPI_F16;
   int block_k = 0;  // EPI_KLOOP_F16 only
+  // B is not row-major [K,N] but the K-blocked image [ceil(K/64)][N][64] fp16: per 64-deep k-block
+  // every column's 64 values are one contiguous 128-byte row, so a CTA's operand tile of a k-block
+  // is ONE contiguous piece of HBM (a row-major B hands the memory system 128-byte pieces a whole
+  // row of B apart, which held DRAM at ~2.9 TB/s when every tile reads its own columns).  Built by
+  // the w8a16 registry for its many-row route; `ldb` is ignored.
+  bool b_kblocked = false;
   const PushTargets *push = nullptr;  // EPI_PUSH16 only
 };
 
@@ -251,7 +257,7 @@ int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, in
 // 24.2): the weight is expanded once to fp16 (2 bytes per weight, kept with the registry entry)
 // and the product goes through the fp16 GEMM.
 // w8a16_tmem.cu
-int w8a16_expand_f16(const void *image, const __half *scales_dev, int64_t k, int64_t n, void **w16);
+int w8a16_expand_f16(const void *image, const __half *scales_dev, int64_t k, int64_t n, void **w16);  // K-blocked image (GemmArgs::b_kblocked)
 int w8a16_build_tmem_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
 int launch_w8a16_tmem(const __half *a, const void *image, const __half *scales_dev, int64_t k, int64_t n,
                       __half *c, int64_t m, int64_t lda, int64_t ldc);

@@ -430,7 +430,9 @@ const char *tc_variant_verdict(int v, const GemmArgs &g) {
   const TcVariantInfo &vi = kVariants[v];
   if (g.m <= 4) return "min-rows";  // HmxTarget.h:100,201 — decode rows go to the vector path
   if (g.k < 8 || g.n < 8) return "tile-alignment";
-  if (g.k % 8 || g.n % 8 || g.lda % 8 || g.ldb % 8) return "tile-alignment";
+  if (g.k % 8 || g.n % 8 || g.lda % 8 || (!g.b_kblocked && g.ldb % 8)) return "tile-alignment";
+  // the K-blocked B image: the pair kernels' plain fp16 read-out only
+  if (g.b_kblocked && (vi.cta_group != 2 || vi.bk != 64 || g.epilogue != EPI_F16)) return "epilogue-unsupported";
   if (g.epilogue == EPI_PUSH16) {
     if (!g.push || g.push->world < 1 || g.push->world > kMaxPushRanks || g.push->rows_per_rank < 1 ||
         g.push->rows_per_rank * g.push->world != g.m)

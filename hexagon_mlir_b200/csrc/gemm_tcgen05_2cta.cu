@@ -41,7 +41,9 @@ __device__ long long g2_trace_buf[2 * 6 * 64];
 // round every segment to fp16 and keep the row's fp32 running sums in registers
 // (test/python/triton/test_matmul_kloop.py:87-98).
 constexpr int pair_threads(int epi) { return epi == EPI_KLOOP_F16 ? 320 : THREADS2; }
-template <int STAGES, int NSUB, int EPI>
+// BKB: B is the K-blocked image [k/64][N][64] (GemmArgs::b_kblocked): a K-major operand whose tile
+// of one k-block is contiguous in HBM; loaded and described like the int8 form's transposed B.
+template <int STAGES, int NSUB, int EPI, bool BKB = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(EPI), 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmB2, const TcParams p) {
@@ -51,9 +53,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   // int8 form (EPI_I32): both operands K-major (B arrives transposed, this CTA loads its 128 rows
   // of it), 128 int8 per swizzle row and K = 32 per instruction: the fp16 form's bytes per stage
   constexpr bool I8 = EPI == EPI_I32;
+  constexpr bool BKM = I8 || BKB;  // B arrives K-major
   constexpr uint32_t IDESC = I8 ? make_idesc(/*D=s32*/ 2, /*A=s8*/ 1, /*B=s8*/ 1, 0, /*B K-major*/ 0, 256, BN_MMA)
                                 : make_idesc(/*D=f32*/ 1, /*A=f16*/ 0, /*B=f16*/ 0, /*A K-major*/ 0,
-                                             /*B MN-major*/ 1, 256, BN_MMA);
+                                             /*B MN-major unless K-blocked*/ BKB ? 0 : 1, 256, BN_MMA);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   constexpr int STAGE_BYTES = NSUB * STAGE2_BYTES;
@@ -132,6 +135,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tma_load_2d_pair(sa, &tmA, full, k0, m0);
             if (I8) {
               tma_load_2d_pair(sb, &tmB, full, k0, n0 + (int)rank * 128);  // 128 rows of Bᵀ x 128 bytes
+            } else if (BKB) {
+              // rows (k-block, n) of the image: this CTA's 128 columns of the block, 16 KiB contiguous
+              tma_load_2d_pair(sb, &tmB, full, 0, (kb * NSUB + sub) * p.n + n0 + (int)rank * 128);
             } else if (EPI == EPI_SWIGLU) {
               const CUtensorMap *mb = leader ? &tmB : &tmB2;  // gate half / up half
               tma_load_2d_pair(sb, mb, full, n0, k0);
@@ -183,14 +189,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * STAGE2_BYTES;
             const uint32_t sb = sa + A2_BYTES;
             const uint64_t adesc = smem_desc_sw128(sa, 16, 1024);
-            const uint64_t bdesc = I8 ? smem_desc_sw128(sb, 16, 1024) : smem_desc_sw128(sb, SLAB_BYTES, 1024);
+            const uint64_t bdesc = BKM ? smem_desc_sw128(sb, 16, 1024) : smem_desc_sw128(sb, SLAB_BYTES, 1024);
 #pragma unroll
             for (int k = 0; k < BK2 / 16; ++k) {
               const uint32_t accum = (seg_start && sub == 0 && k == 0) ? 0u : 1u;
               if (I8)
                 mma_i8_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC, accum);
               else
-                mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), IDESC, accum);
+                mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(BKB ? k * 2 : k * 128), IDESC, accum);
             }
           }
           mma_commit_pair(bar_empty + 8 * stage);  // both producers may refill the stage
@@ -229,14 +235,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t sa = smem_base + stage * STAGE_BYTES + sub * STAGE2_BYTES;
             const uint32_t sb = sa + A2_BYTES;
             const uint64_t adesc = smem_desc_sw128(sa, 16, 1024);
-            const uint64_t bdesc = I8 ? smem_desc_sw128(sb, 16, 1024) : smem_desc_sw128(sb, SLAB_BYTES, 1024);
+            const uint64_t bdesc = BKM ? smem_desc_sw128(sb, 16, 1024) : smem_desc_sw128(sb, SLAB_BYTES, 1024);
 #pragma unroll
             for (int k = 0; k < BK2 / 16; ++k) {
               if (I8)
                 mma_i8_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), IDESC,
                             (kb | sub | k) != 0 ? 1u : 0u);
               else
-                mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), IDESC,
+                mma_f16_pair(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(BKB ? k * 2 : k * 128), IDESC,
                              (kb | sub | k) != 0 ? 1u : 0u);
             }
           }
@@ -359,13 +365,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
 constexpr int kSmem2 = 6 * STAGE2_BYTES + 16 * 6 + 64 + 1024;  // the same ring bytes for (6 x 64) and (3 x 128)
 
-template <int STAGES, int NSUB, int EPI>
+template <int STAGES, int NSUB, int EPI, bool BKB = false>
 int launch_pair(const GemmArgs &g, const char *name) {
   constexpr int BN_OUT = (EPI == EPI_SWIGLU) ? 128 : 256;
   Context &c = ctx();
   CUtensorMap tmA, tmB, tmB2;
   B200_TRY(make_map_2d(&tmA, g.a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.k, g.m, g.lda, BK2, BM2));
-  B200_TRY(make_map_2d(&tmB, g.b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.n, g.k, g.ldb, 64, BK2));
+  if (BKB)  // the image as rows of 64 fp16: [ceil(K/64) * N][64], boxes of 128 rows
+    B200_TRY(make_map_2d(&tmB, g.b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, 64, ((g.k + 63) / 64) * g.n, 64, 64, 128));
+  else
+    B200_TRY(make_map_2d(&tmB, g.b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.n, g.k, g.ldb, 64, BK2));
   if (EPI == EPI_SWIGLU)
     B200_TRY(make_map_2d(&tmB2, g.b2, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, g.n, g.k, g.ldb, 64, BK2));
   else
@@ -386,7 +395,7 @@ int launch_pair(const GemmArgs &g, const char *name) {
   p.seg_kb = (EPI == EPI_KLOOP_F16 && g.block_k >= NSUB * BK2) ? g.block_k / (NSUB * BK2) : 1;
   set_push_params(p, g);
   p.status = c.d_status;
-  auto kern = gemm_tc2_kernel<STAGES, NSUB, EPI>;
+  auto kern = gemm_tc2_kernel<STAGES, NSUB, EPI, BKB>;
   static int max_pairs = 0;  // one per template instantiation
   if (max_pairs == 0) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem2));
@@ -421,6 +430,12 @@ extern "C" __attribute__((visibility("default"))) int b200mlir_debug_get_trace2(
 
 template <int STAGES, int NSUB>
 int launch_pair_epi(const GemmArgs &g, const char *name) {
+  if (g.b_kblocked) {
+    if constexpr (NSUB == 1) {
+      if (g.epilogue == EPI_F16) return launch_pair<STAGES, NSUB, EPI_F16, true>(g, name);
+    }
+    return set_error(B200MLIR_ERR_UNSUPPORTED, "a K-blocked B is built for the plain fp16 read-out and 64-deep stages");
+  }
   switch (g.epilogue) {
     case EPI_F16: return launch_pair<STAGES, NSUB, EPI_F16>(g, name);
     case EPI_F32_RES: return launch_pair<STAGES, NSUB, EPI_F32_RES>(g, name);

@@ -30,8 +30,8 @@ constexpr double kCvFactor = 3.0;       // hmx_search.py:1184
 constexpr double kMarginFloor = 0.15;   // hmx_search.py:1185
 constexpr int kReps = 3;                // hexagon_bench reps
 constexpr int kSimtVariant = -1;
-constexpr double kStreamKDrag = 1.05;     // modelled loss of the stream-K form per k-block against whole tiles
-constexpr double kStreamKFixup = 2500.0;  // clocks to combine one more contributor's partial of a cut tile
+constexpr double kStreamKFixup = 4000.0;  // clocks to combine one more contributor's partial of a cut tile
+constexpr double kStreamKDrift = 0.25;    // modelled loss of the k-block phase, in tile times
 
 std::mutex g_cache_mu;
 struct CacheEntry {
@@ -67,13 +67,18 @@ double model_clocks(const TcVariantInfo &vi, int64_t m, int64_t n, int64_t k, in
   const double kblocks = std::ceil((double)k / vi.bk);
   const double per_block = (double)vi.bm * vi.bn * vi.bk * 2.0 / (8192.0 * vi.cta_group) / vi.model_eff;
   if (vi.stream_k) {
-    // k-blocks dealt out evenly: no round is left part-filled, but every tile cut between pairs
-    // costs a trip of its fp32 partials through the workspace (kStreamKFixup clocks on the pair
-    // that combines them), and a pair that changes tile mid-range restarts its accumulator
-    const double units = tiles * kblocks, share = std::ceil(units / std::min(slots, units));
-    const bool cut = std::fmod(tiles, slots) != 0.0 || tiles < slots;
-    const double parts = std::max(1.0, std::ceil(std::min(slots, units) / tiles));  // contributors per cut tile
-    return share * per_block * kStreamKDrag + 1500.0 + (cut ? kStreamKFixup * parts : 0.0);
+    // whole tiles for all rounds but the last full one, then the k-blocks of the last P..2P-1
+    // tiles (all tiles below P) dealt out evenly: no round is left part-filled, but the pair that
+    // combines a cut tile pulls every other contributor's fp32 partial through the workspace
+    if (std::fmod(tiles, slots) == 0.0) return (tiles / slots) * (kblocks * per_block + 1500.0) + 1.0;  // nothing to cut
+    const double dp_rounds = tiles >= slots ? std::floor(tiles / slots) - 1.0 : 0.0;
+    const double sk_tiles = tiles - dp_rounds * slots, units = sk_tiles * kblocks;
+    const double pairs = std::min(slots, units), share = std::ceil(units / pairs);
+    const double others = std::max(1.0, std::ceil(kblocks / share));  // contributors beside the combining pair
+    // measured: pairs that run the same tile's k-range out of step share less in L2 than pairs
+    // that start their tiles together; charged as a quarter of a tile's time
+    return dp_rounds * (kblocks * per_block + 1500.0) + (share + kStreamKDrift * kblocks) * per_block + 1500.0 +
+           kStreamKFixup * others;
   }
   const double waves = std::ceil(tiles / slots);
   return waves * (kblocks * per_block + 1500.0);

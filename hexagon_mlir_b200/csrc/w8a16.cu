@@ -204,6 +204,7 @@ int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, in
     g.m = m; g.n = w.n; g.k = w.k;
     g.lda = lda; g.ldb = w.n; g.ldc = ldc;
     g.epilogue = EPI_F16;
+    g.b_kblocked = true;  // the registry's expanded weight is the K-blocked image
     return gemm_dispatch(g);
   }
   // rows in passes of at most 128 (the widest activation tile the kernel holds)

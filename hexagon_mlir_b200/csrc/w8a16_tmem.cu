@@ -527,14 +527,21 @@ w8a16_expand_kernel(const uint4 *__restrict__ image, const __half *__restrict__ 
     const uint4 v = image[((int64_t)ks * N + n) * 8 + (j ^ (n & 7))];
     const float sc = __half2float(scales[n]);
     const uint32_t words[4] = {v.x, v.y, v.z, v.w};
+    // 16 consecutive k of one channel: 32 contiguous bytes of the K-blocked image
+    // [k/64][n][64] (GemmArgs::b_kblocked); k at or past K reads as zero
+    const int k0 = ks * STEP_K + j * 16;
+    uint32_t outw[8];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const int k = ks * STEP_K + j * 16 + e;
-      if (k < K) {
-        const int q = (int)((words[e >> 2] >> (8 * (e & 3))) & 0xffu) - 128;
-        w16[(int64_t)k * N + n] = __float2half_rn((float)q * sc);
-      }
+    for (int e = 0; e < 16; e += 2) {
+      const int q0 = (int)((words[e >> 2] >> (8 * (e & 3))) & 0xffu) - 128;
+      const int q1 = (int)((words[(e + 1) >> 2] >> (8 * ((e + 1) & 3))) & 0xffu) - 128;
+      const __half h0 = k0 + e < K ? __float2half_rn((float)q0 * sc) : __float2half_rn(0.0f);
+      const __half h1 = k0 + e + 1 < K ? __float2half_rn((float)q1 * sc) : __float2half_rn(0.0f);
+      outw[e >> 1] = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
     }
+    uint4 *dst = reinterpret_cast<uint4 *>(w16 + ((int64_t)(k0 >> 6) * N + n) * 64 + (k0 & 63));
+    dst[0] = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+    dst[1] = make_uint4(outw[4], outw[5], outw[6], outw[7]);
   }
 }
 
@@ -604,7 +611,7 @@ int w8a16_expand_f16(const void *image, const __half *scales_dev, int64_t k, int
   B200_TRY(ensure_ready());
   const int ksteps = (int)((k + STEP_K - 1) / STEP_K);
   void *out = nullptr;
-  B200_CUDA(cudaMalloc(&out, (size_t)k * n * 2));
+  B200_CUDA(cudaMalloc(&out, (size_t)ksteps * STEP_K * n * 2));  // K padded to whole 128-deep steps (two 64-deep blocks each)
   int64_t blocks = ((int64_t)ksteps * n * 8 + 255) / 256;
   const int64_t cap = (int64_t)ctx().sm_count * 32;
   if (blocks > cap) blocks = cap;

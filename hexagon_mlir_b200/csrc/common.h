@@ -48,6 +48,7 @@ struct Options {
   double attention_splits = 0;     // key splits of the attention kernel: 0 chooses by size
   double attention_tiles = 0;      // query tiles per CTA of the attention kernel: 0 chooses by size, 1 or 2
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
+  double row_kernel_walk = -1;     // softmax / RMSNorm grid: 0 one group per row, k resident blocks per SM walking the rows, -1 by size
 };
 
 // The stream kernels are enqueued on is a property of the calling thread: b200mlir_set_stream

@@ -49,6 +49,11 @@ union H8 {
 };
 
 // ---- softmax, fp16, row in registers ------------------------------------------------
+// One row per group of TPR threads (a warp, or the whole block).  The grid may be smaller than
+// the row count: a group then walks rows `first, first + stride, ...` and issues the loads of its
+// NEXT row before it reduces the current one, so that a launch which is one wave deep still has
+// reads arriving while earlier rows are being written (stores of row i, arithmetic of row i+1 and
+// loads of row i+2 are in flight together).
 template <int TPR, int VPL>
 __global__ void __launch_bounds__(TPR > 32 ? TPR : 256)
 softmax_f16_kernel(const __half *__restrict__ x, __half *__restrict__ y, int64_t rows, int cols,
@@ -56,61 +61,76 @@ softmax_f16_kernel(const __half *__restrict__ x, __half *__restrict__ y, int64_t
   __shared__ float scratch[32];
   constexpr int ROWS_PER_BLOCK = TPR > 32 ? 1 : 256 / 32;
   const int lane = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
-  const int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + (TPR > 32 ? 0 : (threadIdx.x >> 5));
-  const bool live = row < rows;  // dead warps still take part in no block-level sync (TPR==32)
+  int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + (TPR > 32 ? 0 : (threadIdx.x >> 5));
+  const int64_t stride = (int64_t)gridDim.x * ROWS_PER_BLOCK;
   pdl_trigger();
-  if (TPR == 32 && !live) return;
+  if (TPR == 32 && row >= rows) return;  // (block-wide groups: every block owns at least one row)
   const int nvec = cols >> 3;
-  const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * ldx);
-  uint4 *yr = reinterpret_cast<uint4 *>(y + row * ldy);
   pdl_wait();
 
-  H8 v[VPL];
+  H8 v[VPL], nv[VPL];
+  {
+    const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * ldx);
 #pragma unroll
-  for (int i = 0; i < VPL; ++i) {
-    int idx = i * TPR + lane;
-    if (idx < nvec) v[i].u = __ldg(xr + idx);
+    for (int i = 0; i < VPL; ++i) {
+      int idx = i * TPR + lane;
+      if (idx < nvec) v[i].u = __ldg(xr + idx);
+    }
   }
-  // 1. running max in f16 (softmax.md:167-177), two lanes per instruction
-  __half2 m2 = __float2half2_rn(-INFINITY);
+  for (; row < rows; row += stride) {
+    const int64_t next = row + stride;
+    if (next < rows) {
+      const uint4 *xn = reinterpret_cast<const uint4 *>(x + next * ldx);
 #pragma unroll
-  for (int i = 0; i < VPL; ++i)
-    if (i * TPR + lane < nvec) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, v[i].h2[j]);
-    }
-  float m = fmaxf(__low2float(m2), __high2float(m2));
-  m = group_reduce<TPR, true>(m, scratch);
-  m2 = __float2half2_rn(m);  // exact: m is an f16 value
-  // 2. e = f16(exp(f32(x - m))) with the subtract in f16; 3. s = sum f32(e)
-  float s = 0.0f;
-#pragma unroll
-  for (int i = 0; i < VPL; ++i)
-    if (i * TPR + lane < nvec) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 z = __half22float2(__hsub2(v[i].h2[j], m2));
-        const __half2 e = __floats2half2_rn(__expf(z.x), __expf(z.y));
-        v[i].h2[j] = e;
-        const float2 ef = __half22float2(e);
-        s += ef.x + ef.y;
+      for (int i = 0; i < VPL; ++i) {
+        int idx = i * TPR + lane;
+        if (idx < nvec) nv[i].u = __ldg(xn + idx);
       }
     }
-  s = group_reduce<TPR, false>(s, scratch);
-  // 4. y = f16(f32(e) / s), as a multiply by the row's reciprocal
-  //    (qcom_hexagon_backend/lib/Transforms/DivToMulOptimizationPass.cpp:9-18)
-  const float inv = __frcp_rn(s);
+    uint4 *yr = reinterpret_cast<uint4 *>(y + row * ldy);
+    // 1. running max in f16 (softmax.md:167-177), two lanes per instruction
+    __half2 m2 = __float2half2_rn(-INFINITY);
 #pragma unroll
-  for (int i = 0; i < VPL; ++i) {
-    int idx = i * TPR + lane;
-    if (idx < nvec) {
+    for (int i = 0; i < VPL; ++i)
+      if (i * TPR + lane < nvec) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 ef = __half22float2(v[i].h2[j]);
-        v[i].h2[j] = __floats2half2_rn(ef.x * inv, ef.y * inv);
+        for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, v[i].h2[j]);
       }
-      yr[idx] = v[i].u;
+    float m = fmaxf(__low2float(m2), __high2float(m2));
+    m = group_reduce<TPR, true>(m, scratch);
+    m2 = __float2half2_rn(m);  // exact: m is an f16 value
+    // 2. e = f16(exp(f32(x - m))) with the subtract in f16; 3. s = sum f32(e)
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+      if (i * TPR + lane < nvec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 z = __half22float2(__hsub2(v[i].h2[j], m2));
+          const __half2 e = __floats2half2_rn(__expf(z.x), __expf(z.y));
+          v[i].h2[j] = e;
+          const float2 ef = __half22float2(e);
+          s += ef.x + ef.y;
+        }
+      }
+    s = group_reduce<TPR, false>(s, scratch);
+    // 4. y = f16(f32(e) / s), as a multiply by the row's reciprocal
+    //    (qcom_hexagon_backend/lib/Transforms/DivToMulOptimizationPass.cpp:9-18)
+    const float inv = __frcp_rn(s);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      int idx = i * TPR + lane;
+      if (idx < nvec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 ef = __half22float2(v[i].h2[j]);
+          v[i].h2[j] = __floats2half2_rn(ef.x * inv, ef.y * inv);
+        }
+        yr[idx] = v[i].u;
+      }
     }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) v[i].u = nv[i].u;
   }
 }
 
@@ -163,6 +183,9 @@ softmax_f32_generic(const float *__restrict__ x, float *__restrict__ y, int64_t 
 }
 
 // ---- RMSNorm -------------------------------------------------------------------------
+// Same row walk as the softmax kernel (next row's loads issued before the current row's
+// reduction); the gain vector is fetched once per thread, before the first reduction, instead of
+// after it.
 template <int TPR, int VPL>
 __global__ void __launch_bounds__(TPR > 32 ? TPR : 256)
 rmsnorm_f16_kernel(const __half *__restrict__ x, const __half *__restrict__ w,
@@ -171,47 +194,67 @@ rmsnorm_f16_kernel(const __half *__restrict__ x, const __half *__restrict__ w,
   __shared__ float scratch[32];
   constexpr int ROWS_PER_BLOCK = TPR > 32 ? 1 : 256 / 32;
   const int lane = TPR > 32 ? threadIdx.x : (threadIdx.x & 31);
-  const int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + (TPR > 32 ? 0 : (threadIdx.x >> 5));
+  int64_t row = (int64_t)blockIdx.x * ROWS_PER_BLOCK + (TPR > 32 ? 0 : (threadIdx.x >> 5));
+  const int64_t stride = (int64_t)gridDim.x * ROWS_PER_BLOCK;
   pdl_trigger();
   if (TPR == 32 && row >= rows) return;
   const int nvec = cols >> 3;
-  const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * ldx);
   const uint4 *wr = reinterpret_cast<const uint4 *>(w);
-  uint4 *yr = reinterpret_cast<uint4 *>(y + row * ldy);
   pdl_wait();
-  H8 v[VPL];
+  H8 v[VPL], nv[VPL], g[VPL];
+  {
+    const uint4 *xr = reinterpret_cast<const uint4 *>(x + row * ldx);
 #pragma unroll
-  for (int i = 0; i < VPL; ++i) {
-    int idx = i * TPR + lane;
-    if (idx < nvec) v[i].u = __ldg(xr + idx);
+    for (int i = 0; i < VPL; ++i) {
+      int idx = i * TPR + lane;
+      if (idx < nvec) v[i].u = __ldg(xr + idx);
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      int idx = i * TPR + lane;
+      if (idx < nvec) g[i].u = __ldg(wr + idx);
+    }
   }
-  float ss = 0.0f;
+  const float inv_cols = 1.0f / (float)cols;
+  for (; row < rows; row += stride) {
+    const int64_t next = row + stride;
+    if (next < rows) {
+      const uint4 *xn = reinterpret_cast<const uint4 *>(x + next * ldx);
 #pragma unroll
-  for (int i = 0; i < VPL; ++i)
-    if (i * TPR + lane < nvec) {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __half22float2(v[i].h2[j]);
-        ss = fmaf(f.x, f.x, ss);
-        ss = fmaf(f.y, f.y, ss);
+      for (int i = 0; i < VPL; ++i) {
+        int idx = i * TPR + lane;
+        if (idx < nvec) nv[i].u = __ldg(xn + idx);
       }
     }
-  ss = group_reduce<TPR, false>(ss, scratch);
-  const float inv = rsqrtf(ss / (float)cols + eps);
+    uint4 *yr = reinterpret_cast<uint4 *>(y + row * ldy);
+    float ss = 0.0f;
 #pragma unroll
-  for (int i = 0; i < VPL; ++i) {
-    int idx = i * TPR + lane;
-    if (idx < nvec) {
-      H8 g;
-      g.u = __ldg(wr + idx);
+    for (int i = 0; i < VPL; ++i)
+      if (i * TPR + lane < nvec) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __half22float2(v[i].h2[j]);
-        float2 gg = __half22float2(g.h2[j]);
-        v[i].h2[j] = __floats2half2_rn(f.x * inv * gg.x, f.y * inv * gg.y);
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __half22float2(v[i].h2[j]);
+          ss = fmaf(f.x, f.x, ss);
+          ss = fmaf(f.y, f.y, ss);
+        }
       }
-      yr[idx] = v[i].u;
+    ss = group_reduce<TPR, false>(ss, scratch);
+    const float inv = rsqrtf(ss * inv_cols + eps);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      int idx = i * TPR + lane;
+      if (idx < nvec) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __half22float2(v[i].h2[j]);
+          float2 gg = __half22float2(g[i].h2[j]);
+          v[i].h2[j] = __floats2half2_rn(f.x * inv * gg.x, f.y * inv * gg.y);
+        }
+        yr[idx] = v[i].u;
+      }
     }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) v[i].u = nv[i].u;
   }
 }
 
@@ -404,24 +447,43 @@ int launch_ew(const __half *a, const __half *b, __half *y, int64_t n, const char
 
 }  // namespace
 
-#define ROW_DISPATCH(KERNEL, ...)                                                        \
+// Grid of a row kernel.  `rows` row groups are wanted (one per row, rows_per_block per block).
+// Option rowKernelWalk: 0 = one group per row (every load of the launch in flight at once);
+// k > 0 = at most k resident blocks per SM and the groups walk the rows (loads of the next row
+// under the arithmetic and the stores of the current one); -1 = the measured choice per kernel
+// (`auto_walk`): softmax is fastest with one group per row at every shape tried (4096x1024 5.05 us
+// against 5.4-7.8 walking; bytes in flight matter more than the overlap), RMSNorm gains from a
+// walk (2048x4096: 7.6 us at 6 blocks per SM against 8.5; 4096x1024: 5.3 at 2 against 5.9).
+static unsigned row_grid(int64_t rows, int rows_per_block, int block_threads, int auto_walk) {
+  const int64_t want = (rows + rows_per_block - 1) / rows_per_block;
+  int walk = (int)ctx().opt.row_kernel_walk;
+  if (walk < 0) walk = auto_walk;
+  if (walk == 0) return (unsigned)want;
+  const int resident = 2048 / block_threads;  // blocks of this size an SM holds
+  const int per_sm = walk > resident ? resident : walk;
+  const int64_t cap = (int64_t)ctx().sm_count * per_sm;
+  if ((int)ctx().opt.row_kernel_walk < 0 && want > cap * 8) return (unsigned)want;  // deep launches: the plain form is at the roofline
+  return (unsigned)(want < cap ? want : cap);
+}
+
+#define ROW_DISPATCH(KERNEL, WALK_WARP, WALK_BLOCK, ...)                                                        \
   do {                                                                                   \
     if (cols <= 256) {                                                                   \
-      launch_pdl(KERNEL<32, 1>, dim3((unsigned)(((rows + 7) / 8))), dim3(256), 0, s, __VA_ARGS__);             \
+      launch_pdl(KERNEL<32, 1>, dim3(row_grid(rows, 8, 256, WALK_WARP)), dim3(256), 0, s, __VA_ARGS__);             \
     } else if (cols <= 512) {                                                            \
-      launch_pdl(KERNEL<32, 2>, dim3((unsigned)(((rows + 7) / 8))), dim3(256), 0, s, __VA_ARGS__);             \
+      launch_pdl(KERNEL<32, 2>, dim3(row_grid(rows, 8, 256, WALK_WARP)), dim3(256), 0, s, __VA_ARGS__);             \
     } else if (cols <= 1024) {                                                           \
-      launch_pdl(KERNEL<32, 4>, dim3((unsigned)(((rows + 7) / 8))), dim3(256), 0, s, __VA_ARGS__);             \
+      launch_pdl(KERNEL<32, 4>, dim3(row_grid(rows, 8, 256, WALK_WARP)), dim3(256), 0, s, __VA_ARGS__);             \
     } else if (cols <= 2048) {                                                           \
-      launch_pdl(KERNEL<32, 8>, dim3((unsigned)(((rows + 7) / 8))), dim3(256), 0, s, __VA_ARGS__);             \
+      launch_pdl(KERNEL<32, 8>, dim3(row_grid(rows, 8, 256, WALK_WARP)), dim3(256), 0, s, __VA_ARGS__);             \
     } else if (cols <= 4096) {                                                           \
-      launch_pdl(KERNEL<128, 4>, dim3((unsigned)(rows)), dim3(128), 0, s, __VA_ARGS__);                        \
+      launch_pdl(KERNEL<128, 4>, dim3(row_grid(rows, 1, 128, WALK_BLOCK)), dim3(128), 0, s, __VA_ARGS__);            \
     } else if (cols <= 8192) {                                                           \
-      launch_pdl(KERNEL<256, 4>, dim3((unsigned)(rows)), dim3(256), 0, s, __VA_ARGS__);                        \
+      launch_pdl(KERNEL<256, 4>, dim3(row_grid(rows, 1, 256, WALK_BLOCK)), dim3(256), 0, s, __VA_ARGS__);            \
     } else if (cols <= 16384) {                                                          \
-      launch_pdl(KERNEL<512, 4>, dim3((unsigned)(rows)), dim3(512), 0, s, __VA_ARGS__);                        \
+      launch_pdl(KERNEL<512, 4>, dim3(row_grid(rows, 1, 512, WALK_BLOCK)), dim3(512), 0, s, __VA_ARGS__);            \
     } else {                                                                             \
-      launch_pdl(KERNEL<1024, 4>, dim3((unsigned)(rows)), dim3(1024), 0, s, __VA_ARGS__);                      \
+      launch_pdl(KERNEL<1024, 4>, dim3(row_grid(rows, 1, 1024, WALK_BLOCK)), dim3(1024), 0, s, __VA_ARGS__);         \
     }                                                                                    \
   } while (0)
 
@@ -472,7 +534,7 @@ int launch_softmax_f16(const __half *x, __half *y, int64_t rows, int64_t cols, i
   if (rows > 0x7fffffff) return set_error(B200MLIR_ERR_BAD_ARG, "softmax: too many rows");
   cudaStream_t s = ctx().stream;
   if (row_fast_path(x, y, cols, ldx, ldy)) {
-    ROW_DISPATCH(softmax_f16_kernel, x, y, rows, (int)cols, ldx, ldy);
+    ROW_DISPATCH(softmax_f16_kernel, 0, 0, x, y, rows, (int)cols, ldx, ldy);
   } else {
     softmax_f16_generic<<<(unsigned)rows, 256, 0, s>>>(x, y, rows, cols, ldx, ldy);
   }
@@ -495,7 +557,7 @@ int launch_rmsnorm_f16(const __half *x, const __half *w, __half *y, int64_t rows
   if (rows > 0x7fffffff) return set_error(B200MLIR_ERR_BAD_ARG, "rms_norm: too many rows");
   cudaStream_t s = ctx().stream;
   if (row_fast_path(x, y, cols, ldx, ldy) && aligned16(w)) {
-    ROW_DISPATCH(rmsnorm_f16_kernel, x, w, y, rows, (int)cols, ldx, ldy, eps);
+    ROW_DISPATCH(rmsnorm_f16_kernel, 2, 6, x, w, y, rows, (int)cols, ldx, ldy, eps);
   } else {
     rmsnorm_generic<__half><<<(unsigned)rows, 256, 0, s>>>(x, w, y, rows, cols, ldx, ldy, eps);
   }

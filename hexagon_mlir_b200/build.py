@@ -13,7 +13,7 @@ OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200mlir.so")
 
 SOURCES = ["runtime.cu", "row_kernels.cu", "layout.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu", "gemm_tcgen05_streamk.cu",
-           "w8a16.cu", "w8a16_tmem.cu", "attention_tmem.cu", "tuner.cu", "report.cu", "entry.cu", "harness_kernels.cu",
+           "w8a16.cu", "w8a16_tmem.cu", "attention_tmem.cu", "tuner.cu", "report.cu", "entry.cu", "harness_kernels.cu", "tp_nccl.cu",
            "readout_executor.cpp"]
 
 NVCC_FLAGS = [
@@ -59,7 +59,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(compile_one, SOURCES))
     if force or _stale(LIB, objs):
-        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs]
+        cmd = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB, *objs, "-ldl"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

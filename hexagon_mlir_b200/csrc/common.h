@@ -48,6 +48,7 @@ struct Options {
   double attention_splits = 0;     // key splits of the attention kernel: 0 chooses by size
   double attention_tiles = 0;      // query tiles per CTA of the attention kernel: 0 chooses by size, 1 or 2
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
+  double replicated_operand_a = 0;  // host-buffer GEMM in a tensor-parallel group: every rank passes the same A; each uploads a row slab and the slabs are exchanged GPU to GPU
   double row_kernel_walk = -1;     // softmax / RMSNorm grid: 0 one group per row, k resident blocks per SM walking the rows, -1 by size
 };
 
@@ -269,6 +270,13 @@ int launch_w8a16_tmem(const __half *a, const void *image, const __half *scales_d
 int launch_attention(const void *q, const void *k, const void *v, void *out, bool f32, int64_t z, int64_t h,
                      int64_t n, int64_t d, int64_t sz, int64_t sh, int64_t sn, int64_t soz, int64_t soh,
                      int64_t son, double sm_scale, bool causal);
+
+// tp_nccl.cu — the process's tensor-parallel group (NCCL bound at run time)
+int tp_rank();
+int tp_world();  // 1 when no group is initialised
+int tp_all_gather_bytes(const void *src, void *dst, size_t bytes_per_rank, cudaStream_t s);
+int tp_all_reduce_f16(void *buf, size_t count, cudaStream_t s);
+int tp_comm_stream(cudaStream_t *s);
 
 // dispatch.cpp
 int gemm_dispatch(const GemmArgs &g);  // picks a variant (option / cache / heuristic) and launches

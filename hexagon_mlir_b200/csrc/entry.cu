@@ -135,6 +135,9 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   // panel edges on multiples of 256 rows / columns (whole tiles of the widest variant)
   const int64_t pm = ((M + P - 1) / P + 255) / 256 * 256, pn = ((N + P - 1) / P + 255) / 256 * 256;
   const int64_t PM = (M + pm - 1) / pm, PN = (N + pn - 1) / pn;
+  // option replicatedOperandA inside a tensor-parallel group: a collective call — every rank
+  // enters with the same M and K (its own B and C column block)
+  const int world = ctx().opt.replicated_operand_a != 0 ? tp_world() : 1;
   cudaStream_t s_in, s_out, s = ctx().stream;
   B200_TRY(copy_streams(&s_in, &s_out));
   void *base = nullptr;
@@ -166,8 +169,17 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   for (int64_t d = 0; d < std::max(PM, PN) && rc == 0; ++d) {
     if (d < PM) {
       const int64_t r0 = d * pm, rows = std::min(pm, M - r0);
-      PIPE_CUDA(cudaMemcpy2DAsync(dA + r0 * K, (size_t)K * 2, (const __half *)A.p + r0 * A.ld, (size_t)A.ld * 2,
-                                  (size_t)K * 2, (size_t)rows, cudaMemcpyHostToDevice, s_in));
+      if (world > 1 && rows % world == 0) {
+        // every rank holds the same A: this rank sends up only its slab of the panel over its own
+        // PCIe link, and the slabs are exchanged GPU to GPU (an in-place all-gather over NVLink)
+        const int64_t slab = rows / world, s0 = r0 + (int64_t)tp_rank() * slab;
+        PIPE_CUDA(cudaMemcpy2DAsync(dA + s0 * K, (size_t)K * 2, (const __half *)A.p + s0 * A.ld, (size_t)A.ld * 2,
+                                    (size_t)K * 2, (size_t)slab, cudaMemcpyHostToDevice, s_in));
+        if (rc == 0) rc = tp_all_gather_bytes(dA + s0 * K, dA + r0 * K, (size_t)slab * K * 2, s_in);
+      } else {
+        PIPE_CUDA(cudaMemcpy2DAsync(dA + r0 * K, (size_t)K * 2, (const __half *)A.p + r0 * A.ld, (size_t)A.ld * 2,
+                                    (size_t)K * 2, (size_t)rows, cudaMemcpyHostToDevice, s_in));
+      }
       PIPE_CUDA(new_event(&a_up[d]));
       PIPE_CUDA(cudaEventRecord(a_up[d], s_in));
     }
@@ -714,6 +726,73 @@ void mlp_block_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *ga
                        int64_t ro, B200MemRef2D *out, float eps, int add_residual, B200_GRID_ARGS) {
   ENTER_KERNEL();
   mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, add_residual, nullptr);
+}
+
+// The tensor-parallel block with the sum over ranks inside the call: every rank computes the
+// partial output of its shard of the hidden dimension (rank 0's carries the residual, so the sum is
+// the finished block) and the partials are added with ncclAllReduce.  `chunks` > 1 cuts the tokens
+// into that many pieces; the all-reduce of a piece runs on a second stream while the next piece is
+// computed.  Device tensors only (the collective works on `out` in place).
+void mlp_block_tp_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
+                          B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
+                          int64_t ro, B200MemRef2D *out, float eps, int chunks, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  if (ensure_ready()) return;
+  const int world = tp_world();
+  if (world == 1) {
+    mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, 1, nullptr);
+    return;
+  }
+  View2 X, O;
+  if (view2("x", rx, x, 2, &X) || view2("out", ro, out, 2, &O)) return;
+  if (X.rows != O.rows || X.cols != O.cols || O.ld != O.cols) {
+    set_error(B200MLIR_ERR_BAD_ARG, "mlp_block_tp: out must be a dense [T, D] tensor of x's shape");
+    return;
+  }
+  if (!is_device_ptr(X.p) || !is_device_ptr(O.p)) {
+    set_error(B200MLIR_ERR_BAD_ARG, "mlp_block_tp: x and out must be device tensors (the all-reduce works on out in place)");
+    return;
+  }
+  const int64_t T = X.rows, D = X.cols;
+  if (T == 0 || D == 0) return;
+  if (chunks < 1) chunks = 1;
+  if (chunks > 16) chunks = 16;
+  const int64_t step = (T + chunks - 1) / chunks;
+  cudaStream_t s = ctx().stream, sc = nullptr;
+  if (chunks > 1 && tp_comm_stream(&sc)) return;
+  cudaEvent_t ev[16] = {}, done[16] = {};
+  int used = 0;
+  const int residual = tp_rank() == 0 ? 1 : 0;
+  for (int64_t r0 = 0; r0 < T; r0 += step, ++used) {
+    const int64_t rows = std::min(step, T - r0);
+    B200MemRef2D xs = *x, os = *out;
+    xs.aligned = (char *)X.p + r0 * X.ld * 2;  xs.offset = 0; xs.sizes[0] = rows; xs.strides[0] = X.ld; xs.strides[1] = 1;
+    os.aligned = (char *)O.p + r0 * O.ld * 2;  os.offset = 0; os.sizes[0] = rows; os.strides[0] = O.ld; os.strides[1] = 1;
+    mlp_block_impl(2, &xs, rg, gain, rwg, wg, rwu, wu, rwd, wd, 2, &os, eps, residual, nullptr);
+    int code = 0;
+    char dummy[8];
+    if ((code = b200mlir_last_error(dummy, sizeof(dummy))) != 0) break;
+    if (chunks == 1) {
+      tp_all_reduce_f16(os.aligned, (size_t)rows * D, s);
+    } else {
+      // fork: the collective of this piece on the side stream, after the piece's kernels
+      if (cudaEventCreateWithFlags(&ev[used], cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventCreateWithFlags(&done[used], cudaEventDisableTiming) != cudaSuccess ||
+          cudaEventRecord(ev[used], s) != cudaSuccess || cudaStreamWaitEvent(sc, ev[used], 0) != cudaSuccess) {
+        set_error(B200MLIR_ERR_CUDA, "mlp_block_tp: event plumbing failed: %s", cudaGetErrorString(cudaGetLastError()));
+        ++used;
+        break;
+      }
+      if (tp_all_reduce_f16(os.aligned, (size_t)rows * D, sc) == 0) cudaEventRecord(done[used], sc);
+    }
+  }
+  if (chunks > 1) {
+    for (int i = 0; i < used; ++i) {  // join: the caller's stream continues after every piece's collective
+      if (done[i]) cudaStreamWaitEvent(s, done[i], 0);
+      if (ev[i]) cudaEventDestroy(ev[i]);
+      if (done[i]) cudaEventDestroy(done[i]);
+    }
+  }
 }
 
 static int fill_push(PushTargets *pt, void *const *peer_recv, int world, int rank, int64_t rows) {

@@ -359,6 +359,7 @@ static double *option_slot(const char *name) {
   if (!strcmp(name, "attentionStage")) return &o.attention_stage;
   if (!strcmp(name, "w8a16ExpandRows")) return &o.w8a16_expand_rows;
   if (!strcmp(name, "rowKernelWalk")) return &o.row_kernel_walk;
+  if (!strcmp(name, "replicatedOperandA")) return &o.replicated_operand_a;
   return nullptr;
 }
 

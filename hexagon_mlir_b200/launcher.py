@@ -208,6 +208,46 @@ def matmul_f32out(a, b, c32, res32=None):
     check()
 
 
+mlp_block_tp = Kernel(
+    "mlp_block_tp_float16", (2, 1, 2, 2, 2, 2),
+    scalars=lambda args, opts: [ctypes.c_float(float(opts.get("eps", 1e-6))), int(opts.get("chunks", 1))])
+_ACCEPTED |= {"chunks"}
+
+
+def tp_unique_id() -> bytes:
+    """128 bytes that name a new tensor-parallel group; rank 0 creates them, every rank passes them to tp_init."""
+    buf = ctypes.create_string_buffer(128)
+    if lib().b200mlir_tp_unique_id(buf) != 0:
+        check()
+    return buf.raw
+
+
+def tp_init(unique_id: bytes, rank: int, world: int) -> None:
+    if len(unique_id) != 128:
+        raise ValueError("the group id is 128 bytes")
+    if lib().b200mlir_tp_init(ctypes.c_char_p(unique_id), int(rank), int(world)) != 0:
+        check()
+
+
+def tp_info():
+    """(initialised, rank, world) of the library's tensor-parallel group."""
+    r, w = ctypes.c_int(), ctypes.c_int()
+    on = lib().b200mlir_tp_info(ctypes.byref(r), ctypes.byref(w))
+    return bool(on), r.value, w.value
+
+
+def tp_shutdown() -> None:
+    if lib().b200mlir_tp_shutdown() != 0:
+        check()
+
+
+def tp_all_reduce(t) -> None:
+    """In-place fp16 sum of a device tensor over the library's group, on the current stream."""
+    _sync_stream([t])
+    if lib().b200mlir_tp_all_reduce_float16(t.data_ptr(), t.numel()) != 0:
+        check()
+
+
 def mlp_block_push(x, gain, wg, wu, wd, peer_recv, world, rank, eps=1e-6):
     """The MLP block whose down projection stores its partial rows into the owners' receive
     buffers (`peer_recv`: one peer-mapped device address per rank)."""

@@ -40,15 +40,32 @@ def _device_mlp(x, gain, wg, wu, wd, out, eps, add_residual):
     _l.mlp_block[(1,)](x, gain, wg, wu, wd, out, eps=eps, add_residual=add_residual)
 
 
+def init_group(group=None) -> None:
+    """Create the library's own NCCL communicator over the ranks of `group` (default: the world):
+    rank 0 draws the 128-byte id in C++, torch.distributed only carries it to the other ranks."""
+    on, _, world = _l.tp_info()
+    want = dist.get_world_size(group)
+    if on:
+        if world != want:
+            raise RuntimeError(f"the library's group has {world} ranks, the process group {want}")
+        return
+    rank = dist.get_rank(group)
+    box = [_l.tp_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    _l.tp_init(box[0], rank, want)
+
+
 class TensorParallelMLP:
     """out = x + down(swiglu(gate(h), up(h))), h = rmsnorm(x)·gain, hidden dimension sharded.
 
     Each rank holds Wg[:, lo:hi], Wu[:, lo:hi], Wd[lo:hi, :] and computes a partial
     [T, D] output (rank 0's includes the residual); the partials are summed with one
     all-reduce per chunk.  The token dimension can be cut into `chunks` pieces so that the
-    all-reduce of piece i runs while piece i+1 is computed; at 2048 tokens one piece is best
-    (a 512-token piece leaves most SM pairs without a 256x256 tile).  `compute` defaults to
-    the library's kernel; the CPU tests of the partitioning logic inject a stand-in.
+    all-reduce of piece i runs while piece i+1 is computed.  The whole step — kernels and
+    ncclAllReduce — is ONE call into the library (`mlp_block_tp_float16`, C++); this class only
+    creates the library's communicator from the process group.  With `compute` given (the CPU tests
+    of the partitioning logic inject a stand-in) the same schedule runs in Python over
+    torch.distributed instead.
     """
 
     def __init__(self, gain, wg, wu, wd, eps=1e-6, group=None, chunks=1, compute=None):
@@ -58,9 +75,12 @@ class TensorParallelMLP:
         self.world = dist.get_world_size(group) if group is not None else 1
         self.rank = dist.get_rank(group) if group is not None else 0
         self.chunks = max(1, int(chunks))
+        self.native = compute is None
         self.compute = compute or _device_mlp
         self._graph = None
         self._graph_key = None
+        if self.native and self.world > 1:
+            init_group(group)
 
     def captured(self, x, out):
         """Run the block through a CUDA graph captured on first use for this (x, out) pair.
@@ -98,6 +118,9 @@ class TensorParallelMLP:
     def __call__(self, x, out):
         if self.world == 1:
             self.compute(x, self.gain, self.wg, self.wu, self.wd, out, self.eps, True)
+            return out
+        if self.native:
+            _l.mlp_block_tp[(1,)](x, self.gain, self.wg, self.wu, self.wd, out, eps=self.eps, chunks=self.chunks)
             return out
         # rank 0's partial carries the residual (added in its down-projection's epilogue), so the
         # all-reduce delivers the finished block: no partial buffer, no separate add pass

@@ -219,6 +219,32 @@ B200_API int b200mlir_tp_reduce_rows_float16(const void *recv, const void *resid
                                              void *const *peer_out, int world, int rank, int64_t rows_per_rank,
                                              int64_t cols);
 
+/* Tensor-parallel group of this process (one process per GPU; NCCL over NVLink, bound at run
+ * time: on a machine without libnccl.so.2 these fail with B200MLIR_ERR_UNSUPPORTED and everything
+ * else works).  Rank 0 obtains 128 bytes with b200mlir_tp_unique_id and hands them to the other
+ * ranks by any means (a file, a pipe, a socket, MPI); every rank then calls
+ * b200mlir_tp_init(id, rank, world) once, after b200mlir_init.  b200mlir_tp_info returns 1 and the
+ * rank / world when a group exists, 0 (rank 0 of 1) otherwise.  No counterpart in the reference,
+ * which drives one device. */
+B200_API int b200mlir_tp_unique_id(void *id128);
+B200_API int b200mlir_tp_init(const void *id128, int rank, int world);
+B200_API int b200mlir_tp_info(int *rank, int *world);
+B200_API int b200mlir_tp_shutdown(void);
+/* In-place sum over the group of `count` fp16 elements at the device address `buf`
+ * (ncclAllReduce on the calling thread's stream). */
+B200_API int b200mlir_tp_all_reduce_float16(void *buf, int64_t count);
+/* The MLP block, tensor-parallel, reduction included: each rank passes its column block of Wg / Wu
+ * and its row block of Wd (as for mlp_block_float16) and the same x; on return (in stream order)
+ * every rank's `out` holds x + down(swiglu(gate(h), up(h))).  Rank 0's partial carries the
+ * residual, the partials are summed in place with one ncclAllReduce per token chunk; `chunks` > 1
+ * runs the all-reduce of a chunk on a second stream while the next chunk is computed.  x and out
+ * are device tensors, out dense.  Without a group it is mlp_block_float16 with the residual.  A
+ * collective call: every rank of the group must make it, with the same T, D and chunks. */
+B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_gain, B200MemRef1D *gain,
+                                   int64_t rank_wg, B200MemRef2D *wg, int64_t rank_wu, B200MemRef2D *wu,
+                                   int64_t rank_wd, B200MemRef2D *wd, int64_t rank_o, B200MemRef2D *out,
+                                   float eps, int chunks, B200_GRID_ARGS);
+
 /* The two-phase ("online") softmax of test/python/triton/test_online_softmax.py:27-77, fp32 rows:
  * running maximum and running sum over column blocks, then exp(x - m) / l.  The block sizes are
  * tl.constexpr there and do not change the result beyond fp32 round-off (the test's tolerance is

@@ -4,13 +4,18 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Headline workload: the large fp16 GEMM M=16384, N=16384, K=8192 (fp32
-accumulate, U[-1,1] inputs, seed 4), N-sharded over the ranks — one step is one
-pass of that GEMM; `value` is whole-job TFLOP/s with inputs resident in HBM.
-`e2e` is the same metric through the C-ABI kernel entry point with pinned HOST
-buffers (copies inside the timed region).  `extra` carries the other configs
-(1024^3 and 4096^3 GEMM, softmax GB/s, w8a16 GB/s, MLP tokens/s).
-`--impl reference` times the CPU restatement of the reference's lowering on the
-host cores on a bounded sample of the same workload.
+accumulate, U[-1,1] inputs), N-sharded over the ranks — one step is one pass of
+that GEMM; `value` is whole-job TFLOP/s with inputs resident in HBM.  `e2e` is
+the same metric through the C-ABI kernel entry point with pinned HOST buffers
+(copies inside the timed region).  `extra` carries the other configs (1024^3
+and 4096^3 GEMM, softmax GB/s, w8a16 GB/s, MLP tokens/s).  `--impl reference`
+times the CPU restatement of the reference's lowering on the host cores on a
+bounded sample of the same workload.
+
+Inputs come from one counter-based generator (Philox4x32-10) implemented in the
+library (device), in the oracle's C++ and in numpy: A is seed 4, B seed 5, both
+U[-1,1); the CPU legs draw the same bytes, and `parity_sample` compares 64
+random 128x128 tiles of the timed GEMM's own output with the oracle.
 """
 from __future__ import annotations
 
@@ -31,6 +36,7 @@ import numpy as np  # noqa: E402
 M, N, K = 16384, 16384, 8192
 WORKLOAD = f"gemm_f16_{M}x{N}x{K}"
 FLOPS = 2.0 * M * N * K
+SEED_A, SEED_B = 4, 5
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -92,19 +98,36 @@ class ClockSampler:
 
 # ---- the reference arm / CPU baseline: the oracle on host cores -----------------------------
 
-# dram__bytes_read.sum + dram__bytes_write.sum of the 16384x16384x8192 launch (one ncu capture)
-HEADLINE_DRAM_BYTES_PER_LAUNCH = 8.371e9 + 0.532e9
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch, by (variant, M, N, K): each entry comes
+# from an ncu capture whose summary is committed under profiles/ (file and capture date beside the
+# number).  A run whose variant or shape has no capture reports traffic null.
+DRAM_TRAFFIC_CAPTURES = {
+    ("tc256x256x64_2cta_s6", 16384, 16384, 8192): {
+        "bytes": 8.371e9 + 0.532e9, "profile": "profiles/bench_gemm_16384x16384x8192_launches.md", "captured": "2026-11-25"},
+}
 
 
-def cpu_gemm_sample(target_s: float = 12.0):
-    """Times the CPU restatement on a slab of M rows (full N, K) sized to about target_s."""
+def operand_rows(r0, rows):
+    """Rows [r0, r0+rows) of A as the device holds them (same generator, same seed)."""
+    import oracle
+    return oracle.random_rows(r0, rows, K, np.float16, SEED_A, oracle.UNIFORM, -1.0, 1.0)
+
+
+def operand_cols(c0, cols):
+    """Columns [c0, c0+cols) of the whole B [K, N]."""
+    import oracle
+    return oracle.random_cols(c0, cols, K, N, np.float16, SEED_B, oracle.UNIFORM, -1.0, 1.0)
+
+
+def cpu_gemm_sample(target_s: float = 4.0):
+    """The CPU restatement on a slab of M rows (full N, K) sized to about target_s per pass; the
+    operands are the bytes the GPU arm multiplies."""
     import oracle
     threads = oracle.hw_threads()
-    rng = np.random.Generator(np.random.Philox(4))
-    b = rng.uniform(-1, 1, (K, N)).astype(np.float16)
+    b = oracle.fill_random((K, N), np.float16, SEED_B, oracle.UNIFORM, -1.0, 1.0)
 
     def once(rows):
-        a = rng.uniform(-1, 1, (rows, K)).astype(np.float16)
+        a = operand_rows(0, rows)
         t0 = time.perf_counter()
         oracle.gemm_f16(a, b, threads=threads)
         return time.perf_counter() - t0
@@ -115,24 +138,28 @@ def cpu_gemm_sample(target_s: float = 12.0):
     fixed = max(t_small - per_row * threads, 0.0)
     rows = int(max(threads, min(4096, (target_s - fixed) / per_row)))
     rows -= rows % threads
-    a = rng.uniform(-1, 1, (max(rows, threads), K)).astype(np.float16)
+    a = operand_rows(0, max(rows, threads))
     return a, b, a.shape[0], threads
 
 
 def cpu_time_once(a, b, threads):
     import oracle
     t0 = time.perf_counter()
-    oracle.gemm_f16(a, b, threads=threads)
-    return time.perf_counter() - t0
+    c = oracle.gemm_f16(a, b, threads=threads)
+    return time.perf_counter() - t0, c
 
 
-def cpu_baseline(target_s: float = 12.0):
+def cpu_baseline(target_s: float = 4.0):
+    """One warm pass, then three timed ones; the median is reported (the harness protocol of the
+    reference: repetitions and quantiles, backend/hmx_search.py:1109-1171)."""
     a, b, rows, threads = cpu_gemm_sample(target_s)
-    dt = cpu_time_once(a, b, threads)
+    cpu_time_once(a, b, threads)
+    times = sorted(cpu_time_once(a, b, threads)[0] for _ in range(3))
+    dt = times[1]
     tflops = 2.0 * rows * N * K / dt / 1e12
     return {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-            "sample": f"{rows} of {M} rows of A (full N={N}, K={K}), one pass, {dt:.2f} s; "
-                      f"whole-problem time extrapolates linearly to {dt * M / rows:.0f} s"}
+            "sample": f"rows 0..{rows} of {M} of A (full N={N}, K={K}), one warm pass + 3 timed, median {dt:.2f} s "
+                      f"(min {times[0]:.2f}, max {times[2]:.2f}); whole problem extrapolates linearly to {dt * M / rows:.0f} s"}
 
 
 def run_reference_arm(args):
@@ -142,10 +169,11 @@ def run_reference_arm(args):
     a, b, rows, threads = cpu_gemm_sample(target_s=max(2.0, 40.0 / max(1, args.steps + args.warmup)))
     for _ in range(args.warmup):
         cpu_time_once(a, b, threads)
-    times = [cpu_time_once(a, b, threads) for _ in range(args.steps)]
+    times = [cpu_time_once(a, b, threads)[0] for _ in range(args.steps)]
     dt = sum(times) / len(times)
     tflops = 2.0 * rows * N * K / dt / 1e12
-    sample = f"{rows} of {M} rows of A per step (full N={N}, K={K}); CPU restatement of the reference lowering"
+    sample = (f"rows 0..{rows} of {M} of A per step (full N={N}, K={K}), the GPU arm's own operand bytes; "
+              "CPU restatement of the reference lowering")
     line = {
         "impl": "reference", "metric": "gemm_f16_tflops", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
@@ -356,11 +384,33 @@ def extras_single_gpu(torch, hm, peaks, only=None):
                 wf()
             ms = graph_timed(torch, wf, reps=10, inner=8)
             ms_hot = graph_timed(torch, wf_same, reps=10, inner=8)
+            # the same weight under an L2 persistence window (registered with l2_persist: the decode
+            # case of weight residency); other traffic (an 80 MB copy between launches) competes for L2
+            hm.unregister_w8a16_weight(Wq[0])
+            hm.register_w8a16_weight(Wq[0], S, l2_persist=True)
+            noise_src = torch.empty(40 << 20, dtype=torch.uint8, device=dev)
+            noise_dst = torch.empty_like(noise_src)
+
+            def wf_noise():
+                noise_dst.copy_(noise_src)
+                hm.w8a16_matmul[(1,)](a, Wq[0], S, c)
+
+            def noise_only():
+                noise_dst.copy_(noise_src)
+            ms_persist = graph_timed(torch, wf_noise, reps=10, inner=8) - graph_timed(torch, noise_only, reps=10, inner=8)
+            hm.unregister_w8a16_weight(Wq[0])
+            hm.register_w8a16_weight(Wq[0], S, l2_persist=False)
+            ms_plain_noise = graph_timed(torch, wf_noise, reps=10, inner=8) - graph_timed(torch, noise_only, reps=10, inner=8)
+            del noise_src, noise_dst
             bytes_ = k * n + 2 * n + 2 * mrows * k + 2 * mrows * n
             gbs = bytes_ / (ms * 1e-3) / 1e9
             out[f"w8a16_m{mrows}_4096x11008"] = {
-                "us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                "us_weight_in_l2": ms_hot * 1e3, "tflops": 2.0 * mrows * k * n / (ms * 1e-3) / 1e12}
+                "us": ms * 1e3, "us_cold": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                "us_weight_in_l2": ms_hot * 1e3,
+                "us_persisting_l2": ms_persist * 1e3, "us_no_window_same_traffic": ms_plain_noise * 1e3,
+                "persisting_note": "one weight re-used with an 80 MB copy between launches; with and without the L2 "
+                                   "persistence window; the copy's own time subtracted",
+                "tflops": 2.0 * mrows * k * n / (ms * 1e-3) / 1e12}
         for wq_ in Wq:
             hm.unregister_w8a16_weight(wq_)
         del Wq
@@ -429,60 +479,84 @@ def extras_single_gpu(torch, hm, peaks, only=None):
 
 
 def mlp_extra(torch, hm, dist, rank, world):
-    """C4: Llama MLP block, 2048 tokens x 4096, ffn 11008, tensor-parallel over the ranks."""
+    """C4: Llama MLP block, 2048 tokens x 4096, ffn 11008, tensor-parallel over the ranks.  Every N is
+    timed the same way: the whole step (kernels and, at N > 1, the all-reduce — one call into the
+    library) replayed from a CUDA graph.  `phases_us` is a separate, eager run with events between
+    the block's phases."""
     from hexagon_mlir_b200 import tp
     t, d, f = 2048, 4096, 11008
-    g = torch.Generator(device="cuda").manual_seed(3)
-    x = torch.randn((t, d), generator=g, device="cuda").half()
+    x = torch.empty((t, d), dtype=torch.float16, device="cuda")
+    hm.fill_random(x, 3, hm.NORMAL, 0.0, 1.0)
     gain = torch.ones(d, dtype=torch.float16, device="cuda")
     lo, hi = tp.shard_bounds(f, rank, world)
-    g2 = torch.Generator(device="cuda").manual_seed(300 + rank)
-    wg = (torch.randn((d, hi - lo), generator=g2, device="cuda") * 0.02).half()
-    wu = (torch.randn((d, hi - lo), generator=g2, device="cuda") * 0.02).half()
-    wd = (torch.randn((hi - lo, d), generator=g2, device="cuda") * 0.02).half()
+
+    def shard(seed, shape, rows=None, cols=None):
+        full = torch.empty(shape, dtype=torch.float16, device="cuda")
+        hm.fill_random(full, seed, hm.NORMAL, 0.0, 0.02)
+        part = full[:, lo:hi] if cols else full[lo:hi]
+        return part.contiguous()
+    wg, wu, wd = shard(31, (d, f), cols=True), shard(32, (d, f), cols=True), shard(33, (f, d), rows=True)
     out = torch.empty_like(x)
-    block = tp.TensorParallelMLP(gain, wg, wu, wd, eps=1e-6, group=dist.group.WORLD if world > 1 else None)
-
-    def step():
+    group = dist.group.WORLD if world > 1 else None
+    block = tp.TensorParallelMLP(gain, wg, wu, wd, eps=1e-6, group=group)
+    block.captured(x, out)
+    ms = timed(torch, lambda: block.captured(x, out), 20, 5, dist if world > 1 else None)
+    mode = "cuda-graph"
+    # per-phase times (eager, events inside the call)
+    hm.set_option("mlpPhaseTiming", 1)
+    for _ in range(3):
         block(x, out)
-    mode = "eager"
-    if world > 1:
-        try:
-            block.captured(x, out)
-
-            def step():
-                block.captured(x, out)
-            mode = "cuda-graph"
-        except Exception as exc:  # capture of the collective is an optimisation, not a requirement
-            mode = f"eager ({type(exc).__name__})"
-    ms = timed(torch, step, 20, 5, dist if world > 1 else None)
+    phases = {k: round(v, 2) for k, v in hm.mlp_phase_times().items()}
+    hm.set_option("mlpPhaseTiming", 0)
+    torch.cuda.synchronize()
     flops = 6.0 * t * d * f
-    block.release()  # the captured graph holds NCCL work: drop it before the process group goes
-    reduction = "nccl all-reduce" if world > 1 else "none"
+    reduction = "ncclAllReduce inside mlp_block_tp_float16 (C++)" if world > 1 else "none"
     forms = {}
     if world > 1:
-        # the same block with the reduction fused into the kernels (peer stores over NVLink)
         forms["nccl_all_reduce_ms"] = ms
+        # two token chunks: the all-reduce of chunk 0 under the kernels of chunk 1
+        try:
+            b2 = tp.TensorParallelMLP(gain, wg, wu, wd, eps=1e-6, group=group, chunks=2)
+            b2.captured(x, out)
+            forms["nccl_two_chunks_ms"] = timed(torch, lambda: b2.captured(x, out), 20, 5, dist)
+            b2.release()
+            if forms["nccl_two_chunks_ms"] < ms:
+                ms, reduction = forms["nccl_two_chunks_ms"], reduction + ", two token chunks overlapped"
+        except Exception as exc:  # noqa: BLE001
+            forms["nccl_two_chunks_ms"] = f"unavailable ({type(exc).__name__})"
+        # the same block with the reduction fused into the kernels (peer stores over NVLink)
         try:
             fused = tp.FusedTensorParallelMLP(gain, wg, wu, wd, tokens=t, eps=1e-6, group=dist.group.WORLD)
-            fms = timed(torch, lambda: fused(x), 20, 5, dist)
-            fmode = "eager"
-            try:
-                fused.captured(x)
-                gms = timed(torch, lambda: fused.captured(x), 20, 5, dist)
-                if gms < fms:
-                    fms, fmode = gms, "cuda-graph"
-            except Exception:  # capture of the symmetric-memory barriers is an optimisation only
-                pass
+            fused.captured(x)
+            fms = timed(torch, lambda: fused.captured(x), 20, 5, dist)
             fused.release()
             forms["fused_peer_store_ms"] = fms
-            forms["fused_launch"] = fmode
             if fms < ms:
-                ms, reduction, mode = fms, "fused: read-out pushes partial rows to their owners", fmode
+                ms, reduction = fms, "fused: read-out pushes partial rows to their owners"
         except Exception as exc:  # symmetric memory is a property of the box, not of this code
             forms["fused_peer_store_ms"] = f"unavailable ({type(exc).__name__})"
+    block.release()  # the captured graph holds NCCL work: drop it before the process group goes
     return {"ms": ms, "reduction": reduction, **forms, "tokens_per_s": t / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
-            "parallelism": f"tp{world}", "allreduce_bytes": t * d * 2 if world > 1 else 0, "launch": mode}
+            "parallelism": f"tp{world}", "allreduce_bytes": t * d * 2 if world > 1 else 0, "launch": mode,
+            "phases_us": phases}
+
+
+def parity_sample(torch, hm, c, n_lo, tiles=64, tile=128):
+    """`tiles` random tile x tile blocks of the timed GEMM's output against the oracle (full K);
+    the operand rows and columns are drawn on the CPU from the generator that filled the device."""
+    import oracle
+    rng = np.random.Generator(np.random.Philox(1234))
+    picks = set()
+    while len(picks) < tiles:
+        picks.add((int(rng.integers(c.shape[0] // tile)), int(rng.integers(c.shape[1] // tile))))
+    worst, rows_cache = 0.0, {}
+    for tm, tn in sorted(picks):
+        if tm not in rows_cache:
+            rows_cache[tm] = operand_rows(tm * tile, tile)
+        want = oracle.gemm_f16(rows_cache[tm], operand_cols(n_lo + tn * tile, tile)).astype(np.float32)
+        got = c[tm * tile:(tm + 1) * tile, tn * tile:(tn + 1) * tile].cpu().numpy().astype(np.float32)
+        worst = max(worst, float(np.abs(got - want).max() / max(float(np.abs(want).max()), 1e-30)))
+    return {"tiles": len(picks), "tile": tile, "max_abs_rel": worst, "against": "oracle.gemm_f16, full K"}
 
 
 def run_product_arm(args):
@@ -514,13 +588,16 @@ def run_product_arm(args):
         os.write(json_fd, (line + "\n").encode())
         return 0
 
-    # inputs resident in HBM: A replicated, this rank's column block of B and C
+    # inputs resident in HBM: A replicated, this rank's column block of B and C; the bytes are the
+    # generator's (A seed 4, the whole B seed 5), so every rank and the CPU legs see the same operands
     n_lo, n_hi = rank * N // world, (rank + 1) * N // world
     n_loc = n_hi - n_lo
-    g = torch.Generator(device="cuda").manual_seed(4)
-    a = (torch.rand((M, K), generator=g, device="cuda") * 2 - 1).half()
-    gb = torch.Generator(device="cuda").manual_seed(40 + rank)
-    b = (torch.rand((K, n_loc), generator=gb, device="cuda") * 2 - 1).half()
+    a = torch.empty((M, K), dtype=torch.float16, device="cuda")
+    hm.fill_random(a, SEED_A, hm.UNIFORM, -1.0, 1.0)
+    b_full = torch.empty((K, N), dtype=torch.float16, device="cuda")
+    hm.fill_random(b_full, SEED_B, hm.UNIFORM, -1.0, 1.0)
+    b = b_full[:, n_lo:n_hi].contiguous() if world > 1 else b_full
+    del b_full
     c = torch.empty((M, n_loc), dtype=torch.float16, device="cuda")
 
     def step():
@@ -539,12 +616,32 @@ def run_product_arm(args):
     kernel_tflops = (2.0 * M * n_loc * K) / (ms * 1e-3) / 1e12  # this rank's kernel
     plan = hm.gemm_explain(M, n_loc, K)
 
-    # sampled parity of the timed result against the CUDA-core path on 64 random tiles is in
-    # the test-suite; here only a checksum guard that the kernel wrote something sane
-    if not bool(torch.isfinite(c[:256, :256].float()).all()):
-        raise SystemExit("bench.py: non-finite output")
+    # the same loop kept running for --min-time seconds: the chip settles at the clock its power
+    # limit allows, and time x median SM MHz lets runs at different N be compared at equal clocks
+    long_run = None
+    if args.min_time > 0:
+        per_round = max(1, int(0.25 / (ms * 1e-3)))
+        total_ms, total_steps = 0.0, 0
+        with ClockSampler(local) as lclk:
+            t_wall = time.perf_counter()
+            while time.perf_counter() - t_wall < args.min_time:
+                total_ms += timed(torch, step, per_round, 0, dist if multi else None) * per_round
+                total_steps += per_round
+        lsum = lclk.summary()
+        lms = total_ms / total_steps
+        long_run = {"seconds": round(time.perf_counter() - t_wall, 2), "steps": total_steps, "ms_per_step": lms,
+                    "value": FLOPS / (lms * 1e-3) / 1e12, "sm_mhz_median": lsum["sm_mhz"], "reasons": lsum["reasons"],
+                    "ms_x_mhz": lms * lsum["sm_mhz"] if lsum["sm_mhz"] else None}
 
-    # e2e: same GEMM through the kernel entry point with pinned host buffers
+    # parity of the timed result itself (untimed): sampled tiles against the oracle
+    parity = parity_sample(torch, hm, c, n_lo) if rank == 0 else None
+    if parity is not None and not parity["max_abs_rel"] <= 1e-2:
+        raise SystemExit(f"bench.py: the timed GEMM disagrees with the oracle: {parity}")
+
+    # e2e: same GEMM through the kernel entry point with pinned host buffers.  At N > 1 every rank's
+    # host holds the same A: each rank sends up its 1/N row slab over its own PCIe link and the
+    # slabs are exchanged GPU to GPU inside the call (option replicatedOperandA; needs the library's
+    # own communicator, which tp.init_group creates).
     e2e_steps = max(1, min(2, args.steps))
     ha = torch.empty((M, K), dtype=torch.float16).pin_memory()
     hb = torch.empty((K, n_loc), dtype=torch.float16).pin_memory()
@@ -553,12 +650,24 @@ def run_product_arm(args):
     hb.copy_(b)
     torch.cuda.synchronize()
     npa, npb, npc = ha.numpy(), hb.numpy(), hc.numpy()
+    sharded_upload = False
+    if multi:
+        from hexagon_mlir_b200 import tp
+        tp.init_group(dist.group.WORLD)
+        hm.set_option("replicatedOperandA", 1)
+        sharded_upload = True
 
     def e2e_step():
         hm.matmul[(1,)](npa, npb, npc)  # H2D A and B, GEMM, D2H C, wait — all inside the call
     e2e_ms = timed(torch, e2e_step, e2e_steps, 1, dist if multi else None)
+    hm.set_option("replicatedOperandA", 0)
     e2e_tflops = FLOPS / (e2e_ms * 1e-3) / 1e12
-    e2e_ok = bool(torch.equal(hc[:128].cuda(), c[:128]))
+    # the strips of the host path and the whole-problem device run may take different variants
+    # (fp32 sums associated differently): agreement is stated as an error, not as byte equality
+    sl = slice(0, 256)
+    dref = c[sl].float()
+    e2e_err = float((hc[sl].cuda().float() - dref).abs().max() / dref.abs().max())
+    h2d_step = (M * K // (world if sharded_upload else 1) + K * n_loc) * 2 * world
     del ha, hb, hc
 
     extra = {}
@@ -575,25 +684,28 @@ def run_product_arm(args):
         dist.barrier()
     if rank == 0:
         peak = peaks["bf16_tflops"]
+        capture = DRAM_TRAFFIC_CAPTURES.get((plan["name"], M, n_loc, K))
         line = {
             "metric": "gemm_f16_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "sharding": f"N split over {world} rank(s), A replicated, no collective",
                        "l2": "inputs larger than L2 (A 268 MB per rank)", "variant": plan["name"],
+                       "inputs": f"Philox4x32-10, A seed {SEED_A}, B seed {SEED_B}, U[-1,1)",
                        "accumulate": "fp32 in TMEM, one fp16 rounding"},
             "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
                          "frac": kernel_tflops / peak,
-                         # DRAM read + write bytes of one whole-problem launch (ncu capture summarised in
-                         # profiles/bench_gemm_16384x16384x8192_launches.md); not captured for the shards at N > 1
-                         "traffic": HEADLINE_DRAM_BYTES_PER_LAUNCH if world == 1 else None,
+                         "traffic": (capture or {}).get("bytes"), "traffic_source": capture,
                          "peak_source": f"{peak_kind} cuBLAS bf16 burst; sustained {peaks.get('bf16_tflops_sustained')}",
                          "frac_of_sustained": kernel_tflops / peaks.get("bf16_tflops_sustained", peak),
                          "frac_of_nominal_2250": kernel_tflops / 2250.0,
                          "algorithmic_flops_per_launch": 2.0 * M * n_loc * K},
             "cpu_baseline": cpu,
-            "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": (M * K + K * n_loc) * 2 * world,
-                    "d2h_bytes_per_step": M * n_loc * 2 * world, "steps": e2e_steps, "matches_device_run": e2e_ok},
+            "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_step,
+                    "d2h_bytes_per_step": M * n_loc * 2 * world, "steps": e2e_steps,
+                    "a_upload": "1/N row slab per rank, slabs all-gathered over NVLink" if sharded_upload else "whole A",
+                    "max_abs_rel_vs_device_run": e2e_err},
+            "parity_sample": parity, "long_run": long_run,
             "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
         }
         sys.stdout.flush()
@@ -619,6 +731,8 @@ def main():
     ap.add_argument("--case", default="", help="run one case of `extra` only (profiling captures): gemm_f16_1024, "
                                                "gemm_f16_4096, gemm_f16_8192, kloop, gemm_i8, softmax, rmsnorm, swiglu, w8a16, attention_f16_4x16x4096x64, ...")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--min-time", type=float, default=2.0,
+                    help="seconds the timed GEMM loop is kept running for the long-run value (0: skip)")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -49,6 +49,7 @@ struct Options {
   double attention_tiles = 0;      // query tiles per CTA of the attention kernel: 0 chooses by size, 1 or 2
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
   double replicated_operand_a = 0;  // host-buffer GEMM in a tensor-parallel group: every rank passes the same A; each uploads a row slab and the slabs are exchanged GPU to GPU
+  double mlp_phase_timing = 0;      // the MLP block records an event after each of its phases (b200mlir_mlp_phase_times reads them; the read synchronises)
   double row_kernel_walk = -1;     // softmax / RMSNorm grid: 0 one group per row, k resident blocks per SM walking the rows, -1 by size
 };
 

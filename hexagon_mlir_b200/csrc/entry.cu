@@ -669,6 +669,21 @@ void w8a16_matmul(int64_t ra, B200MemRef2D *a, int64_t rw, B200MemRef2D *wq, int
   }
 }
 
+// Phase stamps of the most recent MLP block on this thread (option mlpPhaseTiming): events after
+// the block's start, RMSNorm, gate/up GEMM, down GEMM and, in the tensor-parallel entry, the collective.
+struct PhaseStamps {
+  cudaEvent_t ev[5] = {};
+  int n = 0;
+  void mark(int i) {
+    if (ctx().opt.mlp_phase_timing == 0) return;
+    if (!ev[i] && cudaEventCreate(&ev[i]) != cudaSuccess) return;
+    cudaEventRecord(ev[i], ctx().stream);
+    if (i + 1 > n) n = i + 1;
+    if (i == 0) n = 1;
+  }
+};
+static thread_local PhaseStamps t_phases;
+
 // rmsnorm -> gate/up GEMM with SwiGLU read-out -> down GEMM.  The down GEMM either writes
 // `out` (with the residual when asked) or, given push targets, stores its fp16 partial rows
 // into the receive slots of the ranks that own them.
@@ -697,6 +712,7 @@ static void mlp_block_impl(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D
     return;
   void *h = nullptr, *act = nullptr;
   if (workspace((size_t)T * D * 2, &h) || workspace2((size_t)T * F * 2, &act)) return;
+  t_phases.mark(0);
   // 1. h = rmsnorm(x) * gain
   if (launch_rmsnorm_f16((const __half *)dx, (const __half *)dg, (__half *)h, T, D, X.ld, D, eps)) return;
   // 2. act = silu(h·Wg) * (h·Wu), fused in the GEMM epilogue
@@ -704,7 +720,9 @@ static void mlp_block_impl(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D
   g1.a = h; g1.b = dwg; g1.b2 = dwu; g1.c = act;
   g1.m = T; g1.n = F; g1.k = D; g1.lda = D; g1.ldb = WG.ld; g1.ldc = F;
   g1.epilogue = EPI_SWIGLU;
+  t_phases.mark(1);
   if (gemm_dispatch(g1)) return;
+  t_phases.mark(2);
   // 3. out = act·Wd (+ x through the f32 residual read-out), or the partial rows pushed to their owners
   GemmArgs g2;
   g2.a = act; g2.b = dwd; g2.c = dout;
@@ -718,6 +736,7 @@ static void mlp_block_impl(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D
     g2.ldres = X.ld;
   }
   if (gemm_dispatch(g2)) return;
+  t_phases.mark(3);
   st.finish();
 }
 
@@ -774,6 +793,7 @@ void mlp_block_tp_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D 
     if ((code = b200mlir_last_error(dummy, sizeof(dummy))) != 0) break;
     if (chunks == 1) {
       tp_all_reduce_f16(os.aligned, (size_t)rows * D, s);
+      t_phases.mark(4);
     } else {
       // fork: the collective of this piece on the side stream, after the piece's kernels
       if (cudaEventCreateWithFlags(&ev[used], cudaEventDisableTiming) != cudaSuccess ||
@@ -826,6 +846,28 @@ int b200mlir_tp_reduce_rows_float16(const void *recv, const void *residual, int6
     return set_error(B200MLIR_ERR_BAD_ARG, "tp_reduce_rows: device buffers required");
   return launch_reduce_rows_push((const __half *)recv, (const __half *)residual, ldres, peer_out, world, rank,
                                  rows_per_rank, cols);
+}
+
+int b200mlir_mlp_phase_times(double *us, int cap) {
+  clear_error();
+  if (!us || cap < 1) {
+    set_error(B200MLIR_ERR_BAD_ARG, "mlp_phase_times: null buffer");
+    return -1;
+  }
+  PhaseStamps &ph = t_phases;
+  if (ph.n < 2) return 0;
+  int out = 0;
+  cudaError_t e = cudaEventSynchronize(ph.ev[ph.n - 1]);
+  for (int i = 1; e == cudaSuccess && i < ph.n && out < cap; ++i, ++out) {
+    float ms = 0;
+    e = cudaEventElapsedTime(&ms, ph.ev[i - 1], ph.ev[i]);
+    us[out] = (double)ms * 1000.0;
+  }
+  if (e != cudaSuccess) {
+    set_error(B200MLIR_ERR_CUDA, "mlp_phase_times: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  return out;
 }
 
 int b200mlir_pack_weight_f16(const void *src, void *dst, int64_t k, int64_t n, int64_t ld) {

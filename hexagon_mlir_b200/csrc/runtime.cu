@@ -360,6 +360,7 @@ static double *option_slot(const char *name) {
   if (!strcmp(name, "w8a16ExpandRows")) return &o.w8a16_expand_rows;
   if (!strcmp(name, "rowKernelWalk")) return &o.row_kernel_walk;
   if (!strcmp(name, "replicatedOperandA")) return &o.replicated_operand_a;
+  if (!strcmp(name, "mlpPhaseTiming")) return &o.mlp_phase_timing;
   return nullptr;
 }
 

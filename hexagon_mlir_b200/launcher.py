@@ -248,6 +248,16 @@ def tp_all_reduce(t) -> None:
         check()
 
 
+def mlp_phase_times():
+    """{"rmsnorm", "gate_up", "down"[, "collective"]} in microseconds for the last MLP block issued with
+    option mlpPhaseTiming set."""
+    buf = (ctypes.c_double * 8)()
+    n = lib().b200mlir_mlp_phase_times(buf, 8)
+    if n < 0:
+        check()
+    return dict(zip(("rmsnorm", "gate_up", "down", "collective"), [buf[i] for i in range(n)]))
+
+
 def mlp_block_push(x, gain, wg, wu, wd, peer_recv, world, rank, eps=1e-6):
     """The MLP block whose down projection stores its partial rows into the owners' receive
     buffers (`peer_recv`: one peer-mapped device address per rank)."""

@@ -245,6 +245,14 @@ B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank
                                    int64_t rank_wd, B200MemRef2D *wd, int64_t rank_o, B200MemRef2D *out,
                                    float eps, int chunks, B200_GRID_ARGS);
 
+/* Phase times of the most recent MLP block issued by the calling thread while option
+ * "mlpPhaseTiming" was non-zero: microseconds of RMSNorm, gate/up GEMM (SwiGLU read-out), down
+ * GEMM and — tensor-parallel entry with one chunk — the all-reduce, from CUDA events recorded
+ * between the phases.  Returns how many were written (0 when none were recorded, -1 on error); synchronises
+ * with the last phase.  The analogue of the reference's per-region cycle counts
+ * (qcom_hexagon_backend/lib/Transforms/HexagonLWPInstrumentation.cpp). */
+B200_API int b200mlir_mlp_phase_times(double *us, int cap);
+
 /* The two-phase ("online") softmax of test/python/triton/test_online_softmax.py:27-77, fp32 rows:
  * running maximum and running sum over column blocks, then exp(x - m) / l.  The block sizes are
  * tl.constexpr there and do not change the result beyond fp32 round-off (the test's tolerance is

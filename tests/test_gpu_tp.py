@@ -60,8 +60,26 @@ def _worker(rank, world, port, q):
     torch.cuda.synchronize()
     status = status or hm.device_status()
     fused_same = all(torch.equal(r, runs[0]) for r in runs)
-    q.put((rank, status, out.cpu().numpy(), lo, hi, cshard.cpu().numpy(), runs[0].cpu().numpy(), fused_same))
+    # the library's own communicator exists (the block created it): a host-buffer GEMM whose A every
+    # rank holds — each rank uploads its row slab of every panel, the slabs are all-gathered on the GPUs
+    on, lib_rank, lib_world = hm.tp_info()
+    rng = np.random.Generator(np.random.Philox(11))
+    m, k, n_loc = 4096, 4096, 4224
+    ha = rng.uniform(-1, 1, (m, k)).astype(np.float16)                      # the same on every rank
+    hb = np.random.Generator(np.random.Philox(12 + rank)).uniform(-1, 1, (k, n_loc)).astype(np.float16)
+    hc = np.zeros((m, n_loc), np.float16)
+    hm.set_option("replicatedOperandA", 1)
+    hm.matmul[(1,)](ha, hb, hc)
+    hm.set_option("replicatedOperandA", 0)
+    status = status or hm.device_status()
+    rows = np.arange(0, m, 97)
+    import oracle
+    want = oracle.gemm_f16(np.ascontiguousarray(ha[rows]), hb).astype(np.float32)
+    host_err = float(np.abs(hc[rows].astype(np.float32) - want).max() / np.abs(want).max())
+    q.put((rank, status, out.cpu().numpy(), lo, hi, cshard.cpu().numpy(), runs[0].cpu().numpy(), fused_same,
+           (on, lib_rank, lib_world), host_err))
     dist.barrier()
+    hm.tp_shutdown()
     q.close()
     q.join_thread()  # results flushed to the parent
     os._exit(0)      # (tearing the group down under live symmetric-memory mappings can block)
@@ -85,8 +103,10 @@ def test_tensor_parallel_mlp_on_gpus(oracle, cuda, world):
     x, gain, wg, wu, wd = _problem()
     want = oracle.mlp(x, gain, wg, wu, wd, 1e-6).astype(np.float32)
     full = np.zeros((x.shape[0], wg.shape[1]), np.float16)
-    for rank, status, out, lo, hi, cshard, fused_out, fused_same in results:
+    for rank, status, out, lo, hi, cshard, fused_out, fused_same, lib_group, host_err in results:
         assert status == 0
+        assert lib_group == (True, rank, world)       # ncclAllReduce ran inside the library, on its own communicator
+        assert host_err <= 1e-2, (rank, host_err)      # sharded upload + all-gather of A
         err = np.abs(out.astype(np.float32) - want).max() / np.abs(want).max()
         assert err <= 1e-2, (rank, err)
         full[:, lo:hi] = cshard

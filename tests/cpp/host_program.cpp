@@ -150,7 +150,12 @@ int main(int argc, char **argv) {
   std::vector<pid_t> kids;
   for (int r = 0; r < world; ++r) {
     pid_t pid = fork();
-    if (pid == 0) _exit(run_rank(r, world, rd[r], wr));
+    if (pid == 0) {
+      const int rc = run_rank(r, world, rd[r], wr);
+      fflush(stdout);
+      fflush(stderr);
+      _exit(rc);
+    }
     kids.push_back(pid);
   }
   int bad = 0;

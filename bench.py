@@ -535,6 +535,20 @@ def mlp_extra(torch, hm, dist, rank, world):
                 ms, reduction = fms, "fused: read-out pushes partial rows to their owners"
         except Exception as exc:  # symmetric memory is a property of the box, not of this code
             forms["fused_peer_store_ms"] = f"unavailable ({type(exc).__name__})"
+        # the all-reduce by this library's own kernel over NVSwitch multicast (multimem.ld_reduce / multimem.st)
+        try:
+            mc = tp.MulticastTensorParallelMLP(gain, wg, wu, wd, tokens=t, eps=1e-6, group=dist.group.WORLD)
+            if mc.available():
+                mc.captured(x)
+                mms = timed(torch, lambda: mc.captured(x), 20, 5, dist)
+                mc.release()
+                forms["multicast_all_reduce_ms"] = mms
+                if mms < ms:
+                    ms, reduction = mms, "own kernel over NVSwitch multicast: multimem.ld_reduce + multimem.st"
+            else:
+                forms["multicast_all_reduce_ms"] = "unavailable (no multicast mapping)"
+        except Exception as exc:  # noqa: BLE001
+            forms["multicast_all_reduce_ms"] = f"unavailable ({type(exc).__name__}: {exc})"[:200]
     block.release()  # the captured graph holds NCCL work: drop it before the process group goes
     return {"ms": ms, "reduction": reduction, **forms, "tokens_per_s": t / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
             "parallelism": f"tp{world}", "allreduce_bytes": t * d * 2 if world > 1 else 0, "launch": mode,

@@ -162,6 +162,9 @@ int launch_add_f16(const __half *a, const __half *b, __half *y, int64_t n);
 int launch_reduce_rows_push(const __half *recv, const __half *residual, int64_t ldres, void *const *peer_out,
                             int world, int rank, int64_t rows_per_rank, int64_t cols);
 
+// sum over the ranks' copies of elements [offset, offset + count) of a multicast-mapped fp16 buffer, written back to every copy
+int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offset, int64_t count);
+
 // layout.cu
 int launch_transpose_i8(const int8_t *src, int8_t *dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst);
 int launch_pack_weight_f16(const uint16_t *src, uint16_t *dst, int64_t k, int64_t n, int64_t ld);

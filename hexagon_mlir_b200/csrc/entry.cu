@@ -848,6 +848,11 @@ int b200mlir_tp_reduce_rows_float16(const void *recv, const void *residual, int6
                                  rows_per_rank, cols);
 }
 
+int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_out, int64_t elem_offset, int64_t count) {
+  clear_error();
+  return launch_allreduce_multimem(mc_in, mc_out, elem_offset, count);
+}
+
 int b200mlir_mlp_phase_times(double *us, int cap) {
   clear_error();
   if (!us || cap < 1) {

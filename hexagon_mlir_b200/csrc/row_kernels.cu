@@ -425,6 +425,38 @@ reduce_rows_push_kernel(const ReducePushParams p) {
   }
 }
 
+// All-reduce of one rank's slice through the NVSwitch's multicast addresses: `mc_in` and `mc_out`
+// are multicast mappings of a buffer every rank of the group holds at the same offset.  One
+// multimem.ld_reduce returns the SUM over all ranks' copies of 8 fp16 values (added in fp32 inside
+// the switch, rounded once); one multimem.st writes the result into every rank's copy.  A rank
+// reduces only its own slice, so per GPU 1/world of the buffer comes in and 1/world goes out —
+// against (world-1)/world each way for exchanges through peer loads and stores.
+__global__ void __launch_bounds__(256)
+allreduce_multimem_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ mc_out, int64_t nvec) {
+  constexpr int UNR = 4;
+  for (int64_t base = ((int64_t)blockIdx.x * 256) * UNR + threadIdx.x; base < nvec;
+       base += (int64_t)gridDim.x * 256 * UNR) {
+    uint32_t v[UNR][4];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t i = base + (int64_t)u * 256;
+      if (i < nvec)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3])
+                     : "l"(mc_in + i)
+                     : "memory");
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t i = base + (int64_t)u * 256;
+      if (i < nvec)
+        asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_out + i), "r"(v[u][0]),
+                     "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3])
+                     : "memory");
+    }
+  }
+}
+
 template <int OP>
 int launch_ew(const __half *a, const __half *b, __half *y, int64_t n, const char *what) {
   B200_TRY(ensure_ready());
@@ -520,6 +552,23 @@ int launch_reduce_rows_push(const __half *recv, const __half *residual, int64_t 
     default: reduce_rows_push_kernel<0><<<g, 256, 0, ctx().stream>>>(p); break;
   }
   return check_launch("reduce_rows_push");
+}
+
+int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offset, int64_t count) {
+  B200_TRY(ensure_ready());
+  if (!mc_in || !mc_out || elem_offset < 0 || count < 0 || elem_offset % 8 || count % 8 || !aligned16(mc_in) ||
+      !aligned16(mc_out))
+    return set_error(B200MLIR_ERR_BAD_ARG,
+                     "allreduce_multimem: multicast addresses 16-byte aligned, offset and count multiples of 8 elements");
+  if (count == 0) return 0;
+  const int64_t nvec = count >> 3;
+  int64_t blocks = (nvec + 256 * 4 - 1) / (256 * 4);
+  const int64_t cap = (int64_t)ctx().sm_count * 4;
+  if (blocks > cap) blocks = cap;
+  allreduce_multimem_kernel<<<(unsigned)blocks, 256, 0, ctx().stream>>>(
+      reinterpret_cast<const uint4 *>((const __half *)mc_in + elem_offset),
+      reinterpret_cast<uint4 *>((__half *)mc_out + elem_offset), nvec);
+  return check_launch("allreduce_multimem");
 }
 
 static bool row_fast_path(const void *x, const void *y, int64_t cols, int64_t ldx, int64_t ldy) {

@@ -251,7 +251,9 @@ std::vector<Measured> enumerate(const GemmArgs &g) {
     r.variant = v;
     r.label = tc_variant_info(v).name;
     r.verdict = tc_variant_verdict(v, g);
-    r.model = model_clocks(tc_variant_info(v), g.m, g.n, g.k, ctx().sm_count ? ctx().sm_count : 148);
+    // (the SwiGLU read-out multiplies by [Wg | Wu] side by side: twice the columns of work per output column)
+    r.model = model_clocks(tc_variant_info(v), g.m, g.epilogue == EPI_SWIGLU ? 2 * g.n : g.n, g.k,
+                           ctx().sm_count ? ctx().sm_count : 148);
     rows.push_back(r);
   }
   std::stable_sort(rows.begin(), rows.end(), [](const Measured &a, const Measured &b) {

@@ -248,6 +248,14 @@ def tp_all_reduce(t) -> None:
         check()
 
 
+def tp_allreduce_multimem(mc_in: int, mc_out: int, elem_offset: int, count: int, like=None) -> None:
+    """This rank's slice of an all-reduce through the switch's multicast addresses (see the header)."""
+    if like is not None:
+        _sync_stream([like])
+    if lib().b200mlir_tp_allreduce_multimem_float16(int(mc_in), int(mc_out), int(elem_offset), int(count)) != 0:
+        check()
+
+
 def mlp_phase_times():
     """{"rmsnorm", "gate_up", "down"[, "collective"]} in microseconds for the last MLP block issued with
     option mlpPhaseTiming set."""

@@ -211,6 +211,72 @@ class FusedTensorParallelMLP:
         return self.out
 
 
+class MulticastTensorParallelMLP:
+    """The block with its all-reduce done by this library's own kernel over NVSwitch multicast.
+
+    Every rank writes its fp16 partial [T, D] (rank 0's with the residual) into a symmetric buffer;
+    after a barrier each rank sums ITS rows over all ranks' copies with `multimem.ld_reduce` (the
+    switch adds in fp32 and rounds once) and writes the sums into every copy with `multimem.st`;
+    after a second barrier every rank holds the block output.  Per GPU 1/world of the buffer
+    crosses NVLink in each direction.  Needs a multicast mapping (NVSwitch; `available()` tells),
+    tokens divisible by the world size."""
+
+    def __init__(self, gain, wg, wu, wd, tokens, eps=1e-6, group=None, timeout_ms=10000):
+        import torch.distributed._symmetric_memory as symm
+        if group is None:
+            group = dist.group.WORLD
+        self.gain, self.wg, self.wu, self.wd = gain, wg, wu, wd
+        self.eps = float(eps)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.tokens, self.width = int(tokens), int(wd.shape[1])
+        if self.tokens % self.world:
+            raise ValueError("tokens must be divisible by the world size")
+        self.rows = self.tokens // self.world
+        self.timeout_ms = int(timeout_ms)
+        self.out = symm.empty((self.tokens, self.width), dtype=torch.float16, device=wd.device)
+        self._h = symm.rendezvous(self.out, group)
+        self._mc = int(getattr(self._h, "multicast_ptr", 0) or 0)
+        self._graph = None
+
+    def available(self) -> bool:
+        return self._mc != 0
+
+    def __call__(self, x):
+        """Returns the block output (a buffer this object owns; valid until the next call)."""
+        if not self._mc:
+            raise RuntimeError("no multicast mapping on this machine")
+        _l.mlp_block[(1,)](x, self.gain, self.wg, self.wu, self.wd, self.out, eps=self.eps, add_residual=self.rank == 0)
+        self._h.barrier(channel=0, timeout_ms=self.timeout_ms)   # every rank's partial is written
+        n = self.rows * self.width
+        _l.tp_allreduce_multimem(self._mc, self._mc, self.rank * n, n, like=self.out)
+        self._h.barrier(channel=1, timeout_ms=self.timeout_ms)   # every rank's rows have been written everywhere
+        return self.out
+
+    def captured(self, x):
+        key = (x.data_ptr(), tuple(x.shape))
+        if self._graph is None or self._graph_key != key:
+            self(x)
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                self(x)
+                torch.cuda.synchronize()
+                with torch.cuda.graph(graph, stream=side):
+                    self(x)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self._graph, self._graph_key = graph, key
+        self._graph.replay()
+        return self.out
+
+    def release(self):
+        if self._graph is not None:
+            torch.cuda.synchronize()
+            self._graph = None
+
+
 class ColumnShardedGemm:
     """C[:, lo:hi] = A · B[:, lo:hi] on each rank; A replicated; no collective."""
 

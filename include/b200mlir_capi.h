@@ -245,6 +245,17 @@ B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank
                                    int64_t rank_wd, B200MemRef2D *wd, int64_t rank_o, B200MemRef2D *out,
                                    float eps, int chunks, B200_GRID_ARGS);
 
+/* This rank's share of an all-reduce through NVSwitch multicast (NVLS): `mc_in` / `mc_out` are
+ * MULTICAST addresses of fp16 buffers that every rank of the group holds (the symmetric-memory
+ * mapping the host obtained for them; they may be the same buffer).  Elements
+ * [elem_offset, elem_offset + count) are summed over all ranks' copies inside the switch (fp32
+ * accumulation, one rounding) and the sums are written to every rank's copy.  Each rank calls it
+ * for its own disjoint slice after a barrier that follows the producers of the data, and a second
+ * barrier makes the result visible everywhere; the barriers are the caller's.  Offsets and counts
+ * in elements, multiples of 8.  No reference counterpart (single device). */
+B200_API int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_out, int64_t elem_offset,
+                                                    int64_t count);
+
 /* Phase times of the most recent MLP block issued by the calling thread while option
  * "mlpPhaseTiming" was non-zero: microseconds of RMSNorm, gate/up GEMM (SwiGLU read-out), down
  * GEMM and — tensor-parallel entry with one chunk — the all-reduce, from CUDA events recorded

@@ -60,6 +60,17 @@ def _worker(rank, world, port, q):
     torch.cuda.synchronize()
     status = status or hm.device_status()
     fused_same = all(torch.equal(r, runs[0]) for r in runs)
+    # the all-reduce by the library's own kernel over the switch's multicast addresses, where the
+    # machine maps them (bit-identical on every rank and run to run, or skipped)
+    mc = tp.MulticastTensorParallelMLP(T(gain), tp.shard_columns(T(wg), rank, world), tp.shard_columns(T(wu), rank, world),
+                                       tp.shard_rows(T(wd), rank, world), tokens=x.shape[0], eps=1e-6,
+                                       group=dist.group.WORLD, timeout_ms=20000)
+    mc_out = None
+    if mc.available():
+        mruns = [mc(xt).clone() for _ in range(3)]
+        torch.cuda.synchronize()
+        status = status or hm.device_status()
+        mc_out = (mruns[0].cpu().numpy(), all(torch.equal(r, mruns[0]) for r in mruns))
     # the library's own communicator exists (the block created it): a host-buffer GEMM whose A every
     # rank holds — each rank uploads its row slab of every panel, the slabs are all-gathered on the GPUs
     on, lib_rank, lib_world = hm.tp_info()
@@ -77,7 +88,7 @@ def _worker(rank, world, port, q):
     want = oracle.gemm_f16(np.ascontiguousarray(ha[rows]), hb).astype(np.float32)
     host_err = float(np.abs(hc[rows].astype(np.float32) - want).max() / np.abs(want).max())
     q.put((rank, status, out.cpu().numpy(), lo, hi, cshard.cpu().numpy(), runs[0].cpu().numpy(), fused_same,
-           (on, lib_rank, lib_world), host_err))
+           (on, lib_rank, lib_world), host_err, mc_out))
     dist.barrier()
     hm.tp_shutdown()
     q.close()
@@ -103,10 +114,14 @@ def test_tensor_parallel_mlp_on_gpus(oracle, cuda, world):
     x, gain, wg, wu, wd = _problem()
     want = oracle.mlp(x, gain, wg, wu, wd, 1e-6).astype(np.float32)
     full = np.zeros((x.shape[0], wg.shape[1]), np.float16)
-    for rank, status, out, lo, hi, cshard, fused_out, fused_same, lib_group, host_err in results:
+    for rank, status, out, lo, hi, cshard, fused_out, fused_same, lib_group, host_err, mc_out in results:
         assert status == 0
         assert lib_group == (True, rank, world)       # ncclAllReduce ran inside the library, on its own communicator
         assert host_err <= 1e-2, (rank, host_err)      # sharded upload + all-gather of A
+        if mc_out is not None:
+            merr = np.abs(mc_out[0].astype(np.float32) - want).max() / np.abs(want).max()
+            assert merr <= 1e-2 and mc_out[1], (rank, merr)
+            assert np.array_equal(mc_out[0], results[0][10][0])
         err = np.abs(out.astype(np.float32) - want).max() / np.abs(want).max()
         assert err <= 1e-2, (rank, err)
         full[:, lo:hi] = cshard

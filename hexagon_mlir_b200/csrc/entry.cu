@@ -5,6 +5,7 @@
 // dispatcher.  Nothing here computes on the CPU.
 #include <algorithm>
 #include <cstdlib>
+#include <functional>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -687,9 +688,16 @@ static thread_local PhaseStamps t_phases;
 // rmsnorm -> gate/up GEMM with SwiGLU read-out -> down GEMM.  The down GEMM either writes
 // `out` (with the residual when asked) or, given push targets, stores its fp16 partial rows
 // into the receive slots of the ranks that own them.
+// `down_chunks` > 1 cuts the DOWN projection (only) into that many token chunks and calls
+// `after_chunk(first row, rows, device address of the chunk's output rows)` after each one's
+// launch: the tensor-parallel entry starts the chunk's collective there.  RMSNorm and the gate/up
+// GEMM always cover all tokens (cut into chunks they would fill the SM pairs worse; the down
+// projection's 256 x 256 tiles divide evenly over token halves).
+typedef std::function<int(int64_t, int64_t, void *)> ChunkHook;
 static void mlp_block_impl(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
                            B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
-                           int64_t ro, B200MemRef2D *out, float eps, int add_residual, const PushTargets *push) {
+                           int64_t ro, B200MemRef2D *out, float eps, int add_residual, const PushTargets *push,
+                           int down_chunks = 1, const ChunkHook *after_chunk = nullptr) {
   if (ensure_ready()) return;
   View2 X, WG, WU, WD, O{nullptr, 0, 0, 0};
   View1 G;
@@ -735,8 +743,25 @@ static void mlp_block_impl(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D
     g2.res = dx;
     g2.ldres = X.ld;
   }
-  if (gemm_dispatch(g2)) return;
-  t_phases.mark(3);
+  if (push || down_chunks <= 1) {
+    if (gemm_dispatch(g2)) return;
+    t_phases.mark(3);
+    if (after_chunk && (*after_chunk)(0, T, dout)) return;
+  } else {
+    // token chunks on multiples of 256 rows (whole tiles of the pair kernel)
+    int64_t step = ((T + down_chunks - 1) / down_chunks + 255) / 256 * 256;
+    for (int64_t r0 = 0; r0 < T; r0 += step) {
+      const int64_t rows = std::min(step, T - r0);
+      GemmArgs gc = g2;
+      gc.a = (const __half *)act + r0 * F;
+      gc.c = (__half *)dout + r0 * g2.ldc;
+      if (gc.res) gc.res = (const __half *)dx + r0 * X.ld;
+      gc.m = rows;
+      if (gemm_dispatch(gc)) return;
+      if (after_chunk && (*after_chunk)(r0, rows, gc.c)) return;
+    }
+    t_phases.mark(3);
+  }
   st.finish();
 }
 
@@ -749,9 +774,9 @@ void mlp_block_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *ga
 
 // The tensor-parallel block with the sum over ranks inside the call: every rank computes the
 // partial output of its shard of the hidden dimension (rank 0's carries the residual, so the sum is
-// the finished block) and the partials are added with ncclAllReduce.  `chunks` > 1 cuts the tokens
-// into that many pieces; the all-reduce of a piece runs on a second stream while the next piece is
-// computed.  Device tensors only (the collective works on `out` in place).
+// the finished block) and the partials are added with ncclAllReduce.  `chunks` > 1 cuts the down
+// projection into that many token chunks; the all-reduce of a chunk runs on a second stream while
+// the next chunk's GEMM is computed.  Device tensors only (the collective works on `out` in place).
 void mlp_block_tp_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
                           B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
                           int64_t ro, B200MemRef2D *out, float eps, int chunks, B200_GRID_ARGS) {
@@ -772,46 +797,38 @@ void mlp_block_tp_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D 
     set_error(B200MLIR_ERR_BAD_ARG, "mlp_block_tp: x and out must be device tensors (the all-reduce works on out in place)");
     return;
   }
-  const int64_t T = X.rows, D = X.cols;
-  if (T == 0 || D == 0) return;
+  const int64_t D = X.cols;
+  if (X.rows == 0 || D == 0) return;
   if (chunks < 1) chunks = 1;
   if (chunks > 16) chunks = 16;
-  const int64_t step = (T + chunks - 1) / chunks;
   cudaStream_t s = ctx().stream, sc = nullptr;
   if (chunks > 1 && tp_comm_stream(&sc)) return;
   cudaEvent_t ev[16] = {}, done[16] = {};
   int used = 0;
-  const int residual = tp_rank() == 0 ? 1 : 0;
-  for (int64_t r0 = 0; r0 < T; r0 += step, ++used) {
-    const int64_t rows = std::min(step, T - r0);
-    B200MemRef2D xs = *x, os = *out;
-    xs.aligned = (char *)X.p + r0 * X.ld * 2;  xs.offset = 0; xs.sizes[0] = rows; xs.strides[0] = X.ld; xs.strides[1] = 1;
-    os.aligned = (char *)O.p + r0 * O.ld * 2;  os.offset = 0; os.sizes[0] = rows; os.strides[0] = O.ld; os.strides[1] = 1;
-    mlp_block_impl(2, &xs, rg, gain, rwg, wg, rwu, wu, rwd, wd, 2, &os, eps, residual, nullptr);
-    int code = 0;
-    char dummy[8];
-    if ((code = b200mlir_last_error(dummy, sizeof(dummy))) != 0) break;
+  ChunkHook hook = [&](int64_t, int64_t rows, void *dst) -> int {
     if (chunks == 1) {
-      tp_all_reduce_f16(os.aligned, (size_t)rows * D, s);
+      int rc = tp_all_reduce_f16(dst, (size_t)rows * D, s);
       t_phases.mark(4);
-    } else {
-      // fork: the collective of this piece on the side stream, after the piece's kernels
-      if (cudaEventCreateWithFlags(&ev[used], cudaEventDisableTiming) != cudaSuccess ||
-          cudaEventCreateWithFlags(&done[used], cudaEventDisableTiming) != cudaSuccess ||
-          cudaEventRecord(ev[used], s) != cudaSuccess || cudaStreamWaitEvent(sc, ev[used], 0) != cudaSuccess) {
-        set_error(B200MLIR_ERR_CUDA, "mlp_block_tp: event plumbing failed: %s", cudaGetErrorString(cudaGetLastError()));
-        ++used;
-        break;
-      }
-      if (tp_all_reduce_f16(os.aligned, (size_t)rows * D, sc) == 0) cudaEventRecord(done[used], sc);
+      return rc;
     }
-  }
-  if (chunks > 1) {
-    for (int i = 0; i < used; ++i) {  // join: the caller's stream continues after every piece's collective
-      if (done[i]) cudaStreamWaitEvent(s, done[i], 0);
-      if (ev[i]) cudaEventDestroy(ev[i]);
-      if (done[i]) cudaEventDestroy(done[i]);
+    // fork: this chunk's collective on the side stream, after the chunk's GEMM
+    if (used >= 16) return set_error(B200MLIR_ERR_BAD_ARG, "mlp_block_tp: too many chunks");
+    if (cudaEventCreateWithFlags(&ev[used], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&done[used], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventRecord(ev[used], s) != cudaSuccess || cudaStreamWaitEvent(sc, ev[used], 0) != cudaSuccess) {
+      ++used;
+      return set_error(B200MLIR_ERR_CUDA, "mlp_block_tp: event plumbing failed: %s", cudaGetErrorString(cudaGetLastError()));
     }
+    int rc = tp_all_reduce_f16(dst, (size_t)rows * D, sc);
+    if (rc == 0) cudaEventRecord(done[used], sc);
+    ++used;
+    return rc;
+  };
+  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, tp_rank() == 0 ? 1 : 0, nullptr, chunks, &hook);
+  for (int i = 0; i < used; ++i) {  // join: the caller's stream continues after every chunk's collective
+    if (done[i]) cudaStreamWaitEvent(s, done[i], 0);
+    if (ev[i]) cudaEventDestroy(ev[i]);
+    if (done[i]) cudaEventDestroy(done[i]);
   }
 }
 

@@ -237,7 +237,8 @@ B200_API int b200mlir_tp_all_reduce_float16(void *buf, int64_t count);
  * and its row block of Wd (as for mlp_block_float16) and the same x; on return (in stream order)
  * every rank's `out` holds x + down(swiglu(gate(h), up(h))).  Rank 0's partial carries the
  * residual, the partials are summed in place with one ncclAllReduce per token chunk; `chunks` > 1
- * runs the all-reduce of a chunk on a second stream while the next chunk is computed.  x and out
+ * cuts the down projection into token chunks (whole 256-row tiles) and runs the all-reduce of a
+ * chunk on a second stream while the next chunk's GEMM is computed.  x and out
  * are device tensors, out dense.  Without a group it is mlp_block_float16 with the residual.  A
  * collective call: every rank of the group must make it, with the same T, D and chunks. */
 B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_gain, B200MemRef1D *gain,

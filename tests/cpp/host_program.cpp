@@ -95,7 +95,7 @@ static int run_rank(int rank, int world, int id_read_fd, const std::vector<int> 
   const int on = b200mlir_tp_info(&r, &w);
   if ((world > 1) != (on == 1) || r != (world > 1 ? rank : 0) || w != world) { fprintf(stderr, "rank %d: tp_info says %d %d %d\n", rank, on, r, w); return 1; }
 
-  const int T = 256, D = 512, F = 1024;  // F / world columns per rank
+  const int T = 512, D = 512, F = 1024;  // F / world columns per rank; two 256-row chunks of the down projection
   std::vector<f16> x((size_t)T * D), gain(D), wg((size_t)D * F), wu((size_t)D * F), wd((size_t)F * D);
   fill(x, 1.0f); for (auto &g : gain) g = (f16)(1.0f + 0.25f * uniform()); fill(wg, 0.05f); fill(wu, 0.05f); fill(wd, 0.05f);
   // the unsharded block on the CPU: rmsnorm -> gate/up -> silu(gate)*up -> down -> + x

@@ -254,7 +254,6 @@ struct W8A16Weight {
   size_t image_bytes = 0;
   bool l2_persist = false;
 };
-int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes);
 int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
                  int64_t ldc);
 // Above option w8a16ExpandRows activation rows (default 64) every CTA of the streaming kernel

@@ -321,7 +321,7 @@ int register_weight_locked(const void *wq, const void *scales, int64_t k, int64_
     B200_CUDA(cudaMemcpyAsync(tmp, wq, (size_t)k * n, cudaMemcpyHostToDevice, c.stream));
     wq_dev = (const int8_t *)tmp;
   }
-  int rc = w8a16_build_image(wq_dev, k, n, &w.image, &w.image_bytes);
+  int rc = w8a16_build_tmem_image(wq_dev, k, n, &w.image, &w.image_bytes);
   if (rc == 0) {
     cudaError_t e = cudaMalloc(&w.scales_dev, (size_t)n * 2);
     if (e == cudaSuccess) e = cudaMemcpyAsync(w.scales_dev, scales, (size_t)n * 2, cudaMemcpyDefault, c.stream);
@@ -655,7 +655,7 @@ void w8a16_matmul(int64_t ra, B200MemRef2D *a, int64_t rw, B200MemRef2D *wq, int
     const void *dw, *ds;
     if (st.in(W.p, (size_t)W.rows * W.cols, &dw) || st.in(S.p, (size_t)S.n * 2, &ds)) return;
     local.k = W.rows; local.n = W.cols; local.scales_dev = const_cast<void *>(ds);
-    if (w8a16_build_image((const int8_t *)dw, W.rows, W.cols, &local.image, &local.image_bytes)) return;
+    if (w8a16_build_tmem_image((const int8_t *)dw, W.rows, W.cols, &local.image, &local.image_bytes)) return;
     tmp_w = local.image;
   }
   const void *da;

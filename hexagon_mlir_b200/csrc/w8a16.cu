@@ -56,11 +56,8 @@ __device__ __forceinline__ uint32_t dq2(uint32_t word, uint32_t selector) {
   return out;
 }
 
-// MT = number of 16-row tiles of A (M <= 16*MT).
-// BLOCKED selects the image layout: false = strip-major [strip][kstep][lane],
-// true = the resident blocked image [n/256][k/64][strip 0..7][kstep 0..3][lane]
-// (w8a16_decode.cu), where `ksteps` counts the padded k16 steps (4 per chunk).
-template <int MT, bool BLOCKED>
+// MT = number of 16-row tiles of A (M <= 16*MT).  The image is strip-major [strip][kstep][lane].
+template <int MT>
 __global__ void __launch_bounds__(WARPS * 32, MT >= 4 ? 1 : 2)
 w8a16_stream_kernel(const __half *__restrict__ A, int64_t lda, const uint4 *__restrict__ image,
                     float *__restrict__ ws, int M, int N, int K, int ksteps, int n_blocks,
@@ -106,8 +103,6 @@ w8a16_stream_kernel(const __half *__restrict__ A, int64_t lda, const uint4 *__re
       // address of this lane's 16 bytes for local step s (global k-step ks0 + s)
       auto wptr = [&](int s) -> const uint4 * {
         const int ks = ks0 + s;
-        if (BLOCKED)
-          return image + ((((int64_t)(strip >> 3) * (ksteps >> 2) + (ks >> 2)) * 8 + (strip & 7)) * 4 + (ks & 3)) * 32 + lane;
         return image + ((int64_t)strip * ksteps + ks) * 32 + lane;
       };
       // ldmatrix source row/col of this lane inside a 16x16 A tile
@@ -169,7 +164,7 @@ w8a16_stream_kernel(const __half *__restrict__ A, int64_t lda, const uint4 *__re
   }
 }
 
-// C = f16(ws * scale[n]); ws is left zeroed for the next call.
+// C = f16(ws * scale[n]).  (The scratch is cleared at the start of every call, not here.)
 __global__ void __launch_bounds__(256)
 w8a16_finalize_kernel(float *__restrict__ ws, const __half *__restrict__ scales,
                       __half *__restrict__ C, int M, int N, int64_t ldc) {
@@ -178,16 +173,11 @@ w8a16_finalize_kernel(float *__restrict__ ws, const __half *__restrict__ scales,
        i += (int64_t)gridDim.x * 256) {
     const int r = (int)(i / N), c = (int)(i - (int64_t)r * N);
     const float v = ws[i];
-    ws[i] = 0.0f;
     C[(int64_t)r * ldc + c] = __float2half_rn(v * __half2float(scales[c]));
   }
 }
 
 }  // namespace
-
-int w8a16_build_image(const int8_t *wq_dev, int64_t k, int64_t n, void **image, size_t *bytes) {
-  return w8a16_build_tmem_image(wq_dev, k, n, image, bytes);
-}
 
 int launch_w8a16(const __half *a, const W8A16Weight &w, __half *c, int64_t m, int64_t lda,
                  int64_t ldc) {
@@ -251,11 +241,11 @@ int static_device_setup(int dev, StaticDevice **out) {
     B200_CUDA(cudaGetSymbolAddress((void **)&p, g_static_scratch));
     int sms = 0;
     B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(1 * 16 * A_PITCH * sizeof(__half))));
-    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(2 * 16 * A_PITCH * sizeof(__half))));
-    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CUDA(cudaFuncSetAttribute(w8a16_stream_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    (int)(4 * 16 * A_PITCH * sizeof(__half))));
     d.scratch = p;
     d.sm_count = sms;
@@ -275,7 +265,7 @@ void launch_stream_static(cudaStream_t s, int sm_count, const __half *a, int64_t
   int64_t total = (int64_t)n_blocks * ksteps;
   int grid = sm_count * 2;
   if (grid > total) grid = (int)total;
-  w8a16_stream_kernel<MT, false><<<grid, WARPS * 32, smem, s>>>(a, lda, image, ws, m, n, k, ksteps, n_blocks, n_strips);
+  w8a16_stream_kernel<MT><<<grid, WARPS * 32, smem, s>>>(a, lda, image, ws, m, n, k, ksteps, n_blocks, n_strips);
 }
 
 }  // namespace
@@ -293,11 +283,16 @@ extern "C" int b200mlir_w8a16_matmul_static_scratch(const void *a, int64_t lda, 
   if (m > kStaticMaxRows || n > kStaticMaxCols)
     return set_error(B200MLIR_ERR_UNSUPPORTED,
                      "w8a16 static-scratch: M=%lld, N=%lld exceed the built-in scratch (M <= %d, N <= %d); "
-                     "use w8a16_matmul, which allocates its scratch",
+                     "use w8a16_matmul, which takes any shape (and may allocate)",
                      (long long)m, (long long)n, kStaticMaxRows, kStaticMaxCols);
-  if (((uintptr_t)a & 15u) || ((uintptr_t)image & 15u) || lda % 8 || k % 8 || lda < k || ldc < n)
+  if (((uintptr_t)a & 15u) || ((uintptr_t)image & 15u) || lda % 8 || k % 8)
     return set_error(B200MLIR_ERR_BAD_ARG,
                      "w8a16 static-scratch: A and the image must be 16-byte aligned, K and lda multiples of 8");
+  if (lda < k || ldc < n)
+    return set_error(B200MLIR_ERR_BAD_ARG, "w8a16 static-scratch: row strides below the row lengths (lda %lld < K %lld or ldc %lld < N %lld)",
+                     (long long)lda, (long long)k, (long long)ldc, (long long)n);
+  if (((k + 15) / 16) * (((n + 31) / 32 + WARPS - 1) / WARPS) > 0x7fffffffLL)
+    return set_error(B200MLIR_ERR_UNSUPPORTED, "w8a16 static-scratch: K x N exceeds the kernel's 32-bit work index");
   int dev = 0;
   B200_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return set_error(B200MLIR_ERR_BAD_ARG, "device index %d out of range", dev);

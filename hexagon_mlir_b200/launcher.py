@@ -145,7 +145,34 @@ rms_norm_fwd_kernel = Kernel("rms_norm_fwd_kernel", (2, 2, 1), by_dtype=True,
 silu_kernel = Kernel("silu_kernel", (1, 1), by_dtype=True)
 add_kernel = Kernel("add_kernel", (1, 1, 1), by_dtype=True)
 swiglu_kernel = Kernel("swiglu_kernel", (1, 1, 1), by_dtype=True)
-w8a16_matmul = Kernel("w8a16_matmul", (2, 2, 1, 2))
+class _W8A16Kernel(Kernel):
+    """`w8a16_matmul` registers every weight it meets by source address.  A torch tensor's storage
+    can be freed and handed to another weight: when the weight tensor is collected, its resident
+    image is dropped with it (numpy arrays and explicit registrations are the caller's to release)."""
+    _watched = {}
+
+    def __getitem__(self, grid):
+        launch = super().__getitem__(grid)
+
+        def run(*args, **options):
+            launch(*args, **options)
+            wq = args[1] if len(args) > 1 else None
+            if torch is not None and isinstance(wq, torch.Tensor) and options.get("enableWeightResident", 1):
+                key = wq.data_ptr()
+                if key not in self._watched:
+                    import weakref
+
+                    def drop(ptr=key):
+                        self._watched.pop(ptr, None)
+                        try:
+                            lib().b200mlir_w8a16_unregister_weight(ptr)
+                        except Exception:  # noqa: BLE001  (interpreter shutdown)
+                            pass
+                    self._watched[key] = weakref.finalize(wq, drop)
+        return run
+
+
+w8a16_matmul = _W8A16Kernel("w8a16_matmul", (2, 2, 1, 2))
 mlp_block = Kernel(
     "mlp_block_float16", (2, 1, 2, 2, 2, 2),
     scalars=lambda args, opts: [ctypes.c_float(float(opts.get("eps", 1e-6))),
@@ -365,7 +392,11 @@ def register_w8a16_weight(wq, scales, l2_persist: bool = False) -> None:
 
 
 def unregister_w8a16_weight(wq) -> None:
-    if lib().b200mlir_w8a16_unregister_weight(_info(wq)[0]) != 0:
+    ptr = _info(wq)[0]
+    fin = _W8A16Kernel._watched.pop(ptr, None)
+    if fin is not None:
+        fin.detach()
+    if lib().b200mlir_w8a16_unregister_weight(ptr) != 0:
         check()
 
 

@@ -380,6 +380,14 @@ B200_API uint32_t hexagon_runtime_dma2d_start(void *src, int srcAS, void *dst, i
                                               int *status);
 B200_API void hexagon_runtime_dma_wait(uint32_t token);
 
+/* Contract of a registered weight (explicit, or implicit through w8a16_matmul while option
+ * "enableWeightResident" is 1, the default): the library identifies the weight by its SOURCE
+ * ADDRESS, as the reference's runtime does (bin/runtime/src/HexagonCAPI.cpp:167-169, no content
+ * hash).  From registration until b200mlir_w8a16_unregister_weight the bytes at that address must
+ * not change and the buffer must stay alive: a buffer freed and re-used for another [K,N] weight,
+ * or updated in place, would be multiplied with the stale image.  Unregister before freeing or
+ * rewriting a weight (or call with enableWeightResident = 0, which builds and drops the image per
+ * call).  The scales are re-read whenever a call passes a different scales pointer. */
 /* ---- weight residency for the GEMMs (replaces the host packer
  * qcom_hexagon_backend/backend/hmx_weight_prepack.py:124-212 and
  * WeightResidentPass, lib/Dialect/Hmx/Transforms/WeightResidentPass.cpp:9-93).
@@ -398,9 +406,11 @@ B200_API int b200mlir_w8a16_unregister_weight(const void *wq);
  * treats any later allocation as a fault, a plugin living inside another
  * runtime's memory pool, or code on a latency-critical thread where the
  * implicit synchronisation of cudaMalloc/cudaFree is not acceptable.
- * w8a16_matmul keeps its fp32 partial-sum scratch in a buffer it allocates and
- * grows; here that scratch is a fixed 4 MiB array inside the library image
- * (every GPU that loads the library holds it until the process exits).
+ * w8a16_matmul builds and keeps device images of the weights it meets (and its
+ * many-row route allocates workspaces); this entry takes a caller-built image
+ * and keeps the fp32 partial sums of its split-K kernel in a fixed 4 MiB array
+ * inside the library image (every GPU that loads the library holds it until the
+ * process exits).
  *
  * Limits: 1 <= M <= 64 and 1 <= N <= 16384 (M*N floats of scratch); larger
  * shapes are rejected with B200MLIR_ERR_UNSUPPORTED.  K and lda multiples of
@@ -417,7 +427,11 @@ B200_API int b200mlir_w8a16_unregister_weight(const void *wq);
  * kernel attributes; make that first call before any stream capture begins.
  * Every call uses the same array: it is cleared at the start of each call, and
  * two calls that overlap on the GPU (different streams, or two threads) race
- * on it and corrupt each other's sums — serialise them.
+ * on it and corrupt each other's sums — serialise them.  The partial sums of a
+ * column are added with atomic adds in the order the CTAs arrive, so the fp32
+ * sum order — and with it the last bit of a result — can differ from call to
+ * call; results agree with w8a16_matmul within the w8a16 tolerance (1e-2), not
+ * bit for bit.
  * Returns 0 or an error code (message through b200mlir_last_error). */
 B200_API int b200mlir_w8a16_matmul_static_scratch(const void *a, int64_t lda, const void *image,
                                                   const void *scales, void *c, int64_t ldc,

@@ -120,6 +120,35 @@ _SIGNATURES = {
     "hexagon_runtime_resident_free_v2": (ctypes.c_int32, [c_void_p, ctypes.c_uint32]),
     "hexagon_runtime_hmx_ensure": (None, []),
     "hexagon_runtime_hmx_unlock": (None, []),
+    "hmx_bias_init_unit_f16": (None, [c_void_p]),
+    "hmx_bias_load_f16": (None, [c_void_p, ctypes.c_uint]),
+    "hmx_acc_clear_f16": (None, []),
+    "hmx_acc_store_f16": (None, [c_void_p, ctypes.c_uint]),
+    "hmx_mma_f16": (None, [c_void_p, c_void_p, ctypes.c_uint]),
+    "hmx_pack_act_f16": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_f16": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_act_f16_bulk": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_f16_bulk": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_act_f32": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_f32": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_act_f32_bulk": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_f32_bulk": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_f16_T": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_f16_T_bulk": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_f32_T": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_f32_T_bulk": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_act_tail_f16": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_tail_f16": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_act_tail_f32": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_tail_f32": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_tail_f16_T": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_pack_weight_tail_f32_T": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_unpack_acc_f16": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_unpack_acc_f16_bulk": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_unpack_acc_f32": (None, [c_void_p, c_void_p, ctypes.c_uint, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_unpack_acc_f32_bulk": (None, [c_void_p, c_void_p, ctypes.c_uint, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_unpack_acc_tail_f16": (None, [c_void_p, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
+    "hmx_unpack_acc_tail_f32": (None, [c_void_p, c_void_p, ctypes.c_uint, c_void_p, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint, ctypes.c_uint]),
     "hexagon_runtime_hmx_exec_configure": (ctypes.c_int32, [HmxReadoutFn, ctypes.c_int32]),
     "hexagon_runtime_hmx_exec_publish": (ctypes.c_uint32, [ctypes.POINTER(HmxReadoutBatch), ctypes.c_uint32]),
     "hexagon_runtime_hmx_exec_drain": (None, []),

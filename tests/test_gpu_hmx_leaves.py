@@ -26,6 +26,12 @@ def L(hm, cuda):
     return Leaves()
 
 
+def rounded(oracle, x):
+    """The fp16 matrix the f32 packs see: "+0.0", then round to nearest even (the oracle's pinned rule)."""
+    x = np.ascontiguousarray(x)
+    return oracle.f32_pack_rounding(x).view(np.float16).reshape(x.shape)
+
+
 def dev(cuda, a):
     return cuda.from_numpy(np.ascontiguousarray(a)).cuda()
 
@@ -54,7 +60,7 @@ def test_pack_leaves_tile_by_tile(hm, oracle, cuda, L, rows, cols, pad):
     s16 = src.astype(np.float16)
     s32 = s16.astype(np.float32) + rng.uniform(-1e-4, 1e-4, src.shape).astype(np.float32)  # not fp16-representable
     want16 = oracle.pack_act_f16(np.ascontiguousarray(s16[:, :cols]))
-    want32 = oracle.pack_act_f16(oracle.f32_pack_rounding(np.ascontiguousarray(s32[:, :cols])).view(np.float16))
+    want32 = oracle.pack_act_f16(rounded(oracle, s32[:, :cols]))
     mt, kt = (rows + 31) // 32, (cols + 31) // 32
     d16, d32 = dev(cuda, s16), dev(cuda, s32)
     # activation order [Mt, Kt]: single tiles, then one bulk call per row tile
@@ -91,7 +97,7 @@ def test_pack_leaves_tile_by_tile(hm, oracle, cuda, L, rows, cols, pad):
     # transposed source: the [n][k] transpose input gives the same image
     t16 = dev(cuda, np.ascontiguousarray(s16[:, :cols].T))           # [cols(n), rows(k)]
     t32 = dev(cuda, np.ascontiguousarray(s32[:, :cols].T))
-    want32w = oracle.pack_weight_f16(oracle.f32_pack_rounding(np.ascontiguousarray(s32[:, :cols])).view(np.float16))
+    want32w = oracle.pack_weight_f16(rounded(oracle, s32[:, :cols]))
     for leaf, srcdev, want in (("f16_T", t16, wwant), ("f32_T", t32, want32w)):
         out.zero_()
         for n_t in range(nt):
@@ -118,7 +124,7 @@ def test_pack_leaves_tile_by_tile(hm, oracle, cuda, L, rows, cols, pad):
         assert np.array_equal(one.cpu().numpy().view(np.uint16), twant.view(np.uint16).ravel()), name
     c32 = np.zeros((32, 32), np.float32)
     c32[:vr, :vc] = s32[:vr, :vc]
-    t32want = oracle.pack_act_f16(oracle.f32_pack_rounding(c32).view(np.float16))
+    t32want = oracle.pack_act_f16(rounded(oracle, c32))
     for name, args in (("hmx_pack_act_tail_f32", (d32, rows, cols, stride)), ("hmx_pack_weight_tail_f32", (d32, rows, cols, stride)),
                        ("hmx_pack_weight_tail_f32_T", (t32, rows, cols, rows))):
         one.fill_(9.0)

@@ -247,7 +247,7 @@ def extras_single_gpu(torch, hm, peaks, only=None):
     g = torch.Generator(device=dev).manual_seed(0)
 
     def want(name):
-        return only is None or name.startswith(only)
+        return only is None or name.startswith(only) or only.startswith(name)
 
     def rand_h(shape, lo=-1.0, hi=1.0):
         return (torch.rand(shape, generator=g, device=dev) * (hi - lo) + lo).half()
@@ -369,6 +369,8 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         Wq = [torch.randint(-127, 128, (k, n), generator=g, device=dev, dtype=torch.int8) for _ in range(4)]
         S = (torch.rand(n, generator=g, device=dev) * 0.019 + 0.001).half()
         for mrows in (1, 16, 256):
+            if not want(f"w8a16_m{mrows}_"):
+                continue
             a = torch.randn((mrows, k), generator=g, device=dev).half()
             c = torch.empty((mrows, n), dtype=torch.float16, device=dev)
             state = {"i": 0}
@@ -414,6 +416,8 @@ def extras_single_gpu(torch, hm, peaks, only=None):
         for wq_ in Wq:
             hm.unregister_w8a16_weight(wq_)
         del Wq
+        if only is not None and not "w8a16_m1_4096x32000".startswith(only):
+            return out
         # the same kernel on a wider weight (a vocabulary projection): twice the bytes per CTA per launch,
         # so the ~6 us a launch costs before and after its streaming phase weigh half as much
         k, n = 4096, 32000
@@ -598,7 +602,11 @@ def run_product_arm(args):
     peaks, peak_kind = load_peaks()
     if args.case:
         # one small case of `extra` alone (what the ncu captures under profiles/ run)
-        line = json.dumps({"case": args.case, "result": extras_single_gpu(torch, hm, peaks, only=args.case)})
+        if args.case == "mlp":
+            result = {"mlp_block_2048x4096x11008": mlp_extra(torch, hm, dist, rank, world)}
+        else:
+            result = extras_single_gpu(torch, hm, peaks, only=args.case)
+        line = json.dumps({"case": args.case, "result": result})
         os.write(json_fd, (line + "\n").encode())
         return 0
 

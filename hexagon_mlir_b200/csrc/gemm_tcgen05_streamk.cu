@@ -2,12 +2,12 @@
 // kernel with the K dimension of its LAST tiles dealt out in k-blocks ("stream-K").
 //
 // Why: with whole tiles per pair, T tiles on P pairs take ceil(T / P) rounds — 43 tiles leave 31
-// of 74 pairs idle, 86 tiles cost two rounds for 1.16 rounds of work.  Here the first
-// (floor(T / P) - 1) * P tiles are handed out whole, round by round, exactly as the pair kernel
-// does (pairs that run together work on neighbouring tiles, which is what keeps their operand
-// panels in L2); the remaining P..2P-1 tiles (all of them when T < P) are cut into 64-deep
-// k-blocks, and those units are dealt out in P contiguous, equal ranges.  A pair's range is then
-// the tail of one tile, possibly a whole tile, and the head of another.
+// of 74 pairs idle, 86 tiles cost two rounds for 1.16 rounds of work.  Here whole rounds of P tiles
+// are handed out exactly as the pair kernel does (pairs that run together work on neighbouring
+// tiles, which is what keeps their operand panels in L2); the tiles of the last, part-filled round
+// (plus one full round's when the remainder is below P/2; all tiles when T < P) are cut into
+// 64-deep k-blocks, and those units are dealt out in P contiguous, equal ranges.  A pair's range
+// is then the tail of one tile, possibly a whole tile, and the head of another.
 //
 // A tile cut between pairs needs its partial sums combined.  The reference combines K segments in
 // fp32 after the engine's read-out (hmx/src/HMXLayout.c:880-901; the span count of a tiling,
@@ -456,11 +456,16 @@ int launch_streamk(const GemmArgs &g) {
     }
     max_pairs = clusters < c.sm_count / 2 ? clusters : c.sm_count / 2;
   }
-  // whole tiles for all rounds but the last full one; the last P..2P-1 tiles (all, below P) in k-blocks
+  // whole tiles round by round; the tiles of the last, part-filled round in k-blocks — together
+  // with one more full round's when that remainder is below half the pairs (each cut tile would
+  // otherwise have four or more contributors); below P tiles, all of them
   const int T = p.num_tiles;
   int pairs = max_pairs, dp_tiles = 0;
   if (T >= max_pairs) {
-    dp_tiles = T % max_pairs == 0 ? T : (T / max_pairs - 1) * max_pairs;
+    const int rem = T % max_pairs;
+    if (rem == 0) dp_tiles = T;
+    else if (2 * rem >= max_pairs) dp_tiles = T - rem;
+    else dp_tiles = T - rem - max_pairs;
   } else {
     const long long units = (long long)T * p.k_blocks;
     pairs = (int)(units < max_pairs ? units : max_pairs);

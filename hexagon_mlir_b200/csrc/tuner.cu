@@ -71,7 +71,8 @@ double model_clocks(const TcVariantInfo &vi, int64_t m, int64_t n, int64_t k, in
     // tiles (all tiles below P) dealt out evenly: no round is left part-filled, but the pair that
     // combines a cut tile pulls every other contributor's fp32 partial through the workspace
     if (std::fmod(tiles, slots) == 0.0) return (tiles / slots) * (kblocks * per_block + 1500.0) + 1.0;  // nothing to cut
-    const double dp_rounds = tiles >= slots ? std::floor(tiles / slots) - 1.0 : 0.0;
+    const double rem = std::fmod(tiles, slots);
+    const double dp_rounds = tiles >= slots ? std::floor(tiles / slots) - (2.0 * rem >= slots ? 0.0 : 1.0) : 0.0;
     const double sk_tiles = tiles - dp_rounds * slots, units = sk_tiles * kblocks;
     const double pairs = std::min(slots, units), share = std::ceil(units / pairs);
     const double others = std::max(1.0, std::ceil(kblocks / share));  // contributors beside the combining pair

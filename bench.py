@@ -104,6 +104,9 @@ class ClockSampler:
 DRAM_TRAFFIC_CAPTURES = {
     ("tc256x256x64_2cta_s6", 16384, 16384, 8192): {
         "bytes": 8.371e9 + 0.532e9, "profile": "profiles/bench_gemm_16384x16384x8192_launches.md", "captured": "2026-11-25"},
+    ("tc256x256x64_2cta_streamk", 16384, 16384, 8192): {
+        "bytes": 6.417e9 + 0.545e9, "profile": "profiles/bench_gemm_16384x16384x8192_launches.md (stream-K section)",
+        "captured": "2026-11-25"},
 }
 
 

@@ -693,6 +693,20 @@ def run_product_arm(args):
     dref = c[sl].float()
     e2e_err = float((hc[sl].cuda().float() - dref).abs().max() / dref.abs().max())
     h2d_step = (M * K // (world if sharded_upload else 1) + K * n_loc) * 2 * world
+    # ... and as byte equality with every launch on ONE whole-tile variant (same fp32 sums in the same order)
+    hm.set_option("gemmVariant", 3)
+    if sharded_upload:
+        hm.set_option("replicatedOperandA", 1)
+    try:
+        e2e_step()
+        c_one = torch.empty_like(c)
+        hm.matmul[(1,)](a, b, c_one)
+        torch.cuda.synchronize()
+        e2e_bytes_equal = bool(torch.equal(hc.cuda(), c_one))
+        del c_one
+    finally:
+        hm.set_option("gemmVariant", -1)
+        hm.set_option("replicatedOperandA", 0)
     del ha, hb, hc
 
     extra = {}
@@ -729,7 +743,7 @@ def run_product_arm(args):
             "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_step,
                     "d2h_bytes_per_step": M * n_loc * 2 * world, "steps": e2e_steps,
                     "a_upload": "1/N row slab per rank, slabs all-gathered over NVLink" if sharded_upload else "whole A",
-                    "max_abs_rel_vs_device_run": e2e_err},
+                    "max_abs_rel_vs_device_run": e2e_err, "bytes_equal_to_device_run_on_one_variant": e2e_bytes_equal},
             "parity_sample": parity, "long_run": long_run,
             "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
         }

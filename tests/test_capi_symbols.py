@@ -106,3 +106,23 @@ def test_resident_scope_rules_without_device(hm):
     tok = lib.hexagon_runtime_dma_start(None, 0, None, 0, 16, False, False, ctypes.byref(st))
     assert tok == 0xFFFFFFFF and st.value == -1
     lib.hexagon_runtime_dma_wait(tok)  # returns at once
+
+
+def test_tensor_parallel_group_state_without_a_group(hm):
+    """No group initialised: rank 0 of 1; the collective entries refuse instead of touching NCCL."""
+    assert hm.tp_info() == (False, 0, 1)
+    hm.tp_shutdown()                     # nothing to shut down: not an error
+    with pytest.raises(ValueError):
+        hm.tp_init(b"short", 0, 2)       # the id is 128 bytes
+
+
+def test_block_table_and_leaf_argument_checks_without_a_device(hm):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("needs the no-device path")
+    lib = hm._capi.lib()
+    lib.hexagon_runtime_free_2d(12345)   # not a table returned by alloc_2d: refused, nothing freed
+    assert hm._capi.last_error()[0] == 2
+    assert lib.hexagon_runtime_alloc_2d(4, 64, 128, False) is None and hm._capi.last_error()[0] == 1   # no device
+    lib.hmx_acc_clear_f16()              # a leaf without a device: the library's error, no crash
+    assert hm._capi.last_error()[0] == 1

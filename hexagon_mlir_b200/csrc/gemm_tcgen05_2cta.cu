@@ -37,13 +37,10 @@ __device__ long long g2_trace_buf[2 * 6 * 64];
 // CTA 1 the Wu tile, and each CTA's accumulator rows hold both halves.
 // NSUB: 64-deep K sub-tiles per stage (one barrier round trip and one commit per stage).
 // K-looped form (EPI_KLOOP_F16): one accumulator stage per K segment of p.seg_kb stages, started
-// with accumulate off; sixteen read-out warps per CTA (four per TMEM lane quadrant, 64 columns each)
+// with accumulate off; eight read-out warps per CTA (two per TMEM lane quadrant, 128 columns each)
 // round every segment to fp16 and keep the row's fp32 running sums in registers
-// (test/python/triton/test_matmul_kloop.py:87-98).  A 64-deep segment is 512 clocks of MMA; with
-// eight warps of 128 columns its read-out took ~1000 and bound the kernel.
-constexpr int KLOOP_PARTS = 4;                       // read-out warps per lane quadrant
-constexpr int KLOOP_COLS = 256 / KLOOP_PARTS;        // columns each of them owns
-constexpr int pair_threads(int epi) { return epi == EPI_KLOOP_F16 ? 64 + 32 * 4 * KLOOP_PARTS : THREADS2; }
+// (test/python/triton/test_matmul_kloop.py:87-98).
+constexpr int pair_threads(int epi) { return epi == EPI_KLOOP_F16 ? 320 : THREADS2; }
 // BKB: B is the K-blocked image [k/64][N][64] (GemmArgs::b_kblocked): a K-major operand whose tile
 // of one k-block is contiguous in HBM; loaded and described like the int8 form's transposed B.
 template <int STAGES, int NSUB, int EPI, bool BKB = false>
@@ -93,7 +90,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar_tfull + 8 * s, 1);
-      mbar_init(bar_tempty + 8 * s, EPI == EPI_KLOOP_F16 ? 8 * KLOOP_PARTS : 8);  // the read-out warps of both CTAs
+      mbar_init(bar_tempty + 8 * s, EPI == EPI_KLOOP_F16 ? 16 : 8);  // the read-out warps of both CTAs
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -266,7 +263,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   } else {
-    // ---------------- epilogue (warps 2..5, K-looped form 2..17): this CTA's 128 rows ----------------
+    // ---------------- epilogue (warps 2..5, K-looped form 2..9): this CTA's 128 rows ----------------
     const int q = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -276,12 +273,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tile_coords(tile, p.m_blocks, p.n_blocks, p.group_m, m_blk, n_blk);
       const int m0 = m_blk * 256 + (int)rank * BM2, n0 = n_blk * BN_OUT;
       if constexpr (EPI == EPI_KLOOP_F16) {
-        // this warp's share of the 256 columns: fp32 running sums of its row, every segment rounded to fp16 first
-        const int part = (warp - 2) >> 2;
+        // this warp's half of the 256 columns: fp32 running sums of its row, every segment rounded to fp16 first
+        const int half = (warp - 2) >> 2;
         const int row = m0 + q * 32 + lane;
-        float sum[KLOOP_COLS];
+        float sum[128];
 #pragma unroll
-        for (int e = 0; e < KLOOP_COLS; ++e) sum[e] = 0.0f;
+        for (int e = 0; e < 128; ++e) sum[e] = 0.0f;
         const int segs = (p.k_blocks + p.seg_kb - 1) / p.seg_kb;
         bool ok = true;
         for (int sg = 0; sg < segs; ++sg) {
@@ -289,9 +286,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA + part * KLOOP_COLS);
+          const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA + half * 128);
 #pragma unroll
-          for (int c = 0; c < KLOOP_COLS / 32; ++c) {
+          for (int c = 0; c < 4; ++c) {
             uint32_t r[32];
             tmem_ld_32x32(t_row + c * 32, r);
             tmem_ld_wait();
@@ -309,11 +306,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         if (!ok) break;
 #pragma unroll
-        for (int c = 0; c < KLOOP_COLS / 32; ++c) {
+        for (int c = 0; c < 4; ++c) {
           uint32_t r[32];
 #pragma unroll
           for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(sum[c * 32 + e]);
-          const int col0 = n0 + part * KLOOP_COLS + c * 32;
+          const int col0 = n0 + half * 128 + c * 32;
           if (row < p.m && col0 < p.n) epilogue_store_chunk<EPI_F16>(r, r, row, col0, p);
         }
         continue;

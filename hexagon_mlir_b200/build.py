@@ -12,7 +12,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libb200mlir.so")
 
-SOURCES = ["runtime.cu", "row_kernels.cu", "layout.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu", "gemm_tcgen05_streamk.cu", "gemm_tcgen05_cluster4.cu",
+SOURCES = ["runtime.cu", "row_kernels.cu", "layout.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_tcgen05_2cta.cu", "gemm_tcgen05_streamk.cu",
            "w8a16.cu", "w8a16_tmem.cu", "attention_tmem.cu", "tuner.cu", "report.cu", "entry.cu", "harness_kernels.cu", "tp_nccl.cu", "hmx_leaves.cu",
            "readout_executor.cpp"]
 

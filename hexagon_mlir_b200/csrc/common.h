@@ -226,7 +226,6 @@ struct TcVariantInfo {
   int smem_bytes, tmem_cols;
   double model_eff;  // fraction of the tensor pipe this tiling sustained when measured
   bool stream_k = false;  // work is dealt out in k-blocks, not whole tiles (gemm_tcgen05_streamk.cu)
-  bool cluster_split_k = false;  // a cluster of two pairs per tile, each on half of K (gemm_tcgen05_cluster4.cu)
 };
 const TcVariantInfo &tc_variant_info(int v);
 // "ok" or a refusal reason for variant v on (m,n,k) with the given epilogue.
@@ -243,10 +242,6 @@ int pair_variant_smem_bytes();
 // gemm_tcgen05_streamk.cu — the pair kernel with the k-blocks of its tiles dealt out evenly over the pairs
 int launch_gemm_tc_streamk(const GemmArgs &g);
 bool streamk_shape_ok(const GemmArgs &g);
-// gemm_tcgen05_cluster4.cu — small problems: four CTAs per 256 x 128 tile, two pairs on the two halves of K
-int launch_gemm_tc_cluster4(const GemmArgs &g);
-bool cluster4_shape_ok(const GemmArgs &g);
-int cluster4_variant_smem_bytes();
 
 // w8a16.cu
 struct W8A16Weight {

@@ -308,9 +308,6 @@ const TcVariantInfo kVariants[] = {
     {"tc256x256x128_2cta_s3", 256, 256, 128, 3, 2, 6 * 32768 + 16 * 6 + 64 + 1024, 512, 0.10},
     // the same pair tile with the k-blocks of all tiles dealt out evenly (gemm_tcgen05_streamk.cu)
     {"tc256x256x64_2cta_streamk", 256, 256, 64, 6, 2, 6 * 32768 + 16 * 6 + 64 + 1024, 512, 0.85, true},
-    // small problems: a cluster of two pairs per 256 x 128 tile, one half of K each, partials added
-    // through distributed shared memory (gemm_tcgen05_cluster4.cu)
-    {"tc256x128x64_cluster4_splitk2", 256, 128, 64, 5, 2, 5 * 24576 + 65536 + 16 * 5 + 64 + 1024, 128, 0.55, false, true},
 };
 constexpr int kNumVariants = sizeof(kVariants) / sizeof(kVariants[0]);
 
@@ -435,7 +432,7 @@ const char *tc_variant_verdict(int v, const GemmArgs &g) {
   if (g.k < 8 || g.n < 8) return "tile-alignment";
   if (g.k % 8 || g.n % 8 || g.lda % 8 || (!g.b_kblocked && g.ldb % 8)) return "tile-alignment";
   // the K-blocked B image: the pair kernels' plain fp16 read-out only
-  if (g.b_kblocked && (vi.cta_group != 2 || vi.bk != 64 || vi.cluster_split_k || g.epilogue != EPI_F16)) return "epilogue-unsupported";
+  if (g.b_kblocked && (vi.cta_group != 2 || vi.bk != 64 || g.epilogue != EPI_F16)) return "epilogue-unsupported";
   if (g.epilogue == EPI_PUSH16) {
     if (!g.push || g.push->world < 1 || g.push->world > kMaxPushRanks || g.push->rows_per_rank < 1 ||
         g.push->rows_per_rank * g.push->world != g.m)
@@ -459,17 +456,12 @@ const char *tc_variant_verdict(int v, const GemmArgs &g) {
   // (the one-CTA 128x128 variant, and the two-CTA variant with 64-deep stages, whose eight read-out warps take 128 columns each)
   if (g.epilogue == EPI_KLOOP_F16 &&
       (!((vi.cta_group == 1 && vi.bn == 128) ||
-         (vi.cta_group == 2 && vi.bk == 64 && !vi.stream_k && !vi.cluster_split_k && ctx().opt.kloop_pairs != 0)) ||
+         (vi.cta_group == 2 && vi.bk == 64 && !vi.stream_k && ctx().opt.kloop_pairs != 0)) ||
        g.block_k < BK || g.block_k % BK))
     return "epilogue-unsupported";
   if (vi.stream_k) {
     if (g.epilogue == EPI_KLOOP_F16 || g.epilogue == EPI_I32) return "epilogue-unsupported";
     if (!streamk_shape_ok(g)) return "extent-range";
-  }
-  if (vi.cluster_split_k) {
-    if (g.epilogue != EPI_F16 && g.epilogue != EPI_F32_RES && g.epilogue != EPI_F16_RES16) return "epilogue-unsupported";
-    if (g.b_kblocked) return "epilogue-unsupported";
-    if (!cluster4_shape_ok(g)) return "min-depth";  // both halves of K need a k-block
   }
   if (g.m > 0x7fffffff || g.n > 0x7fffffff || g.k > 0x7fffffff) return "extent-range";
   if (((g.m + BM - 1) / BM) * ((g.n + 31) / 32) > 0x3fffffff) return "extent-range";
@@ -491,7 +483,6 @@ int launch_gemm_tc(int v, const GemmArgs &g) {
     case 3: return launch_gemm_tc_pair(g, false);
     case 4: return launch_gemm_tc_pair(g, true);
     case 5: return launch_gemm_tc_streamk(g);
-    case 6: return launch_gemm_tc_cluster4(g);
   }
   return set_error(B200MLIR_ERR_BAD_ARG, "no such gemm variant %d", v);
 }

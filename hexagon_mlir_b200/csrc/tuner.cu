@@ -32,7 +32,6 @@ constexpr int kReps = 3;                // hexagon_bench reps
 constexpr int kSimtVariant = -1;
 constexpr double kStreamKFixup = 4000.0;  // clocks to combine one more contributor's partial of a cut tile
 constexpr double kStreamKDrift = 0.25;    // modelled loss of the k-block phase, in tile times
-constexpr double kClusterExchange = 7000.0;  // clocks charged for the cluster launch and the partial tile's crossing (measured: 1024^3 10.2 us against 7.8 us for one-CTA 128x64 tiles)
 
 std::mutex g_cache_mu;
 struct CacheEntry {
@@ -67,13 +66,6 @@ double model_clocks(const TcVariantInfo &vi, int64_t m, int64_t n, int64_t k, in
   const double slots = std::max(1, sms / vi.cta_group);
   const double kblocks = std::ceil((double)k / vi.bk);
   const double per_block = (double)vi.bm * vi.bn * vi.bk * 2.0 / (8192.0 * vi.cta_group) / vi.model_eff;
-  if (vi.cluster_split_k) {
-    // one cluster of four CTAs per tile, all tiles at once when they fit (the grid is not persistent);
-    // each pair runs half of the k-blocks, then one partial tile crosses the cluster
-    const double clusters = std::max(1, sms / 4);
-    const double rounds = std::ceil(tiles / clusters);
-    return rounds * (std::ceil(kblocks / 2.0) * per_block + 1500.0 + kClusterExchange);
-  }
   if (vi.stream_k) {
     // whole tiles for all rounds but the last full one, then the k-blocks of the last P..2P-1
     // tiles (all tiles below P) dealt out evenly: no round is left part-filled, but the pair that

@@ -26,7 +26,7 @@ def n_variants(hm):
     return len(hm.gemm_variants())
 
 
-@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, 3, 4, 5, 6, -1])
+@pytest.mark.parametrize("variant", [SIMT, 0, 1, 2, 3, 4, 5, -1])
 def test_c1_config(hm, oracle, variant):
     """M=N=K=1024, U[-1,1], seed 0."""
     rng = philox(0)
@@ -329,41 +329,3 @@ def test_stream_k_read_outs(hm, oracle):
     assert names and all("streamk" in nm for nm in names), names
     assert max_abs_rel(y, oracle.mlp(x, gain, wg, wu, wd, 1e-6)) <= TOL_GEMM
 
-
-CLUSTER4 = 6
-
-
-@pytest.mark.parametrize("mnk", [(1024, 1024, 1024), (512, 512, 512), (256, 128, 128), (129, 264, 72), (300, 520, 200),
-                                 (1000, 1000, 1000), (2048, 64, 320), (64, 2048, 512), (4096, 1024, 192)])
-def test_cluster_split_k_variant(hm, oracle, cuda, mnk):
-    """Four CTAs per 256 x 128 tile, two SM pairs on the two halves of K, the upper half's fp32
-    partial handed over through distributed shared memory: parity with the oracle, bit-identical
-    run to run (lower half + upper half, always in that order), ragged M / N / K, an odd number
-    of k-blocks, more tiles than one wave of clusters."""
-    m, n, k = mnk
-    rng = philox(63)
-    a = rng.uniform(-1, 1, (m, k)).astype(np.float16)
-    b = rng.uniform(-1, 1, (k, n)).astype(np.float16)
-    assert hm.gemm_variant_verdict(CLUSTER4, m, n, k) == "ok"
-    da, db = cuda.from_numpy(a).cuda(), cuda.from_numpy(b).cuda()
-    outs = []
-    hm.set_option("gemmVariant", CLUSTER4)
-    try:
-        for _ in range(3):
-            c = cuda.full((m, n), 7.0, dtype=cuda.float16, device="cuda")
-            hm.matmul[(1,)](da, db, c)
-            outs.append(c)
-        res = rng.normal(0, 1, (m, n)).astype(np.float32)
-        c32 = np.zeros((m, n), np.float32)
-        hm.matmul_f32out(a, b, c32, res)
-    finally:
-        hm.set_option("gemmVariant", -1)
-    assert hm.device_status() == 0
-    assert max_abs_rel(outs[0].cpu().numpy(), oracle.gemm_f16(a, b)) <= TOL_GEMM
-    assert cuda.equal(outs[0], outs[1]) and cuda.equal(outs[0], outs[2])
-    assert max_abs_rel(c32, oracle.gemm_f16_f32out(a, b, res)) <= TOL_GEMM
-
-
-def test_cluster_split_k_needs_two_k_blocks(hm):
-    assert hm.gemm_variant_verdict(CLUSTER4, 512, 512, 64) == "min-depth"
-    assert hm.gemm_variant_verdict(CLUSTER4, 512, 512, 72) == "ok"

@@ -667,7 +667,7 @@ def run_product_arm(args):
     # host holds the same A: each rank sends up its 1/N row slab over its own PCIe link and the
     # slabs are exchanged GPU to GPU inside the call (option replicatedOperandA; needs the library's
     # own communicator, which tp.init_group creates).
-    e2e_steps = max(1, min(2, args.steps))
+    e2e_steps = max(1, min(3, args.steps))
     ha = torch.empty((M, K), dtype=torch.float16).pin_memory()
     hb = torch.empty((K, n_loc), dtype=torch.float16).pin_memory()
     hc = torch.empty((M, n_loc), dtype=torch.float16).pin_memory()
@@ -682,9 +682,42 @@ def run_product_arm(args):
         hm.set_option("replicatedOperandA", 1)
         sharded_upload = True
 
+    # what the host side gives at this moment, all ranks copying at once: one direction at a time,
+    # then both at once.  The GPUs of a box share one host (and the host is shared with other
+    # tenants), so the aggregate — not the per-GPU link — bounds the host-buffer call at N > 1.
+    def link_rate(up, down):
+        s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+        if multi:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        if up:
+            with torch.cuda.stream(s1):
+                c2.copy_(hc, non_blocking=True)
+        if down:
+            with torch.cuda.stream(s2):
+                hc2.copy_(c, non_blocking=True)
+        torch.cuda.synchronize()
+        gbs = hc.numel() * 2 / (time.perf_counter() - t0) / 1e9
+        if multi:
+            t = torch.tensor([gbs], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            gbs = float(t.item())
+        return gbs
+    c2, hc2 = torch.empty_like(c), torch.empty_like(hc).pin_memory()
+    link_rate(True, True)
+    host_link = {"h2d_gbs_per_gpu": round(link_rate(True, False), 1), "d2h_gbs_per_gpu": round(link_rate(False, True), 1),
+                 "both_ways_gbs_each_per_gpu": round(link_rate(True, True), 1), "ranks_copying_at_once": world,
+                 "rate": "slowest rank"}
+    bytes_rank = (M * K // world + K * n_loc + M * n_loc) * 2
+    host_link["floor_ms"] = round(bytes_rank / 2 / (host_link["both_ways_gbs_each_per_gpu"] * 1e9) * 1e3, 2)
+    del c2, hc2
+
     def e2e_step():
         hm.matmul[(1,)](npa, npb, npc)  # H2D A and B, GEMM, D2H C, wait — all inside the call
-    e2e_ms = timed(torch, e2e_step, e2e_steps, 1, dist if multi else None)
+    e2e_step()
+    e2e_each = [timed(torch, e2e_step, 1, 0, dist if multi else None) for _ in range(e2e_steps)]
+    e2e_ms = sum(e2e_each) / len(e2e_each)
     hm.set_option("replicatedOperandA", 0)
     e2e_tflops = FLOPS / (e2e_ms * 1e-3) / 1e12
     # the strips of the host path and the whole-problem device run may take different variants
@@ -742,6 +775,7 @@ def run_product_arm(args):
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_step,
                     "d2h_bytes_per_step": M * n_loc * 2 * world, "steps": e2e_steps,
+                    "ms_each_step": [round(x, 3) for x in e2e_each], "host_link": host_link,
                     "a_upload": "1/N row slab per rank, slabs all-gathered over NVLink" if sharded_upload else "whole A",
                     "max_abs_rel_vs_device_run": e2e_err, "bytes_equal_to_device_run_on_one_variant": e2e_bytes_equal},
             "parity_sample": parity, "long_run": long_run,

@@ -132,15 +132,19 @@ constexpr size_t kPipelineMinBytes = 96u << 20;
 
 int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   const int64_t M = A.rows, K = A.cols, N = B.cols;
-  const int64_t P = std::max<int64_t>(2, std::min<int64_t>(16, std::min(M, N) / 1024));
+  // panels of about 1024 rows of A and 1024 columns of B, at most 16 of each, counted separately:
+  // a narrow column block (one rank's share of a wide B) still gets a fine-grained pipeline over A
+  const int64_t P_m = std::max<int64_t>(2, std::min<int64_t>(16, M / 1024));
+  const int64_t P_n = std::max<int64_t>(1, std::min<int64_t>(16, N / 1024));
   // panel edges on multiples of 256 rows / columns (whole tiles of the widest variant)
-  const int64_t pm = ((M + P - 1) / P + 255) / 256 * 256, pn = ((N + P - 1) / P + 255) / 256 * 256;
+  const int64_t pm = ((M + P_m - 1) / P_m + 255) / 256 * 256, pn = ((N + P_n - 1) / P_n + 255) / 256 * 256;
   const int64_t PM = (M + pm - 1) / pm, PN = (N + pn - 1) / pn;
   // option replicatedOperandA inside a tensor-parallel group: a collective call — every rank
   // enters with the same M and K (its own B and C column block)
   const int world = ctx().opt.replicated_operand_a != 0 ? tp_world() : 1;
-  cudaStream_t s_in, s_out, s = ctx().stream;
+  cudaStream_t s_in, s_out, s_ag = nullptr, s = ctx().stream;
   B200_TRY(copy_streams(&s_in, &s_out));
+  if (world > 1) B200_TRY(tp_comm_stream(&s_ag));  // slab exchanges run beside the next upload
   void *base = nullptr;
   const size_t a_bytes = (size_t)M * K * 2, b_bytes = (size_t)K * N * 2, c_bytes = (size_t)M * N * 2;
   B200_TRY(staging_workspace(a_bytes + b_bytes + c_bytes + 512, &base));
@@ -148,8 +152,10 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   __half *dB = (__half *)((char *)base + ((a_bytes + 255) & ~(size_t)255));
   __half *dC = (__half *)((char *)dB + ((b_bytes + 255) & ~(size_t)255));
   std::vector<cudaEvent_t> ev;
+  const bool debug = getenv("B200MLIR_DEBUG") != nullptr;  // timed events, and a timeline printed at the end
+  std::vector<std::pair<const char *, cudaEvent_t>> marks;
   auto new_event = [&](cudaEvent_t *e) -> cudaError_t {
-    cudaError_t r = cudaEventCreateWithFlags(e, cudaEventDisableTiming);
+    cudaError_t r = cudaEventCreateWithFlags(e, debug ? cudaEventDefault : cudaEventDisableTiming);
     if (r == cudaSuccess) ev.push_back(*e);
     return r;
   };
@@ -162,11 +168,12 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   rc = set_error(B200MLIR_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e))
   // the copy streams start after whatever the caller queued before this call
   cudaEvent_t t0 = nullptr;
-  if (getenv("B200MLIR_DEBUG")) { cudaEventCreate(&t0); cudaEventRecord(t0, s); }
+  if (debug) { cudaEventCreate(&t0); cudaEventRecord(t0, s); }
   PIPE_CUDA(new_event(&start));
   PIPE_CUDA(cudaEventRecord(start, s));
   PIPE_CUDA(cudaStreamWaitEvent(s_in, start, 0));
   PIPE_CUDA(cudaStreamWaitEvent(s_out, start, 0));
+  if (s_ag) PIPE_CUDA(cudaStreamWaitEvent(s_ag, start, 0));
   for (int64_t d = 0; d < std::max(PM, PN) && rc == 0; ++d) {
     if (d < PM) {
       const int64_t r0 = d * pm, rows = std::min(pm, M - r0);
@@ -176,13 +183,20 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
         const int64_t slab = rows / world, s0 = r0 + (int64_t)tp_rank() * slab;
         PIPE_CUDA(cudaMemcpy2DAsync(dA + s0 * K, (size_t)K * 2, (const __half *)A.p + s0 * A.ld, (size_t)A.ld * 2,
                                     (size_t)K * 2, (size_t)slab, cudaMemcpyHostToDevice, s_in));
-        if (rc == 0) rc = tp_all_gather_bytes(dA + s0 * K, dA + r0 * K, (size_t)slab * K * 2, s_in);
+        cudaEvent_t slab_up;
+        PIPE_CUDA(new_event(&slab_up));
+        PIPE_CUDA(cudaEventRecord(slab_up, s_in));
+        PIPE_CUDA(cudaStreamWaitEvent(s_ag, slab_up, 0));
+        if (rc == 0) rc = tp_all_gather_bytes(dA + s0 * K, dA + r0 * K, (size_t)slab * K * 2, s_ag);
+        PIPE_CUDA(new_event(&a_up[d]));
+        PIPE_CUDA(cudaEventRecord(a_up[d], s_ag));
+        if (debug) { marks.push_back({"slab up", slab_up}); marks.push_back({"slabs exchanged", a_up[d]}); }
       } else {
         PIPE_CUDA(cudaMemcpy2DAsync(dA + r0 * K, (size_t)K * 2, (const __half *)A.p + r0 * A.ld, (size_t)A.ld * 2,
                                     (size_t)K * 2, (size_t)rows, cudaMemcpyHostToDevice, s_in));
+        PIPE_CUDA(new_event(&a_up[d]));
+        PIPE_CUDA(cudaEventRecord(a_up[d], s_in));
       }
-      PIPE_CUDA(new_event(&a_up[d]));
-      PIPE_CUDA(cudaEventRecord(a_up[d], s_in));
     }
     if (d < PN) {
       const int64_t c0 = d * pn, cols = std::min(pn, N - c0);
@@ -190,6 +204,7 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
                                   (size_t)cols * 2, (size_t)K, cudaMemcpyHostToDevice, s_in));
       PIPE_CUDA(new_event(&b_up[d]));
       PIPE_CUDA(cudaEventRecord(b_up[d], s_in));
+      if (debug) marks.push_back({"B panel up", b_up[d]});
     }
     // what panel d completes: the row strip (row panel d x column panels 0..d) and the column
     // strip (row panels 0..d-1 x column panel d); one GEMM and one copy down for each
@@ -219,10 +234,16 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
       PIPE_CUDA(cudaStreamWaitEvent(s_out, blk, 0));
       PIPE_CUDA(cudaMemcpy2DAsync((__half *)C.p + r0 * C.ld + c0, (size_t)C.ld * 2, dC + r0 * N + c0, (size_t)N * 2,
                                   (size_t)cols * 2, (size_t)rows, cudaMemcpyDeviceToHost, s_out));
+      if (debug && rc == 0) {
+        cudaEvent_t dn;
+        PIPE_CUDA(new_event(&dn));
+        PIPE_CUDA(cudaEventRecord(dn, s_out));
+        marks.push_back({strip == 0 ? "row strip computed" : "column strip computed", blk});
+        marks.push_back({"strip down", dn});
+      }
     }
   }
   cudaEvent_t t_up = nullptr, t_mm = nullptr, t_down = nullptr;
-  const bool debug = t0 != nullptr;
   if (debug) {
     cudaEventCreate(&t_up); cudaEventCreate(&t_mm); cudaEventCreate(&t_down);
     cudaEventRecord(t_up, s_in); cudaEventRecord(t_mm, s); cudaEventRecord(t_down, s_out);
@@ -233,11 +254,17 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   PIPE_CUDA(cudaStreamWaitEvent(s, done, 0));
 #undef PIPE_CUDA
   cudaError_t e1 = cudaStreamSynchronize(s_in), e2 = cudaStreamSynchronize(s_out), e3 = cudaStreamSynchronize(s);
+  if (s_ag && e1 == cudaSuccess) e1 = cudaStreamSynchronize(s_ag);
   if (debug) {  // B200MLIR_DEBUG: when each of the three streams finished
     float a = 0, b = 0, c = 0;
     cudaEventElapsedTime(&a, t0, t_up); cudaEventElapsedTime(&b, t0, t_mm); cudaEventElapsedTime(&c, t0, t_down);
-    fprintf(stderr, "[b200mlir] pipelined host GEMM %lldx%lldx%lld P=%lld: up done %.2f ms, compute done %.2f ms, down done %.2f ms\n",
-            (long long)M, (long long)N, (long long)K, (long long)P, a, b, c);
+    fprintf(stderr, "[b200mlir] pipelined host GEMM %lldx%lldx%lld panels %lldx%lld: up done %.2f ms, compute done %.2f ms, down done %.2f ms\n",
+            (long long)M, (long long)N, (long long)K, (long long)PM, (long long)PN, a, b, c);
+    if (getenv("B200MLIR_DEBUG")[0] == '2' && tp_rank() == 0)
+      for (auto &mk : marks) {
+        float t = 0;
+        if (cudaEventElapsedTime(&t, t0, mk.second) == cudaSuccess) fprintf(stderr, "[b200mlir]   %8.3f ms  %s\n", t, mk.first);
+      }
     cudaEventDestroy(t0); cudaEventDestroy(t_up); cudaEventDestroy(t_mm); cudaEventDestroy(t_down);
   }
   for (cudaEvent_t x : ev) cudaEventDestroy(x);
@@ -264,7 +291,8 @@ int matmul_impl(int epilogue, int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRe
   if (has_res && (R.rows != C.rows || R.cols != C.cols))
     return set_error(B200MLIR_ERR_BAD_ARG, "matmul: residual shape differs from C");
   if (C.rows == 0 || C.cols == 0) return 0;
-  if (epilogue == EPI_F16 && A.cols > 0 && std::min(A.rows, B.cols) >= 4096 && A.cols % 8 == 0 && B.cols % 8 == 0 &&
+  if (epilogue == EPI_F16 && A.cols > 0 && std::min(A.rows, B.cols) >= 1024 && std::max(A.rows, B.cols) >= 4096 &&
+      A.cols % 8 == 0 && B.cols % 8 == 0 &&
       A.span(2) + B.span(2) + C.span(2) >= kPipelineMinBytes && !is_device_ptr(A.p) && !is_device_ptr(B.p) &&
       !is_device_ptr(C.p))
     return matmul_host_pipelined(A, B, C);

@@ -220,7 +220,8 @@ def test_autotune_on_device(hm):
     hm.autotune_cache_clear()
 
 
-@pytest.mark.parametrize("mnk,pad", [((4096, 4096, 4096), 0), ((4360, 4104, 4096), 0), ((4096, 4224, 4096), 64)])
+@pytest.mark.parametrize("mnk,pad", [((4096, 4096, 4096), 0), ((4360, 4104, 4096), 0), ((4096, 4224, 4096), 64),
+                                     ((12288, 1024, 4096), 0), ((1280, 9000, 4096), 0), ((9000, 2048, 4096), 64)])
 def test_host_buffers_take_the_pipelined_path(hm, oracle, mnk, pad):
     """All three tensors in host memory and >= 96 MB: panels go up, blocks are computed and come
     back down concurrently.  Checked on sampled rows against the oracle and, bit for bit, against

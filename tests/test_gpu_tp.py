@@ -87,6 +87,19 @@ def _worker(rank, world, port, q):
     import oracle
     want = oracle.gemm_f16(np.ascontiguousarray(ha[rows]), hb).astype(np.float32)
     host_err = float(np.abs(hc[rows].astype(np.float32) - want).max() / np.abs(want).max())
+    # a narrow column block under a tall A: more row panels than column panels, the slab exchanges
+    # on their own stream beside the uploads
+    m2, n2 = 12288, 1280
+    ha2 = rng.uniform(-1, 1, (m2, k)).astype(np.float16)
+    hb2 = np.ascontiguousarray(hb[:, :n2])
+    hc2 = np.zeros((m2, n2), np.float16)
+    hm.set_option("replicatedOperandA", 1)
+    hm.matmul[(1,)](ha2, hb2, hc2)
+    hm.set_option("replicatedOperandA", 0)
+    status = status or hm.device_status()
+    rows2 = np.arange(0, m2, 251)
+    want2 = oracle.gemm_f16(np.ascontiguousarray(ha2[rows2]), hb2).astype(np.float32)
+    host_err = max(host_err, float(np.abs(hc2[rows2].astype(np.float32) - want2).max() / np.abs(want2).max()))
     q.put((rank, status, out.cpu().numpy(), lo, hi, cshard.cpu().numpy(), runs[0].cpu().numpy(), fused_same,
            (on, lib_rank, lib_world), host_err, mc_out))
     dist.barrier()

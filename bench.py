@@ -719,6 +719,7 @@ def run_product_arm(args):
     e2e_each = [timed(torch, e2e_step, 1, 0, dist if multi else None) for _ in range(e2e_steps)]
     e2e_ms = sum(e2e_each) / len(e2e_each)
     hm.set_option("replicatedOperandA", 0)
+    slab_mode = hm.tp_slab_exchange_mode() if multi else "none"
     e2e_tflops = FLOPS / (e2e_ms * 1e-3) / 1e12
     # the strips of the host path and the whole-problem device run may take different variants
     # (fp32 sums associated differently): agreement is stated as an error, not as byte equality
@@ -776,7 +777,7 @@ def run_product_arm(args):
             "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_step,
                     "d2h_bytes_per_step": M * n_loc * 2 * world, "steps": e2e_steps,
                     "ms_each_step": [round(x, 3) for x in e2e_each], "host_link": host_link,
-                    "a_upload": "1/N row slab per rank, slabs all-gathered over NVLink" if sharded_upload else "whole A",
+                    "a_upload": f"1/N row slab per rank, slabs exchanged over NVLink by {slab_mode}" if sharded_upload else "whole A",
                     "max_abs_rel_vs_device_run": e2e_err, "bytes_equal_to_device_run_on_one_variant": e2e_bytes_equal},
             "parity_sample": parity, "long_run": long_run,
             "gpu_launches": int(launches), "clocks": clocks, "extra": extra,

@@ -93,6 +93,7 @@ _SIGNATURES = {
     "b200mlir_tp_unique_id": (c_int, [c_void_p]),
     "b200mlir_tp_init": (c_int, [c_void_p, c_int, c_int]),
     "b200mlir_tp_info": (c_int, [ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
+    "b200mlir_tp_slab_exchange_mode": (c_int, []),
     "b200mlir_tp_shutdown": (c_int, []),
     "b200mlir_tp_all_reduce_float16": (c_int, [c_void_p, c_i64]),
     "mlp_block_tp_float16": (None, [c_i64, _M2, c_i64, _M1, c_i64, _M2, c_i64, _M2, c_i64, _M2,

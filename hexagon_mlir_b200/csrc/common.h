@@ -280,6 +280,27 @@ int tp_world();  // 1 when no group is initialised
 int tp_all_gather_bytes(const void *src, void *dst, size_t bytes_per_rank, cudaStream_t s);
 int tp_all_reduce_f16(void *buf, size_t count, cudaStream_t s);
 int tp_comm_stream(cudaStream_t *s);
+// Exchange of row slabs between the ranks by copy engines, without a kernel: every rank keeps a
+// window (an A buffer and a flag word per panel and rank) that the others map through CUDA IPC; a
+// rank copies its slab into every peer's buffer and then the call's sequence number into the
+// peer's flag, on one stream, so the flag lands after the data.
+struct SlabExchange {
+  char *a = nullptr;                        // this rank's A buffer
+  char *peer_a[kMaxPushRanks] = {};         // the same buffer of every rank, as this process maps it
+  uint32_t *flags = nullptr;                // [panel][kMaxPushRanks], this rank's
+  uint32_t *peer_flags[kMaxPushRanks] = {};
+  const uint32_t *d_seq = nullptr;          // device word holding `seq` (source of the flag copies on `push`)
+  uint32_t seq = 0;
+  cudaStream_t push = nullptr;
+};
+constexpr int kExchangePanels = 16;
+// Collective, called by every rank with the same `a_bytes`: waits (on the host) until every rank
+// is in the call, (re)creates the windows when they are too small, and hands out this call's
+// sequence number.  *x.a stays null when the machine gives no IPC mapping (the caller then
+// exchanges through ncclAllGather).
+int tp_slab_exchange_begin(size_t a_bytes, SlabExchange *x);
+// on stream s: wait (bounded) until every other rank's flag of `panel` has reached x.seq
+int tp_slab_exchange_wait(const SlabExchange &x, int panel, cudaStream_t s);
 
 // dispatch.cpp
 int gemm_dispatch(const GemmArgs &g);  // picks a variant (option / cache / heuristic) and launches

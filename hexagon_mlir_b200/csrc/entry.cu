@@ -144,12 +144,21 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   const int world = ctx().opt.replicated_operand_a != 0 ? tp_world() : 1;
   cudaStream_t s_in, s_out, s_ag = nullptr, s = ctx().stream;
   B200_TRY(copy_streams(&s_in, &s_out));
-  if (world > 1) B200_TRY(tp_comm_stream(&s_ag));  // slab exchanges run beside the next upload
-  void *base = nullptr;
   const size_t a_bytes = (size_t)M * K * 2, b_bytes = (size_t)K * N * 2, c_bytes = (size_t)M * N * 2;
-  B200_TRY(staging_workspace(a_bytes + b_bytes + c_bytes + 512, &base));
-  __half *dA = (__half *)base;
-  __half *dB = (__half *)((char *)base + ((a_bytes + 255) & ~(size_t)255));
+  // The slabs travel between the GPUs by copy engines into windows the ranks map from each other
+  // (no kernel, so nothing competes with the strip GEMMs for SMs); where the machine gives no such
+  // mapping, by ncclAllGather on the communicator's stream.
+  SlabExchange xc;
+  if (world > 1) {
+    B200_TRY(tp_slab_exchange_begin(a_bytes, &xc));
+    B200_TRY(tp_comm_stream(&s_ag));
+    if (xc.a) s_ag = xc.push;
+  }
+  void *base = nullptr;
+  const size_t a_staged = xc.a ? 0 : a_bytes;  // A lives in the exchange window when there is one
+  B200_TRY(staging_workspace(a_staged + b_bytes + c_bytes + 512, &base));
+  __half *dA = xc.a ? (__half *)xc.a : (__half *)base;
+  __half *dB = (__half *)((char *)base + ((a_staged + 255) & ~(size_t)255));
   __half *dC = (__half *)((char *)dB + ((b_bytes + 255) & ~(size_t)255));
   std::vector<cudaEvent_t> ev;
   const bool debug = getenv("B200MLIR_DEBUG") != nullptr;  // timed events, and a timeline printed at the end
@@ -175,6 +184,7 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   PIPE_CUDA(cudaStreamWaitEvent(s_out, start, 0));
   if (s_ag) PIPE_CUDA(cudaStreamWaitEvent(s_ag, start, 0));
   for (int64_t d = 0; d < std::max(PM, PN) && rc == 0; ++d) {
+    bool exchanged_by_flags = false;
     if (d < PM) {
       const int64_t r0 = d * pm, rows = std::min(pm, M - r0);
       if (world > 1 && rows % world == 0) {
@@ -187,9 +197,21 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
         PIPE_CUDA(new_event(&slab_up));
         PIPE_CUDA(cudaEventRecord(slab_up, s_in));
         PIPE_CUDA(cudaStreamWaitEvent(s_ag, slab_up, 0));
-        if (rc == 0) rc = tp_all_gather_bytes(dA + s0 * K, dA + r0 * K, (size_t)slab * K * 2, s_ag);
-        PIPE_CUDA(new_event(&a_up[d]));
-        PIPE_CUDA(cudaEventRecord(a_up[d], s_ag));
+        if (xc.a && d < kExchangePanels) {
+          const size_t off = (size_t)s0 * K * 2, bytes = (size_t)slab * K * 2;
+          const int me = tp_rank();
+          for (int i = 1; i < world; ++i) {  // each rank starts at its right-hand neighbour
+            const int peer = (me + i) % world;
+            PIPE_CUDA(cudaMemcpyAsync(xc.peer_a[peer] + off, xc.a + off, bytes, cudaMemcpyDefault, s_ag));
+            PIPE_CUDA(cudaMemcpyAsync(xc.peer_flags[peer] + d * kMaxPushRanks + me, xc.d_seq, 4, cudaMemcpyDefault, s_ag));
+          }
+          a_up[d] = slab_up;          // the compute stream waits for this rank's slab by event ...
+          exchanged_by_flags = true;  // ... and for the others' by their flags
+        } else {
+          if (rc == 0) rc = tp_all_gather_bytes(dA + s0 * K, dA + r0 * K, (size_t)slab * K * 2, s_ag);
+          PIPE_CUDA(new_event(&a_up[d]));
+          PIPE_CUDA(cudaEventRecord(a_up[d], s_ag));
+        }
         if (debug) { marks.push_back({"slab up", slab_up}); marks.push_back({"slabs exchanged", a_up[d]}); }
       } else {
         PIPE_CUDA(cudaMemcpy2DAsync(dA + r0 * K, (size_t)K * 2, (const __half *)A.p + r0 * A.ld, (size_t)A.ld * 2,
@@ -222,6 +244,10 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
       if (rows <= 0 || cols <= 0) continue;
       if (d < PM) PIPE_CUDA(cudaStreamWaitEvent(s, a_up[d], 0));
       if (d < PN) PIPE_CUDA(cudaStreamWaitEvent(s, b_up[d], 0));
+      if (exchanged_by_flags && rc == 0) {
+        rc = tp_slab_exchange_wait(xc, (int)d, s);
+        exchanged_by_flags = false;  // once per panel: the column strip follows on the same stream
+      }
       GemmArgs g;
       g.a = dA + r0 * K; g.b = dB + c0; g.c = dC + r0 * N + c0;
       g.m = rows; g.n = cols; g.k = K;
@@ -258,8 +284,9 @@ int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
   if (debug) {  // B200MLIR_DEBUG: when each of the three streams finished
     float a = 0, b = 0, c = 0;
     cudaEventElapsedTime(&a, t0, t_up); cudaEventElapsedTime(&b, t0, t_mm); cudaEventElapsedTime(&c, t0, t_down);
-    fprintf(stderr, "[b200mlir] pipelined host GEMM %lldx%lldx%lld panels %lldx%lld: up done %.2f ms, compute done %.2f ms, down done %.2f ms\n",
-            (long long)M, (long long)N, (long long)K, (long long)PM, (long long)PN, a, b, c);
+    fprintf(stderr, "[b200mlir] pipelined host GEMM %lldx%lldx%lld panels %lldx%lld%s: up done %.2f ms, compute done %.2f ms, down done %.2f ms\n",
+            (long long)M, (long long)N, (long long)K, (long long)PM, (long long)PN,
+            world == 1 ? "" : xc.a ? ", slabs by copy engines" : ", slabs by ncclAllGather", a, b, c);
     if (getenv("B200MLIR_DEBUG")[0] == '2' && tp_rank() == 0)
       for (auto &mk : marks) {
         float t = 0;

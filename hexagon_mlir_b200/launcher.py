@@ -263,6 +263,11 @@ def tp_info():
     return bool(on), r.value, w.value
 
 
+def tp_slab_exchange_mode() -> str:
+    """How the last host-buffer GEMM with a replicated A moved the row slabs between the ranks."""
+    return ("none", "copy engines", "ncclAllGather")[lib().b200mlir_tp_slab_exchange_mode()]
+
+
 def tp_shutdown() -> None:
     if lib().b200mlir_tp_shutdown() != 0:
         check()

@@ -230,6 +230,11 @@ B200_API int b200mlir_tp_unique_id(void *id128);
 B200_API int b200mlir_tp_init(const void *id128, int rank, int world);
 B200_API int b200mlir_tp_info(int *rank, int *world);
 B200_API int b200mlir_tp_shutdown(void);
+/* How the last host-buffer GEMM under option replicatedOperandA exchanged the row slabs of A
+ * between the ranks: 0 none yet, 1 copy engines writing into windows the ranks map from one
+ * another through CUDA IPC (a flag word per panel and rank follows each slab), 2 ncclAllGather
+ * (where the machine gives no such mapping, or B200MLIR_SLAB_EXCHANGE=nccl is set). */
+B200_API int b200mlir_tp_slab_exchange_mode(void);
 /* In-place sum over the group of `count` fp16 elements at the device address `buf`
  * (ncclAllReduce on the calling thread's stream). */
 B200_API int b200mlir_tp_all_reduce_float16(void *buf, int64_t count);

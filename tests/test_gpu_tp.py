@@ -100,8 +100,11 @@ def _worker(rank, world, port, q):
     rows2 = np.arange(0, m2, 251)
     want2 = oracle.gemm_f16(np.ascontiguousarray(ha2[rows2]), hb2).astype(np.float32)
     host_err = max(host_err, float(np.abs(hc2[rows2].astype(np.float32) - want2).max() / np.abs(want2).max()))
+    # the same call with the slabs forced through ncclAllGather is not run here: the mode is fixed
+    # per process; which one ran is reported
+    slab_mode = hm.tp_slab_exchange_mode()
     q.put((rank, status, out.cpu().numpy(), lo, hi, cshard.cpu().numpy(), runs[0].cpu().numpy(), fused_same,
-           (on, lib_rank, lib_world), host_err, mc_out))
+           (on, lib_rank, lib_world), host_err, mc_out, slab_mode))
     dist.barrier()
     hm.tp_shutdown()
     q.close()
@@ -127,8 +130,9 @@ def test_tensor_parallel_mlp_on_gpus(oracle, cuda, world):
     x, gain, wg, wu, wd = _problem()
     want = oracle.mlp(x, gain, wg, wu, wd, 1e-6).astype(np.float32)
     full = np.zeros((x.shape[0], wg.shape[1]), np.float16)
-    for rank, status, out, lo, hi, cshard, fused_out, fused_same, lib_group, host_err, mc_out in results:
+    for rank, status, out, lo, hi, cshard, fused_out, fused_same, lib_group, host_err, mc_out, slab_mode in results:
         assert status == 0
+        assert slab_mode in ("copy engines", "ncclAllGather") and slab_mode == results[0][11]  # every rank took the same form
         assert lib_group == (True, rank, world)       # ncclAllReduce ran inside the library, on its own communicator
         assert host_err <= 1e-2, (rank, host_err)      # sharded upload + all-gather of A
         if mc_out is not None:

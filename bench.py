@@ -542,20 +542,26 @@ def mlp_extra(torch, hm, dist, rank, world):
                 ms, reduction = fms, "fused: read-out pushes partial rows to their owners"
         except Exception as exc:  # symmetric memory is a property of the box, not of this code
             forms["fused_peer_store_ms"] = f"unavailable ({type(exc).__name__})"
-        # the all-reduce by this library's own kernel over NVSwitch multicast (multimem.ld_reduce / multimem.st)
-        try:
-            mc = tp.MulticastTensorParallelMLP(gain, wg, wu, wd, tokens=t, eps=1e-6, group=dist.group.WORLD)
-            if mc.available():
-                mc.captured(x)
-                mms = timed(torch, lambda: mc.captured(x), 20, 5, dist)
-                mc.release()
-                forms["multicast_all_reduce_ms"] = mms
-                if mms < ms:
-                    ms, reduction = mms, "own kernel over NVSwitch multicast: multimem.ld_reduce + multimem.st"
-            else:
-                forms["multicast_all_reduce_ms"] = "unavailable (no multicast mapping)"
-        except Exception as exc:  # noqa: BLE001
-            forms["multicast_all_reduce_ms"] = f"unavailable ({type(exc).__name__}: {exc})"[:200]
+        # the all-reduce by this library's own kernel over NVSwitch multicast (multimem.ld_reduce / multimem.st):
+        # with barrier kernels around the launch, and with both rendezvous inside the launch
+        for key, rdv, what in (("multicast_all_reduce_ms", "barriers", "barrier kernels around it"),
+                               ("multicast_in_kernel_rendezvous_ms", "kernel", "both rendezvous inside the launch")):
+            try:
+                mc = tp.MulticastTensorParallelMLP(gain, wg, wu, wd, tokens=t, eps=1e-6, group=dist.group.WORLD,
+                                                   rendezvous=rdv)
+                if mc.available():
+                    mc.captured(x)
+                    mms = timed(torch, lambda: mc.captured(x), 20, 5, dist)
+                    mc.release()
+                    forms[key] = mms
+                    if hm.device_status() != 0:
+                        forms[key] = "a bounded wait ran out"
+                    elif mms < ms:
+                        ms, reduction = mms, f"own kernel over NVSwitch multicast (multimem.ld_reduce + multimem.st), {what}"
+                else:
+                    forms[key] = "unavailable (no multicast mapping)"
+            except Exception as exc:  # noqa: BLE001
+                forms[key] = f"unavailable ({type(exc).__name__}: {exc})"[:200]
     block.release()  # the captured graph holds NCCL work: drop it before the process group goes
     return {"ms": ms, "reduction": reduction, **forms, "tokens_per_s": t / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
             "parallelism": f"tp{world}", "allreduce_bytes": t * d * 2 if world > 1 else 0, "launch": mode,

@@ -925,6 +925,12 @@ int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_out, int6
   return launch_allreduce_multimem(mc_in, mc_out, elem_offset, count);
 }
 
+int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *local_buf, int64_t elem_offset, int64_t count,
+                                                int64_t flags_elem_offset, int rank, int world, void *state) {
+  clear_error();
+  return launch_allreduce_multimem_sync(mc_buf, local_buf, elem_offset, count, flags_elem_offset, rank, world, state);
+}
+
 int b200mlir_mlp_phase_times(double *us, int cap) {
   clear_error();
   if (!us || cap < 1) {

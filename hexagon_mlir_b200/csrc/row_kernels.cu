@@ -457,6 +457,97 @@ allreduce_multimem_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ m
   }
 }
 
+// The same all-reduce with the two rendezvous of the ranks inside the launch (no barrier kernels
+// around it).  `flags` are 16 words at the same offset of every rank's copy: [r] = the launch
+// number at which rank r's partial was complete, [8 + r] = the launch number whose sums rank r has
+// written everywhere.  Each is stored through the multicast address (one store reaches every
+// copy) and polled in the local copy.  `state` is local: [0] launches finished, [1] CTAs finished.
+//  entry: every CTA stores "arrived" (idempotent) and waits until all ranks have arrived;
+//  body:  this rank's slice, as above;
+//  exit:  the last CTA to finish stores "written" and waits for every rank's "written", so the
+//         launch ends only when this rank's copy holds every slice and nobody still reads it.
+// Every wait is bounded; one that runs out records {site 48, late rank} and the launch returns.
+__device__ __forceinline__ bool flags_reached(const uint32_t *flags, int world, uint32_t epoch, int *status, int site) {
+  const int r = threadIdx.x;
+  bool ok = true;
+  if (r < world) {
+    const long long t0 = clock64();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if (*(volatile int *)status != 0 || clock64() - t0 > 2000000000LL) {
+        if (atomicCAS(status, 0, site) == 0) status[1] = r;
+        ok = false;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  return ok;
+}
+
+__global__ void __launch_bounds__(256)
+allreduce_multimem_sync_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ mc_out, int64_t nvec,
+                               uint32_t *mc_flags, const uint32_t *local_flags, int world, int rank, uint32_t *state,
+                               int *status) {
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    const uint32_t e = *(volatile uint32_t *)state + 1;
+    s_epoch = e;
+    __threadfence_system();  // the partial, written by the launch before this one, is complete
+    asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(mc_flags + rank), "r"(e) : "memory");
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
+  if (threadIdx.x < 32) flags_reached(local_flags, world, epoch, status, 48);
+  __syncthreads();
+
+  constexpr int UNR = 4;
+  for (int64_t base = ((int64_t)blockIdx.x * 256) * UNR + threadIdx.x; base < nvec;
+       base += (int64_t)gridDim.x * 256 * UNR) {
+    uint32_t v[UNR][4];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t i = base + (int64_t)u * 256;
+      if (i < nvec)
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3])
+                     : "l"(mc_in + i)
+                     : "memory");
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const int64_t i = base + (int64_t)u * 256;
+      if (i < nvec)
+        asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_out + i), "r"(v[u][0]),
+                     "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3])
+                     : "memory");
+    }
+  }
+
+  __syncthreads();
+  __shared__ int s_last;
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // this CTA's sums are on their way to every copy before it counts as finished
+    s_last = atomicAdd(&state[1], 1u) == gridDim.x - 1;
+    if (s_last) {
+      __threadfence_system();
+      state[1] = 0;
+      asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(mc_flags + 8 + rank), "r"(epoch) : "memory");
+    }
+  }
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < 32) flags_reached(local_flags + 8, world, epoch, status, 48);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      state[0] = epoch;
+      __threadfence();
+    }
+  }
+}
+
 template <int OP>
 int launch_ew(const __half *a, const __half *b, __half *y, int64_t n, const char *what) {
   B200_TRY(ensure_ready());
@@ -569,6 +660,29 @@ int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offs
       reinterpret_cast<const uint4 *>((const __half *)mc_in + elem_offset),
       reinterpret_cast<uint4 *>((__half *)mc_out + elem_offset), nvec);
   return check_launch("allreduce_multimem");
+}
+
+int launch_allreduce_multimem_sync(void *mc_buf, void *local_buf, int64_t elem_offset, int64_t count,
+                                   int64_t flags_elem_offset, int rank, int world, void *state) {
+  B200_TRY(ensure_ready());
+  if (!mc_buf || !local_buf || !state || elem_offset < 0 || count < 0 || elem_offset % 8 || count % 8 ||
+      flags_elem_offset < 0 || flags_elem_offset % 8 || !aligned16(mc_buf) || !aligned16(local_buf) || world < 2 ||
+      world > kMaxPushRanks || rank < 0 || rank >= world)
+    return set_error(B200MLIR_ERR_BAD_ARG,
+                     "allreduce_multimem_sync: 16-byte aligned multicast and local addresses of one buffer, offsets and "
+                     "count multiples of 8 elements, 2 <= world <= %d, a device state of two words", kMaxPushRanks);
+  const int64_t nvec = count >> 3;
+  int64_t blocks = (nvec + 256 * 4 - 1) / (256 * 4);
+  const int64_t cap = (int64_t)ctx().sm_count * 4;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  allreduce_multimem_sync_kernel<<<(unsigned)blocks, 256, 0, ctx().stream>>>(
+      reinterpret_cast<const uint4 *>((const __half *)mc_buf + elem_offset),
+      reinterpret_cast<uint4 *>((__half *)mc_buf + elem_offset), nvec,
+      reinterpret_cast<uint32_t *>((__half *)mc_buf + flags_elem_offset),
+      reinterpret_cast<const uint32_t *>((const __half *)local_buf + flags_elem_offset), world, rank, (uint32_t *)state,
+      ctx().d_status);
+  return check_launch("allreduce_multimem_sync");
 }
 
 static bool row_fast_path(const void *x, const void *y, int64_t cols, int64_t ldx, int64_t ldy) {

@@ -288,6 +288,17 @@ def tp_allreduce_multimem(mc_in: int, mc_out: int, elem_offset: int, count: int,
         check()
 
 
+def tp_allreduce_multimem_sync(mc_buf: int, local, elem_offset: int, count: int, flags_elem_offset: int, rank: int,
+                               world: int, state) -> None:
+    """The same with both rendezvous of the ranks inside the launch: `local` is this rank's tensor
+    over the symmetric buffer (data and 16 flag words), `state` two int32 words on the device."""
+    _sync_stream([local])
+    if lib().b200mlir_tp_allreduce_multimem_sync_float16(int(mc_buf), int(local.data_ptr()), int(elem_offset), int(count),
+                                                         int(flags_elem_offset), int(rank), int(world),
+                                                         int(state.data_ptr())) != 0:
+        check()
+
+
 def mlp_phase_times():
     """{"rmsnorm", "gate_up", "down"[, "collective"]} in microseconds for the last MLP block issued with
     option mlpPhaseTiming set."""

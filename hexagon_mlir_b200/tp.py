@@ -219,9 +219,13 @@ class MulticastTensorParallelMLP:
     switch adds in fp32 and rounds once) and writes the sums into every copy with `multimem.st`;
     after a second barrier every rank holds the block output.  Per GPU 1/world of the buffer
     crosses NVLink in each direction.  Needs a multicast mapping (NVSwitch; `available()` tells),
-    tokens divisible by the world size."""
+    tokens divisible by the world size.
 
-    def __init__(self, gain, wg, wu, wd, tokens, eps=1e-6, group=None, timeout_ms=10000):
+    rendezvous="kernel" (default): both barriers are inside the all-reduce launch (flag words in
+    the symmetric buffer, stored through the multicast address, polled locally, every wait
+    bounded); "barriers": the symmetric-memory handle's barrier kernels around the launch."""
+
+    def __init__(self, gain, wg, wu, wd, tokens, eps=1e-6, group=None, timeout_ms=10000, rendezvous="kernel"):
         import torch.distributed._symmetric_memory as symm
         if group is None:
             group = dist.group.WORLD
@@ -233,9 +237,19 @@ class MulticastTensorParallelMLP:
             raise ValueError("tokens must be divisible by the world size")
         self.rows = self.tokens // self.world
         self.timeout_ms = int(timeout_ms)
-        self.out = symm.empty((self.tokens, self.width), dtype=torch.float16, device=wd.device)
-        self._h = symm.rendezvous(self.out, group)
+        if rendezvous not in ("kernel", "barriers"):
+            raise ValueError("rendezvous is 'kernel' or 'barriers'")
+        self.rendezvous = rendezvous
+        n = self.tokens * self.width
+        self._buf = symm.empty((n + 64,), dtype=torch.float16, device=wd.device)  # the output, then 16 flag words
+        self._h = symm.rendezvous(self._buf, group)
         self._mc = int(getattr(self._h, "multicast_ptr", 0) or 0)
+        self.out = self._buf[:n].view(self.tokens, self.width)
+        self._buf[n:].zero_()
+        self._state = torch.zeros(2, dtype=torch.int32, device=wd.device)
+        torch.cuda.synchronize(wd.device)
+        self._h.barrier(channel=0, timeout_ms=self.timeout_ms)  # every rank's flags read zero before the first launch
+        torch.cuda.synchronize(wd.device)
         self._graph = None
 
     def available(self) -> bool:
@@ -246,8 +260,12 @@ class MulticastTensorParallelMLP:
         if not self._mc:
             raise RuntimeError("no multicast mapping on this machine")
         _l.mlp_block[(1,)](x, self.gain, self.wg, self.wu, self.wd, self.out, eps=self.eps, add_residual=self.rank == 0)
-        self._h.barrier(channel=0, timeout_ms=self.timeout_ms)   # every rank's partial is written
         n = self.rows * self.width
+        if self.rendezvous == "kernel":
+            _l.tp_allreduce_multimem_sync(self._mc, self._buf, self.rank * n, n, self.tokens * self.width, self.rank,
+                                          self.world, self._state)
+            return self.out
+        self._h.barrier(channel=0, timeout_ms=self.timeout_ms)   # every rank's partial is written
         _l.tp_allreduce_multimem(self._mc, self._mc, self.rank * n, n, like=self.out)
         self._h.barrier(channel=1, timeout_ms=self.timeout_ms)   # every rank's rows have been written everywhere
         return self.out

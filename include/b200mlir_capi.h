@@ -261,6 +261,19 @@ B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank
  * in elements, multiples of 8.  No reference counterpart (single device). */
 B200_API int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_out, int64_t elem_offset,
                                                     int64_t count);
+/* The same, in place, with both rendezvous inside the launch: `mc_buf` and `local_buf` are the
+ * multicast and this rank's own address of ONE symmetric fp16 buffer that also holds 16 flag
+ * words (64 bytes, zero before the first call) at element `flags_elem_offset`; `state` is two
+ * zero-initialised 32-bit words of this rank's device memory that the calls keep between them.
+ * Every rank of the group issues the call once per all-reduce, in the same order, after the
+ * producer of its copy on the same stream.  The launch waits (each wait bounded to about a second,
+ * then device status B200MLIR_ERR_DEVICE_WAIT site 48 with the late rank) until every rank's copy
+ * is complete, sums this rank's slice, and ends only when every rank's sums are in this rank's
+ * copy and no rank still reads it.  The flag epoch lives on the device, so the call can be
+ * replayed from a captured graph.  No reference counterpart (single device). */
+B200_API int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *local_buf, int64_t elem_offset,
+                                                         int64_t count, int64_t flags_elem_offset, int rank,
+                                                         int world, void *state);
 
 /* Phase times of the most recent MLP block issued by the calling thread while option
  * "mlpPhaseTiming" was non-zero: microseconds of RMSNorm, gate/up GEMM (SwiGLU read-out), down

@@ -62,15 +62,23 @@ def _worker(rank, world, port, q):
     fused_same = all(torch.equal(r, runs[0]) for r in runs)
     # the all-reduce by the library's own kernel over the switch's multicast addresses, where the
     # machine maps them (bit-identical on every rank and run to run, or skipped)
-    mc = tp.MulticastTensorParallelMLP(T(gain), tp.shard_columns(T(wg), rank, world), tp.shard_columns(T(wu), rank, world),
-                                       tp.shard_rows(T(wd), rank, world), tokens=x.shape[0], eps=1e-6,
-                                       group=dist.group.WORLD, timeout_ms=20000)
     mc_out = None
-    if mc.available():
+    for rdv in ("barriers", "kernel"):   # barrier kernels around the launch / both rendezvous inside it
+        mc = tp.MulticastTensorParallelMLP(T(gain), tp.shard_columns(T(wg), rank, world), tp.shard_columns(T(wu), rank, world),
+                                           tp.shard_rows(T(wd), rank, world), tokens=x.shape[0], eps=1e-6,
+                                           group=dist.group.WORLD, timeout_ms=20000, rendezvous=rdv)
+        if not mc.available():
+            break
         mruns = [mc(xt).clone() for _ in range(3)]
+        mruns.append(mc.captured(xt).clone())     # and replayed from a captured graph (the flag epoch lives on the device)
+        mruns.append(mc.captured(xt).clone())
         torch.cuda.synchronize()
+        mc.release()
         status = status or hm.device_status()
-        mc_out = (mruns[0].cpu().numpy(), all(torch.equal(r, mruns[0]) for r in mruns))
+        same = all(torch.equal(r, mruns[0]) for r in mruns)
+        if mc_out is not None:
+            same = same and bool(np.array_equal(mc_out[0], mruns[0].cpu().numpy()))  # both forms: the same bytes
+        mc_out = (mruns[0].cpu().numpy(), same)
     # the library's own communicator exists (the block created it): a host-buffer GEMM whose A every
     # rank holds — each rank uploads its row slab of every panel, the slabs are all-gathered on the GPUs
     on, lib_rank, lib_world = hm.tp_info()

@@ -544,11 +544,14 @@ def mlp_extra(torch, hm, dist, rank, world):
             forms["fused_peer_store_ms"] = f"unavailable ({type(exc).__name__})"
         # the all-reduce by this library's own kernel over NVSwitch multicast (multimem.ld_reduce / multimem.st):
         # with barrier kernels around the launch, and with both rendezvous inside the launch
-        for key, rdv, what in (("multicast_all_reduce_ms", "barriers", "barrier kernels around it"),
-                               ("multicast_in_kernel_rendezvous_ms", "kernel", "both rendezvous inside the launch")):
+        for key, rdv, ch, what in (
+                ("multicast_all_reduce_ms", "barriers", 1, "barrier kernels around it"),
+                ("multicast_in_kernel_rendezvous_ms", "kernel", 1, "both rendezvous inside the launch"),
+                ("multicast_two_chunks_overlapped_ms", "kernel", 2,
+                 "one call, each token chunk's all-reduce beside the next chunk's down GEMM")):
             try:
                 mc = tp.MulticastTensorParallelMLP(gain, wg, wu, wd, tokens=t, eps=1e-6, group=dist.group.WORLD,
-                                                   rendezvous=rdv)
+                                                   rendezvous=rdv, chunks=ch)
                 if mc.available():
                     mc.captured(x)
                     mms = timed(torch, lambda: mc.captured(x), 20, 5, dist)

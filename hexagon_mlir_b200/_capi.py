@@ -98,6 +98,9 @@ _SIGNATURES = {
     "b200mlir_tp_all_reduce_float16": (c_int, [c_void_p, c_i64]),
     "mlp_block_tp_float16": (None, [c_i64, _M2, c_i64, _M1, c_i64, _M2, c_i64, _M2, c_i64, _M2,
                                     c_i64, _M2, ctypes.c_float, c_int] + _GRID),
+    "mlp_block_tp_multicast_float16": (None, [c_i64, _M2, c_i64, _M1, c_i64, _M2, c_i64, _M2, c_i64, _M2,
+                                              c_i64, _M2, c_void_p, c_i64, c_void_p, c_int, c_int, ctypes.c_float,
+                                              c_int] + _GRID),
     "b200mlir_tp_allreduce_multimem_float16": (c_int, [c_void_p, c_void_p, c_i64, c_i64]),
     "b200mlir_tp_allreduce_multimem_sync_float16": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64, c_int, c_int,
                                                             c_void_p]),

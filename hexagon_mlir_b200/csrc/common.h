@@ -166,7 +166,8 @@ int launch_reduce_rows_push(const __half *recv, const __half *residual, int64_t 
 int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offset, int64_t count);
 // the same with both rendezvous of the ranks inside the launch (flag words in the buffer itself)
 int launch_allreduce_multimem_sync(void *mc_buf, void *local_buf, int64_t elem_offset, int64_t count,
-                                   int64_t flags_elem_offset, int rank, int world, void *state);
+                                   int64_t flags_elem_offset, int rank, int world, void *state,
+                                   cudaStream_t stream = nullptr);  // null: the calling thread's stream
 
 // layout.cu
 int launch_transpose_i8(const int8_t *src, int8_t *dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst);

@@ -887,6 +887,74 @@ void mlp_block_tp_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D 
   }
 }
 
+// The tensor-parallel block with the sum over ranks done by this library's own kernel through
+// the NVSwitch's multicast addresses, overlapped with the math: `out` is this rank's [T, D] view
+// at the start of a symmetric buffer whose multicast address is `mc_buf` and which holds 16 flag
+// words at element `flags_elem_offset` (see b200mlir_tp_allreduce_multimem_sync_float16).  The
+// down projection is cut into `chunks` token chunks; as soon as a chunk's GEMM has been issued its
+// all-reduce is launched on a second stream, where it runs beside the next chunk's GEMM: the
+// kernel uses no shared memory and few registers, so its CTAs fit on the SMs the persistent GEMM
+// occupies.  Both rendezvous of the ranks are inside that launch (bounded waits).
+void mlp_block_tp_multicast_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
+                                    B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
+                                    int64_t ro, B200MemRef2D *out, void *mc_buf, int64_t flags_elem_offset,
+                                    void *state, int rank, int world, float eps, int chunks, B200_GRID_ARGS) {
+  ENTER_KERNEL();
+  if (ensure_ready()) return;
+  View2 X, O;
+  if (view2("x", rx, x, 2, &X) || view2("out", ro, out, 2, &O)) return;
+  const int64_t T = X.rows, D = X.cols;
+  if (O.rows != T || O.cols != D || O.ld != D || !is_device_ptr(X.p) || !is_device_ptr(O.p) || !mc_buf || !state ||
+      world < 2 || world > kMaxPushRanks || rank < 0 || rank >= world || flags_elem_offset < T * D) {
+    set_error(B200MLIR_ERR_BAD_ARG,
+              "mlp_block_tp_multicast: dense device [T, D] out at the start of the symmetric buffer, its multicast "
+              "address, flag words behind the data, 2 <= world <= %d", kMaxPushRanks);
+    return;
+  }
+  if (T == 0 || D == 0) return;
+  if (chunks < 1) chunks = 1;
+  if (chunks > 16) chunks = 16;
+  // every chunk a multiple of 256 rows (whole tiles) whose rows divide over the ranks
+  int64_t step = ((T + chunks - 1) / chunks + 255) / 256 * 256;
+  if (chunks > 1 && (T % step != 0 || step % world != 0)) {
+    chunks = 1;
+    step = T;
+  }
+  if (T % world != 0 || (D % 8) != 0) {
+    set_error(B200MLIR_ERR_BAD_ARG, "mlp_block_tp_multicast: tokens divisible by the world size, width a multiple of 8");
+    return;
+  }
+  cudaStream_t s = ctx().stream, sc = nullptr;
+  if (chunks > 1 && tp_comm_stream(&sc)) return;
+  cudaEvent_t ev[16] = {}, done = nullptr;
+  int used = 0;
+  ChunkHook hook = [&](int64_t r0, int64_t rows, void *) -> int {
+    const int64_t mine = rows / world;  // this rank sums rows [r0 + rank * mine, + mine) of the chunk
+    const int64_t off = (r0 + (int64_t)rank * mine) * D, cnt = mine * D;
+    if (chunks == 1) {
+      int rc = launch_allreduce_multimem_sync(mc_buf, O.p, off, cnt, flags_elem_offset, rank, world, state, s);
+      t_phases.mark(4);
+      return rc;
+    }
+    if (cudaEventCreateWithFlags(&ev[used], cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventRecord(ev[used], s) != cudaSuccess || cudaStreamWaitEvent(sc, ev[used], 0) != cudaSuccess) {
+      ++used;
+      return set_error(B200MLIR_ERR_CUDA, "mlp_block_tp_multicast: event plumbing failed: %s",
+                       cudaGetErrorString(cudaGetLastError()));
+    }
+    ++used;
+    return launch_allreduce_multimem_sync(mc_buf, O.p, off, cnt, flags_elem_offset, rank, world, state, sc);
+  };
+  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, rank == 0 ? 1 : 0, nullptr, chunks, &hook);
+  if (chunks > 1) {  // join: the caller's stream continues after the last chunk's all-reduce
+    if (cudaEventCreateWithFlags(&done, cudaEventDisableTiming) == cudaSuccess && cudaEventRecord(done, sc) == cudaSuccess)
+      cudaStreamWaitEvent(s, done, 0);
+    if (done) cudaEventDestroy(done);
+  }
+  for (int i = 0; i < used; ++i)
+    if (ev[i]) cudaEventDestroy(ev[i]);
+}
+
 static int fill_push(PushTargets *pt, void *const *peer_recv, int world, int rank, int64_t rows) {
   if (!peer_recv || world < 1 || world > kMaxPushRanks || rank < 0 || rank >= world || rows < 1 || rows % world)
     return set_error(B200MLIR_ERR_BAD_ARG, "tensor-parallel push: world 1..%d, rank inside it, rows divisible by world",

@@ -663,7 +663,7 @@ int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offs
 }
 
 int launch_allreduce_multimem_sync(void *mc_buf, void *local_buf, int64_t elem_offset, int64_t count,
-                                   int64_t flags_elem_offset, int rank, int world, void *state) {
+                                   int64_t flags_elem_offset, int rank, int world, void *state, cudaStream_t stream) {
   B200_TRY(ensure_ready());
   if (!mc_buf || !local_buf || !state || elem_offset < 0 || count < 0 || elem_offset % 8 || count % 8 ||
       flags_elem_offset < 0 || flags_elem_offset % 8 || !aligned16(mc_buf) || !aligned16(local_buf) || world < 2 ||
@@ -676,7 +676,7 @@ int launch_allreduce_multimem_sync(void *mc_buf, void *local_buf, int64_t elem_o
   const int64_t cap = (int64_t)ctx().sm_count * 4;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  allreduce_multimem_sync_kernel<<<(unsigned)blocks, 256, 0, ctx().stream>>>(
+  allreduce_multimem_sync_kernel<<<(unsigned)blocks, 256, 0, stream ? stream : ctx().stream>>>(
       reinterpret_cast<const uint4 *>((const __half *)mc_buf + elem_offset),
       reinterpret_cast<uint4 *>((__half *)mc_buf + elem_offset), nvec,
       reinterpret_cast<uint32_t *>((__half *)mc_buf + flags_elem_offset),

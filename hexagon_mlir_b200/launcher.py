@@ -238,7 +238,12 @@ def matmul_f32out(a, b, c32, res32=None):
 mlp_block_tp = Kernel(
     "mlp_block_tp_float16", (2, 1, 2, 2, 2, 2),
     scalars=lambda args, opts: [ctypes.c_float(float(opts.get("eps", 1e-6))), int(opts.get("chunks", 1))])
-_ACCEPTED |= {"chunks"}
+mlp_block_tp_multicast = Kernel(
+    "mlp_block_tp_multicast_float16", (2, 1, 2, 2, 2, 2),
+    scalars=lambda args, opts: [ctypes.c_void_p(int(opts["mc_buf"])), ctypes.c_int64(int(opts["flags_elem_offset"])),
+                                ctypes.c_void_p(int(opts["state"].data_ptr())), int(opts["rank"]), int(opts["world"]),
+                                ctypes.c_float(float(opts.get("eps", 1e-6))), int(opts.get("chunks", 1))])
+_ACCEPTED |= {"chunks", "mc_buf", "flags_elem_offset", "state", "rank", "world"}
 
 
 def tp_unique_id() -> bytes:

@@ -223,9 +223,14 @@ class MulticastTensorParallelMLP:
 
     rendezvous="kernel" (default): both barriers are inside the all-reduce launch (flag words in
     the symmetric buffer, stored through the multicast address, polled locally, every wait
-    bounded); "barriers": the symmetric-memory handle's barrier kernels around the launch."""
+    bounded); "barriers": the symmetric-memory handle's barrier kernels around the launch.
 
-    def __init__(self, gain, wg, wu, wd, tokens, eps=1e-6, group=None, timeout_ms=10000, rendezvous="kernel"):
+    chunks > 1 (rendezvous="kernel" only): the whole block is ONE call into the library
+    (`mlp_block_tp_multicast_float16`); the down projection is cut into token chunks and each
+    chunk's all-reduce runs on a second stream beside the next chunk's GEMM."""
+
+    def __init__(self, gain, wg, wu, wd, tokens, eps=1e-6, group=None, timeout_ms=10000, rendezvous="kernel",
+                 chunks=1):
         import torch.distributed._symmetric_memory as symm
         if group is None:
             group = dist.group.WORLD
@@ -240,6 +245,9 @@ class MulticastTensorParallelMLP:
         if rendezvous not in ("kernel", "barriers"):
             raise ValueError("rendezvous is 'kernel' or 'barriers'")
         self.rendezvous = rendezvous
+        self.chunks = int(chunks)
+        if self.chunks > 1 and rendezvous != "kernel":
+            raise ValueError("token chunks need rendezvous='kernel'")
         n = self.tokens * self.width
         self._buf = symm.empty((n + 64,), dtype=torch.float16, device=wd.device)  # the output, then 16 flag words
         self._h = symm.rendezvous(self._buf, group)
@@ -259,6 +267,11 @@ class MulticastTensorParallelMLP:
         """Returns the block output (a buffer this object owns; valid until the next call)."""
         if not self._mc:
             raise RuntimeError("no multicast mapping on this machine")
+        if self.chunks > 1:
+            _l.mlp_block_tp_multicast[(1,)](x, self.gain, self.wg, self.wu, self.wd, self.out, mc_buf=self._mc,
+                                            flags_elem_offset=self.tokens * self.width, state=self._state,
+                                            rank=self.rank, world=self.world, eps=self.eps, chunks=self.chunks)
+            return self.out
         _l.mlp_block[(1,)](x, self.gain, self.wg, self.wu, self.wd, self.out, eps=self.eps, add_residual=self.rank == 0)
         n = self.rows * self.width
         if self.rendezvous == "kernel":

@@ -250,6 +250,21 @@ B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank
                                    int64_t rank_wg, B200MemRef2D *wg, int64_t rank_wu, B200MemRef2D *wu,
                                    int64_t rank_wd, B200MemRef2D *wd, int64_t rank_o, B200MemRef2D *out,
                                    float eps, int chunks, B200_GRID_ARGS);
+/* The same block with the sum over ranks done by this library's own kernel through the NVSwitch's
+ * multicast addresses and overlapped with the math, one fused call: `out` is this rank's dense
+ * [T, D] view at the START of a symmetric fp16 buffer, `mc_buf` that buffer's multicast address,
+ * `flags_elem_offset` (>= T*D) the element at which the buffer holds 16 zero-initialised flag
+ * words, `state` two zero-initialised 32-bit words of this rank's device memory (both as for
+ * b200mlir_tp_allreduce_multimem_sync_float16).  The down projection is cut into `chunks` token
+ * chunks (whole 256-row tiles whose rows divide over the ranks, else one chunk); a chunk's
+ * all-reduce is launched on a second stream as soon as its GEMM has been issued and runs beside
+ * the next chunk's GEMM on the same SMs.  Tokens divisible by the world size.  A collective call:
+ * every rank makes it with the same T, D and chunks.  No reference counterpart (single device). */
+B200_API void mlp_block_tp_multicast_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_gain, B200MemRef1D *gain,
+                                             int64_t rank_wg, B200MemRef2D *wg, int64_t rank_wu, B200MemRef2D *wu,
+                                             int64_t rank_wd, B200MemRef2D *wd, int64_t rank_o, B200MemRef2D *out,
+                                             void *mc_buf, int64_t flags_elem_offset, void *state, int rank,
+                                             int world, float eps, int chunks, B200_GRID_ARGS);
 
 /* This rank's share of an all-reduce through NVSwitch multicast (NVLS): `mc_in` / `mc_out` are
  * MULTICAST addresses of fp16 buffers that every rank of the group holds (the symmetric-memory

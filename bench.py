@@ -650,6 +650,51 @@ def run_product_arm(args):
     kernel_tflops = (2.0 * M * n_loc * K) / (ms * 1e-3) / 1e12  # this rank's kernel
     plan = hm.gemm_explain(M, n_loc, K)
 
+    # The device-timed value exists from here on.  Everything after it (long run, parity sample, the
+    # host-buffer calls, the extra kernels and the multi-rank MLP forms) is reported in the same
+    # line; should one of those stages fail or stall on some rank, the line is still written, with
+    # what was measured and the stage named in "incomplete".
+    peak = peaks["bf16_tflops"]
+    capture = DRAM_TRAFFIC_CAPTURES.get((plan["name"], M, n_loc, K))
+    line = {
+        "metric": "gemm_f16_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sharding": f"N split over {world} rank(s), A replicated, no collective",
+                   "l2": "inputs larger than L2 (A 268 MB per rank)", "variant": plan["name"],
+                   "inputs": f"Philox4x32-10, A seed {SEED_A}, B seed {SEED_B}, U[-1,1)",
+                   "accumulate": "fp32 in TMEM, one fp16 rounding"},
+        "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
+                     "frac": kernel_tflops / peak,
+                     "traffic": (capture or {}).get("bytes"), "traffic_source": capture,
+                     "peak_source": f"{peak_kind} cuBLAS bf16 burst; sustained {peaks.get('bf16_tflops_sustained')}",
+                     "frac_of_sustained": kernel_tflops / peaks.get("bf16_tflops_sustained", peak),
+                     "frac_of_nominal_2250": kernel_tflops / 2250.0,
+                     "algorithmic_flops_per_launch": 2.0 * M * n_loc * K},
+        "cpu_baseline": None, "e2e": None, "parity_sample": None, "long_run": None,
+        "gpu_launches": int(launches), "clocks": clocks, "extra": {},
+    }
+    stage = {"name": "long_run", "written": False}
+    write_lock = threading.Lock()
+
+    def write_line(incomplete=None):
+        with write_lock:
+            if stage["written"]:
+                return
+            stage["written"] = True
+            if incomplete:
+                line["incomplete"] = incomplete
+            if rank == 0:
+                sys.stdout.flush()
+                os.write(json_fd, (json.dumps(line) + "\n").encode())
+
+    def stalled():
+        write_line(f"stage '{stage['name']}' did not finish within {args.stage_limit:.0f} s on some rank")
+        os._exit(0)
+    watchdog = threading.Timer(args.stage_limit, stalled)
+    watchdog.daemon = True
+    watchdog.start()
+
     # the same loop kept running for --min-time seconds: the chip settles at the clock its power
     # limit allows, and time x median SM MHz lets runs at different N be compared at equal clocks
     long_run = None
@@ -667,135 +712,127 @@ def run_product_arm(args):
                     "value": FLOPS / (lms * 1e-3) / 1e12, "sm_mhz_median": lsum["sm_mhz"], "reasons": lsum["reasons"],
                     "ms_x_mhz": lms * lsum["sm_mhz"] if lsum["sm_mhz"] else None}
 
+    line["long_run"] = long_run
+
     # parity of the timed result itself (untimed): sampled tiles against the oracle
+    stage["name"] = "parity_sample"
     parity = parity_sample(torch, hm, c, n_lo) if rank == 0 else None
     if parity is not None and not parity["max_abs_rel"] <= 1e-2:
         raise SystemExit(f"bench.py: the timed GEMM disagrees with the oracle: {parity}")
+    line["parity_sample"] = parity
+    stage["name"] = "e2e"
 
-    # e2e: same GEMM through the kernel entry point with pinned host buffers.  At N > 1 every rank's
-    # host holds the same A: each rank sends up its 1/N row slab over its own PCIe link and the
-    # slabs are exchanged GPU to GPU inside the call (option replicatedOperandA; needs the library's
-    # own communicator, which tp.init_group creates).
-    e2e_steps = max(1, min(3, args.steps))
-    ha = torch.empty((M, K), dtype=torch.float16).pin_memory()
-    hb = torch.empty((K, n_loc), dtype=torch.float16).pin_memory()
-    hc = torch.empty((M, n_loc), dtype=torch.float16).pin_memory()
-    ha.copy_(a)
-    hb.copy_(b)
-    torch.cuda.synchronize()
-    npa, npb, npc = ha.numpy(), hb.numpy(), hc.numpy()
-    sharded_upload = False
-    if multi:
-        from hexagon_mlir_b200 import tp
-        tp.init_group(dist.group.WORLD)
-        hm.set_option("replicatedOperandA", 1)
-        sharded_upload = True
-
-    # what the host side gives at this moment, all ranks copying at once: one direction at a time,
-    # then both at once.  The GPUs of a box share one host (and the host is shared with other
-    # tenants), so the aggregate — not the per-GPU link — bounds the host-buffer call at N > 1.
-    def link_rate(up, down):
-        s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
-        if multi:
-            dist.barrier()
+    def measure_e2e():
+        # e2e: same GEMM through the kernel entry point with pinned host buffers.  At N > 1 every rank's
+        # host holds the same A: each rank sends up its 1/N row slab over its own PCIe link and the
+        # slabs are exchanged GPU to GPU inside the call (option replicatedOperandA; needs the library's
+        # own communicator, which tp.init_group creates).
+        e2e_steps = max(1, min(3, args.steps))
+        ha = torch.empty((M, K), dtype=torch.float16).pin_memory()
+        hb = torch.empty((K, n_loc), dtype=torch.float16).pin_memory()
+        hc = torch.empty((M, n_loc), dtype=torch.float16).pin_memory()
+        ha.copy_(a)
+        hb.copy_(b)
         torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        if up:
-            with torch.cuda.stream(s1):
-                c2.copy_(hc, non_blocking=True)
-        if down:
-            with torch.cuda.stream(s2):
-                hc2.copy_(c, non_blocking=True)
-        torch.cuda.synchronize()
-        gbs = hc.numel() * 2 / (time.perf_counter() - t0) / 1e9
+        npa, npb, npc = ha.numpy(), hb.numpy(), hc.numpy()
+        sharded_upload = False
         if multi:
-            t = torch.tensor([gbs], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MIN)
-            gbs = float(t.item())
-        return gbs
-    c2, hc2 = torch.empty_like(c), torch.empty_like(hc).pin_memory()
-    link_rate(True, True)
-    host_link = {"h2d_gbs_per_gpu": round(link_rate(True, False), 1), "d2h_gbs_per_gpu": round(link_rate(False, True), 1),
-                 "both_ways_gbs_each_per_gpu": round(link_rate(True, True), 1), "ranks_copying_at_once": world,
-                 "rate": "slowest rank"}
-    bytes_rank = (M * K // world + K * n_loc + M * n_loc) * 2
-    host_link["floor_ms"] = round(bytes_rank / 2 / (host_link["both_ways_gbs_each_per_gpu"] * 1e9) * 1e3, 2)
-    del c2, hc2
+            from hexagon_mlir_b200 import tp
+            tp.init_group(dist.group.WORLD)
+            hm.set_option("replicatedOperandA", 1)
+            sharded_upload = True
 
-    def e2e_step():
-        hm.matmul[(1,)](npa, npb, npc)  # H2D A and B, GEMM, D2H C, wait — all inside the call
-    e2e_step()
-    e2e_each = [timed(torch, e2e_step, 1, 0, dist if multi else None) for _ in range(e2e_steps)]
-    e2e_ms = sum(e2e_each) / len(e2e_each)
-    hm.set_option("replicatedOperandA", 0)
-    slab_mode = hm.tp_slab_exchange_mode() if multi else "none"
-    e2e_tflops = FLOPS / (e2e_ms * 1e-3) / 1e12
-    # the strips of the host path and the whole-problem device run may take different variants
-    # (fp32 sums associated differently): agreement is stated as an error, not as byte equality
-    sl = slice(0, 256)
-    dref = c[sl].float()
-    e2e_err = float((hc[sl].cuda().float() - dref).abs().max() / dref.abs().max())
-    h2d_step = (M * K // (world if sharded_upload else 1) + K * n_loc) * 2 * world
-    # ... and as byte equality with every launch on ONE whole-tile variant (same fp32 sums in the same order)
-    hm.set_option("gemmVariant", 3)
-    if sharded_upload:
-        hm.set_option("replicatedOperandA", 1)
-    try:
+        # what the host side gives at this moment, all ranks copying at once: one direction at a time,
+        # then both at once.  The GPUs of a box share one host (and the host is shared with other
+        # tenants), so the aggregate — not the per-GPU link — bounds the host-buffer call at N > 1.
+        def link_rate(up, down):
+            s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+            if multi:
+                dist.barrier()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            if up:
+                with torch.cuda.stream(s1):
+                    c2.copy_(hc, non_blocking=True)
+            if down:
+                with torch.cuda.stream(s2):
+                    hc2.copy_(c, non_blocking=True)
+            torch.cuda.synchronize()
+            gbs = hc.numel() * 2 / (time.perf_counter() - t0) / 1e9
+            if multi:
+                t = torch.tensor([gbs], device="cuda", dtype=torch.float64)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                gbs = float(t.item())
+            return gbs
+        c2, hc2 = torch.empty_like(c), torch.empty_like(hc).pin_memory()
+        link_rate(True, True)
+        host_link = {"h2d_gbs_per_gpu": round(link_rate(True, False), 1), "d2h_gbs_per_gpu": round(link_rate(False, True), 1),
+                     "both_ways_gbs_each_per_gpu": round(link_rate(True, True), 1), "ranks_copying_at_once": world,
+                     "rate": "slowest rank"}
+        bytes_rank = (M * K // world + K * n_loc + M * n_loc) * 2
+        host_link["floor_ms"] = round(bytes_rank / 2 / (host_link["both_ways_gbs_each_per_gpu"] * 1e9) * 1e3, 2)
+        del c2, hc2
+
+        def e2e_step():
+            hm.matmul[(1,)](npa, npb, npc)  # H2D A and B, GEMM, D2H C, wait — all inside the call
         e2e_step()
-        c_one = torch.empty_like(c)
-        hm.matmul[(1,)](a, b, c_one)
-        torch.cuda.synchronize()
-        e2e_bytes_equal = bool(torch.equal(hc.cuda(), c_one))
-        del c_one
-    finally:
-        hm.set_option("gemmVariant", -1)
+        e2e_each = [timed(torch, e2e_step, 1, 0, dist if multi else None) for _ in range(e2e_steps)]
+        e2e_ms = sum(e2e_each) / len(e2e_each)
         hm.set_option("replicatedOperandA", 0)
-    del ha, hb, hc
+        slab_mode = hm.tp_slab_exchange_mode() if multi else "none"
+        e2e_tflops = FLOPS / (e2e_ms * 1e-3) / 1e12
+        # the strips of the host path and the whole-problem device run may take different variants
+        # (fp32 sums associated differently): agreement is stated as an error, not as byte equality
+        sl = slice(0, 256)
+        dref = c[sl].float()
+        e2e_err = float((hc[sl].cuda().float() - dref).abs().max() / dref.abs().max())
+        h2d_step = (M * K // (world if sharded_upload else 1) + K * n_loc) * 2 * world
+        # ... and as byte equality with every launch on ONE whole-tile variant (same fp32 sums in the same order)
+        hm.set_option("gemmVariant", 3)
+        if sharded_upload:
+            hm.set_option("replicatedOperandA", 1)
+        try:
+            e2e_step()
+            c_one = torch.empty_like(c)
+            hm.matmul[(1,)](a, b, c_one)
+            torch.cuda.synchronize()
+            e2e_bytes_equal = bool(torch.equal(hc.cuda(), c_one))
+            del c_one
+        finally:
+            hm.set_option("gemmVariant", -1)
+            hm.set_option("replicatedOperandA", 0)
+        del ha, hb, hc
+        return {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_step,
+                "d2h_bytes_per_step": M * n_loc * 2 * world, "steps": e2e_steps,
+                "ms_each_step": [round(x, 3) for x in e2e_each], "host_link": host_link,
+                "a_upload": f"1/N row slab per rank, slabs exchanged over NVLink by {slab_mode}" if sharded_upload else "whole A",
+                "max_abs_rel_vs_device_run": e2e_err, "bytes_equal_to_device_run_on_one_variant": e2e_bytes_equal}
 
-    extra = {}
+    try:
+        line["e2e"] = measure_e2e()
+    except Exception as exc:  # noqa: BLE001  (the device-timed value is still reported)
+        line["e2e"] = {"value": None, "unit": "TFLOP/s", "error": f"{type(exc).__name__}: {exc}"[:300]}
+
+    stage["name"] = "extra"
     if not args.no_extras:
-        if not multi:
-            extra.update(extras_single_gpu(torch, hm, peaks))
-        extra["mlp_block_2048x4096x11008"] = mlp_extra(torch, hm, dist, rank, world)
+        try:
+            if not multi:
+                line["extra"].update(extras_single_gpu(torch, hm, peaks))
+            line["extra"]["mlp_block_2048x4096x11008"] = mlp_extra(torch, hm, dist, rank, world)
+        except Exception as exc:  # noqa: BLE001
+            line["extra"]["error"] = f"{type(exc).__name__}: {exc}"[:300]
 
-    cpu = None
+    stage["name"] = "cpu_baseline"
     if rank == 0 and not multi and not args.no_cpu:
-        cpu = cpu_baseline()
+        line["cpu_baseline"] = cpu_baseline()
 
+    stage["name"] = "final barrier"
     if multi:
         dist.barrier()
-    if rank == 0:
-        peak = peaks["bf16_tflops"]
-        capture = DRAM_TRAFFIC_CAPTURES.get((plan["name"], M, n_loc, K))
-        line = {
-            "metric": "gemm_f16_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sharding": f"N split over {world} rank(s), A replicated, no collective",
-                       "l2": "inputs larger than L2 (A 268 MB per rank)", "variant": plan["name"],
-                       "inputs": f"Philox4x32-10, A seed {SEED_A}, B seed {SEED_B}, U[-1,1)",
-                       "accumulate": "fp32 in TMEM, one fp16 rounding"},
-            "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s",
-                         "frac": kernel_tflops / peak,
-                         "traffic": (capture or {}).get("bytes"), "traffic_source": capture,
-                         "peak_source": f"{peak_kind} cuBLAS bf16 burst; sustained {peaks.get('bf16_tflops_sustained')}",
-                         "frac_of_sustained": kernel_tflops / peaks.get("bf16_tflops_sustained", peak),
-                         "frac_of_nominal_2250": kernel_tflops / 2250.0,
-                         "algorithmic_flops_per_launch": 2.0 * M * n_loc * K},
-            "cpu_baseline": cpu,
-            "e2e": {"value": e2e_tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_step,
-                    "d2h_bytes_per_step": M * n_loc * 2 * world, "steps": e2e_steps,
-                    "ms_each_step": [round(x, 3) for x in e2e_each], "host_link": host_link,
-                    "a_upload": f"1/N row slab per rank, slabs exchanged over NVLink by {slab_mode}" if sharded_upload else "whole A",
-                    "max_abs_rel_vs_device_run": e2e_err, "bytes_equal_to_device_run_on_one_variant": e2e_bytes_equal},
-            "parity_sample": parity, "long_run": long_run,
-            "gpu_launches": int(launches), "clocks": clocks, "extra": extra,
-        }
-        sys.stdout.flush()
-        os.write(json_fd, (json.dumps(line) + "\n").encode())
+    watchdog.cancel()
+    write_line()
     if multi:
         # The line is out; tear down, but never let a stuck teardown hold the launcher.
-        import threading
         threading.Timer(60.0, lambda: os._exit(0)).start()
         torch.cuda.synchronize()
         dist.barrier()
@@ -814,6 +851,9 @@ def main():
     ap.add_argument("--case", default="", help="run one case of `extra` only (profiling captures): gemm_f16_1024, "
                                                "gemm_f16_4096, gemm_f16_8192, kloop, gemm_i8, softmax, rmsnorm, swiglu, w8a16, attention_f16_4x16x4096x64, ...")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--stage-limit", type=float, default=420.0,
+                    help="seconds the stages after the device-timed loop may take together before the line is "
+                         "written without the unfinished ones")
     ap.add_argument("--min-time", type=float, default=2.0,
                     help="seconds the timed GEMM loop is kept running for the long-run value (0: skip)")
     args = ap.parse_args()

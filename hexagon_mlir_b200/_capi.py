@@ -94,6 +94,7 @@ _SIGNATURES = {
     "b200mlir_tp_init": (c_int, [c_void_p, c_int, c_int]),
     "b200mlir_tp_info": (c_int, [ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
     "b200mlir_tp_slab_exchange_mode": (c_int, []),
+    "b200mlir_host_gemm_plan": (c_int, [c_i64, c_i64, c_i64, ctypes.POINTER(c_i64)]),
     "b200mlir_tp_shutdown": (c_int, []),
     "b200mlir_tp_all_reduce_float16": (c_int, [c_void_p, c_i64]),
     "mlp_block_tp_float16": (None, [c_i64, _M2, c_i64, _M1, c_i64, _M2, c_i64, _M2, c_i64, _M2,

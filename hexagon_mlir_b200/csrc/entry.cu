@@ -130,15 +130,32 @@ int check_grid(int nx, int ny, int nz, int px, int py, int pz) {
 // full duplex, so the call approaches max(bytes up, bytes down) / link rate instead of their sum.
 constexpr size_t kPipelineMinBytes = 96u << 20;
 
-int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
-  const int64_t M = A.rows, K = A.cols, N = B.cols;
-  // panels of about 1024 rows of A and 1024 columns of B, at most 16 of each, counted separately:
-  // a narrow column block (one rank's share of a wide B) still gets a fine-grained pipeline over A
+// Which host-buffer fp16 GEMMs take the pipelined path, and their panels: about 1024 rows of A and
+// 1024 columns of B per panel, at most 16 of each, counted separately (a narrow column block — one
+// rank's share of a wide B — still gets a fine-grained pipeline over A); panel edges on multiples
+// of 256 (whole tiles of the widest variant).
+struct HostGemmPlan {
+  bool pipelined;
+  int64_t pm, pn, PM, PN;  // panel height / width, panel counts
+};
+HostGemmPlan host_gemm_plan(int64_t M, int64_t N, int64_t K) {
+  HostGemmPlan h{};
+  h.pipelined = K > 0 && std::min(M, N) >= 1024 && std::max(M, N) >= 4096 && K % 8 == 0 && N % 8 == 0 &&
+                (size_t)(M * K + K * N + M * N) * 2 >= kPipelineMinBytes;
+  if (!h.pipelined) return h;
   const int64_t P_m = std::max<int64_t>(2, std::min<int64_t>(16, M / 1024));
   const int64_t P_n = std::max<int64_t>(1, std::min<int64_t>(16, N / 1024));
-  // panel edges on multiples of 256 rows / columns (whole tiles of the widest variant)
-  const int64_t pm = ((M + P_m - 1) / P_m + 255) / 256 * 256, pn = ((N + P_n - 1) / P_n + 255) / 256 * 256;
-  const int64_t PM = (M + pm - 1) / pm, PN = (N + pn - 1) / pn;
+  h.pm = ((M + P_m - 1) / P_m + 255) / 256 * 256;
+  h.pn = ((N + P_n - 1) / P_n + 255) / 256 * 256;
+  h.PM = (M + h.pm - 1) / h.pm;
+  h.PN = (N + h.pn - 1) / h.pn;
+  return h;
+}
+
+int matmul_host_pipelined(const View2 &A, const View2 &B, const View2 &C) {
+  const int64_t M = A.rows, K = A.cols, N = B.cols;
+  const HostGemmPlan hp = host_gemm_plan(M, N, K);
+  const int64_t pm = hp.pm, pn = hp.pn, PM = hp.PM, PN = hp.PN;
   // option replicatedOperandA inside a tensor-parallel group: a collective call — every rank
   // enters with the same M and K (its own B and C column block)
   const int world = ctx().opt.replicated_operand_a != 0 ? tp_world() : 1;
@@ -318,9 +335,7 @@ int matmul_impl(int epilogue, int64_t ra, B200MemRef2D *a, int64_t rb, B200MemRe
   if (has_res && (R.rows != C.rows || R.cols != C.cols))
     return set_error(B200MLIR_ERR_BAD_ARG, "matmul: residual shape differs from C");
   if (C.rows == 0 || C.cols == 0) return 0;
-  if (epilogue == EPI_F16 && A.cols > 0 && std::min(A.rows, B.cols) >= 1024 && std::max(A.rows, B.cols) >= 4096 &&
-      A.cols % 8 == 0 && B.cols % 8 == 0 &&
-      A.span(2) + B.span(2) + C.span(2) >= kPipelineMinBytes && !is_device_ptr(A.p) && !is_device_ptr(B.p) &&
+  if (epilogue == EPI_F16 && host_gemm_plan(A.rows, B.cols, A.cols).pipelined && !is_device_ptr(A.p) && !is_device_ptr(B.p) &&
       !is_device_ptr(C.p))
     return matmul_host_pipelined(A, B, C);
   Stager st;
@@ -997,6 +1012,18 @@ int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *local_buf, i
                                                 int64_t flags_elem_offset, int rank, int world, void *state) {
   clear_error();
   return launch_allreduce_multimem_sync(mc_buf, local_buf, elem_offset, count, flags_elem_offset, rank, world, state);
+}
+
+int b200mlir_host_gemm_plan(int64_t m, int64_t n, int64_t k, int64_t *panels4) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  const HostGemmPlan h = host_gemm_plan(m, n, k);
+  if (h.pipelined && panels4) {
+    panels4[0] = h.pm;
+    panels4[1] = h.pn;
+    panels4[2] = h.PM;
+    panels4[3] = h.PN;
+  }
+  return h.pipelined ? 1 : 0;
 }
 
 int b200mlir_mlp_phase_times(double *us, int cap) {

@@ -508,6 +508,15 @@ def gemm_variant_verdict(variant: int, m: int, n: int, k: int) -> str:
     return buf.value.decode()
 
 
+def host_gemm_plan(m: int, n: int, k: int):
+    """None when a host-buffer fp16 GEMM of this shape is staged whole, else its panels
+    {"panel_rows", "panel_cols", "row_panels", "col_panels"} (needs no device)."""
+    out = (ctypes.c_int64 * 4)()
+    if not lib().b200mlir_host_gemm_plan(int(m), int(n), int(k), out):
+        return None
+    return dict(zip(("panel_rows", "panel_cols", "row_panels", "col_panels"), (int(v) for v in out)))
+
+
 def gemm_explain(m: int, n: int, k: int) -> dict:
     return _json_call(lib().b200mlir_gemm_explain, m, n, k)[1]
 

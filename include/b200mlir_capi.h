@@ -576,6 +576,12 @@ B200_API int b200mlir_gemm_variant_verdict(int variant, int64_t m, int64_t n, in
  * (plan / reason vocabulary of
  * include/hexagon/Dialect/Hmx/Transforms/HmxManifest.h:81-100). */
 B200_API int b200mlir_gemm_explain(int64_t m, int64_t n, int64_t k, char *json, int cap);
+/* How `matmul` treats an fp16 GEMM whose three tensors are host memory: returns 1 when it is cut
+ * into row panels of A and column panels of B that go up, are multiplied and come back down
+ * concurrently (panels4 = {panel rows, panel columns, row panels, column panels}; edges on
+ * multiples of 256, at most 16 panels each way), 0 when it is staged whole (small problems, or
+ * K or N not a multiple of 8).  Pure: needs no device. */
+B200_API int b200mlir_host_gemm_plan(int64_t m, int64_t n, int64_t k, int64_t *panels4);
 /* Search the variant list for one shape on the current device: enumerate,
  * refuse illegal ones, order by modelled lower bound, measure each with one
  * discarded launch + timed launches (3 repetitions, q50/q20/q80), verify the

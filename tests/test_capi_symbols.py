@@ -126,3 +126,22 @@ def test_block_table_and_leaf_argument_checks_without_a_device(hm):
     assert lib.hexagon_runtime_alloc_2d(4, 64, 128, False) is None and hm._capi.last_error()[0] == 1   # no device
     lib.hmx_acc_clear_f16()              # a leaf without a device: the library's error, no crash
     assert hm._capi.last_error()[0] == 1
+
+
+def test_host_gemm_panel_plan(hm):
+    """Which host-buffer GEMMs are pipelined, and how they are cut: panel edges on multiples of
+    256, at most 16 panels each way, the panels cover the problem, row and column panels counted
+    separately (the per-rank column blocks of the headline GEMM at 1, 2, 4 and 8 ranks)."""
+    assert hm.host_gemm_plan(1024, 1024, 1024) is None           # small: staged whole
+    assert hm.host_gemm_plan(16384, 512, 8192) is None           # a block narrower than a panel
+    assert hm.host_gemm_plan(4096, 4100, 4096) is None           # N not a multiple of 8
+    for world in (1, 2, 4, 8):
+        plan = hm.host_gemm_plan(16384, 16384 // world, 8192)
+        assert plan["row_panels"] == 16 and plan["panel_rows"] == 1024
+        assert plan["col_panels"] == min(16, 16 // world) and plan["panel_cols"] == 1024
+    for m, n, k in ((4360, 4104, 4096), (12288, 1280, 4096), (1280, 9000, 4096), (9000, 2048, 4096), (100000, 1024, 512)):
+        plan = hm.host_gemm_plan(m, n, k)
+        assert plan["panel_rows"] % 256 == 0 and plan["panel_cols"] % 256 == 0
+        assert 1 <= plan["row_panels"] <= 16 and 1 <= plan["col_panels"] <= 16
+        assert (plan["row_panels"] - 1) * plan["panel_rows"] < m <= plan["row_panels"] * plan["panel_rows"]
+        assert (plan["col_panels"] - 1) * plan["panel_cols"] < n <= plan["col_panels"] * plan["panel_cols"]

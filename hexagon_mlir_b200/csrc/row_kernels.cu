@@ -462,7 +462,7 @@ allreduce_multimem_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ m
 // number at which rank r's partial was complete, [8 + r] = the launch number whose sums rank r has
 // written everywhere.  Each is stored through the multicast address (one store reaches every
 // copy) and polled in the local copy.  `state` is local: [0] launches finished, [1] CTAs finished.
-//  entry: every CTA stores "arrived" (idempotent) and waits until all ranks have arrived;
+//  entry: CTA 0 stores "arrived", every CTA waits until all ranks have arrived;
 //  body:  this rank's slice, as above;
 //  exit:  the last CTA to finish stores "written" and waits for every rank's "written", so the
 //         launch ends only when this rank's copy holds every slice and nobody still reads it.
@@ -474,15 +474,16 @@ __device__ __forceinline__ bool flags_reached(const uint32_t *flags, int world, 
     const long long t0 = clock64();
     for (;;) {
       uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
       if ((int32_t)(v - epoch) >= 0) break;
       if (*(volatile int *)status != 0 || clock64() - t0 > 2000000000LL) {
         if (atomicCAS(status, 0, site) == 0) status[1] = r;
         ok = false;
         break;
       }
-      __nanosleep(64);
+      __nanosleep(32);
     }
+    __threadfence_system();  // what the other ranks wrote before their flags is visible from here on
   }
   return ok;
 }
@@ -495,8 +496,10 @@ allreduce_multimem_sync_kernel(const uint4 *__restrict__ mc_in, uint4 *__restric
   if (threadIdx.x == 0) {
     const uint32_t e = *(volatile uint32_t *)state + 1;
     s_epoch = e;
-    __threadfence_system();  // the partial, written by the launch before this one, is complete
-    asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(mc_flags + rank), "r"(e) : "memory");
+    // the partial, written by the launch before this one, is complete: one CTA says so (the grid
+    // is at most two CTAs per SM, resident at once even beside a GEMM, so CTA 0 runs while the others wait)
+    if (blockIdx.x == 0)
+      asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(mc_flags + rank), "r"(e) : "memory");
   }
   __syncthreads();
   const uint32_t epoch = s_epoch;
@@ -673,7 +676,7 @@ int launch_allreduce_multimem_sync(void *mc_buf, void *local_buf, int64_t elem_o
                      "count multiples of 8 elements, 2 <= world <= %d, a device state of two words", kMaxPushRanks);
   const int64_t nvec = count >> 3;
   int64_t blocks = (nvec + 256 * 4 - 1) / (256 * 4);
-  const int64_t cap = (int64_t)ctx().sm_count * 4;
+  const int64_t cap = (int64_t)ctx().sm_count * 2;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   allreduce_multimem_sync_kernel<<<(unsigned)blocks, 256, 0, stream ? stream : ctx().stream>>>(

@@ -4,7 +4,9 @@
 // draws the tensor-parallel group's id and passes it down pipes, every rank runs
 //   1. matmul            (fp16, checked against a CPU loop in this file)
 //   2. mlp_block_tp_float16 over its shard of the hidden dimension (ncclAllReduce inside the call)
-// and compares with the unsharded block computed on the CPU.  Exit code 0 when every rank agrees.
+//   3. (two ranks or more) a host-buffer matmul whose A every rank holds: each rank uploads its row
+//      slab of every panel and the slabs travel GPU to GPU inside the call
+// and compares with the unsharded block / sampled rows computed on the CPU.  Exit code 0 when every rank agrees.
 //   usage: host_program <world>
 #include <sys/wait.h>
 #include <unistd.h>
@@ -137,6 +139,36 @@ static int run_rank(int rank, int world, int id_read_fd, const std::vector<int> 
       printf("rank %d of %d: mlp block (chunks %d) max-abs-rel %.2e\n", rank, world, chunks, e2);
       if (!(e2 <= 1e-2)) return 1;
     }
+  }
+  // ---- 3. host-buffer matmul, A replicated over the ranks ---------------------------------------
+  if (world > 1) {
+    const int M3 = 8192, K3 = 2048, N3 = 4096;
+    std::vector<f16> a3((size_t)M3 * K3), b3((size_t)K3 * N3), c3((size_t)M3 * N3);
+    g_state = 777u;
+    fill(a3, 1.0f);  // the same A on every rank
+    g_state = 1000u + (uint32_t)rank;
+    fill(b3, 1.0f);  // this rank's column block of B
+    int64_t panels[4] = {0, 0, 0, 0};
+    if (b200mlir_host_gemm_plan(M3, N3, K3, panels) != 1 || panels[2] < 2) { fprintf(stderr, "rank %d: host_gemm_plan\n", rank); return 1; }
+    B200MemRef2D A3 = m2(a3.data(), M3, K3), B3 = m2(b3.data(), K3, N3), C3 = m2(c3.data(), M3, N3);
+    b200mlir_set_option("replicatedOperandA", 1.0);
+    matmul(2, &A3, 2, &B3, 2, &C3, 1, 1, 1, 0, 0, 0);
+    b200mlir_set_option("replicatedOperandA", 0.0);
+    char buf[8];
+    if (b200mlir_last_error(buf, sizeof(buf)) != 0) return fail(rank, "matmul with a replicated A");
+    if (b200mlir_device_status() != 0) return fail(rank, "device status after the host-buffer matmul");
+    double e3 = 0;
+    std::vector<f16> got(N3), want(N3);
+    for (int i = 0; i < 16; ++i) {  // sampled rows, one in every panel
+      const int row = i * (M3 / 16) + 37 * i % (M3 / 16);
+      cpu_gemm(&a3[(size_t)row * K3], b3.data(), want.data(), 1, N3, K3, K3, N3, N3);
+      memcpy(got.data(), &c3[(size_t)row * N3], (size_t)N3 * 2);
+      e3 = std::fmax(e3, max_abs_rel(got, want));
+    }
+    const int mode = b200mlir_tp_slab_exchange_mode();
+    printf("rank %d of %d: host-buffer matmul, replicated A, %lld x %lld panels, slabs by %s, max-abs-rel %.2e\n", rank, world,
+           (long long)panels[2], (long long)panels[3], mode == 1 ? "copy engines" : mode == 2 ? "ncclAllGather" : "nothing", e3);
+    if (!(e3 <= 1e-2) || mode == 0) return 1;
   }
   if (b200mlir_tp_shutdown() != 0) return fail(rank, "tp_shutdown");
   return 0;

@@ -2,7 +2,9 @@
 include/b200mlir_capi.h, linked with the shared library and run — one forked process per GPU.
 It runs `matmul` and the tensor-parallel MLP block (the library's own NCCL communicator, created
 from an id that rank 0 hands the others through a pipe; ncclAllReduce inside
-`mlp_block_tp_float16`) and checks both against CPU loops of its own."""
+`mlp_block_tp_float16`) and, on two ranks, a host-buffer `matmul` whose A every rank holds (row
+slabs uploaded per rank and exchanged between the GPUs), and checks all three against CPU loops
+of its own."""
 import os
 import subprocess
 
@@ -41,3 +43,5 @@ def test_two_ranks_nccl_all_reduce_in_cpp(program, cuda):
         pytest.skip("needs 2 GPUs")
     out = run(program, 2)
     assert "rank 1 of 2: mlp block (chunks 1)" in out and "rank 0 of 2: mlp block (chunks 2)" in out
+    assert "rank 0 of 2: host-buffer matmul, replicated A, 8 x 4 panels" in out
+    assert "rank 1 of 2: host-buffer matmul, replicated A, 8 x 4 panels" in out

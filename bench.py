@@ -571,6 +571,40 @@ def mlp_extra(torch, hm, dist, rank, world):
             "phases_us": phases}
 
 
+def mlp_shard_compute(torch, hm):
+    """The compute side of the tensor-parallel MLP on ONE GPU: rank 0's shard of 2, 4 and 8 ranks
+    (F / ways columns of Wg and Wu, rows of Wd), no collective, replayed from a CUDA graph, with
+    the phase times of an eager run.  What a step at N ranks takes beyond this is the exchange."""
+    from hexagon_mlir_b200 import tp
+    t, d, f = 2048, 4096, 11008
+    x = torch.empty((t, d), dtype=torch.float16, device="cuda")
+    hm.fill_random(x, 3, hm.NORMAL, 0.0, 1.0)
+    gain = torch.ones(d, dtype=torch.float16, device="cuda")
+    out = torch.empty_like(x)
+    res = {}
+    for ways in (2, 4, 8):
+        lo, hi = tp.shard_bounds(f, 0, ways)
+        w = []
+        for seed, shape, cols in ((31, (d, f), True), (32, (d, f), True), (33, (f, d), False)):
+            full = torch.empty(shape, dtype=torch.float16, device="cuda")
+            hm.fill_random(full, seed, hm.NORMAL, 0.0, 0.02)
+            w.append((full[:, lo:hi] if cols else full[lo:hi]).contiguous())
+            del full
+        block = tp.TensorParallelMLP(gain, w[0], w[1], w[2], eps=1e-6, group=None)
+        block.captured(x, out)
+        ms = timed(torch, lambda: block.captured(x, out), 20, 5, None)
+        hm.set_option("mlpPhaseTiming", 1)
+        for _ in range(3):
+            block(x, out)
+        phases = {k: round(v, 2) for k, v in hm.mlp_phase_times().items()}
+        hm.set_option("mlpPhaseTiming", 0)
+        torch.cuda.synchronize()
+        block.release()
+        res[f"tp{ways}_shard"] = {"ms": ms, "ffn_columns": hi - lo, "phases_us": phases,
+                                  "tflops": 6.0 * t * d * (hi - lo) / (ms * 1e-3) / 1e12}
+    return res
+
+
 def parity_sample(torch, hm, c, n_lo, tiles=64, tile=128):
     """`tiles` random tile x tile blocks of the timed GEMM's output against the oracle (full K);
     the operand rows and columns are drawn on the CPU from the generator that filled the device."""
@@ -616,6 +650,8 @@ def run_product_arm(args):
         # one small case of `extra` alone (what the ncu captures under profiles/ run)
         if args.case == "mlp":
             result = {"mlp_block_2048x4096x11008": mlp_extra(torch, hm, dist, rank, world)}
+        elif args.case == "mlp_shards":
+            result = {"mlp_shard_compute_one_gpu": mlp_shard_compute(torch, hm)}
         else:
             result = extras_single_gpu(torch, hm, peaks, only=args.case)
         line = json.dumps({"case": args.case, "result": result})
@@ -819,6 +855,8 @@ def run_product_arm(args):
             if not multi:
                 line["extra"].update(extras_single_gpu(torch, hm, peaks))
             line["extra"]["mlp_block_2048x4096x11008"] = mlp_extra(torch, hm, dist, rank, world)
+            if not multi:
+                line["extra"]["mlp_shard_compute_one_gpu"] = mlp_shard_compute(torch, hm)
         except Exception as exc:  # noqa: BLE001
             line["extra"]["error"] = f"{type(exc).__name__}: {exc}"[:300]
 

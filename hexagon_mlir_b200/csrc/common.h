@@ -46,6 +46,8 @@ struct Options {
   double w8a16_expand_rows = 64;   // above this many activation rows a w8a16 product takes the expanded fp16 weight
   double attention_stage = 1;      // STAGE of the reference kernel's signature: 1 all keys, 3 causal
   double attention_splits = 0;     // key splits of the attention kernel: 0 chooses by size
+  double mlp_residual_mod = 1;     // mlp_block with the residual: add x only in 256-row blocks b with b % mod == rem
+  double mlp_residual_rem = 0;     //   (tensor-parallel ranks that sum their partials take turns)
   double attention_tiles = 0;      // query tiles per CTA of the attention kernel: 0 chooses by size, 1 or 2
   double enable_pdl = 0;           // programmatic dependent launch of the row kernels (measured: no gain)
   double replicated_operand_a = 0;  // host-buffer GEMM in a tensor-parallel group: every rank passes the same A; each uploads a row slab and the slabs are exchanged GPU to GPU
@@ -208,6 +210,9 @@ struct GemmArgs {
   int64_t lda = 0, ldb = 0, ldc = 0, ldres = 0;
   int epilogue = EPI_F16;
   int block_k = 0;  // EPI_KLOOP_F16 only
+  // EPI_F16_RES16: the residual is added only in the 256-row blocks b with b % res_mod == res_rem
+  // (tensor-parallel ranks share the residual read-out: each adds it to its blocks of the partial)
+  int res_mod = 1, res_rem = 0;
   // B is not row-major [K,N] but the K-blocked image [ceil(K/64)][N][64] fp16: per 64-deep k-block
   // every column's 64 values are one contiguous 128-byte row, so a CTA's operand tile of a k-block
   // is ONE contiguous piece of HBM (a row-major B hands the memory system 128-byte pieces a whole

@@ -767,7 +767,8 @@ typedef std::function<int(int64_t, int64_t, void *)> ChunkHook;
 static void mlp_block_impl(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
                            B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
                            int64_t ro, B200MemRef2D *out, float eps, int add_residual, const PushTargets *push,
-                           int down_chunks = 1, const ChunkHook *after_chunk = nullptr) {
+                           int down_chunks = 1, const ChunkHook *after_chunk = nullptr, int res_mod = 1,
+                           int res_rem = 0) {
   if (ensure_ready()) return;
   View2 X, WG, WU, WD, O{nullptr, 0, 0, 0};
   View1 G;
@@ -812,6 +813,8 @@ static void mlp_block_impl(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D
     g2.epilogue = EPI_F16_RES16;
     g2.res = dx;
     g2.ldres = X.ld;
+    g2.res_mod = res_mod;  // tensor-parallel callers: the ranks take turns, by 256-row block, in adding x
+    g2.res_rem = res_rem;
   }
   if (push || down_chunks <= 1) {
     if (gemm_dispatch(g2)) return;
@@ -839,11 +842,13 @@ void mlp_block_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *ga
                        B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
                        int64_t ro, B200MemRef2D *out, float eps, int add_residual, B200_GRID_ARGS) {
   ENTER_KERNEL();
-  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, add_residual, nullptr);
+  const int mod = (int)ctx().opt.mlp_residual_mod, rem = (int)ctx().opt.mlp_residual_rem;
+  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, add_residual, nullptr, 1, nullptr,
+                 mod > 1 ? mod : 1, mod > 1 ? rem : 0);
 }
 
 // The tensor-parallel block with the sum over ranks inside the call: every rank computes the
-// partial output of its shard of the hidden dimension (rank 0's carries the residual, so the sum is
+// partial output of its shard of the hidden dimension (each carries the residual of its share of the 256-row blocks, so the sum is
 // the finished block) and the partials are added with ncclAllReduce.  `chunks` > 1 cuts the down
 // projection into that many token chunks; the all-reduce of a chunk runs on a second stream while
 // the next chunk's GEMM is computed.  Device tensors only (the collective works on `out` in place).
@@ -894,7 +899,9 @@ void mlp_block_tp_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D 
     ++used;
     return rc;
   };
-  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, tp_rank() == 0 ? 1 : 0, nullptr, chunks, &hook);
+  // every rank's partial carries the residual of ITS 256-row blocks (block b: rank b % world), so
+  // the sum holds x once and no rank's read-out pays for all of it
+  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, 1, nullptr, chunks, &hook, world, tp_rank());
   for (int i = 0; i < used; ++i) {  // join: the caller's stream continues after every chunk's collective
     if (done[i]) cudaStreamWaitEvent(s, done[i], 0);
     if (ev[i]) cudaEventDestroy(ev[i]);
@@ -960,7 +967,7 @@ void mlp_block_tp_multicast_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B20
     ++used;
     return launch_allreduce_multimem_sync(mc_buf, O.p, off, cnt, flags_elem_offset, rank, world, state, sc);
   };
-  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, rank == 0 ? 1 : 0, nullptr, chunks, &hook);
+  mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, 1, nullptr, chunks, &hook, world, rank);
   if (chunks > 1) {  // join: the caller's stream continues after the last chunk's all-reduce
     if (cudaEventCreateWithFlags(&done, cudaEventDisableTiming) == cudaSuccess && cudaEventRecord(done, sc) == cudaSuccess)
       cudaStreamWaitEvent(s, done, 0);

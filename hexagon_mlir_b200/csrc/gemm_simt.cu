@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const __half *__restrict__ A, const __half *__restrict__ B,
                  const __half *__restrict__ B2, void *__restrict__ Cv,
                  const void *__restrict__ Rv, int64_t M, int64_t N, int64_t K, int64_t lda,
-                 int64_t ldb, int64_t ldc, int64_t ldr, int block_k) {
+                 int64_t ldb, int64_t ldc, int64_t ldr, int block_k, int res_mod, int res_rem) {
   __shared__ float As[TK][TM + 1];
   __shared__ float Bs[TK][TN];
   __shared__ float B2s[EPI == EPI_SWIGLU ? TK : 1][TN];
@@ -92,8 +92,9 @@ gemm_simt_kernel(const __half *__restrict__ A, const __half *__restrict__ B,
         if (Rv) v += ((const float *)Rv)[gm * ldr + gn];
         ((float *)Cv)[gm * ldc + gn] = v;
       } else if (EPI == EPI_F16_RES16) {
+        const bool mine = res_mod <= 1 || (int)((gm >> 8) % res_mod) == res_rem;
         float v = __half2float(__float2half_rn(acc[i][j])) +
-                  __half2float(((const __half *)Rv)[gm * ldr + gn]);
+                  (mine ? __half2float(((const __half *)Rv)[gm * ldr + gn]) : 0.0f);
         ((__half *)Cv)[gm * ldc + gn] = __float2half_rn(v);
       } else {  // EPI_SWIGLU
         __half g = __float2half_rn(acc[i][j]), u = __float2half_rn(acc2[i][j]);
@@ -155,7 +156,7 @@ int launch_gemm_simt(const GemmArgs &g) {
   const __half *A = (const __half *)g.a, *B = (const __half *)g.b, *B2 = (const __half *)g.b2;
 #define SIMT_LAUNCH(E)                                                                      \
   gemm_simt_kernel<E><<<grid, 256, 0, s>>>(A, B, B2, g.c, g.res, g.m, g.n, g.k, g.lda, g.ldb, \
-                                           g.ldc, g.ldres, g.block_k)
+                                           g.ldc, g.ldres, g.block_k, g.res_mod, g.res_rem)
   switch (g.epilogue) {
     case EPI_F16: SIMT_LAUNCH(EPI_F16); break;
     case EPI_F32_RES: SIMT_LAUNCH(EPI_F32_RES); break;

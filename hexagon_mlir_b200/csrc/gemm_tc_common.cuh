@@ -24,6 +24,7 @@ struct TcParams {
   void *push_recv[kMaxPushRanks];  // EPI_PUSH16: receive buffers, by owner rank
   int push_rank, push_rows;
   int *status;
+  int res_mod = 1, res_rem = 0;  // EPI_F16_RES16: residual only in 256-row blocks b with b % res_mod == res_rem
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_blocks, int n_blocks, int group_m, int &m_blk,
@@ -69,14 +70,33 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 }
 
 
+// The fp16 residual of one 32-column chunk of a row.  A read-out thread owns a row, so these are
+// four lone 16-byte loads whose latency nothing else of the chunk hides: they are issued one chunk
+// ahead (the first before the wait for the accumulators), and the chunk's store finds them landed.
+struct ResChunk {
+  uint4 v[4];
+};
+template <int EPI>
+__device__ __forceinline__ void residual_prefetch(ResChunk &rc, int row, int col0, bool row_ok, const TcParams &p) {
+  if (EPI != EPI_F16_RES16) return;
+  const __half *rp = reinterpret_cast<const __half *>(p.res) + (int64_t)row * p.ldres + col0;
+  if (p.res_mod > 1 && (row >> 8) % p.res_mod != p.res_rem) row_ok = false;  // another rank adds it here: + 0 is exact
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    if (row_ok && col0 + v * 8 < p.n)
+      rc.v[v] = __ldg(reinterpret_cast<const uint4 *>(rp + v * 8));
+    else
+      rc.v[v] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 // One 32-column chunk of one accumulator row: r (and r2 for the SwiGLU pair) hold the
-// fp32 accumulators of columns [col0, col0+32) of `row`.
+// fp32 accumulators of columns [col0, col0+32) of `row`; rc the chunk's residual (EPI_F16_RES16).
 template <int EPI>
 __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], const uint32_t (&r2)[32], int row,
-                                                     int col0, const TcParams &p) {
+                                                     int col0, const TcParams &p, const ResChunk &rc) {
   if (EPI == EPI_F16 || EPI == EPI_F16_RES16 || EPI == EPI_SWIGLU) {
     __half *cp = reinterpret_cast<__half *>(p.c) + (int64_t)row * p.ldc + col0;
-    const __half *rp = reinterpret_cast<const __half *>(p.res) + (int64_t)row * p.ldres + col0;
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
       if (col0 + v * 8 >= p.n) break;  // N is a multiple of 8
@@ -88,7 +108,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
           ow[j] = pack_h2(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
       } else if (EPI == EPI_F16_RES16) {
         // f16(f32(f16(acc)) + f32(res)): the engine reads out fp16, the residual is added wide
-        const uint4 rv = *reinterpret_cast<const uint4 *>(rp + v * 8);
+        const uint4 rv = rc.v[v];
         const __half2 *rh = reinterpret_cast<const __half2 *>(&rv);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -152,6 +172,14 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
       *reinterpret_cast<float4 *>(cp + v * 4) = o;
     }
   }
+}
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], const uint32_t (&r2)[32], int row,
+                                                     int col0, const TcParams &p) {
+  static_assert(EPI != EPI_F16_RES16, "the fp16 residual is passed in, fetched a chunk ahead");
+  ResChunk none;
+  epilogue_store_chunk<EPI>(r, r2, row, col0, p, none);
 }
 
 // Fills the EPI_PUSH16 part of the kernel parameters.

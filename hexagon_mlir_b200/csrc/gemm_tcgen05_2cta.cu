@@ -315,24 +315,27 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
         continue;
       }
+      const int row = m0 + q * 32 + lane;
+      const bool row_ok = row < p.m;
+      ResChunk rc, rc_next;
+      residual_prefetch<EPI>(rc, row, n0, row_ok, p);  // under the tile's main loop
       bool ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, 34, tile);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
       if (threadIdx.x == 64) TR2(3, tord);
-      const int row = m0 + q * 32 + lane;
-      const bool row_ok = row < p.m;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN_MMA);
 #pragma unroll 1
       for (int c = 0; c < BN_OUT / 32; ++c) {
+        if (c + 1 < BN_OUT / 32) residual_prefetch<EPI>(rc_next, row, n0 + (c + 1) * 32, row_ok, p);
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         uint32_t r2[32];
         if (EPI == EPI_SWIGLU) tmem_ld_32x32(t_row + BN_OUT + c * 32, r2);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (!row_ok || col0 >= p.n) continue;
-        epilogue_store_chunk<EPI>(r, r2, row, col0, p);
+        if (row_ok && col0 < p.n) epilogue_store_chunk<EPI>(r, r2, row, col0, p, rc);
+        if (EPI == EPI_F16_RES16) rc = rc_next;
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -384,6 +387,8 @@ int launch_pair(const GemmArgs &g, const char *name) {
   p.res = g.res;
   p.ldc = g.ldc;
   p.ldres = g.ldres;
+  p.res_mod = g.res_mod;
+  p.res_rem = g.res_rem;
   p.m = (int)g.m;
   p.n = (int)g.n;
   p.k = (int)g.k;

@@ -331,6 +331,8 @@ gemm_tc2_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 #pragma unroll 1
             for (int cc = 0; cc < CH; ++cc) {
               const int c = step * CH + cc;
+              ResChunk rc;
+              residual_prefetch<EPI>(rc, row, n0 + c * 32, row_ok, p);  // lands under the loads and sums below
               uint32_t r[32];
               tmem_ld_32x32(t_row + c * 32, r);
               uint32_t r2[32];
@@ -350,7 +352,7 @@ gemm_tc2_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
               }
               const int col0 = n0 + c * 32;
               if (!row_ok || col0 >= p.n) continue;
-              epilogue_store_chunk<EPI>(r, r2, row, col0, p);
+              epilogue_store_chunk<EPI>(r, r2, row, col0, p, rc);
             }
             __syncwarp();
             fence_proxy_async_all();  // the buffers were read; the next step's copies may overwrite them
@@ -359,6 +361,8 @@ gemm_tc2_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         } else {
 #pragma unroll 1
         for (int c = 0; c < BN_OUT / 32; ++c) {
+          ResChunk rc;
+          residual_prefetch<EPI>(rc, row, n0 + c * 32, row_ok, p);  // lands under the loads and sums below
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
           uint32_t r2[32];
@@ -381,7 +385,7 @@ gemm_tc2_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           }
           const int col0 = n0 + c * 32;
           if (!row_ok || col0 >= p.n) continue;
-          epilogue_store_chunk<EPI>(r, r2, row, col0, p);
+          epilogue_store_chunk<EPI>(r, r2, row, col0, p, rc);
         }
         }
       }
@@ -430,6 +434,8 @@ int launch_streamk(const GemmArgs &g) {
   p.res = g.res;
   p.ldc = g.ldc;
   p.ldres = g.ldres;
+  p.res_mod = g.res_mod;
+  p.res_rem = g.res_rem;
   p.m = (int)g.m;
   p.n = (int)g.n;
   p.k = (int)g.k;

@@ -355,6 +355,8 @@ static double *option_slot(const char *name) {
   if (!strcmp(name, "w8a16DependentLaunch")) return &o.w8a16_dependent_launch;
   if (!strcmp(name, "gemmDependentLaunch")) return &o.gemm_dependent_launch;
   if (!strcmp(name, "attentionTiles")) return &o.attention_tiles;
+  if (!strcmp(name, "mlpResidualMod")) return &o.mlp_residual_mod;
+  if (!strcmp(name, "mlpResidualRem")) return &o.mlp_residual_rem;
   if (!strcmp(name, "attentionSplits")) return &o.attention_splits;
   if (!strcmp(name, "attentionStage")) return &o.attention_stage;
   if (!strcmp(name, "w8a16ExpandRows")) return &o.w8a16_expand_rows;

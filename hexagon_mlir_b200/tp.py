@@ -214,7 +214,8 @@ class FusedTensorParallelMLP:
 class MulticastTensorParallelMLP:
     """The block with its all-reduce done by this library's own kernel over NVSwitch multicast.
 
-    Every rank writes its fp16 partial [T, D] (rank 0's with the residual) into a symmetric buffer;
+    Every rank writes its fp16 partial [T, D] (with the residual in its share of the 256-row blocks:
+    options mlpResidualMod / mlpResidualRem) into a symmetric buffer;
     after a barrier each rank sums ITS rows over all ranks' copies with `multimem.ld_reduce` (the
     switch adds in fp32 and rounds once) and writes the sums into every copy with `multimem.st`;
     after a second barrier every rank holds the block output.  Per GPU 1/world of the buffer
@@ -272,7 +273,12 @@ class MulticastTensorParallelMLP:
                                             flags_elem_offset=self.tokens * self.width, state=self._state,
                                             rank=self.rank, world=self.world, eps=self.eps, chunks=self.chunks)
             return self.out
-        _l.mlp_block[(1,)](x, self.gain, self.wg, self.wu, self.wd, self.out, eps=self.eps, add_residual=self.rank == 0)
+        _l.set_option("mlpResidualMod", self.world)   # the ranks take turns, by 256-row block, in adding x
+        _l.set_option("mlpResidualRem", self.rank)
+        try:
+            _l.mlp_block[(1,)](x, self.gain, self.wg, self.wu, self.wd, self.out, eps=self.eps, add_residual=True)
+        finally:
+            _l.set_option("mlpResidualMod", 1)
         n = self.rows * self.width
         if self.rendezvous == "kernel":
             _l.tp_allreduce_multimem_sync(self._mc, self._buf, self.rank * n, n, self.tokens * self.width, self.rank,

@@ -240,9 +240,9 @@ B200_API int b200mlir_tp_slab_exchange_mode(void);
 B200_API int b200mlir_tp_all_reduce_float16(void *buf, int64_t count);
 /* The MLP block, tensor-parallel, reduction included: each rank passes its column block of Wg / Wu
  * and its row block of Wd (as for mlp_block_float16) and the same x; on return (in stream order)
- * every rank's `out` holds x + down(swiglu(gate(h), up(h))).  Rank 0's partial carries the
- * residual, the partials are summed in place with one ncclAllReduce per token chunk; `chunks` > 1
- * cuts the down projection into token chunks (whole 256-row tiles) and runs the all-reduce of a
+ * every rank's `out` holds x + down(swiglu(gate(h), up(h))).  Every rank's partial carries the
+ * residual of its share of the 256-row blocks (block b: rank b mod world), the partials are summed
+ * in place with one ncclAllReduce per token chunk; `chunks` > 1 cuts the down projection into token chunks (whole 256-row tiles) and runs the all-reduce of a
  * chunk on a second stream while the next chunk's GEMM is computed.  x and out
  * are device tensors, out dense.  Without a group it is mlp_block_float16 with the residual.  A
  * collective call: every rank of the group must make it, with the same T, D and chunks. */

@@ -91,8 +91,10 @@ def test_large_gemm_and_its_shards_against_the_oracle(hm, oracle, cuda, operands
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_mlp_block_at_tensor_parallel_shard_shapes(hm, oracle, cuda, world):
     """2048 x 4096, ffn 11008 (seed 3) cut the way `tp.shard_bounds` cuts it for `world` ranks; every
-    rank's partial is computed here in turn (rank 0's carries the residual, as in the NCCL form) and
-    the partials are summed in fp16, the way an fp16 all-reduce sums them."""
+    rank's partial is computed here in turn and the partials are summed in fp16, the way an fp16
+    all-reduce sums them.  Twice: with rank 0's partial carrying the residual, and with the ranks
+    taking turns by 256-row block (options mlpResidualMod / mlpResidualRem, what the tensor-parallel
+    entries do), where exactly one partial of every block differs from its residual-free self."""
     from hexagon_mlir_b200 import tp
     t, d, f = 2048, 4096, 11008
     x = cuda.empty((t, d), dtype=cuda.float16, device="cuda")
@@ -104,15 +106,30 @@ def test_mlp_block_at_tensor_parallel_shard_shapes(hm, oracle, cuda, world):
     hm.fill_random(wu, 32, hm.NORMAL, 0.0, 0.02)
     hm.fill_random(wd, 33, hm.NORMAL, 0.0, 0.02)
     gain = cuda.ones(d, dtype=cuda.float16, device="cuda")
-    total = None
+    total, shared = None, None
     widths = []
     for r in range(world):
         lo, hi = tp.shard_bounds(f, r, world)
         widths.append(hi - lo)
+        shard = (wg[:, lo:hi].contiguous(), wu[:, lo:hi].contiguous(), wd[lo:hi].contiguous())
         part = cuda.zeros((t, d), dtype=cuda.float16, device="cuda")
-        hm.mlp_block[(1,)](x, gain, wg[:, lo:hi].contiguous(), wu[:, lo:hi].contiguous(), wd[lo:hi].contiguous(),
-                           part, eps=1e-6, add_residual=(r == 0))
+        hm.mlp_block[(1,)](x, gain, *shard, part, eps=1e-6, add_residual=(r == 0))
         total = part if total is None else total + part          # fp16 add, rounded per step
+        bare = part if r != 0 else None
+        if bare is None:
+            bare = cuda.zeros((t, d), dtype=cuda.float16, device="cuda")
+            hm.mlp_block[(1,)](x, gain, *shard, bare, eps=1e-6, add_residual=False)
+        turn = cuda.zeros((t, d), dtype=cuda.float16, device="cuda")
+        hm.set_option("mlpResidualMod", world)
+        hm.set_option("mlpResidualRem", r)
+        try:
+            hm.mlp_block[(1,)](x, gain, *shard, turn, eps=1e-6, add_residual=True)
+        finally:
+            hm.set_option("mlpResidualMod", 1)
+            hm.set_option("mlpResidualRem", 0)
+        blocks_changed = (turn != bare).view(t // 256, 256 * d).any(dim=1).cpu().numpy()
+        assert np.array_equal(np.nonzero(blocks_changed)[0], np.arange(r, t // 256, world))   # this rank's blocks only
+        shared = turn if shared is None else shared + turn
     assert hm.device_status() == 0
     assert sum(widths) == f and max(widths) - min(widths) <= 8
     rows = np.sort(philox(99).choice(t, 96, replace=False))
@@ -122,3 +139,4 @@ def test_mlp_block_at_tensor_parallel_shard_shapes(hm, oracle, cuda, world):
          for s, seed in (((d, f), 31), ((d, f), 32), ((f, d), 33))]
     want = oracle.mlp(xh[rows], np.ones(d, np.float16), *W, 1e-6)
     assert max_abs_rel(total.cpu().numpy()[rows], want) <= 1e-2
+    assert max_abs_rel(shared.cpu().numpy()[rows], want) <= 1e-2

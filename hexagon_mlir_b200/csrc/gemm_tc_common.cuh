@@ -74,10 +74,21 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 // four lone 16-byte loads whose latency nothing else of the chunk hides: they are issued one chunk
 // ahead (the first before the wait for the accumulators), and the chunk's store finds them landed.
 struct ResChunk {
-  uint4 v[4];
+  uint4 v[8];  // four vectors of 8 fp16 values, or eight of 4 fp32 values (the fp32 read-out's residual)
 };
 template <int EPI>
 __device__ __forceinline__ void residual_prefetch(ResChunk &rc, int row, int col0, bool row_ok, const TcParams &p) {
+  if (EPI == EPI_F32_RES) {
+    const float *rp = reinterpret_cast<const float *>(p.res) + (int64_t)row * p.ldres + col0;
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+      if (p.res && row_ok && col0 + v * 4 < p.n)
+        rc.v[v] = __ldg(reinterpret_cast<const uint4 *>(rp + v * 4));
+      else
+        rc.v[v] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    return;
+  }
   if (EPI != EPI_F16_RES16) return;
   const __half *rp = reinterpret_cast<const __half *>(p.res) + (int64_t)row * p.ldres + col0;
   if (p.res_mod > 1 && (row >> 8) % p.res_mod != p.res_rem) row_ok = false;  // another rank adds it here: + 0 is exact
@@ -156,7 +167,6 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
     }
   } else if (EPI == EPI_F32_RES) {
     float *cp = reinterpret_cast<float *>(p.c) + (int64_t)row * p.ldc + col0;
-    const float *rp = reinterpret_cast<const float *>(p.res) + (int64_t)row * p.ldres + col0;
 #pragma unroll
     for (int v = 0; v < 8; ++v) {
       if (col0 + v * 4 >= p.n) break;  // N is a multiple of 8
@@ -165,9 +175,9 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
 #pragma unroll
       for (int j = 0; j < 4; ++j)
         of[j] = __half2float(__float2half_rn(__uint_as_float(r[v * 4 + j])));
-      if (p.res) {
-        const float4 rv = *reinterpret_cast<const float4 *>(rp + v * 4);
-        o.x += rv.x; o.y += rv.y; o.z += rv.z; o.w += rv.w;
+      if (p.res) {  // fetched a chunk ahead (zeros where there is none: the sum is then exact)
+        const uint4 rv = rc.v[v];
+        o.x += __uint_as_float(rv.x); o.y += __uint_as_float(rv.y); o.z += __uint_as_float(rv.z); o.w += __uint_as_float(rv.w);
       }
       *reinterpret_cast<float4 *>(cp + v * 4) = o;
     }
@@ -177,7 +187,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], co
 template <int EPI>
 __device__ __forceinline__ void epilogue_store_chunk(const uint32_t (&r)[32], const uint32_t (&r2)[32], int row,
                                                      int col0, const TcParams &p) {
-  static_assert(EPI != EPI_F16_RES16, "the fp16 residual is passed in, fetched a chunk ahead");
+  static_assert(EPI != EPI_F16_RES16 && EPI != EPI_F32_RES, "the residual is passed in, fetched a chunk ahead");
   ResChunk none;
   epilogue_store_chunk<EPI>(r, r2, row, col0, p, none);
 }

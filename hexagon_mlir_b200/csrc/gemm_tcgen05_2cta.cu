@@ -335,7 +335,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
         if (row_ok && col0 < p.n) epilogue_store_chunk<EPI>(r, r2, row, col0, p, rc);
-        if (EPI == EPI_F16_RES16) rc = rc_next;
+        if (EPI == EPI_F16_RES16 || EPI == EPI_F32_RES) rc = rc_next;
       }
       tc_fence_before_sync();
       __syncwarp();

@@ -100,11 +100,11 @@ _SIGNATURES = {
     "mlp_block_tp_float16": (None, [c_i64, _M2, c_i64, _M1, c_i64, _M2, c_i64, _M2, c_i64, _M2,
                                     c_i64, _M2, ctypes.c_float, c_int] + _GRID),
     "mlp_block_tp_multicast_float16": (None, [c_i64, _M2, c_i64, _M1, c_i64, _M2, c_i64, _M2, c_i64, _M2,
-                                              c_i64, _M2, c_void_p, c_i64, c_void_p, c_int, c_int, ctypes.c_float,
-                                              c_int] + _GRID),
+                                              c_i64, _M2, c_void_p, ctypes.POINTER(c_void_p), c_i64, c_void_p, c_int,
+                                              c_int, ctypes.c_float, c_int] + _GRID),
     "b200mlir_tp_allreduce_multimem_float16": (c_int, [c_void_p, c_void_p, c_i64, c_i64]),
-    "b200mlir_tp_allreduce_multimem_sync_float16": (c_int, [c_void_p, c_void_p, c_i64, c_i64, c_i64, c_int, c_int,
-                                                            c_void_p]),
+    "b200mlir_tp_allreduce_multimem_sync_float16": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_i64, c_i64, c_i64,
+                                                            c_int, c_int, c_void_p]),
     "b200mlir_mlp_phase_times": (c_int, [ctypes.POINTER(ctypes.c_double), c_int]),
     "b200mlir_tp_reduce_rows_float16": (c_int, [c_void_p, c_void_p, c_i64, ctypes.POINTER(c_void_p), c_int, c_int,
                                                 c_i64, c_i64]),

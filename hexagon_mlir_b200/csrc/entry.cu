@@ -919,15 +919,17 @@ void mlp_block_tp_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D 
 // occupies.  Both rendezvous of the ranks are inside that launch (bounded waits).
 void mlp_block_tp_multicast_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
                                     B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
-                                    int64_t ro, B200MemRef2D *out, void *mc_buf, int64_t flags_elem_offset,
-                                    void *state, int rank, int world, float eps, int chunks, B200_GRID_ARGS) {
+                                    int64_t ro, B200MemRef2D *out, void *mc_buf, void *const *peer_bufs,
+                                    int64_t flags_elem_offset, void *state, int rank, int world, float eps, int chunks,
+                                    B200_GRID_ARGS) {
   ENTER_KERNEL();
   if (ensure_ready()) return;
   View2 X, O;
   if (view2("x", rx, x, 2, &X) || view2("out", ro, out, 2, &O)) return;
   const int64_t T = X.rows, D = X.cols;
   if (O.rows != T || O.cols != D || O.ld != D || !is_device_ptr(X.p) || !is_device_ptr(O.p) || !mc_buf || !state ||
-      world < 2 || world > kMaxPushRanks || rank < 0 || rank >= world || flags_elem_offset < T * D) {
+      !peer_bufs || world < 2 || world > kMaxPushRanks || rank < 0 || rank >= world || flags_elem_offset < T * D ||
+      peer_bufs[rank] != O.p) {
     set_error(B200MLIR_ERR_BAD_ARG,
               "mlp_block_tp_multicast: dense device [T, D] out at the start of the symmetric buffer, its multicast "
               "address, flag words behind the data, 2 <= world <= %d", kMaxPushRanks);
@@ -954,7 +956,7 @@ void mlp_block_tp_multicast_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B20
     const int64_t mine = rows / world;  // this rank sums rows [r0 + rank * mine, + mine) of the chunk
     const int64_t off = (r0 + (int64_t)rank * mine) * D, cnt = mine * D;
     if (chunks == 1) {
-      int rc = launch_allreduce_multimem_sync(mc_buf, O.p, off, cnt, flags_elem_offset, rank, world, state, s);
+      int rc = launch_allreduce_multimem_sync(mc_buf, peer_bufs, off, cnt, flags_elem_offset, rank, world, state, s);
       t_phases.mark(4);
       return rc;
     }
@@ -965,7 +967,7 @@ void mlp_block_tp_multicast_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B20
                        cudaGetErrorString(cudaGetLastError()));
     }
     ++used;
-    return launch_allreduce_multimem_sync(mc_buf, O.p, off, cnt, flags_elem_offset, rank, world, state, sc);
+    return launch_allreduce_multimem_sync(mc_buf, peer_bufs, off, cnt, flags_elem_offset, rank, world, state, sc);
   };
   mlp_block_impl(rx, x, rg, gain, rwg, wg, rwu, wu, rwd, wd, ro, out, eps, 1, nullptr, chunks, &hook, world, rank);
   if (chunks > 1) {  // join: the caller's stream continues after the last chunk's all-reduce
@@ -1015,10 +1017,10 @@ int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_out, int6
   return launch_allreduce_multimem(mc_in, mc_out, elem_offset, count);
 }
 
-int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *local_buf, int64_t elem_offset, int64_t count,
+int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *const *peer_bufs, int64_t elem_offset, int64_t count,
                                                 int64_t flags_elem_offset, int rank, int world, void *state) {
   clear_error();
-  return launch_allreduce_multimem_sync(mc_buf, local_buf, elem_offset, count, flags_elem_offset, rank, world, state);
+  return launch_allreduce_multimem_sync(mc_buf, peer_bufs, elem_offset, count, flags_elem_offset, rank, world, state);
 }
 
 int b200mlir_host_gemm_plan(int64_t m, int64_t n, int64_t k, int64_t *panels4) {

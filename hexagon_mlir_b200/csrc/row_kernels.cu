@@ -434,12 +434,13 @@ reduce_rows_push_kernel(const ReducePushParams p) {
 __global__ void __launch_bounds__(256)
 allreduce_multimem_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ mc_out, int64_t nvec) {
   constexpr int UNR = 4;
-  for (int64_t base = ((int64_t)blockIdx.x * 256) * UNR + threadIdx.x; base < nvec;
-       base += (int64_t)gridDim.x * 256 * UNR) {
+  const int64_t nthr = blockDim.x;
+  for (int64_t base = ((int64_t)blockIdx.x * nthr) * UNR + threadIdx.x; base < nvec;
+       base += (int64_t)gridDim.x * nthr * UNR) {
     uint32_t v[UNR][4];
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      const int64_t i = base + (int64_t)u * 256;
+      const int64_t i = base + (int64_t)u * nthr;
       if (i < nvec)
         asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
                      : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3])
@@ -448,7 +449,7 @@ allreduce_multimem_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ m
     }
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      const int64_t i = base + (int64_t)u * 256;
+      const int64_t i = base + (int64_t)u * nthr;
       if (i < nvec)
         asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_out + i), "r"(v[u][0]),
                      "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3])
@@ -458,15 +459,24 @@ allreduce_multimem_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ m
 }
 
 // The same all-reduce with the two rendezvous of the ranks inside the launch (no barrier kernels
-// around it).  `flags` are 16 words at the same offset of every rank's copy: [r] = the launch
-// number at which rank r's partial was complete, [8 + r] = the launch number whose sums rank r has
-// written everywhere.  Each is stored through the multicast address (one store reaches every
-// copy) and polled in the local copy.  `state` is local: [0] launches finished, [1] CTAs finished.
+// around it).  Every rank's copy of the buffer holds 16 flag words: [r] = the launch number at
+// which rank r's partial was complete, [8 + r] = the launch number whose sums rank r has written
+// everywhere.  A rank stores its flag into every peer's copy with plain release stores over NVLink
+// (one thread per peer; a store through the multicast address costs a trip through the switch
+// and back and measured three times the latency) and polls its own copy.  `state` is local:
+// [0] launches finished, [1] CTAs finished.
 //  entry: CTA 0 stores "arrived", every CTA waits until all ranks have arrived;
 //  body:  this rank's slice, as above;
 //  exit:  the last CTA to finish stores "written" and waits for every rank's "written", so the
 //         launch ends only when this rank's copy holds every slice and nobody still reads it.
 // Every wait is bounded; one that runs out records {site 48, late rank} and the launch returns.
+struct PeerFlags {
+  uint32_t *f[kMaxPushRanks];  // the flag words of every rank's copy, as this rank addresses them
+};
+__device__ __forceinline__ void flag_store_all(const PeerFlags &pf, int world, int slot, uint32_t v) {
+  const int r = threadIdx.x;
+  if (r < world) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf.f[r] + slot), "r"(v) : "memory");
+}
 __device__ __forceinline__ bool flags_reached(const uint32_t *flags, int world, uint32_t epoch, int *status, int site) {
   const int r = threadIdx.x;
   bool ok = true;
@@ -490,29 +500,23 @@ __device__ __forceinline__ bool flags_reached(const uint32_t *flags, int world, 
 
 __global__ void __launch_bounds__(256)
 allreduce_multimem_sync_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ mc_out, int64_t nvec,
-                               uint32_t *mc_flags, const uint32_t *local_flags, int world, int rank, uint32_t *state,
-                               int *status) {
-  __shared__ uint32_t s_epoch;
-  if (threadIdx.x == 0) {
-    const uint32_t e = *(volatile uint32_t *)state + 1;
-    s_epoch = e;
-    // the partial, written by the launch before this one, is complete: one CTA says so (the grid
-    // is at most two CTAs per SM, resident at once even beside a GEMM, so CTA 0 runs while the others wait)
-    if (blockIdx.x == 0)
-      asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(mc_flags + rank), "r"(e) : "memory");
-  }
-  __syncthreads();
-  const uint32_t epoch = s_epoch;
+                               const PeerFlags pf, int world, int rank, uint32_t *state, int *status) {
+  const uint32_t *local_flags = pf.f[rank];
+  const uint32_t epoch = *(volatile uint32_t *)state + 1;
+  // the partial, written by the launch before this one, is complete: one CTA says so (CTA 0 is
+  // among the first dispatched; CTAs that start later find the flags set)
+  if (blockIdx.x == 0) flag_store_all(pf, world, rank, epoch);
   if (threadIdx.x < 32) flags_reached(local_flags, world, epoch, status, 48);
   __syncthreads();
 
   constexpr int UNR = 4;
-  for (int64_t base = ((int64_t)blockIdx.x * 256) * UNR + threadIdx.x; base < nvec;
-       base += (int64_t)gridDim.x * 256 * UNR) {
+  const int64_t nthr = blockDim.x;
+  for (int64_t base = ((int64_t)blockIdx.x * nthr) * UNR + threadIdx.x; base < nvec;
+       base += (int64_t)gridDim.x * nthr * UNR) {
     uint32_t v[UNR][4];
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      const int64_t i = base + (int64_t)u * 256;
+      const int64_t i = base + (int64_t)u * nthr;
       if (i < nvec)
         asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
                      : "=r"(v[u][0]), "=r"(v[u][1]), "=r"(v[u][2]), "=r"(v[u][3])
@@ -521,7 +525,7 @@ allreduce_multimem_sync_kernel(const uint4 *__restrict__ mc_in, uint4 *__restric
     }
 #pragma unroll
     for (int u = 0; u < UNR; ++u) {
-      const int64_t i = base + (int64_t)u * 256;
+      const int64_t i = base + (int64_t)u * nthr;
       if (i < nvec)
         asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc_out + i), "r"(v[u][0]),
                      "r"(v[u][1]), "r"(v[u][2]), "r"(v[u][3])
@@ -537,11 +541,11 @@ allreduce_multimem_sync_kernel(const uint4 *__restrict__ mc_in, uint4 *__restric
     if (s_last) {
       __threadfence_system();
       state[1] = 0;
-      asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(mc_flags + 8 + rank), "r"(epoch) : "memory");
     }
   }
   __syncthreads();
   if (s_last) {
+    flag_store_all(pf, world, 8 + rank, epoch);  // release stores: after every CTA's sums (fence + counter above)
     if (threadIdx.x < 32) flags_reached(local_flags + 8, world, epoch, status, 48);
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -656,18 +660,32 @@ int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offs
                      "allreduce_multimem: multicast addresses 16-byte aligned, offset and count multiples of 8 elements");
   if (count == 0) return 0;
   const int64_t nvec = count >> 3;
-  int64_t blocks = (nvec + 256 * 4 - 1) / (256 * 4);
-  const int64_t cap = (int64_t)ctx().sm_count * 4;
+  // one CTA of 128 threads per SM: the exchange is bound by the links, a few tens of KB in flight
+  // per SM saturate them, and wider or deeper grids measured slower (two ranks, 16.8 MB: 43.7 us
+  // against 52.5 with four CTAs of 256 threads per SM)
+  const int threads = 128;
+  int64_t blocks = (nvec + threads * 4 - 1) / (threads * 4);
+  const int64_t cap = (int64_t)ctx().sm_count;
   if (blocks > cap) blocks = cap;
-  allreduce_multimem_kernel<<<(unsigned)blocks, 256, 0, ctx().stream>>>(
+  allreduce_multimem_kernel<<<(unsigned)blocks, threads, 0, ctx().stream>>>(
       reinterpret_cast<const uint4 *>((const __half *)mc_in + elem_offset),
       reinterpret_cast<uint4 *>((__half *)mc_out + elem_offset), nvec);
   return check_launch("allreduce_multimem");
 }
 
-int launch_allreduce_multimem_sync(void *mc_buf, void *local_buf, int64_t elem_offset, int64_t count,
+int launch_allreduce_multimem_sync(void *mc_buf, void *const *peer_bufs, int64_t elem_offset, int64_t count,
                                    int64_t flags_elem_offset, int rank, int world, void *state, cudaStream_t stream) {
   B200_TRY(ensure_ready());
+  if (!peer_bufs || world < 2 || world > kMaxPushRanks || rank < 0 || rank >= world)
+    return set_error(B200MLIR_ERR_BAD_ARG, "allreduce_multimem_sync: the buffer's address on every rank, 2 <= world <= %d",
+                     kMaxPushRanks);
+  void *local_buf = peer_bufs[rank];
+  PeerFlags pf;
+  for (int r = 0; r < kMaxPushRanks; ++r) {
+    if (r < world && (!peer_bufs[r] || !aligned16(peer_bufs[r])))
+      return set_error(B200MLIR_ERR_BAD_ARG, "allreduce_multimem_sync: buffer address of rank %d missing or unaligned", r);
+    pf.f[r] = r < world ? reinterpret_cast<uint32_t *>((__half *)peer_bufs[r] + flags_elem_offset) : nullptr;
+  }
   if (!mc_buf || !local_buf || !state || elem_offset < 0 || count < 0 || elem_offset % 8 || count % 8 ||
       flags_elem_offset < 0 || flags_elem_offset % 8 || !aligned16(mc_buf) || !aligned16(local_buf) || world < 2 ||
       world > kMaxPushRanks || rank < 0 || rank >= world)
@@ -675,16 +693,17 @@ int launch_allreduce_multimem_sync(void *mc_buf, void *local_buf, int64_t elem_o
                      "allreduce_multimem_sync: 16-byte aligned multicast and local addresses of one buffer, offsets and "
                      "count multiples of 8 elements, 2 <= world <= %d, a device state of two words", kMaxPushRanks);
   const int64_t nvec = count >> 3;
-  int64_t blocks = (nvec + 256 * 4 - 1) / (256 * 4);
-  const int64_t cap = (int64_t)ctx().sm_count * 2;
+  // one CTA of 128 threads per SM: two ranks, 16.8 MB, measured 63 us against 65-76 for wider or
+  // deeper grids (the exchange is bound by the links, and every extra CTA adds a system-scope
+  // fence and a flag round to the end of the launch); it also leaves the SMs to a GEMM beside it
+  const int threads = 128;
+  int64_t blocks = (nvec + threads * 4 - 1) / (threads * 4);
+  const int64_t cap = (int64_t)ctx().sm_count;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
-  allreduce_multimem_sync_kernel<<<(unsigned)blocks, 256, 0, stream ? stream : ctx().stream>>>(
+  allreduce_multimem_sync_kernel<<<(unsigned)blocks, threads, 0, stream ? stream : ctx().stream>>>(
       reinterpret_cast<const uint4 *>((const __half *)mc_buf + elem_offset),
-      reinterpret_cast<uint4 *>((__half *)mc_buf + elem_offset), nvec,
-      reinterpret_cast<uint32_t *>((__half *)mc_buf + flags_elem_offset),
-      reinterpret_cast<const uint32_t *>((const __half *)local_buf + flags_elem_offset), world, rank, (uint32_t *)state,
-      ctx().d_status);
+      reinterpret_cast<uint4 *>((__half *)mc_buf + elem_offset), nvec, pf, world, rank, (uint32_t *)state, ctx().d_status);
   return check_launch("allreduce_multimem_sync");
 }
 

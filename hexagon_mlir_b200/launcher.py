@@ -238,12 +238,18 @@ def matmul_f32out(a, b, c32, res32=None):
 mlp_block_tp = Kernel(
     "mlp_block_tp_float16", (2, 1, 2, 2, 2, 2),
     scalars=lambda args, opts: [ctypes.c_float(float(opts.get("eps", 1e-6))), int(opts.get("chunks", 1))])
+def _ptr_array(addresses):
+    """A C array of device addresses (void *const *) from a sequence of ints."""
+    return (ctypes.c_void_p * len(addresses))(*[int(a) for a in addresses])
+
+
 mlp_block_tp_multicast = Kernel(
     "mlp_block_tp_multicast_float16", (2, 1, 2, 2, 2, 2),
-    scalars=lambda args, opts: [ctypes.c_void_p(int(opts["mc_buf"])), ctypes.c_int64(int(opts["flags_elem_offset"])),
+    scalars=lambda args, opts: [ctypes.c_void_p(int(opts["mc_buf"])), _ptr_array(opts["peer_bufs"]),
+                                ctypes.c_int64(int(opts["flags_elem_offset"])),
                                 ctypes.c_void_p(int(opts["state"].data_ptr())), int(opts["rank"]), int(opts["world"]),
                                 ctypes.c_float(float(opts.get("eps", 1e-6))), int(opts.get("chunks", 1))])
-_ACCEPTED |= {"chunks", "mc_buf", "flags_elem_offset", "state", "rank", "world"}
+_ACCEPTED |= {"chunks", "mc_buf", "peer_bufs", "flags_elem_offset", "state", "rank", "world"}
 
 
 def tp_unique_id() -> bytes:
@@ -293,12 +299,13 @@ def tp_allreduce_multimem(mc_in: int, mc_out: int, elem_offset: int, count: int,
         check()
 
 
-def tp_allreduce_multimem_sync(mc_buf: int, local, elem_offset: int, count: int, flags_elem_offset: int, rank: int,
+def tp_allreduce_multimem_sync(mc_buf: int, peer_bufs, elem_offset: int, count: int, flags_elem_offset: int, rank: int,
                                world: int, state) -> None:
-    """The same with both rendezvous of the ranks inside the launch: `local` is this rank's tensor
-    over the symmetric buffer (data and 16 flag words), `state` two int32 words on the device."""
-    _sync_stream([local])
-    if lib().b200mlir_tp_allreduce_multimem_sync_float16(int(mc_buf), int(local.data_ptr()), int(elem_offset), int(count),
+    """The same with both rendezvous of the ranks inside the launch: `peer_bufs` are the addresses
+    of every rank's copy of the symmetric buffer (data and 16 flag words), `state` two int32 words
+    on the device."""
+    _sync_stream([state])
+    if lib().b200mlir_tp_allreduce_multimem_sync_float16(int(mc_buf), _ptr_array(peer_bufs), int(elem_offset), int(count),
                                                          int(flags_elem_offset), int(rank), int(world),
                                                          int(state.data_ptr())) != 0:
         check()

@@ -252,7 +252,11 @@ class MulticastTensorParallelMLP:
         n = self.tokens * self.width
         self._buf = symm.empty((n + 64,), dtype=torch.float16, device=wd.device)  # the output, then 16 flag words
         self._h = symm.rendezvous(self._buf, group)
+        off = int(getattr(self._h, "offset", 0) or 0)          # of this tensor inside the rendezvoused allocation
         self._mc = int(getattr(self._h, "multicast_ptr", 0) or 0)
+        if self._mc:
+            self._mc += off
+        self._peers = [int(p) + off for p in self._h.buffer_ptrs]   # every rank's copy, as this process maps it
         self.out = self._buf[:n].view(self.tokens, self.width)
         self._buf[n:].zero_()
         self._state = torch.zeros(2, dtype=torch.int32, device=wd.device)
@@ -270,7 +274,7 @@ class MulticastTensorParallelMLP:
             raise RuntimeError("no multicast mapping on this machine")
         if self.chunks > 1:
             _l.mlp_block_tp_multicast[(1,)](x, self.gain, self.wg, self.wu, self.wd, self.out, mc_buf=self._mc,
-                                            flags_elem_offset=self.tokens * self.width, state=self._state,
+                                            peer_bufs=self._peers, flags_elem_offset=self.tokens * self.width, state=self._state,
                                             rank=self.rank, world=self.world, eps=self.eps, chunks=self.chunks)
             return self.out
         _l.set_option("mlpResidualMod", self.world)   # the ranks take turns, by 256-row block, in adding x
@@ -281,7 +285,7 @@ class MulticastTensorParallelMLP:
             _l.set_option("mlpResidualMod", 1)
         n = self.rows * self.width
         if self.rendezvous == "kernel":
-            _l.tp_allreduce_multimem_sync(self._mc, self._buf, self.rank * n, n, self.tokens * self.width, self.rank,
+            _l.tp_allreduce_multimem_sync(self._mc, self._peers, self.rank * n, n, self.tokens * self.width, self.rank,
                                           self.world, self._state)
             return self.out
         self._h.barrier(channel=0, timeout_ms=self.timeout_ms)   # every rank's partial is written

@@ -253,7 +253,7 @@ B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank
 /* The same block with the sum over ranks done by this library's own kernel through the NVSwitch's
  * multicast addresses and overlapped with the math, one fused call: `out` is this rank's dense
  * [T, D] view at the START of a symmetric fp16 buffer, `mc_buf` that buffer's multicast address,
- * `flags_elem_offset` (>= T*D) the element at which the buffer holds 16 zero-initialised flag
+ * `peer_bufs[r]` the address of rank r's copy (peer_bufs[rank] == out's data), `flags_elem_offset` (>= T*D) the element at which the buffer holds 16 zero-initialised flag
  * words, `state` two zero-initialised 32-bit words of this rank's device memory (both as for
  * b200mlir_tp_allreduce_multimem_sync_float16).  The down projection is cut into `chunks` token
  * chunks (whole 256-row tiles whose rows divide over the ranks, else one chunk); a chunk's
@@ -263,8 +263,9 @@ B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank
 B200_API void mlp_block_tp_multicast_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank_gain, B200MemRef1D *gain,
                                              int64_t rank_wg, B200MemRef2D *wg, int64_t rank_wu, B200MemRef2D *wu,
                                              int64_t rank_wd, B200MemRef2D *wd, int64_t rank_o, B200MemRef2D *out,
-                                             void *mc_buf, int64_t flags_elem_offset, void *state, int rank,
-                                             int world, float eps, int chunks, B200_GRID_ARGS);
+                                             void *mc_buf, void *const *peer_bufs, int64_t flags_elem_offset,
+                                             void *state, int rank, int world, float eps, int chunks,
+                                             B200_GRID_ARGS);
 
 /* This rank's share of an all-reduce through NVSwitch multicast (NVLS): `mc_in` / `mc_out` are
  * MULTICAST addresses of fp16 buffers that every rank of the group holds (the symmetric-memory
@@ -276,17 +277,19 @@ B200_API void mlp_block_tp_multicast_float16(int64_t rank_x, B200MemRef2D *x, in
  * in elements, multiples of 8.  No reference counterpart (single device). */
 B200_API int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_out, int64_t elem_offset,
                                                     int64_t count);
-/* The same, in place, with both rendezvous inside the launch: `mc_buf` and `local_buf` are the
- * multicast and this rank's own address of ONE symmetric fp16 buffer that also holds 16 flag
- * words (64 bytes, zero before the first call) at element `flags_elem_offset`; `state` is two
- * zero-initialised 32-bit words of this rank's device memory that the calls keep between them.
- * Every rank of the group issues the call once per all-reduce, in the same order, after the
- * producer of its copy on the same stream.  The launch waits (each wait bounded to about a second,
- * then device status B200MLIR_ERR_DEVICE_WAIT site 48 with the late rank) until every rank's copy
- * is complete, sums this rank's slice, and ends only when every rank's sums are in this rank's
- * copy and no rank still reads it.  The flag epoch lives on the device, so the call can be
- * replayed from a captured graph.  No reference counterpart (single device). */
-B200_API int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *local_buf, int64_t elem_offset,
+/* The same, in place, with both rendezvous inside the launch: `mc_buf` is the multicast address
+ * of ONE symmetric fp16 buffer and `peer_bufs[r]` the address of rank r's copy as this process
+ * maps it (peer_bufs[rank] is this rank's own); the buffer also holds 16 flag words (64 bytes, zero
+ * before the first call) at element `flags_elem_offset`; `state` is two zero-initialised 32-bit
+ * words of this rank's device memory that the calls keep between them.  Every rank of the group
+ * issues the call once per all-reduce, in the same order, after the producer of its copy on the
+ * same stream.  The launch tells every peer (a release store into its flag words over NVLink) that
+ * this rank's copy is complete, waits (each wait bounded to about a second, then device status
+ * B200MLIR_ERR_DEVICE_WAIT site 48 with the late rank) until every rank's is, sums this rank's
+ * slice, and ends only when every rank's sums are in this rank's copy and no rank still reads
+ * it.  The flag epoch lives on the device, so the call can be replayed from a captured graph.
+ * No reference counterpart (single device). */
+B200_API int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *const *peer_bufs, int64_t elem_offset,
                                                          int64_t count, int64_t flags_elem_offset, int rank,
                                                          int world, void *state);
 

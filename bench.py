@@ -319,7 +319,17 @@ def extras_single_gpu(torch, hm, peaks, only=None):
             hm.softmax_kernel[(1,)](X[i], Y[i])
         ms = graph_timed(torch, sm, reps=10, inner=sets * 2)
         gbs = 2 * 4096 * 1024 * 2 / (ms * 1e-3) / 1e9
-        out["softmax_f16_4096x1024"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+        # yardstick: a plain device copy of the same buffers, timed the same way (launch and first-byte
+        # latency weigh on a 16 MiB launch whatever it computes; the HBM peak is a large copy's)
+        state["i"] = 0
+
+        def cp():
+            i = state["i"] % sets
+            state["i"] += 1
+            Y[i].copy_(X[i])
+        cms = graph_timed(torch, cp, reps=10, inner=sets * 2)
+        out["softmax_f16_4096x1024"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                        "same_size_copy_us": cms * 1e3, "frac_of_same_size_copy": cms / ms}
         del X, Y
         # the same kernel where the launch and the first-byte latency no longer dominate: 8x the rows
         X = [(torch.randn((32768, 1024), generator=g, device=dev) * 3).half() for _ in range(3)]
@@ -348,7 +358,15 @@ def extras_single_gpu(torch, hm, peaks, only=None):
             hm.rms_norm_fwd_kernel[(1,)](xs[i], ys[i], w, EPSILON=1e-6)
         ms = graph_timed(torch, rn, reps=10, inner=16)
         gbs = (2 * 2048 * 4096 * 2 + 4096 * 2) / (ms * 1e-3) / 1e9
-        out["rmsnorm_f16_2048x4096"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]}
+        state["i"] = 0
+
+        def rcp():
+            i = state["i"] % 8
+            state["i"] += 1
+            ys[i].copy_(xs[i])
+        cms = graph_timed(torch, rcp, reps=10, inner=16)
+        out["rmsnorm_f16_2048x4096"] = {"us": ms * 1e3, "gbs": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                        "same_size_copy_us": cms * 1e3, "frac_of_same_size_copy": cms / ms}
         del xs, ys
     if want("swiglu"):
         nel = 2048 * 11008

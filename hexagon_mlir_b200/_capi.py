@@ -104,7 +104,7 @@ _SIGNATURES = {
                                               c_int, ctypes.c_float, c_int] + _GRID),
     "b200mlir_tp_allreduce_multimem_float16": (c_int, [c_void_p, c_void_p, c_i64, c_i64]),
     "b200mlir_tp_allreduce_multimem_sync_float16": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_i64, c_i64, c_i64,
-                                                            c_int, c_int, c_void_p]),
+                                                            c_int, c_int, c_void_p, c_int]),
     "b200mlir_mlp_phase_times": (c_int, [ctypes.POINTER(ctypes.c_double), c_int]),
     "b200mlir_tp_reduce_rows_float16": (c_int, [c_void_p, c_void_p, c_i64, ctypes.POINTER(c_void_p), c_int, c_int,
                                                 c_i64, c_i64]),

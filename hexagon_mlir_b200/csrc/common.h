@@ -169,7 +169,8 @@ int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offs
 // the same with both rendezvous of the ranks inside the launch (flag words in the buffer itself)
 int launch_allreduce_multimem_sync(void *mc_buf, void *const *peer_bufs, int64_t elem_offset, int64_t count,
                                    int64_t flags_elem_offset, int rank, int world, void *state,
-                                   cudaStream_t stream = nullptr);  // null: the calling thread's stream
+                                   cudaStream_t stream = nullptr,  // null: the calling thread's stream
+                                   int exit_rendezvous = 1);       // 0: the caller puts a barrier after the launch
 
 // layout.cu
 int launch_transpose_i8(const int8_t *src, int8_t *dst, int64_t rows, int64_t cols, int64_t ld_src, int64_t ld_dst);

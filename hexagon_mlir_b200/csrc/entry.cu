@@ -1018,9 +1018,11 @@ int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_out, int6
 }
 
 int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *const *peer_bufs, int64_t elem_offset, int64_t count,
-                                                int64_t flags_elem_offset, int rank, int world, void *state) {
+                                                int64_t flags_elem_offset, int rank, int world, void *state,
+                                                int exit_rendezvous) {
   clear_error();
-  return launch_allreduce_multimem_sync(mc_buf, peer_bufs, elem_offset, count, flags_elem_offset, rank, world, state);
+  return launch_allreduce_multimem_sync(mc_buf, peer_bufs, elem_offset, count, flags_elem_offset, rank, world, state,
+                                        nullptr, exit_rendezvous ? 1 : 0);
 }
 
 int b200mlir_host_gemm_plan(int64_t m, int64_t n, int64_t k, int64_t *panels4) {

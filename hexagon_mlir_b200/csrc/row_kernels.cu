@@ -500,7 +500,8 @@ __device__ __forceinline__ bool flags_reached(const uint32_t *flags, int world, 
 
 __global__ void __launch_bounds__(256)
 allreduce_multimem_sync_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ mc_out, int64_t nvec,
-                               const PeerFlags pf, int world, int rank, uint32_t *state, int *status) {
+                               const PeerFlags pf, int world, int rank, uint32_t *state, int *status,
+                               int exit_rendezvous) {
   const uint32_t *local_flags = pf.f[rank];
   const uint32_t epoch = *(volatile uint32_t *)state + 1;
   // the partial, written by the launch before this one, is complete: one CTA says so (CTA 0 is
@@ -536,17 +537,22 @@ allreduce_multimem_sync_kernel(const uint4 *__restrict__ mc_in, uint4 *__restric
   __syncthreads();
   __shared__ int s_last;
   if (threadIdx.x == 0) {
-    __threadfence_system();  // this CTA's sums are on their way to every copy before it counts as finished
+    // this CTA's sums are on their way to every copy before it counts as finished (with the exit
+    // rendezvous left to the caller's barrier, the end of the launch does that)
+    if (exit_rendezvous) __threadfence_system();
+    else __threadfence();
     s_last = atomicAdd(&state[1], 1u) == gridDim.x - 1;
     if (s_last) {
-      __threadfence_system();
+      if (exit_rendezvous) __threadfence_system();
       state[1] = 0;
     }
   }
   __syncthreads();
   if (s_last) {
-    flag_store_all(pf, world, 8 + rank, epoch);  // release stores: after every CTA's sums (fence + counter above)
-    if (threadIdx.x < 32) flags_reached(local_flags + 8, world, epoch, status, 48);
+    if (exit_rendezvous) {
+      flag_store_all(pf, world, 8 + rank, epoch);  // release stores: after every CTA's sums (fence + counter above)
+      if (threadIdx.x < 32) flags_reached(local_flags + 8, world, epoch, status, 48);
+    }
     __syncthreads();
     if (threadIdx.x == 0) {
       state[0] = epoch;
@@ -674,7 +680,8 @@ int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offs
 }
 
 int launch_allreduce_multimem_sync(void *mc_buf, void *const *peer_bufs, int64_t elem_offset, int64_t count,
-                                   int64_t flags_elem_offset, int rank, int world, void *state, cudaStream_t stream) {
+                                   int64_t flags_elem_offset, int rank, int world, void *state, cudaStream_t stream,
+                                   int exit_rendezvous) {
   B200_TRY(ensure_ready());
   if (!peer_bufs || world < 2 || world > kMaxPushRanks || rank < 0 || rank >= world)
     return set_error(B200MLIR_ERR_BAD_ARG, "allreduce_multimem_sync: the buffer's address on every rank, 2 <= world <= %d",
@@ -703,7 +710,8 @@ int launch_allreduce_multimem_sync(void *mc_buf, void *const *peer_bufs, int64_t
   if (blocks < 1) blocks = 1;
   allreduce_multimem_sync_kernel<<<(unsigned)blocks, threads, 0, stream ? stream : ctx().stream>>>(
       reinterpret_cast<const uint4 *>((const __half *)mc_buf + elem_offset),
-      reinterpret_cast<uint4 *>((__half *)mc_buf + elem_offset), nvec, pf, world, rank, (uint32_t *)state, ctx().d_status);
+      reinterpret_cast<uint4 *>((__half *)mc_buf + elem_offset), nvec, pf, world, rank, (uint32_t *)state, ctx().d_status,
+      exit_rendezvous);
   return check_launch("allreduce_multimem_sync");
 }
 

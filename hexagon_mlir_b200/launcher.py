@@ -300,14 +300,14 @@ def tp_allreduce_multimem(mc_in: int, mc_out: int, elem_offset: int, count: int,
 
 
 def tp_allreduce_multimem_sync(mc_buf: int, peer_bufs, elem_offset: int, count: int, flags_elem_offset: int, rank: int,
-                               world: int, state) -> None:
+                               world: int, state, exit_rendezvous: bool = True) -> None:
     """The same with both rendezvous of the ranks inside the launch: `peer_bufs` are the addresses
     of every rank's copy of the symmetric buffer (data and 16 flag words), `state` two int32 words
     on the device."""
     _sync_stream([state])
     if lib().b200mlir_tp_allreduce_multimem_sync_float16(int(mc_buf), _ptr_array(peer_bufs), int(elem_offset), int(count),
                                                          int(flags_elem_offset), int(rank), int(world),
-                                                         int(state.data_ptr())) != 0:
+                                                         int(state.data_ptr()), 1 if exit_rendezvous else 0) != 0:
         check()
 
 

@@ -224,7 +224,8 @@ class MulticastTensorParallelMLP:
 
     rendezvous="kernel" (default): both barriers are inside the all-reduce launch (flag words in
     the symmetric buffer, stored through the multicast address, polled locally, every wait
-    bounded); "barriers": the symmetric-memory handle's barrier kernels around the launch.
+    bounded); "barriers": the symmetric-memory handle's barrier kernels around the launch; "entry":
+    the wait for the other ranks' partials inside the launch, a barrier kernel after it.
 
     chunks > 1 (rendezvous="kernel" only): the whole block is ONE call into the library
     (`mlp_block_tp_multicast_float16`); the down projection is cut into token chunks and each
@@ -243,8 +244,8 @@ class MulticastTensorParallelMLP:
             raise ValueError("tokens must be divisible by the world size")
         self.rows = self.tokens // self.world
         self.timeout_ms = int(timeout_ms)
-        if rendezvous not in ("kernel", "barriers"):
-            raise ValueError("rendezvous is 'kernel' or 'barriers'")
+        if rendezvous not in ("kernel", "barriers", "entry"):
+            raise ValueError("rendezvous is 'kernel', 'entry' or 'barriers'")
         self.rendezvous = rendezvous
         self.chunks = int(chunks)
         if self.chunks > 1 and rendezvous != "kernel":
@@ -287,6 +288,11 @@ class MulticastTensorParallelMLP:
         if self.rendezvous == "kernel":
             _l.tp_allreduce_multimem_sync(self._mc, self._peers, self.rank * n, n, self.tokens * self.width, self.rank,
                                           self.world, self._state)
+            return self.out
+        if self.rendezvous == "entry":   # the wait for the partials inside the launch, a barrier kernel after it
+            _l.tp_allreduce_multimem_sync(self._mc, self._peers, self.rank * n, n, self.tokens * self.width, self.rank,
+                                          self.world, self._state, exit_rendezvous=False)
+            self._h.barrier(channel=1, timeout_ms=self.timeout_ms)
             return self.out
         self._h.barrier(channel=0, timeout_ms=self.timeout_ms)   # every rank's partial is written
         _l.tp_allreduce_multimem(self._mc, self._mc, self.rank * n, n, like=self.out)

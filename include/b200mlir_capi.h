@@ -287,11 +287,13 @@ B200_API int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_
  * this rank's copy is complete, waits (each wait bounded to about a second, then device status
  * B200MLIR_ERR_DEVICE_WAIT site 48 with the late rank) until every rank's is, sums this rank's
  * slice, and ends only when every rank's sums are in this rank's copy and no rank still reads
- * it.  The flag epoch lives on the device, so the call can be replayed from a captured graph.
- * No reference counterpart (single device). */
+ * it.  With `exit_rendezvous` = 0 the launch ends after this rank's sums are issued and the
+ * caller puts a barrier of its own after it (the rendezvous at the end costs a system-scope fence
+ * per CTA; a barrier kernel in a graph measured cheaper).  The flag epoch lives on the device, so
+ * the call can be replayed from a captured graph.  No reference counterpart (single device). */
 B200_API int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *const *peer_bufs, int64_t elem_offset,
                                                          int64_t count, int64_t flags_elem_offset, int rank,
-                                                         int world, void *state);
+                                                         int world, void *state, int exit_rendezvous);
 
 /* Phase times of the most recent MLP block issued by the calling thread while option
  * "mlpPhaseTiming" was non-zero: microseconds of RMSNorm, gate/up GEMM (SwiGLU read-out), down

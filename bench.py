@@ -169,7 +169,8 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    a, b, rows, threads = cpu_gemm_sample(target_s=max(2.0, 40.0 / max(1, args.steps + args.warmup)))
+    a, b, rows, threads = cpu_gemm_sample(target_s=max(min(2.0, args.reference_seconds),
+                                                       args.reference_seconds / max(1, args.steps + args.warmup)))
     for _ in range(args.warmup):
         cpu_time_once(a, b, threads)
     times = [cpu_time_once(a, b, threads)[0] for _ in range(args.steps)]
@@ -908,6 +909,8 @@ def main():
     ap.add_argument("--case", default="", help="run one case of `extra` only (profiling captures): gemm_f16_1024, "
                                                "gemm_f16_4096, gemm_f16_8192, kloop, gemm_i8, softmax, rmsnorm, swiglu, w8a16, attention_f16_4x16x4096x64, ...")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--reference-seconds", type=float, default=40.0,
+                    help="--impl reference: CPU seconds to spend over all passes (the slab of A is sized to it)")
     ap.add_argument("--stage-limit", type=float, default=420.0,
                     help="seconds the stages after the device-timed loop may take together before the line is "
                          "written without the unfinished ones")

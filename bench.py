@@ -565,6 +565,7 @@ def mlp_extra(torch, hm, dist, rank, world):
         # with barrier kernels around the launch, and with both rendezvous inside the launch
         for key, rdv, ch, what in (
                 ("multicast_all_reduce_ms", "barriers", 1, "barrier kernels around it"),
+                ("multicast_own_barriers_ms", "own_barriers", 1, "the whole block one C++ call, the library's barrier launches around its all-reduce"),
                 ("multicast_in_kernel_rendezvous_ms", "kernel", 1, "both rendezvous inside the launch"),
                 ("multicast_entry_rendezvous_ms", "entry", 1, "the wait for the partials inside the launch, a barrier kernel after it"),
                 ("multicast_two_chunks_overlapped_ms", "kernel", 2,

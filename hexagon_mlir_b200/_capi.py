@@ -103,6 +103,7 @@ _SIGNATURES = {
                                               c_i64, _M2, c_void_p, ctypes.POINTER(c_void_p), c_i64, c_void_p, c_int,
                                               c_int, ctypes.c_float, c_int] + _GRID),
     "b200mlir_tp_allreduce_multimem_float16": (c_int, [c_void_p, c_void_p, c_i64, c_i64]),
+    "b200mlir_tp_barrier": (c_int, [ctypes.POINTER(c_void_p), c_i64, c_int, c_int, c_int, c_void_p]),
     "b200mlir_tp_allreduce_multimem_sync_float16": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_i64, c_i64, c_i64,
                                                             c_int, c_int, c_void_p, c_int]),
     "b200mlir_mlp_phase_times": (c_int, [ctypes.POINTER(ctypes.c_double), c_int]),

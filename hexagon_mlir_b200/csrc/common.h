@@ -166,6 +166,8 @@ int launch_reduce_rows_push(const __half *recv, const __half *residual, int64_t 
 
 // sum over the ranks' copies of elements [offset, offset + count) of a multicast-mapped fp16 buffer, written back to every copy
 int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offset, int64_t count);
+// a barrier of the ranks as its own one-warp launch (flag words in the symmetric buffer, two slots)
+int launch_rank_barrier(void *const *peer_bufs, int64_t flags_elem_offset, int slot, int rank, int world, void *state);
 // the same with both rendezvous of the ranks inside the launch (flag words in the buffer itself)
 int launch_allreduce_multimem_sync(void *mc_buf, void *const *peer_bufs, int64_t elem_offset, int64_t count,
                                    int64_t flags_elem_offset, int rank, int world, void *state,

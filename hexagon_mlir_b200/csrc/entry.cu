@@ -916,7 +916,8 @@ void mlp_block_tp_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D 
 // down projection is cut into `chunks` token chunks; as soon as a chunk's GEMM has been issued its
 // all-reduce is launched on a second stream, where it runs beside the next chunk's GEMM: the
 // kernel uses no shared memory and few registers, so its CTAs fit on the SMs the persistent GEMM
-// occupies.  Both rendezvous of the ranks are inside that launch (bounded waits).
+// occupies.  Both rendezvous of the ranks are inside that launch (bounded waits).  With one chunk
+// the rendezvous are the library's one-warp barrier launches around the plain all-reduce.
 void mlp_block_tp_multicast_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B200MemRef1D *gain, int64_t rwg,
                                     B200MemRef2D *wg, int64_t rwu, B200MemRef2D *wu, int64_t rwd, B200MemRef2D *wd,
                                     int64_t ro, B200MemRef2D *out, void *mc_buf, void *const *peer_bufs,
@@ -956,7 +957,11 @@ void mlp_block_tp_multicast_float16(int64_t rx, B200MemRef2D *x, int64_t rg, B20
     const int64_t mine = rows / world;  // this rank sums rows [r0 + rank * mine, + mine) of the chunk
     const int64_t off = (r0 + (int64_t)rank * mine) * D, cnt = mine * D;
     if (chunks == 1) {
-      int rc = launch_allreduce_multimem_sync(mc_buf, peer_bufs, off, cnt, flags_elem_offset, rank, world, state, s);
+      // one chunk: the library's barrier launches around the plain all-reduce (measured faster than
+      // both rendezvous inside the launch: a system-scope fence per CTA costs more than a launch)
+      int rc = launch_rank_barrier(peer_bufs, flags_elem_offset, 0, rank, world, state);
+      if (rc == 0) rc = launch_allreduce_multimem(mc_buf, mc_buf, off, cnt);
+      if (rc == 0) rc = launch_rank_barrier(peer_bufs, flags_elem_offset, 1, rank, world, state);
       t_phases.mark(4);
       return rc;
     }
@@ -1023,6 +1028,11 @@ int b200mlir_tp_allreduce_multimem_sync_float16(void *mc_buf, void *const *peer_
   clear_error();
   return launch_allreduce_multimem_sync(mc_buf, peer_bufs, elem_offset, count, flags_elem_offset, rank, world, state,
                                         nullptr, exit_rendezvous ? 1 : 0);
+}
+
+int b200mlir_tp_barrier(void *const *peer_bufs, int64_t flags_elem_offset, int slot, int rank, int world, void *state) {
+  clear_error();
+  return launch_rank_barrier(peer_bufs, flags_elem_offset, slot, rank, world, state);
 }
 
 int b200mlir_host_gemm_plan(int64_t m, int64_t n, int64_t k, int64_t *panels4) {

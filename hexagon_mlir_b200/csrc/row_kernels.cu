@@ -498,6 +498,37 @@ __device__ __forceinline__ bool flags_reached(const uint32_t *flags, int world, 
   return ok;
 }
 
+// A barrier of the ranks as a launch of its own: one warp; thread r tells rank r (a release store of
+// this barrier's launch number into the flag word [slot * 8 + rank] of rank r's copy, over NVLink)
+// and waits, bounded, for rank r's word in the local copy.  `state[2 + slot]` keeps the launch
+// number on the device (graph replay).  Two slots, so that the barrier before and the one after an
+// all-reduce never share a word.  A wait that runs out records {site 49, late rank}.
+__global__ void __launch_bounds__(32)
+rank_barrier_kernel(const PeerFlags pf, int world, int rank, int slot, uint32_t *state, int *status) {
+  const uint32_t epoch = *(volatile uint32_t *)(state + 2 + slot) + 1;
+  __syncwarp();
+  const int r = threadIdx.x;
+  if (r < world) {
+    // what this rank wrote before the barrier was written by launches that have completed: the flag
+    // needs no fence of its own in front of it
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(pf.f[r] + slot * 8 + rank), "r"(epoch) : "memory");
+    const uint32_t *mine = pf.f[rank] + slot * 8 + r;
+    const long long t0 = clock64();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if (*(volatile int *)status != 0 || clock64() - t0 > 2000000000LL) {
+        if (atomicCAS(status, 0, 49) == 0) status[1] = r;
+        break;
+      }
+    }
+    __threadfence_system();  // what the other ranks wrote before their flags is visible to the launches that follow
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) state[2 + slot] = epoch;
+}
+
 __global__ void __launch_bounds__(256)
 allreduce_multimem_sync_kernel(const uint4 *__restrict__ mc_in, uint4 *__restrict__ mc_out, int64_t nvec,
                                const PeerFlags pf, int world, int rank, uint32_t *state, int *status,
@@ -677,6 +708,21 @@ int launch_allreduce_multimem(const void *mc_in, void *mc_out, int64_t elem_offs
       reinterpret_cast<const uint4 *>((const __half *)mc_in + elem_offset),
       reinterpret_cast<uint4 *>((__half *)mc_out + elem_offset), nvec);
   return check_launch("allreduce_multimem");
+}
+
+int launch_rank_barrier(void *const *peer_bufs, int64_t flags_elem_offset, int slot, int rank, int world, void *state) {
+  B200_TRY(ensure_ready());
+  if (!peer_bufs || !state || world < 2 || world > kMaxPushRanks || rank < 0 || rank >= world || slot < 0 || slot > 1 ||
+      flags_elem_offset < 0 || flags_elem_offset % 8)
+    return set_error(B200MLIR_ERR_BAD_ARG, "tp_barrier: the buffer's address on every rank, slot 0 or 1, 2 <= world <= %d, "
+                     "a device state of four words", kMaxPushRanks);
+  PeerFlags pf;
+  for (int r = 0; r < kMaxPushRanks; ++r) {
+    if (r < world && !peer_bufs[r]) return set_error(B200MLIR_ERR_BAD_ARG, "tp_barrier: buffer address of rank %d missing", r);
+    pf.f[r] = r < world ? reinterpret_cast<uint32_t *>((__half *)peer_bufs[r] + flags_elem_offset) : nullptr;
+  }
+  rank_barrier_kernel<<<1, 32, 0, ctx().stream>>>(pf, world, rank, slot, (uint32_t *)state, ctx().d_status);
+  return check_launch("tp_barrier");
 }
 
 int launch_allreduce_multimem_sync(void *mc_buf, void *const *peer_bufs, int64_t elem_offset, int64_t count,

@@ -299,6 +299,14 @@ def tp_allreduce_multimem(mc_in: int, mc_out: int, elem_offset: int, count: int,
         check()
 
 
+def tp_barrier(peer_bufs, flags_elem_offset: int, slot: int, rank: int, world: int, state) -> None:
+    """A barrier of the ranks as a one-warp launch (flag words in the symmetric buffer; see the header)."""
+    _sync_stream([state])
+    if lib().b200mlir_tp_barrier(_ptr_array(peer_bufs), int(flags_elem_offset), int(slot), int(rank), int(world),
+                                 int(state.data_ptr())) != 0:
+        check()
+
+
 def tp_allreduce_multimem_sync(mc_buf: int, peer_bufs, elem_offset: int, count: int, flags_elem_offset: int, rank: int,
                                world: int, state, exit_rendezvous: bool = True) -> None:
     """The same with both rendezvous of the ranks inside the launch: `peer_bufs` are the addresses

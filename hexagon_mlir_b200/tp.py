@@ -225,7 +225,9 @@ class MulticastTensorParallelMLP:
     rendezvous="kernel" (default): both barriers are inside the all-reduce launch (flag words in
     the symmetric buffer, stored through the multicast address, polled locally, every wait
     bounded); "barriers": the symmetric-memory handle's barrier kernels around the launch; "entry":
-    the wait for the other ranks' partials inside the launch, a barrier kernel after it.
+    the wait for the other ranks' partials inside the launch, a barrier kernel after it;
+    "own_barriers": the whole block as ONE call into the library (`mlp_block_tp_multicast_float16`),
+    which puts its own one-warp barrier launches (`b200mlir_tp_barrier`) around the all-reduce.
 
     chunks > 1 (rendezvous="kernel" only): the whole block is ONE call into the library
     (`mlp_block_tp_multicast_float16`); the down projection is cut into token chunks and each
@@ -244,8 +246,8 @@ class MulticastTensorParallelMLP:
             raise ValueError("tokens must be divisible by the world size")
         self.rows = self.tokens // self.world
         self.timeout_ms = int(timeout_ms)
-        if rendezvous not in ("kernel", "barriers", "entry"):
-            raise ValueError("rendezvous is 'kernel', 'entry' or 'barriers'")
+        if rendezvous not in ("kernel", "barriers", "entry", "own_barriers"):
+            raise ValueError("rendezvous is 'kernel', 'entry', 'barriers' or 'own_barriers'")
         self.rendezvous = rendezvous
         self.chunks = int(chunks)
         if self.chunks > 1 and rendezvous != "kernel":
@@ -260,7 +262,7 @@ class MulticastTensorParallelMLP:
         self._peers = [int(p) + off for p in self._h.buffer_ptrs]   # every rank's copy, as this process maps it
         self.out = self._buf[:n].view(self.tokens, self.width)
         self._buf[n:].zero_()
-        self._state = torch.zeros(2, dtype=torch.int32, device=wd.device)
+        self._state = torch.zeros(4, dtype=torch.int32, device=wd.device)
         torch.cuda.synchronize(wd.device)
         self._h.barrier(channel=0, timeout_ms=self.timeout_ms)  # every rank's flags read zero before the first launch
         torch.cuda.synchronize(wd.device)
@@ -273,7 +275,7 @@ class MulticastTensorParallelMLP:
         """Returns the block output (a buffer this object owns; valid until the next call)."""
         if not self._mc:
             raise RuntimeError("no multicast mapping on this machine")
-        if self.chunks > 1:
+        if self.chunks > 1 or self.rendezvous == "own_barriers":   # ONE call into the library
             _l.mlp_block_tp_multicast[(1,)](x, self.gain, self.wg, self.wu, self.wd, self.out, mc_buf=self._mc,
                                             peer_bufs=self._peers, flags_elem_offset=self.tokens * self.width, state=self._state,
                                             rank=self.rank, world=self.world, eps=self.eps, chunks=self.chunks)

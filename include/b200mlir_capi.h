@@ -254,8 +254,9 @@ B200_API void mlp_block_tp_float16(int64_t rank_x, B200MemRef2D *x, int64_t rank
  * multicast addresses and overlapped with the math, one fused call: `out` is this rank's dense
  * [T, D] view at the START of a symmetric fp16 buffer, `mc_buf` that buffer's multicast address,
  * `peer_bufs[r]` the address of rank r's copy (peer_bufs[rank] == out's data), `flags_elem_offset` (>= T*D) the element at which the buffer holds 16 zero-initialised flag
- * words, `state` two zero-initialised 32-bit words of this rank's device memory (both as for
- * b200mlir_tp_allreduce_multimem_sync_float16).  The down projection is cut into `chunks` token
+ * words, `state` FOUR zero-initialised 32-bit words of this rank's device memory (as for
+ * b200mlir_tp_allreduce_multimem_sync_float16 and b200mlir_tp_barrier).  With one chunk the block
+ * ends with b200mlir_tp_barrier, the plain multicast all-reduce and a second barrier.  The down projection is cut into `chunks` token
  * chunks (whole 256-row tiles whose rows divide over the ranks, else one chunk); a chunk's
  * all-reduce is launched on a second stream as soon as its GEMM has been issued and runs beside
  * the next chunk's GEMM on the same SMs.  Tokens divisible by the world size.  A collective call:
@@ -277,6 +278,17 @@ B200_API void mlp_block_tp_multicast_float16(int64_t rank_x, B200MemRef2D *x, in
  * in elements, multiples of 8.  No reference counterpart (single device). */
 B200_API int b200mlir_tp_allreduce_multimem_float16(const void *mc_in, void *mc_out, int64_t elem_offset,
                                                     int64_t count);
+/* A barrier of the ranks as a one-warp launch on the calling thread's stream: rank r's flag word
+ * [slot * 8 + rank] in every peer's copy of a symmetric buffer (16 flag words at element
+ * `flags_elem_offset`, zero before the first call; `peer_bufs[r]` = rank r's copy as this process
+ * maps it) is set with a release store over NVLink, the local words are polled (bounded: device
+ * status site 49 with the late rank).  `slot` is 0 or 1 (the barrier before and the one after an
+ * all-reduce use different words); `state` is FOUR zero-initialised 32-bit words of this rank's
+ * device memory shared with b200mlir_tp_allreduce_multimem_sync_float16 (words 2 and 3 are the
+ * barriers' launch numbers), so the call can be replayed from a captured graph.  Every rank issues
+ * the same sequence of barriers.  No reference counterpart (single device). */
+B200_API int b200mlir_tp_barrier(void *const *peer_bufs, int64_t flags_elem_offset, int slot, int rank, int world,
+                                 void *state);
 /* The same, in place, with both rendezvous inside the launch: `mc_buf` is the multicast address
  * of ONE symmetric fp16 buffer and `peer_bufs[r]` the address of rank r's copy as this process
  * maps it (peer_bufs[rank] is this rank's own); the buffer also holds 16 flag words (64 bytes, zero

@@ -65,7 +65,7 @@ def _worker(rank, world, port, q):
     mc_out = None
     # barrier kernels around the launch / both rendezvous inside it / the fused call with two token
     # chunks, each chunk's all-reduce beside the next chunk's GEMM
-    for rdv, ch in (("barriers", 1), ("kernel", 1), ("entry", 1), ("kernel", 2)):
+    for rdv, ch in (("barriers", 1), ("own_barriers", 1), ("kernel", 1), ("entry", 1), ("kernel", 2)):
         mc = tp.MulticastTensorParallelMLP(T(gain), tp.shard_columns(T(wg), rank, world), tp.shard_columns(T(wu), rank, world),
                                            tp.shard_rows(T(wd), rank, world), tokens=x.shape[0], eps=1e-6,
                                            group=dist.group.WORLD, timeout_ms=20000, rendezvous=rdv, chunks=ch)
